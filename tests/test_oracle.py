@@ -1,0 +1,199 @@
+"""The CPU oracle against the reference's golden vectors and (where built) the reference itself."""
+import numpy as np
+import pytest
+
+from helpers import compare_case_inputs, mixed_case_inputs, rel_l2
+from oracle import MlpShape
+
+
+def test_mix64_known_answers(oracle):
+    # SplitMix64 finaliser: native/src/random_walk_cpu.cpp:7-12
+    def mix(x):
+        m = 2**64 - 1
+        x = (x + 0x9E3779B97F4A7C15) & m
+        x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & m
+        x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & m
+        return x ^ (x >> 31)
+    for x in (0, 1, 1234, 2**63, 2**64 - 1, 0x100000001B3):
+        assert oracle.mix64(x) == mix(x)
+
+
+def test_walks_match_golden(oracle, golden):
+    w = golden.walks
+    moves, target = w["moves"], w["target"]
+    m2, t2 = oracle.cyclic_puzzle(72, 18)
+    assert np.array_equal(moves, m2) and np.array_equal(target, t2)
+    for idx, (seed, epoch, step, rank, kmin, kmax, n) in enumerate(w["cases"]):
+        st, states, labels, meta = oracle.random_walks(moves, target, seed=int(seed), epoch=int(epoch), step=int(step),
+                                                       rank=int(rank), k_min=int(kmin), k_max=int(kmax), samples=int(n))
+        assert st == 0
+        assert np.array_equal(states, w[f"states_{idx}"])
+        assert np.array_equal(labels, w[f"labels_{idx}"])
+        assert np.array_equal(meta["depth"], w[f"depth_{idx}"])
+        assert np.array_equal(meta["last_move"], w[f"last_move_{idx}"])
+        assert np.array_equal(meta["rng_counter"], w[f"rng_{idx}"])
+
+
+def test_walk_known_answers_from_reference_cpu_generator(oracle):
+    # (depth, last_move, rng_counter, v[0]) produced by the reference's GenerateRandomWalksCpu
+    kats = {
+        (0, 0): [(14, 0, 6900420249570471822, 59), (4, 0, 12471801683350609746, 20),
+                 (14, 3, 17413974358338838791, 32), (7, 16, 2555033919457901260, 69)],
+        (1, 0): [(10, 16, 9791726640709000624, 17), (18, 10, 9252228466933077447, 64),
+                 (25, 3, 1436227961509692489, 18), (3, 15, 1811655705602829704, 35)],
+        (0, 1): [(16, 8, 14035942854177696080, 67), (7, 5, 2368657771244461589, 59),
+                 (15, 10, 2934877263533333506, 16), (26, 15, 988611748774771281, 23)],
+        (1, 1): [(17, 16, 4504469246695374766, 27), (19, 9, 1997979116450941161, 42),
+                 (9, 6, 6457830207986809914, 2), (22, 10, 15402372295923721072, 24)],
+    }
+    moves, target = oracle.cyclic_puzzle(72, 18)
+    for (step, rank), rows in kats.items():
+        st, states, labels, meta = oracle.random_walks(moves, target, seed=1234, epoch=0, step=step, rank=rank,
+                                                       k_min=1, k_max=29, samples=4)
+        assert st == 0
+        for i, (d, lm, rng, v0) in enumerate(rows):
+            assert (int(meta["depth"][i]), int(meta["last_move"][i]), int(meta["rng_counter"][i]), int(states[i, 0])) == (d, lm, rng, v0)
+
+
+def test_walk_properties_and_errors(oracle):
+    # native/tests/test_random_walk_cpu.cpp
+    moves, target = oracle.cyclic_puzzle(72, 18)
+    kw = dict(seed=1234, epoch=5, step=7, k_min=1, k_max=9, samples=64)
+    st, s2, l2, m2 = oracle.random_walks(moves, target, rank=2, **kw)
+    st, s3, l3, m3 = oracle.random_walks(moves, target, rank=3, **kw)
+    assert st == 0
+    assert ((m2["depth"] >= 1) & (m2["depth"] <= 9)).all()
+    assert np.array_equal(l2, m2["depth"].astype(np.float32))
+    assert (m2["last_move"] < 18).all() and (s2[:, 72:] == 0).all()
+    assert not np.array_equal(m2["rng_counter"], m3["rng_counter"])
+    assert (s2[:, :72] != target[:72]).any()
+    st, *_ = oracle.random_walks(moves, target, seed=1, epoch=0, step=0, rank=0, k_min=9, k_max=1, samples=4)
+    assert st == 1
+    st, *_ = oracle.random_walks(moves, target, seed=1, epoch=0, step=0, rank=0, k_min=0, k_max=1, samples=4)
+    assert st == 1
+
+
+def test_mlp_known_answer(oracle, golden):
+    g = golden.mlp
+    shape = MlpShape(*[int(x) for x in g["kat_shape"]])
+    i = np.arange(shape.param_count, dtype=np.int64)
+    weights = ((i % 11 - 5) * 0.01).astype(np.float32)
+    states = np.zeros((2, 80), np.uint8)
+    for s in range(2):
+        for k in range(4):
+            states[s, k] = (k + s) % 8
+    labels = np.array([[1.0], [3.0]], np.float32)
+    st, out = oracle.forward(shape, weights, states)
+    assert st == 0 and np.array_equal(out, g["kat_outputs"])
+    st, loss, grad = oracle.loss_grad(shape, weights, states, labels)
+    assert st == 0 and np.float32(loss) == g["kat_loss"] and np.array_equal(grad, g["kat_grad"])
+    # the survey's printed KAT
+    assert abs(out[0, 0] + 0.0405305214) < 1e-9 and abs(loss - 5.16307878) < 1e-6
+    assert abs(grad[7] - 0.00150364335) < 1e-10 and abs(grad[-1] + 4.08083534) < 1e-6
+
+
+def test_mlp_matches_golden_bit_exact(oracle, golden):
+    g = golden.mlp
+    for idx, row in enumerate(g["cmp_cases"]):
+        shape = MlpShape(*[int(x) for x in row[:6]])
+        w, s, l = compare_case_inputs(shape, int(row[6]))
+        st, loss, grad = oracle.loss_grad(shape, w, s, l)
+        assert st == 0
+        assert np.float32(loss) == g[f"cmp_loss_{idx}"]
+        assert np.array_equal(grad, g[f"cmp_grad_{idx}"])
+        st, out = oracle.forward(shape, w, s)
+        assert np.array_equal(out, g[f"cmp_out_{idx}"])
+
+
+def test_mlp_finite_difference(oracle):
+    # native/tests/test_mlp_cpu_ref.cpp:37-51
+    shape = MlpShape(4, 8, 5, 3, 1, 1)
+    i = np.arange(shape.param_count, dtype=np.int64)
+    w = ((i % 11 - 5) * 0.01).astype(np.float32)
+    states = np.zeros((2, 80), np.uint8)
+    for s in range(2):
+        for k in range(4):
+            states[s, k] = (k + s) % 8
+    labels = np.array([[1.0], [3.0]], np.float32)
+    _, _, grad = oracle.loss_grad(shape, w, states, labels)
+    for idx in (0, 7, 31, shape.param_count - 2):
+        wp, wm = w.copy(), w.copy()
+        wp[idx] += 1e-3
+        wm[idx] -= 1e-3
+        lp = oracle.loss_grad(shape, wp, states, labels)[1]
+        lm = oracle.loss_grad(shape, wm, states, labels)[1]
+        assert abs((lp - lm) / 2e-3 - grad[idx]) <= 5e-3
+
+
+def test_mixed_with_rounding_off_equals_fp32_path(oracle):
+    # With both fp16 switches off the layer-major restatement must agree with the sample-major
+    # fp32 reference up to summation order.
+    for dims, n in (((4, 8, 5, 3, 1, 1), 8), ((4, 8, 5, 3, 1, 3), 8), ((6, 8, 9, 7, 2, 11), 10)):
+        shape = MlpShape(*dims)
+        w, s, l = compare_case_inputs(shape, n)
+        _, loss_a, grad_a = oracle.loss_grad(shape, w, s, l)
+        st, loss_b, grad_b = oracle.loss_grad_mixed(shape, w, s, l, half_linear=False, half_input_grad=False)
+        assert st == 0
+        assert abs(loss_a - loss_b) <= 1e-5 + 1e-5 * abs(loss_a)
+        assert np.allclose(grad_a, grad_b, atol=2e-5, rtol=2e-5)
+
+
+def test_mixed_inside_reference_envelope(oracle):
+    # native/tests/cuda/test_cuda_mlp_backward_mixed_precision_error.cu:26-29,150-166,196-204
+    for dims, n in (((8, 8, 16, 16, 2, 1), 32), ((8, 8, 16, 16, 2, 3), 32), ((8, 8, 16, 16, 2, 17), 32), ((5, 8, 8, 8, 1, 128), 16)):
+        shape = MlpShape(*dims)
+        w, s, l = mixed_case_inputs(shape, n)
+        _, loss_ref, grad_ref = oracle.loss_grad(shape, w, s, l)
+        st, loss_mx, grad_mx = oracle.loss_grad_mixed(shape, w, s, l)
+        assert st == 0
+        assert abs(loss_ref - loss_mx) <= 2e-3 + 2e-2 * max(abs(loss_ref), abs(loss_mx))
+        assert rel_l2(grad_mx, grad_ref) <= 8e-2
+        assert np.abs(grad_mx - grad_ref).max() <= 2e-2
+
+
+def test_adamw_matches_golden(oracle, golden):
+    a = golden.adamw
+    w = a["w0"].copy()
+    m = np.zeros_like(w)
+    v = np.zeros_like(w)
+    for step in (1, 2, 3):
+        mirror = np.zeros(w.size, np.uint16)
+        assert oracle.adamw(w, a[f"g_{step}"], m, v, step=step, lr=1e-3, wd=0.01 if step == 3 else 0.0, half_mirror=mirror) == 0
+        assert np.array_equal(w, a[f"w_{step}"]) and np.array_equal(m, a[f"m_{step}"]) and np.array_equal(v, a[f"v_{step}"])
+        assert np.array_equal(mirror.view(np.float16), w.astype(np.float16))
+    assert oracle.adamw(w, a["g_1"], m, v, step=0, lr=1e-3) == 1
+    assert oracle.adamw(w, a["g_1"], m, v, step=1, lr=0.0) == 1
+
+
+def test_half_conversions(oracle):
+    rng = np.random.default_rng(3)
+    x = np.concatenate([rng.standard_normal(4000).astype(np.float32) * s for s in (1e-8, 1e-6, 1e-4, 1e-2, 1.0, 1e3, 7e4)])
+    x = np.concatenate([x, np.array([0.0, -0.0, 65504.0, 65519.9, 65520.0, 2.0**-24, 2.0**-25, 1.5 * 2.0**-25, np.inf, -np.inf], np.float32)])
+    got = oracle.float_to_half(x)
+    with np.errstate(over="ignore"):
+        want = x.astype(np.float16).view(np.uint16)
+    assert np.array_equal(got, want)
+    back = np.array([oracle.lib.orc_half_to_float(int(h)) for h in got[:2000]], np.float32)
+    assert np.array_equal(back, got[:2000].view(np.float16).astype(np.float32))
+    # the artefact converter rounds half up: differs from RN-even only on exact ties
+    exp = oracle.export_fp16(x[:8000])
+    rn = got[:8000]
+    assert (np.abs(exp.astype(np.int32) - rn.astype(np.int32)) <= 1).mean() > 0.99
+
+
+@pytest.mark.skipif("not __import__('os').path.exists(__import__('os').path.join(__import__('os').path.dirname(__import__('os').path.dirname(__import__('os').path.abspath(__file__))), 'oracle', '_ref', 'libmgt_ref.so'))")
+def test_oracle_equals_reference_library(oracle, reference):
+    moves, target = oracle.cyclic_puzzle(72, 18)
+    for seed, step, rank, kmin, kmax in ((99, 3, 5, 1, 29), (2**63 + 5, 1000, 0, 3, 17)):
+        a = oracle.random_walks(moves, target, seed=seed, epoch=2, step=step, rank=rank, k_min=kmin, k_max=kmax, samples=500)
+        b = reference.random_walks(moves, target, seed=seed, epoch=2, step=step, rank=rank, k_min=kmin, k_max=kmax, samples=500)
+        assert a[0] == b[0] == 0
+        for x, y in zip(a[1:], b[1:]):
+            assert np.array_equal(x, y)
+    rng = np.random.default_rng(11)
+    shape = MlpShape(72, 72, 48, 24, 3, 1)
+    w = (rng.standard_normal(shape.param_count) * 0.05).astype(np.float32)
+    _, states, labels, _ = oracle.random_walks(moves, target, seed=5, epoch=0, step=0, rank=0, k_min=1, k_max=29, samples=12)
+    la = oracle.loss_grad(shape, w, states, labels.reshape(-1, 1))
+    lb = reference.loss_grad(shape, w, states, labels.reshape(-1, 1))
+    assert la[0] == lb[0] == 0 and la[1] == lb[1] and np.array_equal(la[2], lb[2])
