@@ -1,0 +1,184 @@
+/*
+ * mgt_b200 - C ABI of the B200-native (sm_100a) training-step library.
+ *
+ * Drop-in boundary for the per-step data-parallel training hot path of MultiGPUTrainMLP:
+ * the functions below take the place of the reference's in-process launch API
+ * (namespace mgt_cuda, native/cuda/mgt_cuda/ *.cuh). Conventions kept from the reference:
+ *   - every function returns an int32 status with the reference's numeric values
+ *     (native/include/mgt/status.hpp:5-13); nothing throws;
+ *   - launches are asynchronous on the caller's stream (a cudaStream_t passed as void*);
+ *   - all device buffers are owned by the caller; the library allocates nothing per step.
+ * Differences: cuBLAS/cuBLASLt handles are replaced by one opaque engine handle, and the
+ * workspace is much smaller than the reference's (query it, do not assume).
+ *
+ * Plain pointers and sizes only: no C++ or torch types cross this boundary.
+ */
+#ifndef MGT_B200_H_
+#define MGT_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+/* native/include/mgt/status.hpp:5-13; values above 6 are additions of this library. */
+typedef int32_t mgt_status_t;
+enum {
+    MGT_OK = 0,
+    MGT_INVALID_CONFIG = 1,
+    MGT_INVALID_PUZZLE = 2,
+    MGT_CAPACITY_EXCEEDED = 3,
+    MGT_CUDA_FAILURE = 4,
+    MGT_NCCL_FAILURE = 5,
+    MGT_IO_FAILURE = 6,
+    MGT_DEVICE_TIMEOUT = 7 /* a bounded device-side wait ran out; the context stays usable */
+};
+
+/* Compile-time limits of the reference (native/include/mgt/config.hpp:8-11,32-35). */
+#define MGT_STATE_LEN 72
+#define MGT_STATE_STORAGE_LEN 80
+#define MGT_STATE_VALUE_PAD 72
+#define MGT_MOVE_COUNT 18
+/* native/cuda/mlp_forward.cu:7-9 */
+#define MGT_MAX_HD1 4096
+#define MGT_MAX_HD2 512
+#define MGT_MAX_RESIDUAL_BLOCKS 32
+
+/* 80-byte state record, 16-byte walk record: native/include/mgt/static_contracts.hpp:11-19. */
+typedef struct { uint8_t v[MGT_STATE_STORAGE_LEN]; } mgt_train_state_t;
+typedef struct { uint32_t depth; uint32_t last_move; uint64_t rng_counter; } mgt_walk_meta_t;
+
+/* ---- on-GPU random-walk generator ------------------------------------------------------
+ * Replaces mgt_cuda::RandomWalkKernelConfig / ValidateRandomWalkKernelConfig /
+ * LaunchRandomWalkKernel (native/cuda/mgt_cuda/random_walk_kernel.cuh:10-29,
+ * native/cuda/random_walk_kernel.cu:66-99). Bit-exact with the reference for the same
+ * (seed, epoch, step, rank, sample). */
+typedef struct {
+    uint32_t sample_count;
+    uint32_t k_min;
+    uint32_t k_max;
+    uint32_t move_count;
+    uint32_t state_len;
+    uint32_t state_storage_len;
+} mgt_random_walk_config_t;
+
+mgt_status_t mgt_validate_random_walk_config(const mgt_random_walk_config_t* config);
+mgt_status_t mgt_launch_random_walk(const mgt_random_walk_config_t* config, uint64_t base_seed, uint64_t epoch,
+                                    uint64_t step, uint32_t global_rank, const mgt_train_state_t* device_moves,
+                                    const mgt_train_state_t* device_target, mgt_train_state_t* device_states,
+                                    float* device_labels, mgt_walk_meta_t* device_meta, void* stream);
+
+/* Replaces ExpandScalarLabelsKernel (native/tools/mgt_native_train_smoke.cu:74-80). */
+mgt_status_t mgt_launch_expand_scalar_labels(const float* device_scalar_labels, uint32_t samples, uint32_t output_dim,
+                                             float* device_labels, void* stream);
+
+/* ---- model shape -------------------------------------------------------------------------
+ * Replaces mgt_cuda::CudaMlpShape / ValidateCudaMlpShape (native/cuda/mgt_cuda/mlp_forward.cuh:9-18,
+ * native/cuda/mlp_forward.cu:89-97). Flat parameter layout: native/cuda/mlp_backward.cu:25-36. */
+typedef struct {
+    uint32_t state_len;
+    uint32_t state_value_pad;
+    uint32_t hd1;
+    uint32_t hd2;
+    uint32_t residual_blocks;
+    uint32_t output_dim;
+} mgt_mlp_shape_t;
+
+mgt_status_t mgt_validate_mlp_shape(const mgt_mlp_shape_t* shape);
+uint64_t mgt_mlp_param_count(const mgt_mlp_shape_t* shape);
+
+/* ---- engine handle -----------------------------------------------------------------------
+ * Takes the place of the cublasHandle_t / cublasLtHandle_t pair of the reference signatures
+ * (native/cuda/mgt_cuda/mlp_backward.cuh:224-287): it caches TMA descriptors and owns a
+ * 4-byte device status word. Create once per device, before the step loop. */
+typedef struct mgt_engine mgt_engine_t;
+mgt_status_t mgt_engine_create(int32_t device_id, mgt_engine_t** out_engine);
+mgt_status_t mgt_engine_destroy(mgt_engine_t* engine);
+/* Synchronises `stream`, then reads and clears the device status word: MGT_OK, or
+ * MGT_DEVICE_TIMEOUT if a kernel gave up on a bounded wait since the last call. */
+mgt_status_t mgt_engine_check(mgt_engine_t* engine, void* stream, int32_t* out_device_code);
+
+/* ---- loss + gradient (forward, MSE loss, backward) -----------------------------------------
+ * Replaces MlpLossGradWorkspaceFloats (native/cuda/mgt_cuda/mlp_backward.cuh:27-43) and the
+ * LaunchMlpLossGrad...ExternalHalf family (mlp_backward.cuh:224-314,
+ * native/cuda/mlp_backward.cu:1228-1510). */
+typedef struct {
+    float input_forward_ms;
+    float hidden_forward_ms;
+    float residual_forward_ms;
+    float output_ms;
+    float residual_backward_ms;
+    float hidden_backward_ms;
+    float input_grad_ms;
+} mgt_backward_profile_t; /* mlp_backward.cuh:11-19 */
+
+/* mlp_backward.cuh:21-25. Called synchronously on the launching thread, 2*residual_blocks+3 times
+ * per launch, in the reference's order: output, (fc2, fc1) of each block from last to first,
+ * hidden, embedding+input bias. */
+typedef mgt_status_t (*mgt_gradient_ready_fn)(void* user, uint32_t ready_id, uint64_t param_offset,
+                                              uint64_t param_count, void* producer_stream);
+
+/* Number of floats of caller-owned scratch the launch needs (0 = invalid arguments). */
+uint64_t mgt_mlp_loss_grad_workspace_floats(const mgt_mlp_shape_t* shape, uint32_t sample_count,
+                                            uint32_t input_grad_partial_chunks, int32_t use_half_input_grad,
+                                            int32_t use_half_linear);
+
+/* device_weights_half may be NULL (the fp16 mirror is then rebuilt from device_weights each call).
+ * input_grad_partial_chunks / positions_per_block / position_tile select among the reference's
+ * input-gradient back-ends; they are validated like the reference does and otherwise ignored:
+ * this library has one back-end (one-hot operand synthesised in shared memory for tcgen05). */
+mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* engine, const mgt_mlp_shape_t* shape, const float* device_weights,
+                                      const uint16_t* device_weights_half, const mgt_train_state_t* device_states,
+                                      const float* device_labels, uint32_t sample_count, float* device_loss,
+                                      float* device_grad, float* workspace, uint64_t workspace_floats,
+                                      uint32_t input_grad_partial_chunks, uint32_t input_grad_positions_per_block,
+                                      int32_t use_half_input_grad, int32_t use_half_linear,
+                                      mgt_backward_profile_t* profile, mgt_gradient_ready_fn gradient_ready,
+                                      void* gradient_ready_user, void* stream, uint32_t input_grad_position_tile);
+
+/* ---- AdamW ---------------------------------------------------------------------------------
+ * Replaces AdamWKernelConfig / ValidateAdamWKernelConfig / LaunchAdamWKernel /
+ * LaunchAdamWKernelWithHalfMirror (native/cuda/mgt_cuda/adamw.cuh:10-34, native/cuda/adamw.cu:8-88). */
+typedef struct {
+    uint64_t param_count;
+    uint64_t step;
+    float learning_rate;
+    float beta1;
+    float beta2;
+    float eps;
+    float weight_decay;
+} mgt_adamw_config_t;
+
+mgt_status_t mgt_validate_adamw_config(const mgt_adamw_config_t* config);
+mgt_status_t mgt_launch_adamw(const mgt_adamw_config_t* config, float* device_weights, const float* device_grad,
+                              float* device_m, float* device_v, void* stream);
+mgt_status_t mgt_launch_adamw_with_half_mirror(const mgt_adamw_config_t* config, float* device_weights,
+                                               uint16_t* device_weights_half, const float* device_grad,
+                                               float* device_m, float* device_v, void* stream);
+/* Replaces FloatToHalfMirrorKernel (native/tools/mgt_native_train_smoke.cu:68-72). */
+mgt_status_t mgt_launch_float_to_half(const float* device_values, uint64_t count, uint16_t* device_half, void* stream);
+
+/* ---- diagnostics ---------------------------------------------------------------------------
+ * One plain GEMM through the tcgen05 kernel, used by the parity tests to pin each operand form.
+ * D[M x N] fp32 = A * B with fp16 operands; a_mn_major: A stored [K][M] (else [M][K]);
+ * b_mn_major: B stored [K][N] (else [N][K]); lda/ldb are row pitches in elements.
+ * No counterpart in the reference. */
+mgt_status_t mgt_debug_gemm(mgt_engine_t* engine, const uint16_t* a, uint32_t lda, int32_t a_mn_major,
+                            const uint16_t* b, uint32_t ldb, int32_t b_mn_major, float* d, uint32_t m, uint32_t n,
+                            uint32_t k, uint32_t splits, float* partial_scratch, void* stream);
+
+const char* mgt_status_name(mgt_status_t status);
+const char* mgt_version(void);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* MGT_B200_H_ */

@@ -1,0 +1,203 @@
+"""Host-side mirror of the reference's launch API (namespace mgt_cuda) over the C ABI.
+
+Names follow the reference: RandomWalkKernelConfig / LaunchRandomWalkKernel
+(native/cuda/mgt_cuda/random_walk_kernel.cuh), CudaMlpShape / MlpLossGradWorkspaceFloats /
+LaunchMlpLossGrad... (native/cuda/mgt_cuda/mlp_backward.cuh), AdamWKernelConfig /
+LaunchAdamWKernel[WithHalfMirror] (native/cuda/mgt_cuda/adamw.cuh). Functions return the
+reference's status codes as ints; device buffers are torch CUDA tensors owned by the caller.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+from . import _lib
+
+STATUS = {0: "ok", 1: "invalid_config", 2: "invalid_puzzle", 3: "capacity_exceeded", 4: "cuda_failure",
+          5: "nccl_failure", 6: "io_failure", 7: "device_timeout"}
+
+
+class MgtError(RuntimeError):
+    def __init__(self, status: int, what: str):
+        super().__init__(f"{what}: status {status} ({STATUS.get(status, 'unknown')})")
+        self.status = status
+
+
+def status_name(status: int) -> str:
+    return _lib.load().mgt_status_name(status).decode()
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if hasattr(t, "data_ptr"):
+        return C.c_void_p(t.data_ptr())
+    return C.c_void_p(int(t))
+
+
+def _stream(stream):
+    if stream is None:
+        import torch
+        stream = torch.cuda.current_stream()
+    return C.c_void_p(stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream))
+
+
+class _WalkCfg(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("sample_count", "k_min", "k_max", "move_count", "state_len", "state_storage_len")]
+
+
+class _Shape(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("state_len", "state_value_pad", "hd1", "hd2", "residual_blocks", "output_dim")]
+
+
+class _Adam(C.Structure):
+    _fields_ = [("param_count", C.c_uint64), ("step", C.c_uint64), ("learning_rate", C.c_float), ("beta1", C.c_float),
+                ("beta2", C.c_float), ("eps", C.c_float), ("weight_decay", C.c_float)]
+
+
+class BackwardProfile(C.Structure):
+    """mgt_cuda::MlpBackwardProfile (native/cuda/mgt_cuda/mlp_backward.cuh:11-19)."""
+    _fields_ = [(n, C.c_float) for n in ("input_forward_ms", "hidden_forward_ms", "residual_forward_ms", "output_ms",
+                                         "residual_backward_ms", "hidden_backward_ms", "input_grad_ms")]
+
+
+@dataclass
+class RandomWalkKernelConfig:
+    sample_count: int = 0
+    k_min: int = 0
+    k_max: int = 0
+    move_count: int = 18
+    state_len: int = 72
+    state_storage_len: int = 80
+
+    def c(self):
+        return _WalkCfg(self.sample_count, self.k_min, self.k_max, self.move_count, self.state_len, self.state_storage_len)
+
+
+@dataclass
+class CudaMlpShape:
+    state_len: int
+    state_value_pad: int
+    hd1: int
+    hd2: int
+    residual_blocks: int
+    output_dim: int = 1
+
+    def c(self):
+        return _Shape(self.state_len, self.state_value_pad, self.hd1, self.hd2, self.residual_blocks, self.output_dim)
+
+    @property
+    def param_count(self) -> int:
+        shape = self.c()
+        return int(_lib.load().mgt_mlp_param_count(C.byref(shape)))
+
+
+@dataclass
+class AdamWKernelConfig:
+    param_count: int
+    step: int
+    learning_rate: float
+    beta1: float = 0.9
+    beta2: float = 0.999
+    eps: float = 1e-8
+    weight_decay: float = 0.0
+
+    def c(self):
+        return _Adam(self.param_count, self.step, self.learning_rate, self.beta1, self.beta2, self.eps, self.weight_decay)
+
+
+def validate_random_walk_kernel_config(config: RandomWalkKernelConfig) -> int:
+    cfg = config.c()
+    return int(_lib.load().mgt_validate_random_walk_config(C.byref(cfg)))
+
+
+def launch_random_walk_kernel(config, base_seed, epoch, step, global_rank, device_moves, device_target, device_states,
+                              device_labels, device_meta, stream=None) -> int:
+    cfg = config.c()
+    return int(_lib.load().mgt_launch_random_walk(C.byref(cfg), base_seed & (2**64 - 1), epoch, step, global_rank,
+                                                  _ptr(device_moves), _ptr(device_target), _ptr(device_states),
+                                                  _ptr(device_labels), _ptr(device_meta), _stream(stream)))
+
+
+def validate_cuda_mlp_shape(shape: CudaMlpShape) -> int:
+    s = shape.c()
+    return int(_lib.load().mgt_validate_mlp_shape(C.byref(s)))
+
+
+def mlp_loss_grad_workspace_floats(shape, sample_count, input_grad_partial_chunks=1, use_half_input_grad=True,
+                                   use_half_linear=True) -> int:
+    s = shape.c()
+    return int(_lib.load().mgt_mlp_loss_grad_workspace_floats(C.byref(s), sample_count, input_grad_partial_chunks,
+                                                              int(use_half_input_grad), int(use_half_linear)))
+
+
+GRADIENT_READY_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint64, C.c_void_p)
+
+
+class Engine:
+    """Owner of the opaque engine handle (stands where the reference passes cuBLAS handles)."""
+
+    def __init__(self, device_id: int = 0):
+        self._lib = _lib.load()
+        handle = C.c_void_p()
+        st = self._lib.mgt_engine_create(device_id, C.byref(handle))
+        if st != 0:
+            raise MgtError(st, "mgt_engine_create")
+        self.handle = handle
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self._lib.mgt_engine_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def check(self, stream=None):
+        code = C.c_int32(0)
+        st = int(self._lib.mgt_engine_check(self.handle, _stream(stream), C.byref(code)))
+        return st, int(code.value)
+
+    def launch_mlp_loss_grad(self, shape, device_weights, device_weights_half, device_states, device_labels, sample_count,
+                             device_loss, device_grad, workspace, workspace_floats, input_grad_partial_chunks=1,
+                             input_grad_positions_per_block=1, use_half_input_grad=True, use_half_linear=True,
+                             profile=None, gradient_ready=None, stream=None, input_grad_position_tile=0) -> int:
+        """LaunchMlpLossGrad...ExternalHalf (native/cuda/mgt_cuda/mlp_backward.cuh:224-287)."""
+        s = shape.c()
+        cb = GRADIENT_READY_FN(gradient_ready) if gradient_ready is not None else None
+        self._keepalive = cb
+        return int(self._lib.mgt_launch_mlp_loss_grad(
+            self.handle, C.byref(s), _ptr(device_weights), _ptr(device_weights_half), _ptr(device_states), _ptr(device_labels),
+            sample_count, _ptr(device_loss), _ptr(device_grad), _ptr(workspace), workspace_floats, input_grad_partial_chunks,
+            input_grad_positions_per_block, int(use_half_input_grad), int(use_half_linear),
+            C.byref(profile) if profile is not None else None, C.cast(cb, C.c_void_p) if cb is not None else None, None,
+            _stream(stream), input_grad_position_tile))
+
+    def debug_gemm(self, a, lda, a_mn_major, b, ldb, b_mn_major, d, m, n, k, splits=1, partial=None, stream=None) -> int:
+        return int(self._lib.mgt_debug_gemm(self.handle, _ptr(a), lda, int(a_mn_major), _ptr(b), ldb, int(b_mn_major), _ptr(d),
+                                            m, n, k, splits, _ptr(partial), _stream(stream)))
+
+
+def validate_adamw_kernel_config(config: AdamWKernelConfig) -> int:
+    cfg = config.c()
+    return int(_lib.load().mgt_validate_adamw_config(C.byref(cfg)))
+
+
+def launch_adamw_kernel(config, device_weights, device_grad, device_m, device_v, stream=None) -> int:
+    cfg = config.c()
+    return int(_lib.load().mgt_launch_adamw(C.byref(cfg), _ptr(device_weights), _ptr(device_grad), _ptr(device_m),
+                                            _ptr(device_v), _stream(stream)))
+
+
+def launch_adamw_kernel_with_half_mirror(config, device_weights, device_weights_half, device_grad, device_m, device_v,
+                                         stream=None) -> int:
+    cfg = config.c()
+    return int(_lib.load().mgt_launch_adamw_with_half_mirror(C.byref(cfg), _ptr(device_weights), _ptr(device_weights_half),
+                                                             _ptr(device_grad), _ptr(device_m), _ptr(device_v), _stream(stream)))
+
+
+def launch_float_to_half(device_values, count, device_half, stream=None) -> int:
+    return int(_lib.load().mgt_launch_float_to_half(_ptr(device_values), count, _ptr(device_half), _stream(stream)))

@@ -1,0 +1,40 @@
+// AdamW update of one parameter, shared by the stand-alone optimizer kernel and by the fused
+// allreduce + AdamW kernels. Arithmetic follows native/cuda/adamw.cu:8-23 operation by operation
+// (fp32, bias corrections from powf, L2-style decay folded into the gradient).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mgt {
+
+struct AdamWScalars {
+    float lr, beta1, beta2, eps, wd, one_minus_b1, one_minus_b2, bias1, bias2;
+};
+
+__device__ __forceinline__ AdamWScalars MakeAdamWScalars(uint64_t step, float lr, float beta1, float beta2, float eps, float wd) {
+    AdamWScalars s;
+    s.lr = lr;
+    s.beta1 = beta1;
+    s.beta2 = beta2;
+    s.eps = eps;
+    s.wd = wd;
+    s.one_minus_b1 = 1.0f - beta1;
+    s.one_minus_b2 = 1.0f - beta2;
+    s.bias1 = 1.0f - powf(beta1, static_cast<float>(step));
+    s.bias2 = 1.0f - powf(beta2, static_cast<float>(step));
+    return s;
+}
+
+__device__ __forceinline__ float AdamWUpdateOne(const AdamWScalars& s, float weight, float grad, float* m, float* v) {
+    const float decayed = grad + s.wd * weight;
+    const float next_m = s.beta1 * *m + s.one_minus_b1 * decayed;
+    const float next_v = s.beta2 * *v + s.one_minus_b2 * decayed * decayed;
+    *m = next_m;
+    *v = next_v;
+    const float m_hat = next_m / s.bias1;
+    const float v_hat = next_v / s.bias2;
+    return weight - s.lr * m_hat / (sqrtf(v_hat) + s.eps);
+}
+
+}  // namespace mgt

@@ -1,0 +1,785 @@
+// Loss + gradient engine: forward, MSE loss and backward of the residual MLP on tcgen05 tensor
+// cores, behind the C ABI of include/mgt_b200.h. Follows the data flow of the reference's fp16
+// path (native/cuda/mlp_backward.cu:1228-1510): fp16 operands rounded at the same tensors, fp32
+// accumulation, fp32 master biases for the hidden/residual layers, fp16 mirror for the embedding
+// table and its bias. What differs is how it is computed:
+//   * the embedding layer and its gradient are one-hot GEMMs whose one-hot operand is synthesised
+//     in shared memory from the 80-byte states (never materialised in HBM);
+//   * bias, ReLU, residual add, ReLU-mask and the fp16 down-cast are epilogues of the GEMMs;
+//   * bias gradients are fp32 column sums taken in the epilogue that produces each dz tensor
+//     (the reference sums the fp32 dz, not its fp16 copy: tiny gradients that underflow in fp16
+//     still reach the bias), reduced over CTAs in a fixed order;
+//   * activations are kept once (fp16 tape + one in-place fp32 residual stream).
+#include "../../include/mgt_b200.h"
+#include "umma_gemm.cuh"
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+namespace mgt {
+namespace {
+
+// ---- flat parameter layout (native/cuda/mlp_backward.cu:25-36) -----------------------------
+inline uint64_t BlockParams(const mgt_mlp_shape_t& s) { return 2ULL * ((uint64_t)s.hd2 * s.hd2 + s.hd2); }
+inline uint64_t InputBias(const mgt_mlp_shape_t& s) { return (uint64_t)s.state_len * s.state_value_pad * s.hd1; }
+inline uint64_t HiddenWeight(const mgt_mlp_shape_t& s) { return InputBias(s) + s.hd1; }
+inline uint64_t HiddenBias(const mgt_mlp_shape_t& s) { return HiddenWeight(s) + (uint64_t)s.hd1 * s.hd2; }
+inline uint64_t ResidualBase(const mgt_mlp_shape_t& s) { return HiddenBias(s) + s.hd2; }
+inline uint64_t OutputWeight(const mgt_mlp_shape_t& s) { return ResidualBase(s) + (uint64_t)s.residual_blocks * BlockParams(s); }
+inline uint64_t OutputBias(const mgt_mlp_shape_t& s) { return OutputWeight(s) + (uint64_t)s.hd2 * s.output_dim; }
+inline uint64_t ParamCount(const mgt_mlp_shape_t& s) { return OutputBias(s) + s.output_dim; }
+inline uint64_t Fc1W(const mgt_mlp_shape_t& s, uint32_t b) { return ResidualBase(s) + (uint64_t)b * BlockParams(s); }
+inline uint64_t Fc1B(const mgt_mlp_shape_t& s, uint32_t b) { return Fc1W(s, b) + (uint64_t)s.hd2 * s.hd2; }
+inline uint64_t Fc2W(const mgt_mlp_shape_t& s, uint32_t b) { return Fc1B(s, b) + s.hd2; }
+inline uint64_t Fc2B(const mgt_mlp_shape_t& s, uint32_t b) { return Fc2W(s, b) + (uint64_t)s.hd2 * s.hd2; }
+
+inline uint64_t RoundUp(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+
+bool ValidShape(const mgt_mlp_shape_t* s) {
+    return s != nullptr && s->state_len > 0 && s->state_len <= MGT_STATE_LEN && s->state_value_pad > 0 &&
+           s->state_value_pad <= MGT_STATE_VALUE_PAD && s->hd1 > 0 && s->hd1 <= MGT_MAX_HD1 && s->hd2 > 0 &&
+           s->hd2 <= MGT_MAX_HD2 && s->residual_blocks <= MGT_MAX_RESIDUAL_BLOCKS && s->output_dim > 0;
+}
+
+// ---- workspace ------------------------------------------------------------------------------
+// All offsets are in bytes from a 1024-byte aligned base inside the caller's float arena.
+struct Workspace {
+    uint32_t B, H1, H2, R, OUT, IN;
+    uint32_t p_a1;    // pitch (halfs) of a1_h, rounded to 8
+    uint32_t p_act;   // pitch (halfs) of x_h / r1_h, rounded to 8
+    uint32_t p_dz;    // pitch (halfs) of dz tensors over H2
+    uint32_t p_dz1;   // pitch (halfs) of dz1 over H1
+    uint32_t p_f32;   // pitch (floats) of the fp32 residual / gradient streams
+    uint32_t p_w1, p_w2, p_wout;  // pitches of the internal fp16 weight copy
+    uint64_t off_a1, off_x, off_r1, off_xf, off_dzf, off_dza, off_dzb, off_dz1, off_partial, off_head, off_wint, off_dy, off_dyh, off_colsum;
+    uint64_t colsum_floats;
+    uint64_t x_stride, r1_stride;  // bytes between consecutive blocks' tensors
+    uint64_t partial_floats, head_blocks;
+    uint64_t total_bytes;
+};
+
+constexpr uint32_t kHeadBlocks = 296;   // two CTAs per SM on a 148-SM part
+constexpr uint32_t kHeadThreads = 256;
+
+Workspace PlanWorkspace(const mgt_mlp_shape_t& s, uint32_t B, uint32_t sm_count) {
+    Workspace w{};
+    w.B = B; w.H1 = s.hd1; w.H2 = s.hd2; w.R = s.residual_blocks; w.OUT = s.output_dim;
+    w.IN = s.state_len * s.state_value_pad;
+    w.p_a1 = (uint32_t)RoundUp(s.hd1, 8);
+    w.p_act = (uint32_t)RoundUp(s.hd2, 8);
+    w.p_dz = (uint32_t)RoundUp(s.hd2, 8);
+    w.p_dz1 = (uint32_t)RoundUp(s.hd1, 8);
+    w.p_f32 = (uint32_t)RoundUp(s.hd2, 4);
+    w.p_w1 = (uint32_t)RoundUp(s.hd1, 8);
+    w.p_w2 = (uint32_t)RoundUp(s.hd2, 8);
+    w.p_wout = (uint32_t)RoundUp(s.output_dim, 8);
+    uint64_t off = 0;
+    auto take = [&](uint64_t bytes) { const uint64_t o = off; off = RoundUp(off + bytes, 1024); return o; };
+    w.off_a1 = take((uint64_t)B * w.p_a1 * 2);
+    w.x_stride = RoundUp((uint64_t)B * w.p_act * 2, 1024);
+    w.off_x = take(w.x_stride * (w.R + 1));
+    w.r1_stride = w.x_stride;
+    w.off_r1 = take(w.r1_stride * (w.R > 0 ? w.R : 1));
+    w.off_xf = take((uint64_t)B * w.p_f32 * 4);
+    w.off_dzf = take((uint64_t)B * w.p_f32 * 4);
+    w.off_dza = take((uint64_t)B * w.p_dz * 2);
+    w.off_dzb = take((uint64_t)B * w.p_dz * 2);
+    w.off_dz1 = take((uint64_t)B * w.p_dz1 * 2);
+    // split-K partials: at most one CTA wave of [128 x 256] fp32 tiles plus slack for tile padding
+    const uint64_t hidden_units = (uint64_t)((s.hd1 + 127) / 128) * ((s.hd2 + 255) / 256);
+    const uint64_t resid_units = (uint64_t)((s.hd2 + 127) / 128) * ((s.hd2 + 255) / 256);
+    const uint64_t hidden_splits = hidden_units >= sm_count ? 1 : sm_count / hidden_units;
+    const uint64_t resid_splits = resid_units >= sm_count ? 1 : sm_count / resid_units;
+    const uint64_t p1 = hidden_splits * (uint64_t)s.hd1 * s.hd2;
+    const uint64_t p2 = resid_splits * (uint64_t)s.hd2 * s.hd2;
+    w.partial_floats = p1 > p2 ? p1 : p2;
+    w.off_partial = take(w.partial_floats * 4);
+    w.head_blocks = kHeadBlocks;
+    w.off_head = take((uint64_t)kHeadBlocks * (2ULL * s.hd2 + 2) * 4);
+    w.colsum_floats = (uint64_t)sm_count * 4 * (s.hd1 > s.hd2 ? s.hd1 : s.hd2);
+    w.off_colsum = take(w.colsum_floats * 4);
+    // internal fp16 weight copy (used when the caller's mirror cannot be addressed by TMA as it lies)
+    const uint64_t wint_halfs = (uint64_t)(w.IN + 1) * w.p_w1 + (uint64_t)s.hd1 * w.p_w2 + 2ULL * w.R * s.hd2 * w.p_w2 + (uint64_t)s.hd2 * w.p_wout;
+    w.off_wint = take(wint_halfs * 2 + 1024ULL * (2 * w.R + 4));
+    w.off_dy = take((uint64_t)B * s.output_dim * 4);
+    w.off_dyh = take((uint64_t)B * w.p_wout * 2);
+    w.total_bytes = off + 1024;  // slack to align the caller's base
+    return w;
+}
+
+// ---- engine -----------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct MapKey {
+    const void* base;
+    uint64_t inner, outer, pitch;
+    uint32_t box_inner, box_outer;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && inner == o.inner && outer == o.outer && pitch == o.pitch && box_inner == o.box_inner && box_outer == o.box_outer;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        uint64_t h = reinterpret_cast<uint64_t>(k.base);
+        auto mix = [&](uint64_t v) { h ^= v + 0x9e3779b97f4a7c15ULL + (h << 6) + (h >> 2); };
+        mix(k.inner); mix(k.outer); mix(k.pitch); mix(k.box_inner); mix(k.box_outer);
+        return (size_t)h;
+    }
+};
+
+}  // namespace
+}  // namespace mgt
+
+struct mgt_engine {
+    int device = 0;
+    int sm_count = 148;
+    int* status_word = nullptr;  // device
+    mgt::EncodeTiledFn encode = nullptr;
+    std::unordered_map<mgt::MapKey, CUtensorMap, mgt::MapKeyHash> maps;
+    std::mutex mu;
+    cudaEvent_t ev_last = nullptr, ev_now = nullptr;
+
+    // fp16 2-D tensor map with 128-byte swizzle: `inner` contiguous elements per row, `outer` rows.
+    bool Map(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch_elems, uint32_t box_inner, uint32_t box_outer) {
+        const mgt::MapKey key{base, inner, outer, pitch_elems, box_inner, box_outer};
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = maps.find(key);
+        if (it != maps.end()) { *out = it->second; return true; }
+        if ((reinterpret_cast<uintptr_t>(base) & 15U) != 0 || ((pitch_elems * 2) & 15U) != 0 || box_inner * 2 > 128 || box_outer > 256) return false;
+        const cuuint64_t dims[2] = {inner, outer};
+        const cuuint64_t strides[1] = {pitch_elems * 2};
+        const cuuint32_t box[2] = {box_inner, box_outer};
+        const cuuint32_t elem[2] = {1, 1};
+        CUtensorMap m;
+        const CUresult r = encode(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return false;
+        if (maps.size() > 4096) maps.clear();
+        maps.emplace(key, m);
+        *out = m;
+        return true;
+    }
+};
+
+namespace mgt {
+namespace {
+
+template <class Cfg>
+mgt_status_t LaunchGemm(mgt_engine* e, const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs args, cudaStream_t stream) {
+    // the opt-in shared-memory size is a per-device attribute of each kernel instantiation
+    static bool attr_done[64] = {};
+    if (e->device >= 64) return MGT_INVALID_CONFIG;
+    if (!attr_done[e->device]) {
+        if (cudaFuncSetAttribute(umma_gemm_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return MGT_CUDA_FAILURE;
+        attr_done[e->device] = true;
+    }
+    const uint64_t units = (uint64_t)args.m_tiles * args.n_tiles * args.splits;
+    if (units == 0) return MGT_INVALID_CONFIG;
+    const uint32_t grid = (uint32_t)(units < (uint64_t)e->sm_count ? units : (uint64_t)e->sm_count);
+    args.status = e->status_word;
+    umma_gemm_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, args);
+    return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
+}
+
+// Tile configurations. BN = 224 serves the p888 residual width without padded MMA columns.
+template <int BN, Epi EPI> using CfgFwd = GemmCfg<BN, 1, false, BSource::kTmaMN, EPI, 4, 4>;   // act[K-major] x W[K][N]
+template <int BN, Epi EPI> using CfgDx = GemmCfg<BN, 1, false, BSource::kTmaK, EPI, 4, 4>;     // dz[K-major] x W[N][K]
+template <int BN> using CfgDw = GemmCfg<BN, 1, true, BSource::kTmaMN, Epi::kPartialF32, 4, 4>; // act^T x dz
+using CfgEmbFwd = GemmCfg<256, 2, true, BSource::kOneHotFwd, Epi::kEmbFwd, 4, 2>;
+using CfgEmbGrad = GemmCfg<256, 2, true, BSource::kOneHotGrad, Epi::kEmbGrad, 4, 2>;
+using CfgDbgKK = GemmCfg<256, 1, false, BSource::kTmaK, Epi::kPartialF32, 4, 4>;
+using CfgDbgKM = GemmCfg<256, 1, false, BSource::kTmaMN, Epi::kPartialF32, 4, 4>;
+using CfgDbgMK = GemmCfg<256, 1, true, BSource::kTmaK, Epi::kPartialF32, 4, 4>;
+
+inline uint32_t PickBN(uint32_t n) { return n <= 224 ? 224U : 256U; }
+
+GemmArgs BaseArgs(uint32_t M, uint32_t N, uint32_t K, uint32_t bn_total, uint32_t splits) {
+    GemmArgs a{};
+    a.M = M; a.N = N; a.K = K;
+    a.m_tiles = (M + 127) / 128;
+    a.n_tiles = (N + bn_total - 1) / bn_total;
+    a.k_chunks = (K + 63) / 64;
+    a.splits = splits < 1 ? 1 : (splits > a.k_chunks ? a.k_chunks : splits);
+    return a;
+}
+
+// ---- small kernels ------------------------------------------------------------------------------
+
+// fp32 [rows][cols] (pitch src_pitch) -> fp16 [rows][dst_pitch], round-to-nearest-even.
+__global__ void RepackHalfKernel(const float* __restrict__ src, uint32_t rows, uint32_t cols, uint32_t src_pitch, __half* __restrict__ dst, uint32_t dst_pitch) {
+    const uint64_t total = (uint64_t)rows * cols;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const uint32_t r = (uint32_t)(i / cols), c = (uint32_t)(i - (uint64_t)r * cols);
+        dst[(uint64_t)r * dst_pitch + c] = __float2half_rn(src[(uint64_t)r * src_pitch + c]);
+    }
+}
+
+// grad[i] = sum over splits (fixed order) of partial[split][i]
+__global__ void ReducePartialsKernel(const float* __restrict__ partial, uint32_t splits, uint64_t count, float* __restrict__ out) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+        float sum = partial[i];
+        for (uint32_t s = 1; s < splits; ++s) sum += partial[(uint64_t)s * count + i];
+        out[i] = sum;
+    }
+}
+
+// dst[c] = sum over rows r (fixed order) of src[r * row_stride + col_offset + c]
+__global__ void ReduceRowsKernel(const float* __restrict__ src, uint32_t rows, uint64_t row_stride, uint32_t col_offset, uint32_t cols, float* __restrict__ dst) {
+    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    float sum = 0.0f;
+    for (uint32_t r = 0; r < rows; ++r) sum += src[(uint64_t)r * row_stride + col_offset + c];
+    dst[c] = sum;
+}
+
+// Output head for output_dim == 1 (native/cuda/mlp_backward.cu:891-931): y = b + <x, w> with fp32
+// master weights, diff, dy = 2 diff / B, loss term diff^2 / B, dcur = w * dy, then the ReLU mask of
+// the last block. One warp per sample (grid-stride); per-CTA partial sums go to
+// partials[CTA][2*H2+2] = { grad W_out[H2], grad b_out, loss, column sums of dz[H2] } and are added
+// in a fixed order by ReduceRowsKernel.
+constexpr int kHeadMaxPerLane = MGT_MAX_HD2 / 32;
+__global__ void __launch_bounds__(kHeadThreads)
+HeadOut1Kernel(const float* __restrict__ w_out, const float* __restrict__ b_out, const float* __restrict__ labels, const float* __restrict__ x,
+               uint32_t p_f32, uint32_t B, uint32_t H2, float* __restrict__ dzf, __half* __restrict__ dz_h, uint32_t p_dz, float* __restrict__ partials) {
+    __shared__ float s_acc[kHeadThreads / 32][2 * MGT_MAX_HD2 + 2];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31U;
+    const uint32_t warps_total = gridDim.x * (kHeadThreads / 32);
+    const float inv_n = 1.0f / static_cast<float>(B);
+    const float bias = *b_out;
+    float wreg[kHeadMaxPerLane], gacc[kHeadMaxPerLane], dacc[kHeadMaxPerLane];
+#pragma unroll
+    for (int q = 0; q < kHeadMaxPerLane; ++q) {
+        const uint32_t j = q * 32 + lane;
+        wreg[q] = j < H2 ? w_out[j] : 0.0f;
+        gacc[q] = 0.0f;
+        dacc[q] = 0.0f;
+    }
+    float gb = 0.0f, loss = 0.0f;
+    for (uint32_t b = blockIdx.x * (kHeadThreads / 32) + warp; b < B; b += warps_total) {
+        const float* row = x + (uint64_t)b * p_f32;
+        float xv[kHeadMaxPerLane];
+        float dot = 0.0f;
+#pragma unroll
+        for (int q = 0; q < kHeadMaxPerLane; ++q) {
+            const uint32_t j = q * 32 + lane;
+            xv[q] = j < H2 ? row[j] : 0.0f;
+            dot += xv[q] * wreg[q];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xFFFFFFFFU, dot, o);
+        const float diff = (bias + dot) - labels[b];
+        const float dy = 2.0f * diff * inv_n;
+        if (lane == 0) { gb += dy; loss += diff * diff * inv_n; }
+#pragma unroll
+        for (int q = 0; q < kHeadMaxPerLane; ++q) {
+            const uint32_t j = q * 32 + lane;
+            if (j < H2) {
+                gacc[q] += xv[q] * dy;
+                const float d = xv[q] > 0.0f ? wreg[q] * dy : 0.0f;
+                dacc[q] += d;
+                dzf[(uint64_t)b * p_f32 + j] = d;
+                dz_h[(uint64_t)b * p_dz + j] = __float2half_rn(d);
+            }
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < kHeadMaxPerLane; ++q) {
+        const uint32_t j = q * 32 + lane;
+        if (j < H2) { s_acc[warp][j] = gacc[q]; s_acc[warp][H2 + 2 + j] = dacc[q]; }
+    }
+    if (lane == 0) { s_acc[warp][H2] = gb; s_acc[warp][H2 + 1] = loss; }
+    __syncthreads();
+    for (uint32_t j = threadIdx.x; j < 2 * H2 + 2; j += kHeadThreads) {
+        float sum = 0.0f;
+        for (int wi = 0; wi < kHeadThreads / 32; ++wi) sum += s_acc[wi][j];
+        partials[(uint64_t)blockIdx.x * (2 * H2 + 2) + j] = sum;
+    }
+}
+
+// Output head for output_dim > 1 (native/cuda/mlp_backward.cu:1341-1363): fp16 operands, fp32
+// accumulate, MSE against the labels, dy rounded to fp16 for the two products that follow.
+// One warp per sample. Plain SIMT: this path carries little work (B x OUT x H2).
+__global__ void __launch_bounds__(kHeadThreads)
+HeadOutNKernel(const __half* __restrict__ w_out_h, uint32_t p_wout, const float* __restrict__ b_out, const float* __restrict__ labels,
+               const __half* __restrict__ x_h, uint32_t p_act, const float* __restrict__ x_f32, uint32_t p_f32, uint32_t B, uint32_t H2, uint32_t OUT,
+               float* __restrict__ dy, __half* __restrict__ dy_h, float* __restrict__ dzf, __half* __restrict__ dz_h, uint32_t p_dz,
+               float* __restrict__ partials) {
+    extern __shared__ float s_dyn[];  // per warp: OUT floats of rounded dy
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31U;
+    const uint32_t warps_total = gridDim.x * (kHeadThreads / 32);
+    float* s_dy = s_dyn + warp * OUT;
+    const float inv_n = 1.0f / static_cast<float>((uint64_t)B * OUT);
+    float loss = 0.0f;
+    float dacc[kHeadMaxPerLane];
+#pragma unroll
+    for (int q = 0; q < kHeadMaxPerLane; ++q) dacc[q] = 0.0f;
+    for (uint32_t b = blockIdx.x * (kHeadThreads / 32) + warp; b < B; b += warps_total) {
+        const __half* row = x_h + (uint64_t)b * p_act;
+        for (uint32_t o = lane; o < OUT; o += 32) {
+            float acc = 0.0f;
+            for (uint32_t j = 0; j < H2; ++j) acc += __half2float(row[j]) * __half2float(w_out_h[(uint64_t)j * p_wout + o]);
+            const float y = acc + b_out[o];
+            const float diff = y - labels[(uint64_t)b * OUT + o];
+            const float d = 2.0f * diff * inv_n;
+            loss += diff * diff * inv_n;
+            dy[(uint64_t)b * OUT + o] = d;
+            const __half dh = __float2half_rn(d);
+            dy_h[(uint64_t)b * p_wout + o] = dh;
+            s_dy[o] = __half2float(dh);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int q = 0; q < kHeadMaxPerLane; ++q) {
+            const uint32_t j = q * 32 + lane;
+            if (j < H2) {
+                float acc = 0.0f;
+                for (uint32_t o = 0; o < OUT; ++o) acc += s_dy[o] * __half2float(w_out_h[(uint64_t)j * p_wout + o]);
+                const float d = x_f32[(uint64_t)b * p_f32 + j] > 0.0f ? acc : 0.0f;
+                dacc[q] += d;
+                dzf[(uint64_t)b * p_f32 + j] = d;
+                dz_h[(uint64_t)b * p_dz + j] = __float2half_rn(d);
+            }
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) loss += __shfl_xor_sync(0xFFFFFFFFU, loss, o);
+    __shared__ float s_part[kHeadThreads / 32][MGT_MAX_HD2 + 1];
+    if (lane == 0) s_part[warp][0] = loss;
+#pragma unroll
+    for (int q = 0; q < kHeadMaxPerLane; ++q) {
+        const uint32_t j = q * 32 + lane;
+        if (j < H2) s_part[warp][1 + j] = dacc[q];
+    }
+    __syncthreads();
+    for (uint32_t j = threadIdx.x; j < H2 + 1; j += kHeadThreads) {
+        float sum = 0.0f;
+        for (int wi = 0; wi < kHeadThreads / 32; ++wi) sum += s_part[wi][j];
+        partials[(uint64_t)blockIdx.x * (H2 + 1) + j] = sum;
+    }
+}
+
+// grad W_out[j][o] = sum_b x_h[b][j] * dy_h[b][o]; grad b_out[o] = sum_b dy[b][o].
+__global__ void HeadOutNGradKernel(const __half* __restrict__ x_h, uint32_t p_act, const __half* __restrict__ dy_h, uint32_t p_wout, const float* __restrict__ dy,
+                                   uint32_t B, uint32_t H2, uint32_t OUT, float* __restrict__ grad_w, float* __restrict__ grad_b) {
+    const uint32_t item = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t wcount = H2 * OUT;
+    if (item < wcount) {
+        const uint32_t j = item / OUT, o = item - j * OUT;
+        float sum = 0.0f;
+        for (uint32_t b = 0; b < B; ++b) sum += __half2float(x_h[(uint64_t)b * p_act + j]) * __half2float(dy_h[(uint64_t)b * p_wout + o]);
+        grad_w[item] = sum;
+    } else if (item < wcount + OUT) {
+        const uint32_t o = item - wcount;
+        float sum = 0.0f;
+        for (uint32_t b = 0; b < B; ++b) sum += dy[(uint64_t)b * OUT + o];
+        grad_b[o] = sum;
+    }
+}
+
+inline uint32_t GridFor(uint64_t items, uint32_t threads, int sm_count) {
+    const uint64_t want = (items + threads - 1) / threads;
+    const uint64_t cap = (uint64_t)sm_count * 8;
+    return (uint32_t)(want < 1 ? 1 : (want < cap ? want : cap));
+}
+
+struct StageTimer {
+    mgt_engine* e;
+    cudaStream_t stream;
+    mgt_backward_profile_t* profile;
+    bool Start() {
+        if (!profile) return true;
+        std::memset(profile, 0, sizeof(*profile));
+        if (!e->ev_last && cudaEventCreate(&e->ev_last) != cudaSuccess) return false;
+        if (!e->ev_now && cudaEventCreate(&e->ev_now) != cudaSuccess) return false;
+        return cudaEventRecord(e->ev_last, stream) == cudaSuccess;
+    }
+    // As in the reference, every mark synchronises the host (native/cuda/mlp_backward.cu:211-221).
+    bool Mark(float* dst) {
+        if (!profile) return true;
+        if (cudaEventRecord(e->ev_now, stream) != cudaSuccess) return false;
+        if (cudaEventSynchronize(e->ev_now) != cudaSuccess) return false;
+        if (cudaEventElapsedTime(dst, e->ev_last, e->ev_now) != cudaSuccess) return false;
+        std::swap(e->ev_last, e->ev_now);
+        return true;
+    }
+};
+
+#define MGT_TRY(...)                          \
+    do {                                      \
+        const mgt_status_t _st = (__VA_ARGS__); \
+        if (_st != MGT_OK) return _st;        \
+    } while (0)
+#define MGT_MAP(...)                               \
+    do {                                           \
+        if (!(__VA_ARGS__)) return MGT_CUDA_FAILURE; \
+    } while (0)
+
+// D = act[M x K, K-major] * W[K x N, row-major] with a forward epilogue.
+template <Epi EPI>
+mgt_status_t GemmForward(mgt_engine* e, cudaStream_t st, const __half* act, uint32_t act_pitch, const __half* w, uint32_t w_pitch,
+                         uint32_t M, uint32_t N, uint32_t K, GemmArgs epi) {
+    const uint32_t bn = PickBN(N);
+    GemmArgs a = BaseArgs(M, N, K, bn, 1);
+    a.bias = epi.bias; a.out_f32 = epi.out_f32; a.ld_f32 = epi.ld_f32; a.out_f16 = epi.out_f16; a.ld_f16 = epi.ld_f16;
+    a.add_f32 = epi.add_f32; a.ld_add = epi.ld_add; a.mask = epi.mask; a.ld_mask = epi.ld_mask;
+    CUtensorMap ta, tb;
+    MGT_MAP(e->Map(&ta, act, K, M, act_pitch, 64, 128));
+    MGT_MAP(e->Map(&tb, w, N, K, w_pitch, 64, 64));
+    return bn == 224 ? LaunchGemm<CfgFwd<224, EPI>>(e, ta, tb, a, st) : LaunchGemm<CfgFwd<256, EPI>>(e, ta, tb, a, st);
+}
+
+// dX[M x N] = dz[M x K, K-major] * W[N x K, row-major]^T with a backward epilogue that produces the
+// next dz tensor; its fp32 column sums (a bias gradient) are reduced into bias_grad[N].
+template <Epi EPI>
+mgt_status_t GemmBackpropInput(mgt_engine* e, cudaStream_t st, const __half* dz, uint32_t dz_pitch, const __half* w, uint32_t w_pitch,
+                               uint32_t M, uint32_t N, uint32_t K, GemmArgs epi, float* colsum, uint64_t colsum_floats, float* bias_grad) {
+    const uint32_t bn = PickBN(N);
+    GemmArgs a = BaseArgs(M, N, K, bn, 1);
+    a.out_f32 = epi.out_f32; a.ld_f32 = epi.ld_f32; a.out_f16 = epi.out_f16; a.ld_f16 = epi.ld_f16;
+    a.add_f32 = epi.add_f32; a.ld_add = epi.ld_add; a.mask = epi.mask; a.ld_mask = epi.ld_mask;
+    const uint64_t units = (uint64_t)a.m_tiles * a.n_tiles;
+    const uint32_t grid = (uint32_t)(units < (uint64_t)e->sm_count ? units : (uint64_t)e->sm_count);
+    const uint32_t rows = grid * 4U;
+    if ((uint64_t)rows * N > colsum_floats) return MGT_CAPACITY_EXCEEDED;
+    if (cudaMemsetAsync(colsum, 0, (uint64_t)rows * N * sizeof(float), st) != cudaSuccess) return MGT_CUDA_FAILURE;
+    a.colsum = colsum;
+    CUtensorMap ta, tb;
+    MGT_MAP(e->Map(&ta, dz, K, M, dz_pitch, 64, 128));
+    MGT_MAP(e->Map(&tb, w, K, N, w_pitch, 64, bn));
+    MGT_TRY(bn == 224 ? LaunchGemm<CfgDx<224, EPI>>(e, ta, tb, a, st) : LaunchGemm<CfgDx<256, EPI>>(e, ta, tb, a, st));
+    ReduceRowsKernel<<<(N + 127) / 128, 128, 0, st>>>(colsum, rows, N, 0, N, bias_grad);
+    return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
+}
+
+// grad[in x out] = act^T * dz, reduced over the batch with split-K and a fixed-order reduction.
+mgt_status_t GemmGradWeights(mgt_engine* e, cudaStream_t st, const __half* act, uint32_t act_pitch, const __half* dz, uint32_t dz_pitch,
+                             uint32_t samples, uint32_t in_dim, uint32_t out_dim, float* partial, uint64_t partial_floats, float* grad_out) {
+    const uint32_t M = in_dim, N = out_dim, K = samples;
+    const uint32_t bn = PickBN(N);
+    GemmArgs a = BaseArgs(M, N, K, bn, 1);
+    const uint64_t tiles = (uint64_t)a.m_tiles * a.n_tiles;
+    uint32_t splits = tiles >= (uint64_t)e->sm_count ? 1U : (uint32_t)(e->sm_count / tiles);
+    const uint64_t per_split = (uint64_t)M * N;
+    if ((uint64_t)splits * per_split > partial_floats) splits = (uint32_t)(partial_floats / per_split);
+    if (splits < 1) return MGT_CAPACITY_EXCEEDED;
+    a = BaseArgs(M, N, K, bn, splits);
+    a.partial = partial;
+    CUtensorMap ta, tb;
+    MGT_MAP(e->Map(&ta, act, M, K, act_pitch, 64, 64));
+    MGT_MAP(e->Map(&tb, dz, N, K, dz_pitch, 64, 64));
+    MGT_TRY(bn == 224 ? LaunchGemm<CfgDw<224>>(e, ta, tb, a, st) : LaunchGemm<CfgDw<256>>(e, ta, tb, a, st));
+    ReducePartialsKernel<<<GridFor(per_split, 256, e->sm_count), 256, 0, st>>>(partial, a.splits, per_split, grad_out);
+    return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
+}
+
+struct HalfWeights {
+    const __half* in_table; uint32_t p1;     // [(IN+1)][p1], row IN is the input bias
+    const __half* wh; uint32_t p2;            // [H1][p2]
+    const __half* w1[MGT_MAX_RESIDUAL_BLOCKS];
+    const __half* w2[MGT_MAX_RESIDUAL_BLOCKS];
+    const __half* wout; uint32_t pout;        // [H2][pout]
+};
+
+}  // namespace
+}  // namespace mgt
+
+using namespace mgt;
+
+extern "C" {
+
+const char* mgt_status_name(mgt_status_t status) {
+    switch (status) {
+        case MGT_OK: return "ok";
+        case MGT_INVALID_CONFIG: return "invalid_config";
+        case MGT_INVALID_PUZZLE: return "invalid_puzzle";
+        case MGT_CAPACITY_EXCEEDED: return "capacity_exceeded";
+        case MGT_CUDA_FAILURE: return "cuda_failure";
+        case MGT_NCCL_FAILURE: return "nccl_failure";
+        case MGT_IO_FAILURE: return "io_failure";
+        case MGT_DEVICE_TIMEOUT: return "device_timeout";
+    }
+    return "unknown";
+}
+
+const char* mgt_version(void) { return "mgt_b200 0.1 (sm_100a)"; }
+
+mgt_status_t mgt_validate_mlp_shape(const mgt_mlp_shape_t* shape) { return ValidShape(shape) ? MGT_OK : MGT_INVALID_CONFIG; }
+
+uint64_t mgt_mlp_param_count(const mgt_mlp_shape_t* shape) { return ValidShape(shape) ? ParamCount(*shape) : 0; }
+
+mgt_status_t mgt_engine_create(int32_t device_id, mgt_engine_t** out_engine) {
+    if (out_engine == nullptr || device_id < 0) return MGT_INVALID_CONFIG;
+    *out_engine = nullptr;
+    if (cudaSetDevice(device_id) != cudaSuccess) return MGT_CUDA_FAILURE;
+    cudaDeviceProp prop{};
+    if (cudaGetDeviceProperties(&prop, device_id) != cudaSuccess) return MGT_CUDA_FAILURE;
+    if (prop.major != 10) {
+        std::fprintf(stderr, "mgt_b200: device %d is sm_%d%d; this library only runs on sm_100a (B200)\n", device_id, prop.major, prop.minor);
+        return MGT_CUDA_FAILURE;
+    }
+    auto* e = new mgt_engine();
+    e->device = device_id;
+    e->sm_count = prop.multiProcessorCount;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || fn == nullptr) {
+        delete e;
+        return MGT_CUDA_FAILURE;
+    }
+    e->encode = reinterpret_cast<EncodeTiledFn>(fn);
+    if (cudaMalloc(&e->status_word, sizeof(int)) != cudaSuccess || cudaMemset(e->status_word, 0, sizeof(int)) != cudaSuccess) {
+        delete e;
+        return MGT_CUDA_FAILURE;
+    }
+    *out_engine = e;
+    return MGT_OK;
+}
+
+mgt_status_t mgt_engine_destroy(mgt_engine_t* e) {
+    if (e == nullptr) return MGT_OK;
+    if (e->ev_last) cudaEventDestroy(e->ev_last);
+    if (e->ev_now) cudaEventDestroy(e->ev_now);
+    if (e->status_word) cudaFree(e->status_word);
+    delete e;
+    return MGT_OK;
+}
+
+mgt_status_t mgt_engine_check(mgt_engine_t* e, void* stream, int32_t* out_device_code) {
+    if (e == nullptr) return MGT_INVALID_CONFIG;
+    int code = 0;
+    if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) != cudaSuccess) return MGT_CUDA_FAILURE;
+    if (cudaMemcpy(&code, e->status_word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return MGT_CUDA_FAILURE;
+    if (out_device_code) *out_device_code = code;
+    if (code != 0) {
+        cudaMemset(e->status_word, 0, sizeof(int));
+        return MGT_DEVICE_TIMEOUT;
+    }
+    return MGT_OK;
+}
+
+uint64_t mgt_mlp_loss_grad_workspace_floats(const mgt_mlp_shape_t* shape, uint32_t sample_count, uint32_t chunks,
+                                            int32_t use_half_input_grad, int32_t use_half_linear) {
+    if (!ValidShape(shape) || sample_count == 0 || chunks == 0) return 0;
+    (void)use_half_input_grad;
+    (void)use_half_linear;
+    const Workspace w = PlanWorkspace(*shape, sample_count, 148);
+    return (w.total_bytes + 3) / 4;
+}
+
+mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* shape, const float* w, const uint16_t* w_half_u16,
+                                      const mgt_train_state_t* states, const float* labels, uint32_t B, float* loss, float* grad,
+                                      float* workspace, uint64_t workspace_floats, uint32_t chunks, uint32_t ppb, int32_t half_ig,
+                                      int32_t half_lin, mgt_backward_profile_t* profile, mgt_gradient_ready_fn ready, void* ready_user,
+                                      void* stream_v, uint32_t position_tile) {
+    (void)position_tile;
+    if (e == nullptr || !ValidShape(shape) || w == nullptr || states == nullptr || labels == nullptr || loss == nullptr || grad == nullptr ||
+        B == 0 || workspace == nullptr || chunks == 0 || ppb == 0) {
+        return MGT_INVALID_CONFIG;
+    }
+    // The tensor-core engine computes the reference's fp16 data flow; the fp32/TF32 variant of the
+    // reference (both switches off) and the mixed combinations are not provided.
+    if (!half_ig || !half_lin) return MGT_INVALID_CONFIG;
+    const mgt_mlp_shape_t s = *shape;
+    const Workspace ws = PlanWorkspace(s, B, 148);
+    if (workspace_floats < (ws.total_bytes + 3) / 4) return MGT_CAPACITY_EXCEEDED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream_v);
+    uint8_t* base = reinterpret_cast<uint8_t*>(RoundUp(reinterpret_cast<uintptr_t>(workspace), 1024));
+    __half* a1_h = reinterpret_cast<__half*>(base + ws.off_a1);
+    auto x_h = [&](uint32_t k) { return reinterpret_cast<__half*>(base + ws.off_x + ws.x_stride * k); };
+    auto r1_h = [&](uint32_t k) { return reinterpret_cast<__half*>(base + ws.off_r1 + ws.r1_stride * k); };
+    float* x_f32 = reinterpret_cast<float*>(base + ws.off_xf);
+    float* dzf = reinterpret_cast<float*>(base + ws.off_dzf);
+    __half* dz_a = reinterpret_cast<__half*>(base + ws.off_dza);
+    __half* dz_b = reinterpret_cast<__half*>(base + ws.off_dzb);
+    __half* dz1_h = reinterpret_cast<__half*>(base + ws.off_dz1);
+    float* partial = reinterpret_cast<float*>(base + ws.off_partial);
+    float* head_partial = reinterpret_cast<float*>(base + ws.off_head);
+    float* colsum = reinterpret_cast<float*>(base + ws.off_colsum);
+    const uint32_t H1 = s.hd1, H2 = s.hd2, R = s.residual_blocks, OUT = s.output_dim, IN = ws.IN;
+
+    StageTimer timer{e, st, profile};
+    if (!timer.Start()) return MGT_CUDA_FAILURE;
+    uint32_t ready_id = 0;
+    auto notify = [&](uint64_t off, uint64_t count) -> mgt_status_t {
+        if (ready == nullptr) return MGT_OK;
+        const mgt_status_t r = ready(ready_user, ready_id++, off, count, stream_v);
+        return r == MGT_OK ? MGT_OK : MGT_CUDA_FAILURE;  // the reference maps a failing callback to kCudaFailure
+    };
+
+    // ---- fp16 weights: the caller's mirror as it lies when TMA can address it, else a padded copy
+    HalfWeights hw{};
+    const __half* w_half = reinterpret_cast<const __half*>(w_half_u16);
+    const bool direct = w_half != nullptr && (H1 % 8U) == 0 && (H2 % 8U) == 0 && (reinterpret_cast<uintptr_t>(w_half) & 15U) == 0;
+    if (direct) {
+        hw.in_table = w_half; hw.p1 = H1;
+        hw.wh = w_half + HiddenWeight(s); hw.p2 = H2;
+        for (uint32_t k = 0; k < R; ++k) { hw.w1[k] = w_half + Fc1W(s, k); hw.w2[k] = w_half + Fc2W(s, k); }
+        hw.wout = w_half + OutputWeight(s); hw.pout = OUT;
+    } else {
+        uint8_t* cur = base + ws.off_wint;
+        auto repack = [&](const float* src, uint32_t rows, uint32_t cols, uint32_t pitch) -> const __half* {
+            __half* dst = reinterpret_cast<__half*>(cur);
+            cur += RoundUp((uint64_t)rows * pitch * 2, 1024);
+            cudaMemsetAsync(dst, 0, (uint64_t)rows * pitch * 2, st);
+            RepackHalfKernel<<<GridFor((uint64_t)rows * cols, 256, e->sm_count), 256, 0, st>>>(src, rows, cols, cols, dst, pitch);
+            return dst;
+        };
+        hw.p1 = ws.p_w1; hw.p2 = ws.p_w2; hw.pout = ws.p_wout;
+        hw.in_table = repack(w, IN + 1, H1, ws.p_w1);
+        hw.wh = repack(w + HiddenWeight(s), H1, H2, ws.p_w2);
+        for (uint32_t k = 0; k < R; ++k) {
+            hw.w1[k] = repack(w + Fc1W(s, k), H2, H2, ws.p_w2);
+            hw.w2[k] = repack(w + Fc2W(s, k), H2, H2, ws.p_w2);
+        }
+        hw.wout = repack(w + OutputWeight(s), H2, OUT, ws.p_wout);
+        if (cudaGetLastError() != cudaSuccess) return MGT_CUDA_FAILURE;
+    }
+
+    // ---- embedding forward: a1 = relu([onehot | 1] * [W_in ; b_in])  (mlp_backward.cu:755-832)
+    {
+        GemmArgs a = BaseArgs(H1, B, IN + 1, 512, 1);
+        a.out_f16 = a1_h; a.ld_f16 = ws.p_a1;
+        a.states = reinterpret_cast<const uint8_t*>(states); a.state_len = s.state_len; a.value_pad = s.state_value_pad; a.samples = B; a.in_rows = IN;
+        CUtensorMap ta;
+        MGT_MAP(e->Map(&ta, hw.in_table, H1, IN + 1, hw.p1, 64, 64));
+        MGT_TRY(LaunchGemm<CfgEmbFwd>(e, ta, ta, a, st));
+    }
+    if (!timer.Mark(profile ? &profile->input_forward_ms : nullptr)) return MGT_CUDA_FAILURE;
+
+    // ---- hidden layer: x0 = relu(a1 * Wh + bh)  (mlp_backward.cu:1281-1291)
+    {
+        GemmArgs epi{};
+        epi.bias = w + HiddenBias(s); epi.out_f32 = x_f32; epi.ld_f32 = ws.p_f32; epi.out_f16 = x_h(0); epi.ld_f16 = ws.p_act;
+        MGT_TRY(GemmForward<Epi::kBiasReluF32F16>(e, st, a1_h, ws.p_a1, hw.wh, hw.p2, B, H2, H1, epi));
+    }
+    if (!timer.Mark(profile ? &profile->hidden_forward_ms : nullptr)) return MGT_CUDA_FAILURE;
+
+    // ---- residual blocks forward (mlp_backward.cu:1294-1323)
+    for (uint32_t k = 0; k < R; ++k) {
+        GemmArgs e1{};
+        e1.bias = w + Fc1B(s, k); e1.out_f16 = r1_h(k); e1.ld_f16 = ws.p_act;
+        MGT_TRY(GemmForward<Epi::kBiasReluF16>(e, st, x_h(k), ws.p_act, hw.w1[k], hw.p2, B, H2, H2, e1));
+        GemmArgs e2{};
+        e2.bias = w + Fc2B(s, k); e2.add_f32 = x_f32; e2.ld_add = ws.p_f32; e2.out_f32 = x_f32; e2.ld_f32 = ws.p_f32;
+        e2.out_f16 = x_h(k + 1); e2.ld_f16 = ws.p_act;
+        MGT_TRY(GemmForward<Epi::kBiasResReluF32F16>(e, st, r1_h(k), ws.p_act, hw.w2[k], hw.p2, B, H2, H2, e2));
+    }
+    if (!timer.Mark(profile ? &profile->residual_forward_ms : nullptr)) return MGT_CUDA_FAILURE;
+
+    // ---- output head, loss and the gradient entering the last block (mlp_backward.cu:1327-1364)
+    __half* dz_cur = dz_a;   // fp16 copy of the gradient w.r.t. the pre-activation being processed
+    __half* dz_other = dz_b;
+    // the head also yields the fp32 column sums of dz: the bias gradient of the layer below it
+    float* head_bias_dst = grad + (R > 0 ? Fc2B(s, R - 1) : HiddenBias(s));
+    if (OUT == 1U) {
+        HeadOut1Kernel<<<kHeadBlocks, kHeadThreads, 0, st>>>(w + OutputWeight(s), w + OutputBias(s), labels, x_f32, ws.p_f32, B, H2, dzf, dz_cur, ws.p_dz, head_partial);
+        const uint32_t items = 2 * H2 + 2;
+        ReduceRowsKernel<<<(H2 + 1 + 127) / 128, 128, 0, st>>>(head_partial, kHeadBlocks, items, 0, H2 + 1, grad + OutputWeight(s));
+        ReduceRowsKernel<<<1, 32, 0, st>>>(head_partial, kHeadBlocks, items, H2 + 1, 1, loss);
+        ReduceRowsKernel<<<(H2 + 127) / 128, 128, 0, st>>>(head_partial, kHeadBlocks, items, H2 + 2, H2, head_bias_dst);
+    } else {
+        float* dy = reinterpret_cast<float*>(base + ws.off_dy);
+        __half* dy_h = reinterpret_cast<__half*>(base + ws.off_dyh);
+        HeadOutNKernel<<<kHeadBlocks, kHeadThreads, (kHeadThreads / 32) * OUT * sizeof(float), st>>>(
+            hw.wout, hw.pout, w + OutputBias(s), labels, x_h(R), ws.p_act, x_f32, ws.p_f32, B, H2, OUT, dy, dy_h, dzf, dz_cur, ws.p_dz, head_partial);
+        const uint32_t items = H2 * OUT + OUT;
+        HeadOutNGradKernel<<<(items + 127) / 128, 128, 0, st>>>(x_h(R), ws.p_act, dy_h, hw.pout, dy, B, H2, OUT, grad + OutputWeight(s), grad + OutputBias(s));
+        ReduceRowsKernel<<<1, 32, 0, st>>>(head_partial, kHeadBlocks, H2 + 1, 0, 1, loss);
+        ReduceRowsKernel<<<(H2 + 127) / 128, 128, 0, st>>>(head_partial, kHeadBlocks, H2 + 1, 1, H2, head_bias_dst);
+    }
+    if (cudaGetLastError() != cudaSuccess) return MGT_CUDA_FAILURE;
+    MGT_TRY(notify(OutputWeight(s), (uint64_t)H2 * OUT + OUT));
+    if (!timer.Mark(profile ? &profile->output_ms : nullptr)) return MGT_CUDA_FAILURE;
+
+    // ---- residual blocks backward (mlp_backward.cu:1367-1413). dz_cur holds dz2 of block k in fp16,
+    // dzf the same values in fp32 (they are added to the fc1 input gradient: the skip connection).
+    for (uint32_t rb = R; rb > 0; --rb) {
+        const uint32_t k = rb - 1U;
+        MGT_TRY(GemmGradWeights(e, st, r1_h(k), ws.p_act, dz_cur, ws.p_dz, B, H2, H2, partial, ws.partial_floats, grad + Fc2W(s, k)));
+        MGT_TRY(notify(Fc2W(s, k), (uint64_t)H2 * H2 + H2));
+        GemmArgs d2{};  // dz1 = (dz2 * W2^T) * [r1 > 0]
+        d2.mask = r1_h(k); d2.ld_mask = ws.p_act; d2.out_f16 = dz_other; d2.ld_f16 = ws.p_dz;
+        MGT_TRY(GemmBackpropInput<Epi::kMaskF16>(e, st, dz_cur, ws.p_dz, hw.w2[k], hw.p2, B, H2, H2, d2, colsum, ws.colsum_floats, grad + Fc1B(s, k)));
+        MGT_TRY(GemmGradWeights(e, st, x_h(k), ws.p_act, dz_other, ws.p_dz, B, H2, H2, partial, ws.partial_floats, grad + Fc1W(s, k)));
+        MGT_TRY(notify(Fc1W(s, k), (uint64_t)H2 * H2 + H2));
+        GemmArgs d1{};  // next dz = (dz1 * W1^T + dz2) * [x_k > 0]: ReLU of the previous block (or of the hidden layer)
+        d1.add_f32 = dzf; d1.ld_add = ws.p_f32; d1.out_f32 = dzf; d1.ld_f32 = ws.p_f32; d1.mask = x_h(k); d1.ld_mask = ws.p_act;
+        d1.out_f16 = dz_cur; d1.ld_f16 = ws.p_dz;
+        MGT_TRY(GemmBackpropInput<Epi::kAddMaskF32F16>(e, st, dz_other, ws.p_dz, hw.w1[k], hw.p2, B, H2, H2, d1, colsum, ws.colsum_floats,
+                                                        grad + (k > 0 ? Fc2B(s, k - 1) : HiddenBias(s))));
+    }
+    if (!timer.Mark(profile ? &profile->residual_backward_ms : nullptr)) return MGT_CUDA_FAILURE;
+
+    // ---- hidden layer backward (mlp_backward.cu:1417-1438): dz_cur = dcur * [x0 > 0]
+    MGT_TRY(GemmGradWeights(e, st, a1_h, ws.p_a1, dz_cur, ws.p_dz, B, H1, H2, partial, ws.partial_floats, grad + HiddenWeight(s)));
+    MGT_TRY(notify(HiddenWeight(s), (uint64_t)H1 * H2 + H2));
+    {
+        GemmArgs d{};  // dz1 = (dzh * Wh^T) * [a1 > 0]
+        d.mask = a1_h; d.ld_mask = ws.p_a1; d.out_f16 = dz1_h; d.ld_f16 = ws.p_dz1;
+        MGT_TRY(GemmBackpropInput<Epi::kMaskF16>(e, st, dz_cur, ws.p_dz, hw.wh, hw.p2, B, H1, H2, d, colsum, ws.colsum_floats, grad + InputBias(s)));
+    }
+    if (!timer.Mark(profile ? &profile->hidden_backward_ms : nullptr)) return MGT_CUDA_FAILURE;
+
+    // ---- embedding gradient: grad W_in = onehot^T * dz1  (mlp_backward.cu:1440-1504); the input-bias
+    // gradient (mlp_backward.cu:1505) is the column sum written by the GEMM above
+    {
+        GemmArgs a = BaseArgs(H1, IN, B, 512, 1);
+        const uint64_t tiles = (uint64_t)a.m_tiles * a.n_tiles;
+        // Two splits keep fp32 atomics order-independent (0 + a + b == 0 + b + a); use them when one
+        // split would leave a large part of the last wave idle.
+        const uint64_t waves1 = (tiles + e->sm_count - 1) / e->sm_count;
+        const uint64_t waves2 = (2 * tiles + e->sm_count - 1) / e->sm_count;
+        const uint32_t splits = (a.k_chunks >= 2 && waves2 < 2 * waves1) ? 2U : 1U;
+        a = BaseArgs(H1, IN, B, 512, splits);
+        a.out_f32 = grad; a.ld_f32 = H1;
+        a.states = reinterpret_cast<const uint8_t*>(states); a.state_len = s.state_len; a.value_pad = s.state_value_pad; a.samples = B;
+        a.in_rows = 0xFFFFFFFFU;  // no all-ones row in this direction
+        if (a.splits > 1 && cudaMemsetAsync(grad, 0, (uint64_t)IN * H1 * sizeof(float), st) != cudaSuccess) return MGT_CUDA_FAILURE;
+        CUtensorMap ta;
+        MGT_MAP(e->Map(&ta, dz1_h, H1, B, ws.p_dz1, 64, 64));
+        MGT_TRY(LaunchGemm<CfgEmbGrad>(e, ta, ta, a, st));
+    }
+    MGT_TRY(notify(0, InputBias(s) + H1));
+    if (!timer.Mark(profile ? &profile->input_grad_ms : nullptr)) return MGT_CUDA_FAILURE;
+    return MGT_OK;
+}
+
+mgt_status_t mgt_debug_gemm(mgt_engine_t* e, const uint16_t* a, uint32_t lda, int32_t a_mn, const uint16_t* b, uint32_t ldb, int32_t b_mn,
+                            float* d, uint32_t m, uint32_t n, uint32_t k, uint32_t splits, float* partial_scratch, void* stream) {
+    if (e == nullptr || a == nullptr || b == nullptr || d == nullptr || m == 0 || n == 0 || k == 0 || splits == 0) return MGT_INVALID_CONFIG;
+    if (splits > 1 && partial_scratch == nullptr) return MGT_INVALID_CONFIG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    GemmArgs args = BaseArgs(m, n, k, 256, splits);
+    args.partial = args.splits > 1 ? partial_scratch : d;
+    CUtensorMap ta, tb;
+    const __half* ah = reinterpret_cast<const __half*>(a);
+    const __half* bh = reinterpret_cast<const __half*>(b);
+    if (a_mn) { MGT_MAP(e->Map(&ta, ah, m, k, lda, 64, 64)); } else { MGT_MAP(e->Map(&ta, ah, k, m, lda, 64, 128)); }
+    if (b_mn) { MGT_MAP(e->Map(&tb, bh, n, k, ldb, 64, 64)); } else { MGT_MAP(e->Map(&tb, bh, k, n, ldb, 64, 256)); }
+    mgt_status_t r;
+    if (a_mn && b_mn) r = LaunchGemm<CfgDw<256>>(e, ta, tb, args, st);
+    else if (a_mn) r = LaunchGemm<CfgDbgMK>(e, ta, tb, args, st);
+    else if (b_mn) r = LaunchGemm<CfgDbgKM>(e, ta, tb, args, st);
+    else r = LaunchGemm<CfgDbgKK>(e, ta, tb, args, st);
+    if (r != MGT_OK) return r;
+    if (args.splits > 1) {
+        ReducePartialsKernel<<<GridFor((uint64_t)m * n, 256, e->sm_count), 256, 0, st>>>(partial_scratch, args.splits, (uint64_t)m * n, d);
+        if (cudaGetLastError() != cudaSuccess) return MGT_CUDA_FAILURE;
+    }
+    return MGT_OK;
+}
+
+}  // extern "C"

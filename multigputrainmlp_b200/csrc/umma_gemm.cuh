@@ -1,0 +1,535 @@
+// Warp-specialised, persistent tcgen05 GEMM for sm_100a.
+//
+//   D[M x N] (fp32, TMEM) = A[M x K] * B[K x N]      fp16 operands, 128B-swizzled shared memory
+//
+// One CTA per SM. Warp 0 feeds operands with TMA (plain per-CTA loads, no multicast), warp 1
+// issues tcgen05.mma from one thread and owns TMEM, warps 2-5 drain the accumulator
+// (tcgen05.ld -> registers -> fused epilogue -> global), and, for the embedding layers, warps 6-9
+// synthesise the one-hot operand directly in shared memory from the 80-byte puzzle states, so the
+// one-hot matrix never exists in HBM.
+//
+// Operand forms
+//   A  K-major  : global [M][K] (K contiguous), one TMA box 64(K) x 128(M) per stage
+//   A  MN-major : global [K][M] (M contiguous), two TMA boxes 64(M) x 64(K) per stage
+//   B  K-major  : global [N][K] (K contiguous), one TMA box 64(K) x BN(N)
+//   B  MN-major : global [K][N] (N contiguous), ceil(BN/64) TMA boxes 64(N) x 64(K)
+//   B  one-hot  : K-major rows of 128 bytes written by the synth warps; only the (at most a few)
+//                 non-zero halfs of a row are set before the MMA and cleared after it.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include "ptx_sm100.cuh"
+
+namespace mgt {
+
+enum class BSource : int { kTmaK = 0, kTmaMN = 1, kOneHotFwd = 2, kOneHotGrad = 3 };
+
+enum class Epi : int {
+    kBiasReluF16 = 0,      // out_f16 = relu(acc + bias)
+    kBiasReluF32F16,       // out_f32 = out_f16 = relu(acc + bias)
+    kBiasResReluF32F16,    // v = relu(add + (acc + bias)); out_f32 = v (may alias add); out_f16 = v
+    kMaskF16,              // out_f16 = acc * [mask > 0]
+    kAddMaskF32F16,        // v = (acc + add) * [mask > 0]; out_f32 = v (may alias add); out_f16 = v
+    kPartialF32,           // partial[split][m][n] = acc
+    kEmbFwd,               // out_f16[n][m] = relu(acc)            (D is the transposed activation)
+    kEmbGrad,              // out_f32[n][m] (+)= acc               (D is the transposed gradient)
+};
+
+struct GemmArgs {
+    uint32_t M, N, K;
+    uint32_t m_tiles, n_tiles, splits, k_chunks;
+    const float* bias;
+    float* out_f32;
+    uint32_t ld_f32;
+    __half* out_f16;
+    uint32_t ld_f16;
+    const float* add_f32;
+    uint32_t ld_add;
+    const __half* mask;
+    uint32_t ld_mask;
+    float* partial;
+    // Optional fp32 column sums of the values the kMaskF16 / kAddMaskF32F16 epilogues produce
+    // (bias gradients): row (blockIdx.x * 4 + quad) of colsum[gridDim.x * 4][N] accumulates the
+    // rows this warp handled. The buffer must be zero before the launch.
+    float* colsum;
+    // one-hot operand synthesis
+    const uint8_t* states;   // [samples][80]
+    uint32_t state_len;      // positions per state
+    uint32_t value_pad;      // classes per position
+    uint32_t samples;
+    uint32_t in_rows;        // state_len * value_pad; row `in_rows` is the all-ones (bias) row
+    int* status;             // device status word, 0 = ok
+};
+
+template <int BN_, int NACC_, bool A_MN_, BSource BSRC_, Epi EPI_, int SA_, int SB_>
+struct GemmCfg {
+    static constexpr int BM = 128;
+    static constexpr int BK = 64;
+    static constexpr int BN = BN_;
+    static constexpr int NACC = NACC_;
+    static constexpr bool A_MN = A_MN_;
+    static constexpr BSource BSRC = BSRC_;
+    static constexpr Epi EPI = EPI_;
+    static constexpr int SA = SA_;
+    static constexpr int SB = SB_;
+    static constexpr bool kOneHot = (BSRC_ == BSource::kOneHotFwd || BSRC_ == BSource::kOneHotGrad);
+    static constexpr bool B_MN = (BSRC_ == BSource::kTmaMN);
+    static constexpr int N_GROUPS = (BN_ + 63) / 64;
+    static constexpr int A_STAGE_BYTES = BM * 128;
+    static constexpr int B_ACC_BYTES = B_MN ? N_GROUPS * 8192 : BN_ * 128;
+    static constexpr int B_STAGE_BYTES = NACC_ * B_ACC_BYTES;
+    static constexpr int ACC_BUFS = 2 / NACC_;
+    static constexpr int ACC_COLS = 256;  // TMEM columns reserved per accumulator
+    static constexpr int THREADS = kOneHot ? 320 : 192;
+    static constexpr int SMEM_BYTES = 1024 + SA_ * A_STAGE_BYTES + SB_ * B_STAGE_BYTES + 256;
+    static_assert(BN_ % 16 == 0 && BN_ >= 16 && BN_ <= 256, "UMMA N");
+    static_assert(BN_ % 32 == 0, "epilogue drains 32 columns at a time");
+    static_assert(NACC_ == 1 || NACC_ == 2, "one or two accumulators");
+    static_assert(B_ACC_BYTES % 1024 == 0, "swizzle atoms must stay 1024-byte aligned");
+    static_assert(!kOneHot || SB_ == 2, "the one-hot ring keeps a two-item history");
+    static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+};
+
+namespace detail {
+
+__device__ __forceinline__ void store_f16x32(__half* dst, const float (&v)[32], uint32_t valid, bool vec_ok) {
+    if (valid == 32 && vec_ok) {
+        uint4* p = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            __half2 h0 = __floats2half2_rn(v[q * 8 + 0], v[q * 8 + 1]);
+            __half2 h1 = __floats2half2_rn(v[q * 8 + 2], v[q * 8 + 3]);
+            __half2 h2 = __floats2half2_rn(v[q * 8 + 4], v[q * 8 + 5]);
+            __half2 h3 = __floats2half2_rn(v[q * 8 + 6], v[q * 8 + 7]);
+            uint4 u;
+            u.x = *reinterpret_cast<uint32_t*>(&h0);
+            u.y = *reinterpret_cast<uint32_t*>(&h1);
+            u.z = *reinterpret_cast<uint32_t*>(&h2);
+            u.w = *reinterpret_cast<uint32_t*>(&h3);
+            p[q] = u;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (static_cast<uint32_t>(j) < valid) dst[j] = __float2half_rn(v[j]);
+    }
+}
+
+__device__ __forceinline__ void store_f32x32(float* dst, const float (&v)[32], uint32_t valid, bool vec_ok) {
+    if (valid == 32 && vec_ok) {
+        float4* p = reinterpret_cast<float4*>(dst);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) p[q] = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (static_cast<uint32_t>(j) < valid) dst[j] = v[j];
+    }
+}
+
+__device__ __forceinline__ void load_f32x32(const float* src, float (&v)[32], uint32_t valid, bool vec_ok) {
+    if (valid == 32 && vec_ok) {
+        const float4* p = reinterpret_cast<const float4*>(src);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float4 f = p[q];
+            v[q * 4] = f.x;
+            v[q * 4 + 1] = f.y;
+            v[q * 4 + 2] = f.z;
+            v[q * 4 + 3] = f.w;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = static_cast<uint32_t>(j) < valid ? src[j] : 0.0f;
+    }
+}
+
+// positive-mask from fp16 activations: m[j] = src[j] > 0
+__device__ __forceinline__ uint32_t load_mask32(const __half* src, uint32_t valid, bool vec_ok) {
+    uint32_t bits = 0;
+    if (valid == 32 && vec_ok) {
+        const uint4* p = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint4 u = p[q];
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                // a positive non-zero half has sign 0 and a non-zero magnitude
+                const uint32_t lo = w[e] & 0xFFFFU, hi = w[e] >> 16;
+                if (lo != 0U && (lo & 0x8000U) == 0U) bits |= 1U << (q * 8 + e * 2);
+                if (hi != 0U && (hi & 0x8000U) == 0U) bits |= 1U << (q * 8 + e * 2 + 1);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (static_cast<uint32_t>(j) < valid && __half2float(src[j]) > 0.0f) bits |= 1U << j;
+    }
+    return bits;
+}
+
+// Sums v[j] over the 32 lanes of the warp for every j; lane l returns the total of column l.
+__device__ __forceinline__ float warp_column_sums(float (&v)[32], uint32_t lane) {
+#pragma unroll
+    for (int step = 16; step >= 1; step >>= 1) {
+        const bool upper = (lane & step) != 0U;
+#pragma unroll
+        for (int j = 0; j < step; ++j) {
+            const float send = upper ? v[j] : v[j + step];
+            const float recv = __shfl_xor_sync(0xFFFFFFFFU, send, step);
+            v[j] = (upper ? v[j + step] : v[j]) + recv;
+        }
+    }
+    return v[0];
+}
+
+}  // namespace detail
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmArgs args) {
+    using namespace ptx;
+    constexpr int BM = Cfg::BM, BN = Cfg::BN, NACC = Cfg::NACC, SA = Cfg::SA, SB = Cfg::SB;
+    constexpr int ACC_BUFS = Cfg::ACC_BUFS;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t pad = ((raw_addr + 1023U) & ~1023U) - raw_addr;
+    uint8_t* smem = smem_raw + pad;
+    uint8_t* a_ring = smem;
+    uint8_t* b_ring = smem + SA * Cfg::A_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(b_ring + SB * Cfg::B_STAGE_BYTES);
+    uint64_t* full_a = bars;
+    uint64_t* empty_a = full_a + SA;
+    uint64_t* full_b = empty_a + SA;
+    uint64_t* empty_b = full_b + SB;
+    uint64_t* acc_full = empty_b + SB;
+    uint64_t* acc_empty = acc_full + ACC_BUFS;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + ACC_BUFS);
+    volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31U;
+    const uint32_t total_units = args.m_tiles * args.n_tiles * args.splits;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < SA; ++s) {
+            mbar_init(&full_a[s], 1);
+            mbar_init(&empty_a[s], 1);
+        }
+        for (int s = 0; s < SB; ++s) {
+            mbar_init(&full_b[s], Cfg::kOneHot ? 4 : 1);
+            mbar_init(&empty_b[s], 1);
+        }
+        for (int s = 0; s < ACC_BUFS; ++s) {
+            mbar_init(&acc_full[s], 1);
+            mbar_init(&acc_empty[s], 128);
+        }
+        *cta_abort = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&tma_a);
+        if (!Cfg::kOneHot) prefetch_tensormap(&tma_b);
+    }
+    if (Cfg::kOneHot) {
+        // the one-hot ring starts as all zeros; afterwards only single halfs are set and cleared
+        uint4* z = reinterpret_cast<uint4*>(b_ring);
+        for (uint32_t i = threadIdx.x; i < SB * Cfg::B_STAGE_BYTES / 16; i += Cfg::THREADS) z[i] = make_uint4(0, 0, 0, 0);
+        fence_proxy_async_smem();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_holder, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    // unit -> (m tile, n tile, split): splits of one tile are neighbours for TMA-fed GEMMs; for the
+    // embedding layers units that share the A stream (same m tile and split) are neighbours.
+    auto decode = [&](uint32_t unit, uint32_t& mt, uint32_t& nt, uint32_t& sp) {
+        if (Cfg::kOneHot) {
+            nt = unit % args.n_tiles;
+            const uint32_t rest = unit / args.n_tiles;
+            sp = rest % args.splits;
+            mt = rest / args.splits;
+        } else {
+            sp = unit % args.splits;
+            const uint32_t rest = unit / args.splits;
+            nt = rest % args.n_tiles;
+            mt = rest / args.n_tiles;
+        }
+    };
+    auto chunk_begin = [&](uint32_t sp) { return static_cast<uint32_t>((static_cast<uint64_t>(sp) * args.k_chunks) / args.splits); };
+
+    if (warp == 0) {
+        // ------------------------------- TMA producer -------------------------------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+                uint32_t mt, nt, sp;
+                decode(unit, mt, nt, sp);
+                const uint32_t c0 = chunk_begin(sp), c1 = chunk_begin(sp + 1);
+                for (uint32_t c = c0; c < c1; ++c, ++it) {
+                    const uint32_t sa = it % SA, pa = (it / SA) & 1U;
+                    if (!mbar_wait(&empty_a[sa], pa ^ 1U, cta_abort, kAbortProducerWait)) { ok = false; break; }
+                    uint8_t* a_dst = a_ring + sa * Cfg::A_STAGE_BYTES;
+                    mbar_arrive_expect_tx(&full_a[sa], Cfg::A_STAGE_BYTES);
+                    if (Cfg::A_MN) {
+                        tma_load_2d(a_dst, &tma_a, static_cast<int32_t>(mt * BM), static_cast<int32_t>(c * 64), &full_a[sa]);
+                        tma_load_2d(a_dst + 8192, &tma_a, static_cast<int32_t>(mt * BM + 64), static_cast<int32_t>(c * 64), &full_a[sa]);
+                    } else {
+                        tma_load_2d(a_dst, &tma_a, static_cast<int32_t>(c * 64), static_cast<int32_t>(mt * BM), &full_a[sa]);
+                    }
+                    if (!Cfg::kOneHot) {
+                        const uint32_t sb = it % SB, pb = (it / SB) & 1U;
+                        if (!mbar_wait(&empty_b[sb], pb ^ 1U, cta_abort, kAbortProducerWait)) { ok = false; break; }
+                        uint8_t* b_dst = b_ring + sb * Cfg::B_STAGE_BYTES;
+                        mbar_arrive_expect_tx(&full_b[sb], Cfg::B_STAGE_BYTES);
+#pragma unroll
+                        for (int acc = 0; acc < NACC; ++acc) {
+                            const uint32_t n0 = (nt * NACC + acc) * BN;
+                            if (Cfg::B_MN) {
+#pragma unroll
+                                for (int g = 0; g < Cfg::N_GROUPS; ++g)
+                                    tma_load_2d(b_dst + acc * Cfg::B_ACC_BYTES + g * 8192, &tma_b, static_cast<int32_t>(n0 + g * 64),
+                                                static_cast<int32_t>(c * 64), &full_b[sb]);
+                            } else {
+                                tma_load_2d(b_dst + acc * Cfg::B_ACC_BYTES, &tma_b, static_cast<int32_t>(c * 64), static_cast<int32_t>(n0), &full_b[sb]);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------- UMMA issuer --------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_f16(BM, BN, Cfg::A_MN, Cfg::B_MN);
+            uint32_t it = 0, unit_iter = 0;
+            bool ok = true;
+            for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++unit_iter) {
+                uint32_t mt, nt, sp;
+                decode(unit, mt, nt, sp);
+                const uint32_t c0 = chunk_begin(sp), c1 = chunk_begin(sp + 1);
+                const uint32_t ab = unit_iter % ACC_BUFS, aph = (unit_iter / ACC_BUFS) & 1U;
+                if (!mbar_wait(&acc_empty[ab], aph ^ 1U, cta_abort, kAbortMmaWait)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_base = tmem_base + ab * (NACC * Cfg::ACC_COLS);
+                for (uint32_t c = c0; c < c1; ++c, ++it) {
+                    const uint32_t sa = it % SA, pa = (it / SA) & 1U;
+                    const uint32_t sb = it % SB, pb = (it / SB) & 1U;
+                    if (!mbar_wait(&full_a[sa], pa, cta_abort, kAbortMmaWait)) { ok = false; break; }
+                    if (!mbar_wait(&full_b[sb], pb, cta_abort, kAbortMmaWait)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(a_ring + sa * Cfg::A_STAGE_BYTES);
+                    const uint32_t b_addr = smem_u32(b_ring + sb * Cfg::B_STAGE_BYTES);
+                    const uint32_t k_left = args.K - c * 64U;
+                    const uint32_t ksteps = k_left >= 64U ? 4U : (k_left + 15U) / 16U;
+#pragma unroll
+                    for (int acc = 0; acc < NACC; ++acc) {
+                        for (uint32_t kk = 0; kk < ksteps; ++kk) {
+                            const uint64_t a_desc = Cfg::A_MN ? make_smem_desc(a_addr + kk * 2048U, 8192U, 1024U)
+                                                              : make_smem_desc(a_addr + kk * 32U, 16U, 1024U);
+                            const uint64_t b_desc = Cfg::B_MN ? make_smem_desc(b_addr + acc * Cfg::B_ACC_BYTES + kk * 2048U, 8192U, 1024U)
+                                                              : make_smem_desc(b_addr + acc * Cfg::B_ACC_BYTES + kk * 32U, 16U, 1024U);
+                            umma_f16(d_base + acc * Cfg::ACC_COLS, a_desc, b_desc, idesc, (c > c0 || kk > 0U) ? 1U : 0U);
+                        }
+                    }
+                    umma_commit(&empty_a[sa]);
+                    umma_commit(&empty_b[sb]);
+                }
+                if (ok) umma_commit(&acc_full[ab]);
+            }
+        }
+        __syncwarp();
+    } else if (warp < 6) {
+        // ------------------------------- epilogue -----------------------------------------
+        const uint32_t quad = warp & 3U;  // TMEM lanes [32*quad, 32*quad+32) belong to this warp
+        uint32_t unit_iter = 0;
+        bool ok = true;
+        for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++unit_iter) {
+            uint32_t mt, nt, sp;
+            decode(unit, mt, nt, sp);
+            const uint32_t ab = unit_iter % ACC_BUFS, aph = (unit_iter / ACC_BUFS) & 1U;
+            // the TMEM loads below are warp-collective, so the whole warp takes the same way out
+            if (!__all_sync(0xFFFFFFFFU, mbar_wait(&acc_full[ab], aph, cta_abort, kAbortEpilogueWait))) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t m = mt * BM + quad * 32U + lane;
+            const bool m_ok = m < args.M;
+#pragma unroll 1
+            for (int acc = 0; acc < NACC; ++acc) {
+#pragma unroll 1
+                for (int cc = 0; cc < BN / 32; ++cc) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((quad * 32U) << 16) + ab * (NACC * Cfg::ACC_COLS) + acc * Cfg::ACC_COLS + cc * 32, r);
+                    tmem_ld_wait();
+                    const uint32_t n0 = (nt * NACC + acc) * BN + cc * 32;
+                    if (n0 >= args.N) continue;
+                    const uint32_t valid = min(32U, args.N - n0);
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+
+                    if constexpr (Cfg::EPI == Epi::kEmbFwd) {
+                        if (m_ok) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (static_cast<uint32_t>(j) < valid)
+                                    args.out_f16[static_cast<uint64_t>(n0 + j) * args.ld_f16 + m] = __float2half_rn(fmaxf(v[j], 0.0f));
+                        }
+                    } else if constexpr (Cfg::EPI == Epi::kEmbGrad) {
+                        if (m_ok) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (static_cast<uint32_t>(j) < valid) {
+                                    float* dst = args.out_f32 + static_cast<uint64_t>(n0 + j) * args.ld_f32 + m;
+                                    if (args.splits > 1U) atomicAdd(dst, v[j]); else *dst = v[j];
+                                }
+                        }
+                    } else if constexpr (Cfg::EPI == Epi::kPartialF32) {
+                        if (m_ok) {
+                            float* dst = args.partial + (static_cast<uint64_t>(sp) * args.M + m) * args.N + n0;
+                            detail::store_f32x32(dst, v, valid, (args.N & 3U) == 0U);
+                        }
+                    } else {
+                        if (m_ok) {
+                            if constexpr (Cfg::EPI == Epi::kBiasReluF16 || Cfg::EPI == Epi::kBiasReluF32F16 || Cfg::EPI == Epi::kBiasResReluF32F16) {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j)
+                                    if (static_cast<uint32_t>(j) < valid) v[j] += __ldg(args.bias + n0 + j);
+                            }
+                            if constexpr (Cfg::EPI == Epi::kBiasResReluF32F16 || Cfg::EPI == Epi::kAddMaskF32F16) {
+                                float a[32];
+                                detail::load_f32x32(args.add_f32 + static_cast<uint64_t>(m) * args.ld_add + n0, a, valid, (args.ld_add & 3U) == 0U);
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) v[j] = a[j] + v[j];
+                            }
+                            if constexpr (Cfg::EPI == Epi::kMaskF16 || Cfg::EPI == Epi::kAddMaskF32F16) {
+                                const uint32_t bits = detail::load_mask32(args.mask + static_cast<uint64_t>(m) * args.ld_mask + n0, valid, (args.ld_mask & 7U) == 0U);
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) v[j] = ((bits >> j) & 1U) ? v[j] : 0.0f;
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+                            }
+                            if constexpr (Cfg::EPI == Epi::kBiasReluF32F16 || Cfg::EPI == Epi::kBiasResReluF32F16 || Cfg::EPI == Epi::kAddMaskF32F16)
+                                detail::store_f32x32(args.out_f32 + static_cast<uint64_t>(m) * args.ld_f32 + n0, v, valid, (args.ld_f32 & 3U) == 0U);
+                            detail::store_f16x32(args.out_f16 + static_cast<uint64_t>(m) * args.ld_f16 + n0, v, valid, (args.ld_f16 & 7U) == 0U);
+                        }
+                        if constexpr (Cfg::EPI == Epi::kMaskF16 || Cfg::EPI == Epi::kAddMaskF32F16) {
+                            if (args.colsum != nullptr) {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j)
+                                    if (!m_ok || static_cast<uint32_t>(j) >= valid) v[j] = 0.0f;
+                                const float total = detail::warp_column_sums(v, lane);
+                                if (lane < valid) {
+                                    float* dst = args.colsum + (static_cast<uint64_t>(blockIdx.x) * 4U + quad) * args.N + n0 + lane;
+                                    *dst += total;  // this warp is the only writer of its row
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&acc_empty[ab]);
+        }
+    } else {
+        // ------------------------------- one-hot synthesis --------------------------------
+        if constexpr (Cfg::kOneHot) {
+            const uint32_t t = threadIdx.x - 192U;  // 0..127
+            const uint32_t V = args.value_pad, L = args.state_len, IN = args.in_rows;
+            constexpr uint32_t ROWS = NACC * BN;  // rows of the synthesised operand per stage
+            // writes `value` (fp16 1.0 or 0) at the non-zero places of item (nt, c) in stage buffer `buf`
+            auto apply = [&](uint8_t* buf, uint32_t nt, uint32_t c, uint16_t value) {
+                if constexpr (Cfg::BSRC == BSource::kOneHotFwd) {
+                    // rows = samples, K = input rows [64c, 64c+64)
+                    const uint32_t k0 = c * 64U;
+                    const uint32_t p_lo = k0 / V;
+                    const uint32_t p_hi = min((k0 + 63U) / V, L - 1U);
+                    for (uint32_t n = t; n < ROWS; n += 128U) {
+                        const uint32_t sample = nt * ROWS + n;
+                        if (sample >= args.samples) continue;
+                        uint8_t* row = buf + (n / BN) * Cfg::B_ACC_BYTES + (n % BN) * 128U;
+                        const uint8_t* st = args.states + static_cast<uint64_t>(sample) * 80U;
+                        if (p_lo < L) {
+                            for (uint32_t p = p_lo; p <= p_hi; ++p) {
+                                const uint32_t k = p * V + st[p] - k0;
+                                if (k < 64U) *reinterpret_cast<uint16_t*>(row + ((((k >> 3) ^ (n & 7U)) << 4) | ((k & 7U) << 1))) = value;
+                            }
+                        }
+                        const uint32_t kb = IN - k0;  // the all-ones column that multiplies the bias row
+                        if (kb < 64U) *reinterpret_cast<uint16_t*>(row + ((((kb >> 3) ^ (n & 7U)) << 4) | ((kb & 7U) << 1))) = value;
+                    }
+                } else {
+                    // rows = input rows [r0, r0+ROWS), K = samples [64c, 64c+64)
+                    const uint32_t r0 = nt * ROWS;
+                    const uint32_t k = t & 63U;
+                    const uint32_t sample = c * 64U + k;
+                    if (sample < args.samples) {
+                        const uint8_t* st = args.states + static_cast<uint64_t>(sample) * 80U;
+                        const uint32_t p_lo = r0 / V;
+                        const uint32_t p_hi = min((r0 + ROWS - 1U) / V, L - 1U);
+                        if (p_lo < L) {
+                            for (uint32_t p = p_lo + (t >> 6); p <= p_hi; p += 2U) {
+                                const uint32_t n = p * V + st[p] - r0;
+                                if (n < ROWS) {
+                                    uint8_t* row = buf + (n / BN) * Cfg::B_ACC_BYTES + (n % BN) * 128U;
+                                    *reinterpret_cast<uint16_t*>(row + ((((k >> 3) ^ (n & 7U)) << 4) | ((k & 7U) << 1))) = value;
+                                }
+                            }
+                        }
+                        const uint32_t nb = IN - r0;  // bias-gradient row: every sample contributes
+                        if ((t >> 6) == 0U && nb < ROWS) {
+                            uint8_t* row = buf + (nb / BN) * Cfg::B_ACC_BYTES + (nb % BN) * 128U;
+                            *reinterpret_cast<uint16_t*>(row + ((((k >> 3) ^ (nb & 7U)) << 4) | ((k & 7U) << 1))) = value;
+                        }
+                    }
+                }
+            };
+            uint32_t it = 0;
+            uint32_t h_nt[2] = {0, 0}, h_c[2] = {0, 0};  // what each of the two stages currently holds
+            bool ok = true;
+            for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+                uint32_t mt, nt, sp;
+                decode(unit, mt, nt, sp);
+                const uint32_t c0 = chunk_begin(sp), c1 = chunk_begin(sp + 1);
+                for (uint32_t c = c0; c < c1; ++c, ++it) {
+                    const uint32_t sb = it & 1U, pb = (it >> 1) & 1U;
+                    // all 128 synth threads agree on the outcome before they meet at the next barrier
+                    if (!named_bar_and(1, 128, mbar_wait(&empty_b[sb], pb ^ 1U, cta_abort, kAbortSynthWait))) { ok = false; break; }
+                    uint8_t* buf = b_ring + sb * Cfg::B_STAGE_BYTES;
+                    if (it >= 2U) apply(buf, sb ? h_nt[1] : h_nt[0], sb ? h_c[1] : h_c[0], 0);
+                    named_bar_sync(1, 128);  // a place cleared by one thread may be set by another
+                    apply(buf, nt, c, 0x3C00);
+                    if (sb) { h_nt[1] = nt; h_c[1] = c; } else { h_nt[0] = nt; h_c[0] = c; }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&full_b[sb]);
+                }
+            }
+        }
+    }
+
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*cta_abort != 0) {
+        // give copies that are still in flight time to land before the CTA's memory is released
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+        if (threadIdx.x == 0 && args.status != nullptr) atomicCAS(args.status, 0, *cta_abort);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+}  // namespace mgt

@@ -1,0 +1,135 @@
+"""GPU parity of the loss+gradient engine (forward, loss, backward) against the CPU oracle's
+restatement of the reference's fp16 data flow, through the C ABI."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+if not torch.cuda.is_available():
+    pytest.skip("needs a CUDA device", allow_module_level=True)
+
+import multigputrainmlp_b200 as mgt  # noqa: E402
+from helpers import compare_case_inputs, mixed_case_inputs, rel_l2, trainer_init_weights  # noqa: E402
+from oracle import MlpShape  # noqa: E402
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def engine():
+    e = mgt.Engine(0)
+    yield e
+    e.close()
+
+
+def run_engine(engine, shape: MlpShape, w, states, labels, persistent_mirror=True, callback=None, profile=None):
+    cshape = mgt.CudaMlpShape(shape.state_len, shape.state_value_pad, shape.hd1, shape.hd2, shape.residual_blocks, shape.output_dim)
+    b = states.shape[0]
+    dw = torch.from_numpy(w).to(DEV)
+    dh = dw.half() if persistent_mirror else None
+    ds = torch.from_numpy(states).to(DEV)
+    dl = torch.from_numpy(np.ascontiguousarray(labels)).to(DEV)
+    loss = torch.zeros(1, device=DEV)
+    grad = torch.full((shape.param_count,), float("nan"), device=DEV)
+    floats = mgt.mlp_loss_grad_workspace_floats(cshape, b)
+    assert floats > 0
+    ws = torch.empty(floats, device=DEV)
+    ws.fill_(float("nan"))  # the engine must not depend on the workspace's previous contents
+    st = engine.launch_mlp_loss_grad(cshape, dw, dh, ds, dl, b, loss, grad, ws, floats, gradient_ready=callback, profile=profile)
+    assert st == 0, mgt.status_name(st)
+    st, code = engine.check()
+    assert st == 0, f"device status {code}"
+    return float(loss.item()), grad.cpu().numpy()
+
+
+def check_against_oracle(oracle, engine, shape, w, states, labels, tol=1e-3, **kw):
+    st, loss_o, grad_o = oracle.loss_grad_mixed(shape, w, states, labels)
+    assert st == 0
+    loss_g, grad_g = run_engine(engine, shape, w, states, labels, **kw)
+    assert np.isfinite(grad_g).all()
+    # tolerance of the headline metric: per-step loss and gradients within 1e-3 relative (norm-wise)
+    assert abs(loss_g - loss_o) <= tol * max(abs(loss_o), 1e-6), (loss_g, loss_o)
+    assert rel_l2(grad_g, grad_o) <= tol, rel_l2(grad_g, grad_o)
+    # per-section check so that a small block cannot hide behind the embedding table
+    in_w = shape.state_len * shape.state_value_pad * shape.hd1
+    sections = {"embedding": (0, in_w), "input_bias": (in_w, in_w + shape.hd1),
+                "hidden": (in_w + shape.hd1, in_w + shape.hd1 + shape.hd1 * shape.hd2 + shape.hd2),
+                "tail": (in_w + shape.hd1 + shape.hd1 * shape.hd2 + shape.hd2, shape.param_count)}
+    for name, (lo, hi) in sections.items():
+        if np.abs(grad_o[lo:hi]).max() > 0:
+            assert rel_l2(grad_g[lo:hi], grad_o[lo:hi]) <= 3 * tol, (name, rel_l2(grad_g[lo:hi], grad_o[lo:hi]))
+    return loss_g, grad_g, loss_o, grad_o
+
+
+@pytest.mark.parametrize("dims,n", [((8, 8, 16, 16, 2, 1), 32), ((8, 8, 16, 16, 2, 3), 32), ((8, 8, 16, 16, 2, 17), 32), ((5, 8, 8, 8, 1, 128), 16)])
+def test_reference_mixed_precision_cases(oracle, engine, dims, n):
+    # shapes and inputs of native/tests/cuda/test_cuda_mlp_backward_mixed_precision_error.cu
+    shape = MlpShape(*dims)
+    w, s, l = mixed_case_inputs(shape, n)
+    loss_g, grad_g, _, _ = check_against_oracle(oracle, engine, shape, w, s, l)
+    # and the reference's own envelope against the true-fp32 CPU reference
+    _, loss_ref, grad_ref = oracle.loss_grad(shape, w, s, l)
+    assert abs(loss_ref - loss_g) <= 2e-3 + 2e-2 * max(abs(loss_ref), abs(loss_g))
+    assert rel_l2(grad_g, grad_ref) <= 8e-2 and np.abs(grad_g - grad_ref).max() <= 2e-2
+
+
+@pytest.mark.parametrize("dims,n", [((4, 8, 5, 3, 1, 1), 8), ((4, 8, 5, 3, 1, 3), 8), ((6, 8, 9, 7, 2, 11), 10), ((72, 72, 40, 24, 0, 1), 300)])
+def test_odd_shapes_and_no_mirror(oracle, engine, dims, n):
+    # unaligned hidden sizes (the reference's cpu-compare shapes) go through the padded fp16 weight copy
+    shape = MlpShape(*dims)
+    w, s, l = compare_case_inputs(shape, n)
+    check_against_oracle(oracle, engine, shape, w, s, l, persistent_mirror=False)
+
+
+def test_walk_batch_medium_model(oracle, engine):
+    moves, target = oracle.cyclic_puzzle(72, 18)
+    _, states, labels, _ = oracle.random_walks(moves, target, seed=1234, epoch=0, step=0, rank=0, k_min=1, k_max=29, samples=700)
+    shape = MlpShape(72, 72, 256, 64, 2, 1)
+    rng = np.random.default_rng(1)
+    w = (rng.standard_normal(shape.param_count) * 0.03).astype(np.float32)
+    order = []
+    def cb(user, ready_id, off, count, stream):
+        order.append((ready_id, off, count))
+        return 0
+    check_against_oracle(oracle, engine, shape, w, states, labels.reshape(-1, 1), callback=cb)
+    # gradient-ready notifications: native/cuda/mlp_backward.cu:1364,1385,1402,1427,1506
+    h1, h2, r = 256, 64, 2
+    in_w = 72 * 72 * h1
+    hidden = in_w + h1
+    rbase = hidden + h1 * h2 + h2
+    blk = 2 * (h2 * h2 + h2)
+    want = [(0, rbase + r * blk, h2 + 1)]
+    for k in (1, 0):
+        want.append((len(want), rbase + k * blk + h2 * h2 + h2, h2 * h2 + h2))
+        want.append((len(want), rbase + k * blk, h2 * h2 + h2))
+    want.append((len(want), hidden, h1 * h2 + h2))
+    want.append((len(want), 0, in_w + h1))
+    assert order == want
+
+
+def test_trainer_init_weights_first_step(oracle, engine):
+    # the trainer's deterministic initial weights (tool:648-650) on a walk batch, physical dims of a padded model
+    moves, target = oracle.cyclic_puzzle(72, 18)
+    _, states, labels, _ = oracle.random_walks(moves, target, seed=1234, epoch=0, step=0, rank=0, k_min=1, k_max=29, samples=384)
+    shape = MlpShape(72, 72, 128, 32, 3, 1)
+    w = trainer_init_weights(shape.param_count)
+    prof = mgt.BackwardProfile()
+    check_against_oracle(oracle, engine, shape, w, states, labels.reshape(-1, 1), profile=prof)
+    assert prof.input_forward_ms > 0 and prof.input_grad_ms > 0
+
+
+def test_argument_errors(engine):
+    cshape = mgt.CudaMlpShape(8, 8, 16, 16, 2, 1)
+    t = torch.zeros(4096, device=DEV)
+    floats = mgt.mlp_loss_grad_workspace_floats(cshape, 32)
+    big = torch.zeros(floats, device=DEV)
+    st8 = torch.zeros(32, 80, dtype=torch.uint8, device=DEV)
+    args = (cshape, t, None, st8, t, 32, t, t)
+    assert engine.launch_mlp_loss_grad(*args, big, floats - 1) == 3                      # capacity_exceeded (mlp_backward.cu:1256)
+    assert engine.launch_mlp_loss_grad(*args, big, floats, input_grad_partial_chunks=0) == 1
+    assert engine.launch_mlp_loss_grad(*args, big, floats, input_grad_positions_per_block=0) == 1
+    assert engine.launch_mlp_loss_grad(cshape, None, None, st8, t, 32, t, t, big, floats) == 1
+    assert engine.launch_mlp_loss_grad(mgt.CudaMlpShape(8, 8, 5000, 16, 2, 1), t, None, st8, t, 32, t, t, big, floats) == 1  # hd1 > 4096
+    assert mgt.mlp_loss_grad_workspace_floats(mgt.CudaMlpShape(73, 8, 16, 16, 2, 1), 32) == 0
+    assert mgt.validate_cuda_mlp_shape(mgt.CudaMlpShape(72, 72, 4096, 512, 32, 29)) == 0
