@@ -1,0 +1,370 @@
+#!/usr/bin/env python
+"""Headline benchmark: training candidates/s of the full p888 training step on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is exactly what the reference trainer times between its step_start and step_stop events
+(native/tools/mgt_native_train_smoke.cu:769-846): on-GPU random-walk generation -> forward, MSE
+loss, backward -> gradient average over ranks -> AdamW with fp16 mirror. Configuration: physical
+p888 model (state 72x72, hd1 2556->2560, hd2 218->224, 16 residual blocks, output 1), batch
+53 248 per rank, fp16 linears with fp32 accumulate and fp32 master weights, seed 1234, the
+trainer's built-in cyclic-shift puzzle and deterministic initial weights (synthetic data: the
+training set is generated on the fly, there is no dataset).
+
+One process per GPU (torchrun sets RANK/LOCAL_RANK/WORLD_SIZE). Rank 0 prints ONE JSON line.
+`--impl reference` times the reference's own CPU implementation of the same step on the host
+cores instead (rank 0 only), on a bounded sample of the batch.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+METRIC = "training candidates/sec (device-timed, max over ranks)"
+UNIT = "candidates/s"
+P888 = dict(state_len=72, state_value_pad=72, hd1=2560, hd2=224, residual_blocks=16, output_dim=1)
+BATCH = 53248
+SEED = 1234
+LR = 1e-4
+FLOP_PER_CANDIDATE = 13_444_416          # 3*(2*H1*H2 + 4R*H2^2 + 2*H2*OUT) + 2*L*H1 at the physical dims
+EMB_ALGO_FLOP_PER_CANDIDATE = 72 * 2560   # the embedding forward counted as the sparse work it is (72 row adds)
+EMB_EXEC_FLOP_PER_CANDIDATE = 2 * (72 * 72 + 1) * 2560  # what the one-hot GEMM executes on the tensor cores
+
+
+def workload_config(n_gpus: int) -> dict:
+    return {
+        "workload": "p888 training step: walk gen -> fwd/loss/bwd -> grad average -> AdamW (BASELINE config %d)" % (1 if n_gpus == 1 else 2),
+        "batch_per_rank": BATCH, "global_batch": BATCH * n_gpus, "hd1": 2556, "physical_hd1": 2560, "hd2": 218,
+        "physical_hd2": 224, "nrd": 16, "output_dim": 1, "k_min": 1, "k_max": 29, "seed": SEED,
+        "precision": "fp16 operands, fp32 accumulate, fp32 master weights", "parallelism": "dp%d" % n_gpus,
+        "l2": "inputs larger than L2 (1.5 GB activation tape per step, 126 MB L2)",
+    }
+
+
+def load_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "tflops_burst": p["bf16_tflops"], "tflops_sustained": p["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops_burst": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self, t0: float, t1: float) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ts, line in self.rows:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                smax = float(parts[1])
+                if t0 - 0.05 <= ts <= t1 + 0.05:
+                    sm.append(float(parts[0]))
+                    for name, val in zip(names, parts[3:7]):
+                        if val.lower().startswith("active"):
+                            reasons.add(name)
+            except ValueError:
+                continue
+        if not sm:  # very short regions: take what was seen
+            for ts, line in self.rows[-3:]:
+                parts = [x.strip() for x in line.split(",")]
+                try:
+                    sm.append(float(parts[0]))
+                except (ValueError, IndexError):
+                    pass
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+def run_reference_cpu(args, steps: int, warmup: int) -> dict:
+    """The reference's own CPU path (GenerateRandomWalksCpu + CpuMlpLossAndGrad + CpuAdamWStep) on the
+    host cores. Its code is single-threaded, so the harness runs one sample slice per core with its
+    own gradient buffer, as a data-parallel CPU run would."""
+    from oracle import MlpShape, load_oracle, load_reference
+
+    ref = load_reference()
+    orc = load_oracle()
+    kind = "reference" if ref is not None else "port"
+    impl = ref if ref is not None else orc
+    shape = MlpShape(**P888)
+    params = shape.param_count
+    cores = min(os.cpu_count() or 1, 64)  # one 62 MB gradient buffer per thread: bounded on purpose
+    per_core = args.cpu_samples_per_core
+    idx = np.arange(params, dtype=np.int64)
+    weights = ((idx % 29 - 14) * 0.0001).astype(np.float64).astype(np.float32)
+    moves, target = orc.cyclic_puzzle(72, 18)
+    grads = [np.zeros(params, np.float32) for _ in range(cores)]
+    m = np.zeros(params, np.float32)
+    v = np.zeros(params, np.float32)
+    sample = cores * per_core
+
+    def one_step(step: int) -> float:
+        t0 = time.perf_counter()
+        st, states, labels, _ = impl.random_walks(moves, target, seed=SEED, epoch=0, step=step, rank=0, k_min=1, k_max=29, samples=sample)
+        assert st == 0
+        out = [None] * cores
+
+        def work(c):
+            lo = c * per_core
+            out[c] = impl.loss_grad(shape, weights, states[lo:lo + per_core], labels[lo:lo + per_core].reshape(-1, 1))
+            grads[c][:] = out[c][2]
+
+        threads = [threading.Thread(target=work, args=(c,)) for c in range(cores)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        total = grads[0].copy()
+        for c in range(1, cores):
+            total += grads[c]
+        total *= 1.0 / cores
+        t_grad = time.perf_counter() - t0
+        t1 = time.perf_counter()
+        impl.adamw(weights, total, m, v, step=step + 1, lr=LR)
+        t_adam = time.perf_counter() - t1
+        # the optimizer runs once per full batch: charge the sample its share of that cost
+        return t_grad + t_adam * (sample / BATCH)
+
+    for s in range(warmup):
+        one_step(s)
+    times = [one_step(warmup + s) for s in range(steps)]
+    sec = float(np.mean(times))
+    value = sample / sec
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": workload_config(max(1, args.gpus)),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind,
+                         "sample": f"{sample} samples of the batch per step ({per_core} per core, {cores} threads), optimizer cost scaled by {sample}/{BATCH}"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    return line
+
+
+# ------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=BATCH, help=argparse.SUPPRESS)  # smaller batches are for ncu captures only
+    ap.add_argument("--cpu-samples-per-core", type=int, default=384)
+    ap.add_argument("--steps-cpu", type=int, default=2)
+    ap.add_argument("--warmup-cpu", type=int, default=1)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps(run_reference_cpu(args, args.steps, args.warmup)), flush=True)
+        return
+
+    import torch
+    import multigputrainmlp_b200 as mgt
+    from oracle import load_oracle
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    batch = args.batch
+    shape = mgt.CudaMlpShape(**P888)
+    params = shape.param_count
+    idx = np.arange(params, dtype=np.int64)
+    w_host = ((idx % 29 - 14) * 0.0001).astype(np.float64).astype(np.float32)  # tool:648-650
+    w = torch.from_numpy(w_host).to(dev)
+    w_half = w.half()
+    m = torch.zeros(params, device=dev)
+    v = torch.zeros(params, device=dev)
+    grad = torch.zeros(params, device=dev)
+    loss = torch.zeros(1, device=dev)
+    orc = load_oracle()
+    moves_h, target_h = orc.cyclic_puzzle(72, 18)
+    puzzle_pinned = torch.from_numpy(np.concatenate([moves_h.reshape(-1), target_h.reshape(-1)])).pin_memory()
+    puzzle_dev = torch.empty_like(puzzle_pinned, device=dev)
+    puzzle_dev.copy_(puzzle_pinned)
+    moves_d = puzzle_dev[: 18 * 80]
+    target_d = puzzle_dev[18 * 80:]
+    states = torch.zeros(batch, 80, dtype=torch.uint8, device=dev)
+    labels = torch.zeros(batch, device=dev)
+    meta = torch.zeros(batch, 16, dtype=torch.uint8, device=dev)
+    ws_floats = mgt.mlp_loss_grad_workspace_floats(shape, batch)
+    workspace = torch.empty(ws_floats, device=dev)
+    engine = mgt.Engine(local_rank)
+    walk_cfg = mgt.RandomWalkKernelConfig(batch, 1, 29)
+    comm = None
+    if world > 1:
+        from multigputrainmlp_b200.comm import GradientComm
+        comm = GradientComm(engine, grad, rank, world, dev)
+    loss_pinned = torch.zeros(1).pin_memory()
+    other_launches = 0
+
+    def step(s: int, profile=None):
+        nonlocal other_launches
+        st = mgt.launch_random_walk_kernel(walk_cfg, SEED, 0, s, rank, moves_d, target_d, states, labels, meta)
+        assert st == 0, st
+        st = engine.launch_mlp_loss_grad(shape, w, w_half, states, labels, batch, loss, grad, workspace, ws_floats,
+                                         profile=profile, input_grad_position_tile=36)
+        assert st == 0, mgt.status_name(st)
+        cfg = mgt.AdamWKernelConfig(params, s + 1, LR)
+        if comm is not None:
+            comm.average_and_adamw(cfg, w, w_half, m, v)
+        else:
+            st = mgt.launch_adamw_kernel_with_half_mirror(cfg, w, w_half, grad, m, v)
+            assert st == 0, st
+        other_launches += 2
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for s in range(args.warmup):
+        step(s)
+    barrier()
+    st, code = engine.check()
+    assert st == 0, f"device status {code}"
+
+    # ---- device-timed region: K steps, resident inputs --------------------------------------
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler is not None:
+        time.sleep(0.3)
+    launches0 = engine.launch_count + other_launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_wall0 = time.time()
+    e0.record()
+    for s in range(args.steps):
+        step(args.warmup + s)
+    e1.record()
+    barrier()
+    t_wall1 = time.time()
+    ms_total = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(ms_total, op=dist.ReduceOp.MAX)
+    ms_step = float(ms_total.item()) / args.steps
+    launches = engine.launch_count + other_launches - launches0
+    clocks = sampler.stop(t_wall0, t_wall1) if sampler is not None else None
+    final_loss = float(loss.item())
+    st, code = engine.check()
+    assert st == 0, f"device status {code}"
+
+    # ---- end to end through the public call, as the reference trainer's loop runs it: the step's
+    # host inputs (puzzle definition, 1520 B pinned) go to the device, the step runs, the loss (4 B)
+    # comes back and the host waits for it, every step (tool:836-851).
+    barrier()
+    t0 = time.perf_counter()
+    e2e_steps = max(3, args.steps // 2)
+    for s in range(e2e_steps):
+        puzzle_dev.copy_(puzzle_pinned, non_blocking=True)
+        step(args.warmup + args.steps + s)
+        loss_pinned.copy_(loss, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e2e_sec = torch.tensor([(time.perf_counter() - t0) / e2e_steps], device=dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(e2e_sec, op=dist.ReduceOp.MAX)
+    e2e_value = batch * world / float(e2e_sec.item())
+
+    # ---- roofline of the dominant kernel (embedding-forward one-hot GEMM), timed live with CUDA events
+    # on the launching stream by the engine's stage timer, outside the timed region above.
+    peaks = load_peaks()
+    prof = mgt.BackwardProfile()
+    emb_ms, grad_ms = [], []
+    for s in range(3):
+        step(args.warmup + args.steps + e2e_steps + s, profile=prof)
+        emb_ms.append(prof.input_forward_ms)
+        grad_ms.append(prof.input_grad_ms)
+    stage_ms = {n: round(getattr(prof, n), 4) for n, _ in prof._fields_}
+    emb = float(np.median(emb_ms))
+    algo_tflops = EMB_ALGO_FLOP_PER_CANDIDATE * batch / (emb * 1e-3) / 1e12
+    exec_tflops = EMB_EXEC_FLOP_PER_CANDIDATE * batch / (emb * 1e-3) / 1e12
+    roofline = {
+        "kernel": "umma_gemm_kernel<one-hot forward> (embedding layer)", "bound": "tensor", "achieved": algo_tflops,
+        "peak": peaks["tflops_burst"], "unit": "TFLOP/s", "frac": algo_tflops / peaks["tflops_burst"], "traffic": None,
+        "peak_source": peaks["source"] + " (cuBLAS bf16 burst)", "ms_per_launch": emb,
+        "executed_tflops": exec_tflops, "executed_frac": exec_tflops / peaks["tflops_burst"],
+        "note": "achieved counts the 72 row-adds per candidate the layer needs; executed counts the dense one-hot MMA work",
+    }
+
+    if rank != 0:
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    value = batch * world / (ms_step * 1e-3)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic", "config": workload_config(world), "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(puzzle_pinned.numel()), "d2h_bytes_per_step": 4},
+        "gpu_launches": int(launches), "roofline": roofline,
+        "step_tflops_algorithmic": FLOP_PER_CANDIDATE * value / world / 1e12,
+        "step_frac_of_fp16_peak": FLOP_PER_CANDIDATE * value / world / 1e12 / peaks["tflops_sustained"],
+        "stage_ms": stage_ms, "final_loss": final_loss,
+    }
+    if batch != BATCH:
+        line["config"]["batch_per_rank"] = batch
+        line["config"]["note"] = "reduced batch: profiler capture only, not a benchmark value"
+    if not args.no_cpu_baseline and world == 1:
+        cpu = run_reference_cpu(args, args.steps_cpu, args.warmup_cpu)
+        line["cpu_baseline"] = cpu["cpu_baseline"]
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -101,6 +101,8 @@ mgt_status_t mgt_engine_destroy(mgt_engine_t* engine);
 /* Synchronises `stream`, then reads and clears the device status word: MGT_OK, or
  * MGT_DEVICE_TIMEOUT if a kernel gave up on a bounded wait since the last call. */
 mgt_status_t mgt_engine_check(mgt_engine_t* engine, void* stream, int32_t* out_device_code);
+/* Kernels launched through this engine so far (host-side count; no counterpart in the reference). */
+uint64_t mgt_engine_launch_count(const mgt_engine_t* engine);
 
 /* ---- loss + gradient (forward, MSE loss, backward) -----------------------------------------
  * Replaces MlpLossGradWorkspaceFloats (native/cuda/mgt_cuda/mlp_backward.cuh:27-43) and the

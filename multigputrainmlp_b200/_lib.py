@@ -41,6 +41,8 @@ def _declare(lib: C.CDLL) -> None:
     lib.mgt_engine_create.argtypes = [i32, C.POINTER(vp)]
     lib.mgt_engine_destroy.argtypes = [vp]
     lib.mgt_engine_check.argtypes = [vp, vp, C.POINTER(i32)]
+    lib.mgt_engine_launch_count.restype = u64
+    lib.mgt_engine_launch_count.argtypes = [vp]
     lib.mgt_mlp_loss_grad_workspace_floats.restype = u64
     lib.mgt_mlp_loss_grad_workspace_floats.argtypes = [vp, u32, u32, i32, i32]
     lib.mgt_launch_mlp_loss_grad.argtypes = [vp, vp, vp, vp, vp, vp, u32, vp, vp, vp, u64, u32, u32, i32, i32, vp, vp, vp, vp, u32]
@@ -49,5 +51,3 @@ def _declare(lib: C.CDLL) -> None:
     lib.mgt_launch_adamw_with_half_mirror.argtypes = [vp, vp, vp, vp, vp, vp, vp]
     lib.mgt_launch_float_to_half.argtypes = [vp, u64, vp, vp]
     lib.mgt_debug_gemm.argtypes = [vp, vp, u32, i32, vp, u32, i32, vp, u32, u32, u32, u32, vp, vp]
-    for name in dir(lib):
-        pass

@@ -156,6 +156,10 @@ class Engine:
         except Exception:
             pass
 
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.mgt_engine_launch_count(self.handle))
+
     def check(self, stream=None):
         code = C.c_int32(0)
         st = int(self._lib.mgt_engine_check(self.handle, _stream(stream), C.byref(code)))

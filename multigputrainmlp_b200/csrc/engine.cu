@@ -147,6 +147,7 @@ struct mgt_engine {
     std::unordered_map<mgt::MapKey, CUtensorMap, mgt::MapKeyHash> maps;
     std::mutex mu;
     cudaEvent_t ev_last = nullptr, ev_now = nullptr;
+    uint64_t launches = 0;  // kernels launched through this engine (host-side count)
 
     // fp16 2-D tensor map with 128-byte swizzle: `inner` contiguous elements per row, `outer` rows.
     bool Map(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch_elems, uint32_t box_inner, uint32_t box_outer) {
@@ -188,6 +189,7 @@ mgt_status_t LaunchGemm(mgt_engine* e, const CUtensorMap& ta, const CUtensorMap&
     const uint32_t grid = (uint32_t)(units < (uint64_t)e->sm_count ? units : (uint64_t)e->sm_count);
     args.status = e->status_word;
     umma_gemm_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, args);
+    ++e->launches;
     return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
 }
 
@@ -235,13 +237,34 @@ __global__ void ReducePartialsKernel(const float* __restrict__ partial, uint32_t
     }
 }
 
-// dst[c] = sum over rows r (fixed order) of src[r * row_stride + col_offset + c]
-__global__ void ReduceRowsKernel(const float* __restrict__ src, uint32_t rows, uint64_t row_stride, uint32_t col_offset, uint32_t cols, float* __restrict__ dst) {
-    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= cols) return;
+// dst[c] = sum over rows r of src[r * row_stride + col_offset + c], in a fixed order: each of 8 row
+// groups adds its rows (r = g, g+8, ...) and the groups are then added 0..7. One CTA per 32 columns.
+__global__ void __launch_bounds__(256)
+ReduceRowsKernel(const float* __restrict__ src, uint32_t rows, uint64_t row_stride, uint32_t col_offset, uint32_t cols, float* __restrict__ dst) {
+    __shared__ float s_part[8][33];
+    const uint32_t lane = threadIdx.x & 31U, g = threadIdx.x >> 5;
+    const uint32_t c = blockIdx.x * 32U + lane;
     float sum = 0.0f;
-    for (uint32_t r = 0; r < rows; ++r) sum += src[(uint64_t)r * row_stride + col_offset + c];
-    dst[c] = sum;
+    if (c < cols) {
+        const float* p = src + col_offset + c;
+        uint32_t r = g;
+        for (; r + 24U < rows; r += 32U) {
+            const float a0 = p[(uint64_t)r * row_stride];
+            const float a1 = p[(uint64_t)(r + 8U) * row_stride];
+            const float a2 = p[(uint64_t)(r + 16U) * row_stride];
+            const float a3 = p[(uint64_t)(r + 24U) * row_stride];
+            sum += a0; sum += a1; sum += a2; sum += a3;
+        }
+        for (; r < rows; r += 8U) sum += p[(uint64_t)r * row_stride];
+    }
+    s_part[g][lane] = sum;
+    __syncthreads();
+    if (g == 0 && c < cols) {
+        float total = s_part[0][lane];
+#pragma unroll
+        for (int q = 1; q < 8; ++q) total += s_part[q][lane];
+        dst[c] = total;
+    }
 }
 
 // Output head for output_dim == 1 (native/cuda/mlp_backward.cu:891-931): y = b + <x, w> with fp32
@@ -460,7 +483,8 @@ mgt_status_t GemmBackpropInput(mgt_engine* e, cudaStream_t st, const __half* dz,
     MGT_MAP(e->Map(&ta, dz, K, M, dz_pitch, 64, 128));
     MGT_MAP(e->Map(&tb, w, K, N, w_pitch, 64, bn));
     MGT_TRY(bn == 224 ? LaunchGemm<CfgDx<224, EPI>>(e, ta, tb, a, st) : LaunchGemm<CfgDx<256, EPI>>(e, ta, tb, a, st));
-    ReduceRowsKernel<<<(N + 127) / 128, 128, 0, st>>>(colsum, rows, N, 0, N, bias_grad);
+    ReduceRowsKernel<<<(N + 31) / 32, 256, 0, st>>>(colsum, rows, N, 0, N, bias_grad);
+    ++e->launches;
     return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
 }
 
@@ -482,6 +506,7 @@ mgt_status_t GemmGradWeights(mgt_engine* e, cudaStream_t st, const __half* act, 
     MGT_MAP(e->Map(&tb, dz, N, K, dz_pitch, 64, 64));
     MGT_TRY(bn == 224 ? LaunchGemm<CfgDw<224>>(e, ta, tb, a, st) : LaunchGemm<CfgDw<256>>(e, ta, tb, a, st));
     ReducePartialsKernel<<<GridFor(per_split, 256, e->sm_count), 256, 0, st>>>(partial, a.splits, per_split, grad_out);
+    ++e->launches;
     return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
 }
 
@@ -556,6 +581,8 @@ mgt_status_t mgt_engine_destroy(mgt_engine_t* e) {
     delete e;
     return MGT_OK;
 }
+
+uint64_t mgt_engine_launch_count(const mgt_engine_t* e) { return e == nullptr ? 0 : e->launches; }
 
 mgt_status_t mgt_engine_check(mgt_engine_t* e, void* stream, int32_t* out_device_code) {
     if (e == nullptr) return MGT_INVALID_CONFIG;
@@ -635,6 +662,7 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
             cur += RoundUp((uint64_t)rows * pitch * 2, 1024);
             cudaMemsetAsync(dst, 0, (uint64_t)rows * pitch * 2, st);
             RepackHalfKernel<<<GridFor((uint64_t)rows * cols, 256, e->sm_count), 256, 0, st>>>(src, rows, cols, cols, dst, pitch);
+            ++e->launches;
             return dst;
         };
         hw.p1 = ws.p_w1; hw.p2 = ws.p_w2; hw.pout = ws.p_wout;
@@ -687,9 +715,10 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     if (OUT == 1U) {
         HeadOut1Kernel<<<kHeadBlocks, kHeadThreads, 0, st>>>(w + OutputWeight(s), w + OutputBias(s), labels, x_f32, ws.p_f32, B, H2, dzf, dz_cur, ws.p_dz, head_partial);
         const uint32_t items = 2 * H2 + 2;
-        ReduceRowsKernel<<<(H2 + 1 + 127) / 128, 128, 0, st>>>(head_partial, kHeadBlocks, items, 0, H2 + 1, grad + OutputWeight(s));
-        ReduceRowsKernel<<<1, 32, 0, st>>>(head_partial, kHeadBlocks, items, H2 + 1, 1, loss);
-        ReduceRowsKernel<<<(H2 + 127) / 128, 128, 0, st>>>(head_partial, kHeadBlocks, items, H2 + 2, H2, head_bias_dst);
+        ReduceRowsKernel<<<(H2 + 1 + 31) / 32, 256, 0, st>>>(head_partial, kHeadBlocks, items, 0, H2 + 1, grad + OutputWeight(s));
+        ReduceRowsKernel<<<1, 256, 0, st>>>(head_partial, kHeadBlocks, items, H2 + 1, 1, loss);
+        ReduceRowsKernel<<<(H2 + 31) / 32, 256, 0, st>>>(head_partial, kHeadBlocks, items, H2 + 2, H2, head_bias_dst);
+        e->launches += 4;
     } else {
         float* dy = reinterpret_cast<float*>(base + ws.off_dy);
         __half* dy_h = reinterpret_cast<__half*>(base + ws.off_dyh);
@@ -697,8 +726,9 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
             hw.wout, hw.pout, w + OutputBias(s), labels, x_h(R), ws.p_act, x_f32, ws.p_f32, B, H2, OUT, dy, dy_h, dzf, dz_cur, ws.p_dz, head_partial);
         const uint32_t items = H2 * OUT + OUT;
         HeadOutNGradKernel<<<(items + 127) / 128, 128, 0, st>>>(x_h(R), ws.p_act, dy_h, hw.pout, dy, B, H2, OUT, grad + OutputWeight(s), grad + OutputBias(s));
-        ReduceRowsKernel<<<1, 32, 0, st>>>(head_partial, kHeadBlocks, H2 + 1, 0, 1, loss);
-        ReduceRowsKernel<<<(H2 + 127) / 128, 128, 0, st>>>(head_partial, kHeadBlocks, H2 + 1, 1, H2, head_bias_dst);
+        ReduceRowsKernel<<<1, 256, 0, st>>>(head_partial, kHeadBlocks, H2 + 1, 0, 1, loss);
+        ReduceRowsKernel<<<(H2 + 31) / 32, 256, 0, st>>>(head_partial, kHeadBlocks, H2 + 1, 1, H2, head_bias_dst);
+        e->launches += 4;
     }
     if (cudaGetLastError() != cudaSuccess) return MGT_CUDA_FAILURE;
     MGT_TRY(notify(OutputWeight(s), (uint64_t)H2 * OUT + OUT));

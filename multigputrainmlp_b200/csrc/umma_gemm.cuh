@@ -4,7 +4,7 @@
 //
 // One CTA per SM. Warp 0 feeds operands with TMA (plain per-CTA loads, no multicast), warp 1
 // issues tcgen05.mma from one thread and owns TMEM, warps 2-5 drain the accumulator
-// (tcgen05.ld -> registers -> fused epilogue -> global), and, for the embedding layers, warps 6-9
+// (tcgen05.ld -> registers -> fused epilogue -> global), and, for the embedding layers, warps 6-13
 // synthesise the one-hot operand directly in shared memory from the 80-byte puzzle states, so the
 // one-hot matrix never exists in HBM.
 //
@@ -82,7 +82,8 @@ struct GemmCfg {
     static constexpr int B_STAGE_BYTES = NACC_ * B_ACC_BYTES;
     static constexpr int ACC_BUFS = 2 / NACC_;
     static constexpr int ACC_COLS = 256;  // TMEM columns reserved per accumulator
-    static constexpr int THREADS = kOneHot ? 320 : 192;
+    static constexpr int SYNTH_WARPS = 8;
+    static constexpr int THREADS = kOneHot ? 192 + 32 * SYNTH_WARPS : 192;
     static constexpr int SMEM_BYTES = 1024 + SA_ * A_STAGE_BYTES + SB_ * B_STAGE_BYTES + 256;
     static_assert(BN_ % 16 == 0 && BN_ >= 16 && BN_ <= 256, "UMMA N");
     static_assert(BN_ % 32 == 0, "epilogue drains 32 columns at a time");
@@ -221,7 +222,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             mbar_init(&empty_a[s], 1);
         }
         for (int s = 0; s < SB; ++s) {
-            mbar_init(&full_b[s], Cfg::kOneHot ? 4 : 1);
+            mbar_init(&full_b[s], Cfg::kOneHot ? Cfg::SYNTH_WARPS : 1);
             mbar_init(&empty_b[s], 1);
         }
         for (int s = 0; s < ACC_BUFS; ++s) {
@@ -443,56 +444,58 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     } else {
         // ------------------------------- one-hot synthesis --------------------------------
         if constexpr (Cfg::kOneHot) {
-            const uint32_t t = threadIdx.x - 192U;  // 0..127
+            // Every non-zero place of the operand is owned by one warp (set and later cleared by it),
+            // so the synth warps never wait for one another: each warp polls the stage barrier itself
+            // and arrives once when its share is in place.
+            const uint32_t t = threadIdx.x - 192U;  // 0 .. 32*SYNTH_WARPS-1
+            constexpr uint32_t NT = 32U * Cfg::SYNTH_WARPS;
             const uint32_t V = args.value_pad, L = args.state_len, IN = args.in_rows;
             constexpr uint32_t ROWS = NACC * BN;  // rows of the synthesised operand per stage
+            auto place = [&](uint8_t* buf, uint32_t n, uint32_t k) -> uint16_t* {
+                uint8_t* row = buf + (n / BN) * Cfg::B_ACC_BYTES + (n % BN) * 128U;
+                return reinterpret_cast<uint16_t*>(row + ((((k >> 3) ^ (n & 7U)) << 4) | ((k & 7U) << 1)));
+            };
             // writes `value` (fp16 1.0 or 0) at the non-zero places of item (nt, c) in stage buffer `buf`
             auto apply = [&](uint8_t* buf, uint32_t nt, uint32_t c, uint16_t value) {
                 if constexpr (Cfg::BSRC == BSource::kOneHotFwd) {
-                    // rows = samples, K = input rows [64c, 64c+64)
+                    // rows = samples (thread-owned), K = input rows [64c, 64c+64)
                     const uint32_t k0 = c * 64U;
                     const uint32_t p_lo = k0 / V;
                     const uint32_t p_hi = min((k0 + 63U) / V, L - 1U);
-                    for (uint32_t n = t; n < ROWS; n += 128U) {
+                    const uint32_t kb = IN - k0;  // the all-ones column that multiplies the bias row
+#pragma unroll
+                    for (uint32_t i = 0; i < ROWS / NT; ++i) {
+                        const uint32_t n = t + i * NT;
                         const uint32_t sample = nt * ROWS + n;
-                        if (sample >= args.samples) continue;
-                        uint8_t* row = buf + (n / BN) * Cfg::B_ACC_BYTES + (n % BN) * 128U;
-                        const uint8_t* st = args.states + static_cast<uint64_t>(sample) * 80U;
-                        if (p_lo < L) {
-                            for (uint32_t p = p_lo; p <= p_hi; ++p) {
-                                const uint32_t k = p * V + st[p] - k0;
-                                if (k < 64U) *reinterpret_cast<uint16_t*>(row + ((((k >> 3) ^ (n & 7U)) << 4) | ((k & 7U) << 1))) = value;
+                        if (sample < args.samples) {
+                            const uint8_t* st = args.states + static_cast<uint64_t>(sample) * 80U;
+                            for (uint32_t p = p_lo; p <= p_hi && p < L; ++p) {
+                                const uint32_t k = p * V + __ldg(st + p) - k0;
+                                if (k < 64U) *place(buf, n, k) = value;
                             }
+                            if (kb < 64U) *place(buf, n, kb) = value;
                         }
-                        const uint32_t kb = IN - k0;  // the all-ones column that multiplies the bias row
-                        if (kb < 64U) *reinterpret_cast<uint16_t*>(row + ((((kb >> 3) ^ (n & 7U)) << 4) | ((kb & 7U) << 1))) = value;
                     }
                 } else {
-                    // rows = input rows [r0, r0+ROWS), K = samples [64c, 64c+64)
+                    // rows = input rows [r0, r0+ROWS), K = samples [64c, 64c+64); the four threads that
+                    // share a sample sit in one warp and split its positions
                     const uint32_t r0 = nt * ROWS;
-                    const uint32_t k = t & 63U;
+                    const uint32_t k = t >> 2;
                     const uint32_t sample = c * 64U + k;
                     if (sample < args.samples) {
                         const uint8_t* st = args.states + static_cast<uint64_t>(sample) * 80U;
                         const uint32_t p_lo = r0 / V;
                         const uint32_t p_hi = min((r0 + ROWS - 1U) / V, L - 1U);
-                        if (p_lo < L) {
-                            for (uint32_t p = p_lo + (t >> 6); p <= p_hi; p += 2U) {
-                                const uint32_t n = p * V + st[p] - r0;
-                                if (n < ROWS) {
-                                    uint8_t* row = buf + (n / BN) * Cfg::B_ACC_BYTES + (n % BN) * 128U;
-                                    *reinterpret_cast<uint16_t*>(row + ((((k >> 3) ^ (n & 7U)) << 4) | ((k & 7U) << 1))) = value;
-                                }
-                            }
+                        for (uint32_t p = p_lo + (t & 3U); p <= p_hi && p < L; p += 4U) {
+                            const uint32_t n = p * V + __ldg(st + p) - r0;
+                            if (n < ROWS) *place(buf, n, k) = value;
                         }
-                        const uint32_t nb = IN - r0;  // bias-gradient row: every sample contributes
-                        if ((t >> 6) == 0U && nb < ROWS) {
-                            uint8_t* row = buf + (nb / BN) * Cfg::B_ACC_BYTES + (nb % BN) * 128U;
-                            *reinterpret_cast<uint16_t*>(row + ((((k >> 3) ^ (nb & 7U)) << 4) | ((k & 7U) << 1))) = value;
-                        }
+                        const uint32_t nb = IN - r0;  // optional all-ones row (bias gradient)
+                        if ((t & 3U) == 0U && nb < ROWS) *place(buf, nb, k) = value;
                     }
                 }
             };
+            static_assert(Cfg::BSRC != BSource::kOneHotGrad || NT == 256U, "64 samples x 4 threads");
             uint32_t it = 0;
             uint32_t h_nt[2] = {0, 0}, h_c[2] = {0, 0};  // what each of the two stages currently holds
             bool ok = true;
@@ -502,11 +505,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 const uint32_t c0 = chunk_begin(sp), c1 = chunk_begin(sp + 1);
                 for (uint32_t c = c0; c < c1; ++c, ++it) {
                     const uint32_t sb = it & 1U, pb = (it >> 1) & 1U;
-                    // all 128 synth threads agree on the outcome before they meet at the next barrier
-                    if (!named_bar_and(1, 128, mbar_wait(&empty_b[sb], pb ^ 1U, cta_abort, kAbortSynthWait))) { ok = false; break; }
+                    if (!__all_sync(0xFFFFFFFFU, mbar_wait(&empty_b[sb], pb ^ 1U, cta_abort, kAbortSynthWait))) { ok = false; break; }
                     uint8_t* buf = b_ring + sb * Cfg::B_STAGE_BYTES;
                     if (it >= 2U) apply(buf, sb ? h_nt[1] : h_nt[0], sb ? h_c[1] : h_c[0], 0);
-                    named_bar_sync(1, 128);  // a place cleared by one thread may be set by another
+                    __syncwarp();  // a place cleared by one lane may be set by another lane of this warp
                     apply(buf, nt, c, 0x3C00);
                     if (sb) { h_nt[1] = nt; h_c[1] = c; } else { h_nt[0] = nt; h_c[0] = c; }
                     fence_proxy_async_smem();
