@@ -185,6 +185,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--comm", default="peer", choices=["peer", "nccl"], help="gradient exchange at N>1: the library's NVLink peer kernels, or NCCL + AdamW (the reference's scheme, for comparison)")
+    ap.add_argument("--bucket-bytes", type=int, default=4 << 20)
     ap.add_argument("--batch", type=int, default=BATCH, help=argparse.SUPPRESS)  # smaller batches are for ncu captures only
     ap.add_argument("--cpu-samples-per-core", type=int, default=384)
     ap.add_argument("--steps-cpu", type=int, default=2)
@@ -221,8 +223,26 @@ def main():
     w_half = w.half()
     m = torch.zeros(params, device=dev)
     v = torch.zeros(params, device=dev)
-    grad = torch.zeros(params, device=dev)
     loss = torch.zeros(1, device=dev)
+    backend = None
+    exchange = None
+    if world > 1:
+        import torch.distributed as dist
+        from multigputrainmlp_b200.comm import NcclBackend, OverlappedGradientExchange, PeerBackend, default_id_file
+        if args.comm == "peer":
+            id_file = default_id_file()
+            if rank == 0 and os.path.exists(id_file):
+                os.remove(id_file)  # a stale id file of an earlier run must not be picked up
+            dist.barrier()
+            backend = PeerBackend(local_rank, world, rank, id_file, params)
+            grad = backend.gradient_tensor(dev)
+            exchange = OverlappedGradientExchange(backend, dev, bucket_bytes=args.bucket_bytes, residual_blocks=16, fused_adamw=True)
+        else:
+            grad = torch.zeros(params, device=dev)
+            backend = NcclBackend(grad, world)
+            exchange = OverlappedGradientExchange(backend, dev, bucket_bytes=args.bucket_bytes, residual_blocks=16, fused_adamw=False)
+    else:
+        grad = torch.zeros(params, device=dev)
     orc = load_oracle()
     moves_h, target_h = orc.cyclic_puzzle(72, 18)
     puzzle_pinned = torch.from_numpy(np.concatenate([moves_h.reshape(-1), target_h.reshape(-1)])).pin_memory()
@@ -237,10 +257,6 @@ def main():
     workspace = torch.empty(ws_floats, device=dev)
     engine = mgt.Engine(local_rank)
     walk_cfg = mgt.RandomWalkKernelConfig(batch, 1, 29)
-    comm = None
-    if world > 1:
-        from multigputrainmlp_b200.comm import GradientComm
-        comm = GradientComm(engine, grad, rank, world, dev)
     loss_pinned = torch.zeros(1).pin_memory()
     other_launches = 0
 
@@ -248,16 +264,20 @@ def main():
         nonlocal other_launches
         st = mgt.launch_random_walk_kernel(walk_cfg, SEED, 0, s, rank, moves_d, target_d, states, labels, meta)
         assert st == 0, st
-        st = engine.launch_mlp_loss_grad(shape, w, w_half, states, labels, batch, loss, grad, workspace, ws_floats,
-                                         profile=profile, input_grad_position_tile=36)
-        assert st == 0, mgt.status_name(st)
         cfg = mgt.AdamWKernelConfig(params, s + 1, LR)
-        if comm is not None:
-            comm.average_and_adamw(cfg, w, w_half, m, v)
-        else:
+        if exchange is not None:
+            exchange.begin_step(cfg, w, w_half, m, v)
+        st = engine.launch_mlp_loss_grad(shape, w, w_half, states, labels, batch, loss, grad, workspace, ws_floats,
+                                         profile=profile, input_grad_position_tile=36,
+                                         gradient_ready=exchange.callback if exchange is not None else None)
+        assert st == 0, mgt.status_name(st)
+        other_launches += 1
+        if exchange is not None:
+            exchange.finish_step()
+        if exchange is None or not exchange.fused:
             st = mgt.launch_adamw_kernel_with_half_mirror(cfg, w, w_half, grad, m, v)
             assert st == 0, st
-        other_launches += 2
+            other_launches += 1
 
     def barrier():
         torch.cuda.synchronize()
@@ -277,6 +297,7 @@ def main():
     if sampler is not None:
         time.sleep(0.3)
     launches0 = engine.launch_count + other_launches
+    comm_launches0 = backend.launch_count if (args.comm == "peer" and backend is not None) else 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     t_wall0 = time.time()
@@ -292,6 +313,10 @@ def main():
         dist.all_reduce(ms_total, op=dist.ReduceOp.MAX)
     ms_step = float(ms_total.item()) / args.steps
     launches = engine.launch_count + other_launches - launches0
+    if args.comm == "peer" and backend is not None:
+        launches += backend.launch_count - comm_launches0
+        st, code = backend.check()
+        assert st == 0, f"communicator status {code}"
     clocks = sampler.stop(t_wall0, t_wall1) if sampler is not None else None
     final_loss = float(loss.item())
     st, code = engine.check()
@@ -348,7 +373,7 @@ def main():
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic", "config": workload_config(world), "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(puzzle_pinned.numel()), "d2h_bytes_per_step": 4},
-        "gpu_launches": int(launches), "roofline": roofline,
+        "gpu_launches": int(launches), "roofline": roofline, "comm": (args.comm if world > 1 else "none"),
         "step_tflops_algorithmic": FLOP_PER_CANDIDATE * value / world / 1e12,
         "step_frac_of_fp16_peak": FLOP_PER_CANDIDATE * value / world / 1e12 / peaks["tflops_sustained"],
         "stage_ms": stage_ms, "final_loss": final_loss,

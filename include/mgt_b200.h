@@ -164,6 +164,43 @@ mgt_status_t mgt_launch_adamw_with_half_mirror(const mgt_adamw_config_t* config,
 /* Replaces FloatToHalfMirrorKernel (native/tools/mgt_native_train_smoke.cu:68-72). */
 mgt_status_t mgt_launch_float_to_half(const float* device_values, uint64_t count, uint16_t* device_half, void* stream);
 
+/* ---- gradient exchange between data-parallel ranks --------------------------------------------
+ * Replaces the reference's NCCL wrapper (native/cuda/mgt_cuda/allreduce_nccl.cuh:14-24,
+ * native/cuda/allreduce_nccl.cu:58-150) with peer-to-peer loads/stores over NVLink/NVSwitch.
+ * One process per GPU on one node, world_size <= 8. mgt_comm_create stands where
+ * CreateNcclRankContext stands: ranks rendezvous through `id_file` (rank 0 writes it, the others
+ * poll for up to 30 s) and exchange CUDA IPC handles through files next to it. The communicator
+ * owns the gradient buffer (peers must be able to map it): pass mgt_comm_gradient_buffer() as the
+ * device_grad of mgt_launch_mlp_loss_grad. world_size 1 needs no id file and exchanges nothing. */
+typedef struct mgt_comm mgt_comm_t;
+typedef struct {
+    uint32_t world_size;
+    uint32_t global_rank;
+    uint64_t collective_seq;
+    uint64_t element_count;
+} mgt_allreduce_config_t; /* native/include/mgt/allreduce.hpp:9-14 */
+
+mgt_status_t mgt_comm_create(int32_t device_id, uint32_t world_size, uint32_t global_rank, const char* id_file,
+                             uint64_t gradient_floats, mgt_comm_t** out_comm);
+mgt_status_t mgt_comm_destroy(mgt_comm_t* comm);
+float* mgt_comm_gradient_buffer(mgt_comm_t* comm);
+/* In place on a range of the gradient buffer: sum over ranks (rank order) then * 1/world_size.
+ * Replaces NcclAllreduceAverageFloat (allreduce_nccl.cu:120-150). Every rank must make the same
+ * calls in the same order. */
+mgt_status_t mgt_comm_allreduce_average(mgt_comm_t* comm, const mgt_allreduce_config_t* config, float* device_gradients,
+                                        void* stream);
+/* The same exchange fused with the AdamW update (and fp16 mirror, may be NULL) of parameters
+ * [param_offset, param_offset + param_count): replaces allreduce + ScaleKernel + AdamW kernel
+ * (allreduce_nccl.cu:130-148, native/cuda/adamw.cu:35-46). weights/m/v are the flat full-model
+ * arrays; the gradient buffer afterwards holds the averaged gradient as in the reference. */
+mgt_status_t mgt_comm_allreduce_average_adamw(mgt_comm_t* comm, uint64_t param_offset, uint64_t param_count,
+                                              const mgt_adamw_config_t* adamw, float* device_weights,
+                                              uint16_t* device_weights_half, float* device_m, float* device_v, void* stream);
+/* Synchronises `stream`, reads and clears the communicator's status: MGT_OK or MGT_DEVICE_TIMEOUT
+ * (a peer did not show up within the wait limit; out_code 1 = ready wait, 2 = done wait). */
+mgt_status_t mgt_comm_check(mgt_comm_t* comm, void* stream, int32_t* out_code);
+uint64_t mgt_comm_launch_count(const mgt_comm_t* comm);
+
 /* ---- diagnostics ---------------------------------------------------------------------------
  * One plain GEMM through the tcgen05 kernel, used by the parity tests to pin each operand form.
  * D[M x N] fp32 = A * B with fp16 operands; a_mn_major: A stored [K][M] (else [M][K]);

@@ -26,15 +26,18 @@ __device__ __forceinline__ AdamWScalars MakeAdamWScalars(uint64_t step, float lr
     return s;
 }
 
+// Every operation is an explicitly rounded IEEE fp32 operation (no FMA contraction), so that all
+// call sites - and therefore all data-parallel replicas - produce bit-identical weights, and so that
+// the result equals the plain C expression of the reference evaluated operation by operation.
 __device__ __forceinline__ float AdamWUpdateOne(const AdamWScalars& s, float weight, float grad, float* m, float* v) {
-    const float decayed = grad + s.wd * weight;
-    const float next_m = s.beta1 * *m + s.one_minus_b1 * decayed;
-    const float next_v = s.beta2 * *v + s.one_minus_b2 * decayed * decayed;
+    const float decayed = __fadd_rn(grad, __fmul_rn(s.wd, weight));
+    const float next_m = __fadd_rn(__fmul_rn(s.beta1, *m), __fmul_rn(s.one_minus_b1, decayed));
+    const float next_v = __fadd_rn(__fmul_rn(s.beta2, *v), __fmul_rn(__fmul_rn(s.one_minus_b2, decayed), decayed));
     *m = next_m;
     *v = next_v;
-    const float m_hat = next_m / s.bias1;
-    const float v_hat = next_v / s.bias2;
-    return weight - s.lr * m_hat / (sqrtf(v_hat) + s.eps);
+    const float m_hat = __fdiv_rn(next_m, s.bias1);
+    const float v_hat = __fdiv_rn(next_v, s.bias2);
+    return __fsub_rn(weight, __fdiv_rn(__fmul_rn(s.lr, m_hat), __fadd_rn(__fsqrt_rn(v_hat), s.eps)));
 }
 
 }  // namespace mgt

@@ -1,0 +1,134 @@
+"""Host logic of the gradient exchange: range scheduling (pure Python) and a world_size-2 run over
+gloo on CPU that checks the data-parallel result against a single-process computation."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from multigputrainmlp_b200.comm import GradientRangeScheduler
+
+
+def p888_ranges():
+    """The 35 gradient-ready ranges of the p888 model in notification order
+    (native/cuda/mlp_backward.cu:1364,1385,1402,1427,1506)."""
+    h1, h2, r, inp = 2560, 224, 16, 72 * 72
+    in_w = inp * h1
+    hidden = in_w + h1
+    rbase = hidden + h1 * h2 + h2
+    blk = 2 * (h2 * h2 + h2)
+    out = [(rbase + r * blk, h2 + 1)]
+    for k in range(r - 1, -1, -1):
+        out.append((rbase + k * blk + h2 * h2 + h2, h2 * h2 + h2))
+        out.append((rbase + k * blk, h2 * h2 + h2))
+    out.append((hidden, h1 * h2 + h2))
+    out.append((0, in_w + h1))
+    return out
+
+
+def run_scheduler(lag, bucket_bytes=4 << 20):
+    launches, waits = [], []
+    sched = GradientRangeScheduler(lambda off, cnt: launches.append((off, cnt)), lambda: waits.append(len(launches)),
+                                   bucket_params=bucket_bytes // 4, expected_ranges=35, lag=lag)
+    sched.begin_step()
+    seen_before = []
+    for i, (off, cnt) in enumerate(p888_ranges()):
+        assert sched.on_ready(i, off, cnt) == 0
+        seen_before.append(len(launches))
+    sched.finish()
+    return sched, launches, waits, seen_before
+
+
+def test_schedule_matches_reference_chunking():
+    sched, launches, waits, _ = run_scheduler(lag=0)
+    # 35 ranges; at 4 MiB buckets the embedding range (13 273 600 floats) needs 13 chunks: 47 launches
+    assert sched.scheduled_ranges == 35 and sched.scheduled_chunks == 47 == len(launches)
+    assert launches[0] == (15460064, 225)
+    assert launches[-13][0] == 0 and sum(c for _, c in launches[-13:]) == 72 * 72 * 2560 + 2560
+    assert all(c <= (4 << 20) // 4 for _, c in launches)
+    assert sum(c for _, c in launches) == 15460289  # every parameter exactly once
+    covered = sorted(launches)
+    assert all(covered[i][0] + covered[i][1] == covered[i + 1][0] for i in range(len(covered) - 1))
+
+
+def test_fused_update_is_held_back_one_notification():
+    sched, launches, waits, seen_before = run_scheduler(lag=1)
+    assert sched.scheduled_chunks == 47
+    ranges = p888_ranges()
+    # after notification i only ranges 0..i-1 may have been launched: the GEMM that still reads the
+    # weights of range i is enqueued between notification i and i+1
+    for i in range(35):
+        launched = seen_before[i]
+        assert launched == sum(-(-ranges[j][1] // ((4 << 20) // 4)) for j in range(i))
+    assert len(waits) == 35  # one producer event per flush
+
+
+def test_scheduler_rejects_unexpected_ranges():
+    sched = GradientRangeScheduler(lambda o, c: None, lambda: None, expected_ranges=3)
+    sched.begin_step()
+    assert sched.on_ready(0, 0, 10) == 0
+    assert sched.on_ready(5, 0, 10) == 1
+    assert sched.on_ready(1, 0, 0) == 1
+    with pytest.raises(RuntimeError):
+        sched.finish()
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _gloo_worker(rank, world, port, ranges, params, out_dir):
+    import torch
+    import torch.distributed as dist
+    from oracle import load_oracle
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    orc = load_oracle()
+    rng = np.random.default_rng(100 + rank)
+    w = np.linspace(-0.1, 0.1, params).astype(np.float32)
+    m = np.zeros(params, np.float32)
+    v = np.zeros(params, np.float32)
+    for step in (1, 2):
+        grad = (rng.standard_normal(params) * 1e-3).astype(np.float32)  # each rank's own batch gradient
+        g_t = torch.from_numpy(grad)
+
+        def launch(off, cnt):
+            view = g_t[off:off + cnt]
+            dist.all_reduce(view, op=dist.ReduceOp.SUM)
+            view.mul_(1.0 / world)
+            assert orc.adamw(w[off:off + cnt], grad[off:off + cnt], m[off:off + cnt], v[off:off + cnt], step=step, lr=1e-3) == 0
+
+        sched = GradientRangeScheduler(launch, lambda: None, bucket_params=4096, expected_ranges=len(ranges), lag=1)
+        sched.begin_step()
+        for i, (off, cnt) in enumerate(ranges):
+            assert sched.on_ready(i, off, cnt) == 0
+        sched.finish()
+    np.save(os.path.join(out_dir, f"w{rank}.npy"), w)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_gloo_training_matches_single_process(tmp_path, oracle):
+    import torch.multiprocessing as mp
+    params = 20000
+    ranges = [(15000, 5000), (9000, 6000), (0, 9000)]  # backward order: last layer first
+    port = _free_port()
+    mp.spawn(_gloo_worker, args=(2, port, ranges, params, str(tmp_path)), nprocs=2, join=True)
+    w0 = np.load(tmp_path / "w0.npy")
+    w1 = np.load(tmp_path / "w1.npy")
+    assert np.array_equal(w0, w1)  # replicas stay identical
+    # single-process restatement: average in rank order, then AdamW over all parameters
+    rngs = [np.random.default_rng(100), np.random.default_rng(101)]
+    w = np.linspace(-0.1, 0.1, params).astype(np.float32)
+    m = np.zeros(params, np.float32)
+    v = np.zeros(params, np.float32)
+    for step in (1, 2):
+        grads = [(r.standard_normal(params) * 1e-3).astype(np.float32) for r in rngs]
+        avg = oracle.allreduce_average(grads)
+        assert oracle.adamw(w, avg, m, v, step=step, lr=1e-3) == 0
+    assert np.array_equal(w, w0)
