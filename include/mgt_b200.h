@@ -201,6 +201,31 @@ mgt_status_t mgt_comm_allreduce_average_adamw(mgt_comm_t* comm, uint64_t param_o
 mgt_status_t mgt_comm_check(mgt_comm_t* comm, void* stream, int32_t* out_code);
 uint64_t mgt_comm_launch_count(const mgt_comm_t* comm);
 
+/* ---- run plan and output files (host only, no GPU) --------------------------------------------
+ * The configuration travels as the trainer's own command line: `argv` holds flag/value pairs in
+ * the grammar of mgt_native_train (native/tools/mgt_native_train_smoke.cu:525-613), without the
+ * program name. Replaces BuildTrainPlan (native/src/train_plan.cpp:204-230) and the trainer's
+ * writers (tool:184-404, 888-895); file contents are byte-compatible with the reference's. */
+#define MGT_PLAN_SUMMARY_FIELDS 16
+#define MGT_PLAN_LINEAR_OP_FIELDS 14
+/* out: padded_state_dim, physical_hd1, physical_hd2, param blocks, linear ops, gradient buckets,
+ * total_params, total_bytes, total_rank_bytes, training_scratch_bytes, logical_params,
+ * fits_state_record, states_bytes, layout_allreduce_bytes, walkers, state_capacity_bytes */
+mgt_status_t mgt_plan_summary(int32_t argc, const char* const* argv, uint64_t* out, uint32_t out_count);
+/* out: op_id, phase, role, block_index, transpose_a, transpose_b, m, n, k, backend class,
+ * tensor_core_eligible, logical_tail_masked, lhs_rows, rhs_cols (native/include/mgt/train_plan.hpp:44-63) */
+mgt_status_t mgt_plan_linear_op(int32_t argc, const char* const* argv, uint32_t index, uint32_t* out, uint32_t out_count);
+/* metadata.env, layers.json, linear_ops.json (tool:184-214, 888-895) */
+mgt_status_t mgt_plan_write_files(int32_t argc, const char* const* argv, const char* dir, int32_t overlap_allreduce,
+                                  int32_t comm_enabled, int32_t resumed);
+/* The trainer's software float->fp16 converter used for weights/ files (tool:215-229). */
+uint16_t mgt_export_float_to_fp16(float value);
+/* weights/ (fp16 per-layer files + manifest + weights.f32.bin) and checkpoint/ (tool:241-390) from host arrays. */
+mgt_status_t mgt_write_run_artifacts(int32_t argc, const char* const* argv, const char* dir, const float* weights,
+                                     const float* adam_m, const float* adam_v);
+/* checkpoint/state.f32.bin = weights | adam_m | adam_v (tool:392-404) */
+mgt_status_t mgt_read_checkpoint(const char* checkpoint_dir, uint64_t param_count, float* weights, float* adam_m, float* adam_v);
+
 /* ---- diagnostics ---------------------------------------------------------------------------
  * One plain GEMM through the tcgen05 kernel, used by the parity tests to pin each operand form.
  * D[M x N] fp32 = A * B with fp16 operands; a_mn_major: A stored [K][M] (else [M][K]);

@@ -23,7 +23,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",
 ]
 CUDA_SOURCES = ["walk.cu", "adamw.cu", "engine.cu", "comm.cu"]
-HOST_SOURCES = ["plan.cpp", "artifacts.cpp"]
+HOST_SOURCES = ["plan.cpp", "artifacts.cpp", "host_capi.cpp"]
 
 
 def _nvcc() -> str:
@@ -63,9 +63,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
     train_src = os.path.join(CSRC, "train_main.cpp")
     if os.path.exists(train_src):
         os.makedirs(os.path.dirname(TRAIN_BIN), exist_ok=True)
-        if force or _stale(TRAIN_BIN, [train_src, LIB]):
-            subprocess.run([nvcc, "-O2", "-std=c++17", "-o", TRAIN_BIN, train_src, "-I", os.path.join(ROOT, "include"),
-                            "-L", OUT_DIR, "-lmgt_b200", "-Xlinker", "-rpath,$ORIGIN/../multigputrainmlp_b200/_native"], check=True)
+        host = [train_src, os.path.join(CSRC, "plan.cpp"), os.path.join(CSRC, "artifacts.cpp")]
+        if force or _stale(TRAIN_BIN, host + [LIB]):
+            subprocess.run([nvcc, "-O2", "-std=c++17", "-o", TRAIN_BIN, *host, "-L", OUT_DIR, "-lmgt_b200",
+                            "-Xlinker", "-rpath=$ORIGIN/../multigputrainmlp_b200/_native"], check=True)
     return LIB
 
 

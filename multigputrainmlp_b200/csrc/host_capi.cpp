@@ -1,0 +1,75 @@
+// C entry points over the host-side plan and artefact writers (see include/mgt_b200.h).
+#include "../../include/mgt_b200.h"
+#include "host_plan.hpp"
+
+#include <filesystem>
+#include <vector>
+
+using namespace mgt::host;
+
+namespace {
+bool PlanFromArgs(int32_t argc, const char* const* argv, TrainPlan* plan) {
+    TrainOptions o;
+    std::vector<const char*> full;
+    full.push_back("mgt_native_train");
+    for (int32_t i = 0; i < argc; ++i) full.push_back(argv[i]);
+    if (!ParseTrainOptions(static_cast<int>(full.size()), full.data(), &o)) return false;
+    return BuildTrainPlan(o, plan);
+}
+}  // namespace
+
+extern "C" {
+
+mgt_status_t mgt_plan_summary(int32_t argc, const char* const* argv, uint64_t* out, uint32_t out_count) {
+    TrainPlan p;
+    if (out == nullptr || out_count < MGT_PLAN_SUMMARY_FIELDS || !PlanFromArgs(argc, argv, &p)) return MGT_INVALID_CONFIG;
+    const uint64_t v[MGT_PLAN_SUMMARY_FIELDS] = {
+        p.padded_state_dim, p.physical_hd1, p.physical_hd2, p.blocks.size(), p.linear_ops.size(), p.gradient_bucket_count,
+        p.total_params, p.total_bytes, p.memory.total_rank_bytes, p.memory.training_scratch_bytes, p.logical_params,
+        p.fits_state_record ? 1ULL : 0ULL, p.memory.states_bytes, p.memory.layout_allreduce_bytes, p.options.walkers, p.state_capacity_bytes};
+    for (uint32_t i = 0; i < MGT_PLAN_SUMMARY_FIELDS; ++i) out[i] = v[i];
+    return MGT_OK;
+}
+
+mgt_status_t mgt_plan_linear_op(int32_t argc, const char* const* argv, uint32_t index, uint32_t* out, uint32_t out_count) {
+    TrainPlan p;
+    if (out == nullptr || out_count < MGT_PLAN_LINEAR_OP_FIELDS || !PlanFromArgs(argc, argv, &p) || index >= p.linear_ops.size()) return MGT_INVALID_CONFIG;
+    const LinearOp& op = p.linear_ops[index];
+    const uint32_t v[MGT_PLAN_LINEAR_OP_FIELDS] = {op.op_id, op.phase, static_cast<uint32_t>(op.role), op.block_index, op.transpose_a ? 1U : 0U,
+                                                   op.transpose_b ? 1U : 0U, op.m, op.n, op.k, op.backend, op.tensor_core_eligible ? 1U : 0U,
+                                                   op.logical_tail_masked ? 1U : 0U, op.lhs_rows, op.rhs_cols};
+    for (uint32_t i = 0; i < MGT_PLAN_LINEAR_OP_FIELDS; ++i) out[i] = v[i];
+    return MGT_OK;
+}
+
+mgt_status_t mgt_plan_write_files(int32_t argc, const char* const* argv, const char* dir, int32_t overlap_allreduce, int32_t comm_enabled, int32_t resumed) {
+    TrainPlan p;
+    if (dir == nullptr || !PlanFromArgs(argc, argv, &p)) return MGT_INVALID_CONFIG;
+    std::error_code ec;
+    std::filesystem::create_directories(dir, ec);
+    const bool ok = WriteMetadataEnv(dir, p, overlap_allreduce != 0, comm_enabled != 0, resumed != 0) && WriteLayersJson(dir, p) && WriteLinearOpsManifest(dir, p);
+    return ok ? MGT_OK : MGT_IO_FAILURE;
+}
+
+uint16_t mgt_export_float_to_fp16(float value) { return ExportFloatToFp16(value); }
+
+mgt_status_t mgt_write_run_artifacts(int32_t argc, const char* const* argv, const char* dir, const float* weights, const float* adam_m, const float* adam_v) {
+    TrainPlan p;
+    if (dir == nullptr || weights == nullptr || adam_m == nullptr || adam_v == nullptr || !PlanFromArgs(argc, argv, &p)) return MGT_INVALID_CONFIG;
+    const std::vector<float> w(weights, weights + p.total_params), m(adam_m, adam_m + p.total_params), v(adam_v, adam_v + p.total_params);
+    std::error_code ec;
+    std::filesystem::create_directories(dir, ec);
+    return WriteWeights(dir, p, w) && WriteCheckpoint(dir, p, w, m, v) ? MGT_OK : MGT_IO_FAILURE;
+}
+
+mgt_status_t mgt_read_checkpoint(const char* checkpoint_dir, uint64_t param_count, float* weights, float* adam_m, float* adam_v) {
+    if (checkpoint_dir == nullptr || param_count == 0 || weights == nullptr || adam_m == nullptr || adam_v == nullptr) return MGT_INVALID_CONFIG;
+    std::vector<float> w(param_count), m(param_count), v(param_count);
+    if (!ReadCheckpoint(checkpoint_dir, &w, &m, &v)) return MGT_IO_FAILURE;
+    std::copy(w.begin(), w.end(), weights);
+    std::copy(m.begin(), m.end(), adam_m);
+    std::copy(v.begin(), v.end(), adam_v);
+    return MGT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,260 @@
+// mgt_native_train: one process per GPU rank. Same command line, same output files and the same
+// step loop as the reference trainer (native/tools/mgt_native_train_smoke.cu:619-930); the device
+// work goes through the C ABI of libmgt_b200 (include/mgt_b200.h).
+//
+//   per step:  record step_start -> random walks -> forward/loss/backward (gradient-ready
+//              notifications schedule the peer gradient exchange, fused with AdamW, on a second
+//              stream) -> wait for the exchange -> AdamW (single rank or non-overlapped mode)
+//              -> record step_stop, synchronise, read the loss, write train.log / profile.jsonl
+#include "../../include/mgt_b200.h"
+#include "host_plan.hpp"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <filesystem>
+#include <fstream>
+#include <iostream>
+#include <vector>
+
+using namespace mgt::host;
+
+namespace {
+
+#define CUDA_OK(expr) ((expr) == cudaSuccess)
+
+// Gradient-ready ranges -> exchange launches (the role of ScheduleGradientAllreduce, tool:494-523).
+// The exchange is fused with the AdamW update, so a range is launched one notification late: the
+// backward GEMM that still reads a layer's weights is enqueued right after that layer's notification.
+struct ExchangeContext {
+    bool enabled = false;
+    mgt_comm_t* comm = nullptr;
+    cudaStream_t comm_stream = nullptr;
+    std::vector<cudaEvent_t>* events = nullptr;
+    uint64_t bucket_params = 0;
+    mgt_adamw_config_t adamw{};
+    float* w = nullptr;
+    uint16_t* w_half = nullptr;
+    float* m = nullptr;
+    float* v = nullptr;
+    uint32_t scheduled_ranges = 0, scheduled_chunks = 0, next_event = 0;
+    bool have_pending = false;
+    uint64_t pending_offset = 0, pending_count = 0;
+    bool failed = false;
+
+    bool LaunchRange(uint64_t offset, uint64_t count, cudaStream_t producer) {
+        cudaEvent_t ev = (*events)[next_event++ % events->size()];
+        if (!CUDA_OK(cudaEventRecord(ev, producer)) || !CUDA_OK(cudaStreamWaitEvent(comm_stream, ev, 0))) return false;
+        while (count > 0) {
+            const uint64_t chunk = std::min<uint64_t>(count, bucket_params);
+            if (mgt_comm_allreduce_average_adamw(comm, offset, chunk, &adamw, w, w_half, m, v, comm_stream) != MGT_OK) return false;
+            offset += chunk;
+            count -= chunk;
+            ++scheduled_chunks;
+        }
+        return true;
+    }
+    bool Flush(cudaStream_t producer) {
+        if (!have_pending) return true;
+        have_pending = false;
+        return LaunchRange(pending_offset, pending_count, producer);
+    }
+};
+
+mgt_status_t OnGradientReady(void* user, uint32_t ready_id, uint64_t offset, uint64_t count, void* producer_stream) {
+    auto* ctx = static_cast<ExchangeContext*>(user);
+    if (ctx == nullptr || !ctx->enabled) return MGT_OK;
+    if (ctx->comm == nullptr || ctx->comm_stream == nullptr || ctx->events == nullptr || ctx->bucket_params == 0 || count == 0) return MGT_INVALID_CONFIG;
+    (void)ready_id;
+    ++ctx->scheduled_ranges;
+    if (!ctx->Flush(static_cast<cudaStream_t>(producer_stream))) { ctx->failed = true; return MGT_NCCL_FAILURE; }
+    ctx->have_pending = true;
+    ctx->pending_offset = offset;
+    ctx->pending_count = count;
+    return MGT_OK;
+}
+
+const char kUsage[] =
+    "usage: mgt_native_train --output-dir DIR --steps N --device-id ID --world-size N --global-rank R --local-rank R "
+    "[--batch-size N --k-min N --k-max N --hd1 N --hd2 N --nrd N --write-artifacts 0|1 --backward-profile 0|1 --overlap-allreduce 0|1 "
+    "--input-grad-partial-chunks N --input-grad-positions-per-block N --input-grad-position-tile N --input-grad-fp16 0|1 --linear-fp16 0|1 "
+    "--persistent-half-weights 0|1 --lt-workspace-bytes N --nccl-id-file PATH --resume-checkpoint DIR]\n";
+
+}  // namespace
+
+int main(int argc, char** argv) {
+    TrainOptions opt;
+    if (!ParseTrainOptions(argc, argv, &opt)) {
+        std::cerr << kUsage;
+        return EXIT_FAILURE;
+    }
+    int device_count = 0;
+    if (!CUDA_OK(cudaGetDeviceCount(&device_count)) || device_count <= static_cast<int>(opt.device_id)) return EXIT_FAILURE;
+    if (!CUDA_OK(cudaSetDevice(static_cast<int>(opt.device_id)))) return EXIT_FAILURE;
+
+    TrainPlan plan;
+    if (!BuildTrainPlan(opt, &plan)) return EXIT_FAILURE;
+    if (!plan.fits_state_record || opt.state_len > MGT_STATE_LEN || opt.state_value_count > MGT_STATE_VALUE_PAD || opt.move_count > MGT_MOVE_COUNT) {
+        std::cerr << "current CUDA smoke path supports puzzles fitting TrainStateStorage only\n";
+        return EXIT_FAILURE;
+    }
+    // the device model uses the PHYSICAL (padded) hidden sizes; padded tails are trained (tool:641)
+    const mgt_mlp_shape_t shape{opt.state_len, opt.state_value_count, plan.physical_hd1, plan.physical_hd2, opt.nrd, opt.output_dim};
+    const uint32_t B = opt.batch_size;
+    const uint64_t P = plan.total_params;
+    if (mgt_mlp_param_count(&shape) != P) return EXIT_FAILURE;
+
+    std::vector<float> weights(P), adam_m(P, 0.0f), adam_v(P, 0.0f);
+    InitialWeights(&weights);
+    const bool resumed = !opt.resume_checkpoint.empty();
+    if (resumed && !ReadCheckpoint(opt.resume_checkpoint, &weights, &adam_m, &adam_v)) return EXIT_FAILURE;
+    uint8_t moves[18 * 80], target[80];
+    BuildCyclicPuzzle(plan, moves, target);
+
+    mgt_engine_t* engine = nullptr;
+    if (mgt_engine_create(static_cast<int32_t>(opt.device_id), &engine) != MGT_OK) return EXIT_FAILURE;
+    // the communicator stands where the reference creates its NCCL context, also for one rank (tool:708-713)
+    mgt_comm_t* comm = nullptr;
+    if (mgt_comm_create(static_cast<int32_t>(opt.device_id), opt.world_size, opt.global_rank, opt.nccl_id_file.empty() ? nullptr : opt.nccl_id_file.c_str(), P, &comm) != MGT_OK) {
+        return EXIT_FAILURE;
+    }
+    const bool comm_enabled = true;
+
+    float *d_w = nullptr, *d_labels = nullptr, *d_walk_labels = nullptr, *d_loss = nullptr, *d_ws = nullptr, *d_m = nullptr, *d_v = nullptr;
+    uint16_t* d_w_half = nullptr;
+    mgt_train_state_t *d_states = nullptr, *d_moves = nullptr, *d_target = nullptr;
+    mgt_walk_meta_t* d_meta = nullptr;
+    float* d_grad = mgt_comm_gradient_buffer(comm);  // peers map this buffer; with one rank it is plain device memory
+    const uint64_t ws_floats = mgt_mlp_loss_grad_workspace_floats(&shape, B, opt.input_grad_partial_chunks, opt.input_grad_fp16, opt.linear_fp16);
+    if (ws_floats == 0 || d_grad == nullptr) return EXIT_FAILURE;
+    cudaStream_t compute = nullptr, comm_stream = nullptr;
+    bool ok = CUDA_OK(cudaMalloc(&d_w, P * 4)) && (!(opt.linear_fp16 && opt.persistent_half_weights) || CUDA_OK(cudaMalloc(&d_w_half, P * 2))) &&
+              CUDA_OK(cudaMalloc(&d_labels, static_cast<uint64_t>(B) * opt.output_dim * 4)) &&
+              (opt.output_dim == 1 || CUDA_OK(cudaMalloc(&d_walk_labels, static_cast<uint64_t>(B) * 4))) && CUDA_OK(cudaMalloc(&d_loss, 4)) &&
+              CUDA_OK(cudaMalloc(&d_ws, ws_floats * 4)) && CUDA_OK(cudaMalloc(&d_m, P * 4)) && CUDA_OK(cudaMalloc(&d_v, P * 4)) &&
+              CUDA_OK(cudaMalloc(&d_states, static_cast<uint64_t>(B) * 80)) && CUDA_OK(cudaMalloc(&d_meta, static_cast<uint64_t>(B) * 16)) &&
+              CUDA_OK(cudaMalloc(&d_moves, 18 * 80)) && CUDA_OK(cudaMalloc(&d_target, 80)) &&
+              CUDA_OK(cudaStreamCreateWithFlags(&compute, cudaStreamNonBlocking)) && CUDA_OK(cudaStreamCreateWithFlags(&comm_stream, cudaStreamNonBlocking));
+    if (!ok) return EXIT_FAILURE;
+    ok = CUDA_OK(cudaMemcpy(d_w, weights.data(), P * 4, cudaMemcpyHostToDevice)) && CUDA_OK(cudaMemcpy(d_m, adam_m.data(), P * 4, cudaMemcpyHostToDevice)) &&
+         CUDA_OK(cudaMemcpy(d_v, adam_v.data(), P * 4, cudaMemcpyHostToDevice)) && CUDA_OK(cudaMemcpy(d_moves, moves, sizeof(moves), cudaMemcpyHostToDevice)) &&
+         CUDA_OK(cudaMemcpy(d_target, target, sizeof(target), cudaMemcpyHostToDevice));
+    if (!ok) return EXIT_FAILURE;
+    if (d_w_half != nullptr && mgt_launch_float_to_half(d_w, P, d_w_half, compute) != MGT_OK) return EXIT_FAILURE;
+
+    std::filesystem::create_directories(opt.output_dir);
+    std::ofstream log(std::filesystem::path(opt.output_dir) / "train.log");
+    std::ofstream profile(std::filesystem::path(opt.output_dir) / "profile.jsonl");
+    cudaEvent_t ev_start, ev_walk, ev_backward, ev_allreduce, ev_stop, ev_comm_done;
+    if (!CUDA_OK(cudaEventCreate(&ev_start)) || !CUDA_OK(cudaEventCreate(&ev_walk)) || !CUDA_OK(cudaEventCreate(&ev_backward)) ||
+        !CUDA_OK(cudaEventCreate(&ev_allreduce)) || !CUDA_OK(cudaEventCreate(&ev_stop)) ||
+        !CUDA_OK(cudaEventCreateWithFlags(&ev_comm_done, cudaEventDisableTiming))) return EXIT_FAILURE;
+    const bool overlap = comm_enabled && opt.overlap_allreduce && opt.world_size > 1;
+    const uint32_t expected_ranges = 2U * opt.nrd + 3U;
+    std::vector<cudaEvent_t> ready_events;
+    if (overlap) {
+        ready_events.resize(expected_ranges + 1U, nullptr);
+        for (cudaEvent_t& ev : ready_events)
+            if (!CUDA_OK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming))) return EXIT_FAILURE;
+    }
+    log << StartLogLine(plan, overlap, comm_enabled, resumed);
+
+    const mgt_random_walk_config_t walk_cfg{B, opt.k_min, opt.k_max, opt.move_count, opt.state_len, plan.padded_state_dim};
+    float last_loss = 0.0f;
+    for (uint32_t step = 0; step < opt.steps; ++step) {
+        if (!CUDA_OK(cudaEventRecord(ev_start, compute))) return EXIT_FAILURE;
+        float* walk_labels = opt.output_dim == 1 ? d_labels : d_walk_labels;
+        if (mgt_launch_random_walk(&walk_cfg, opt.seed, 0, step, opt.global_rank, d_moves, d_target, d_states, walk_labels, d_meta, compute) != MGT_OK) return EXIT_FAILURE;
+        if (opt.output_dim > 1 && mgt_launch_expand_scalar_labels(d_walk_labels, B, opt.output_dim, d_labels, compute) != MGT_OK) return EXIT_FAILURE;
+        if (!CUDA_OK(cudaEventRecord(ev_walk, compute))) return EXIT_FAILURE;
+
+        // the resumed run restarts its step counter, as the reference does (tool:765,830)
+        const mgt_adamw_config_t adamw{P, static_cast<uint64_t>(step) + 1ULL, opt.lr, 0.9f, 0.999f, 1.0e-8f, opt.weight_decay};
+        ExchangeContext exchange;
+        if (overlap) {
+            exchange.enabled = true;
+            exchange.comm = comm;
+            exchange.comm_stream = comm_stream;
+            exchange.events = &ready_events;
+            exchange.bucket_params = std::max<uint64_t>(1ULL, opt.allreduce_bucket_bytes / sizeof(float));
+            exchange.adamw = adamw;
+            exchange.w = d_w; exchange.w_half = d_w_half; exchange.m = d_m; exchange.v = d_v;
+        }
+        mgt_backward_profile_t bw{};
+        const mgt_status_t st = mgt_launch_mlp_loss_grad(engine, &shape, d_w, d_w_half, d_states, d_labels, B, d_loss, d_grad, d_ws, ws_floats,
+                                                         opt.input_grad_partial_chunks, opt.input_grad_positions_per_block, opt.input_grad_fp16,
+                                                         opt.linear_fp16, opt.backward_profile ? &bw : nullptr, overlap ? OnGradientReady : nullptr,
+                                                         overlap ? &exchange : nullptr, compute, opt.input_grad_position_tile);
+        if (st != MGT_OK) {
+            log << "rank=" << opt.global_rank << " step=" << step << " phase=backward status=" << mgt_status_name(st) << " status_code=" << st << "\n";
+            std::cerr << "backward failed: " << mgt_status_name(st) << " (" << st << ")\n";
+            return EXIT_FAILURE;
+        }
+        if (!CUDA_OK(cudaEventRecord(ev_backward, compute))) return EXIT_FAILURE;
+        uint32_t overlap_ranges = 0, overlap_chunks = 0;
+        bool weights_updated = false;
+        if (overlap) {
+            if (exchange.failed || exchange.scheduled_ranges != expected_ranges || !exchange.Flush(compute)) return EXIT_FAILURE;
+            overlap_ranges = exchange.scheduled_ranges;
+            overlap_chunks = exchange.scheduled_chunks;
+            if (!CUDA_OK(cudaEventRecord(ev_comm_done, comm_stream)) || !CUDA_OK(cudaStreamWaitEvent(compute, ev_comm_done, 0))) return EXIT_FAILURE;
+            weights_updated = true;  // AdamW ran inside the exchange kernels
+        } else if (opt.world_size > 1) {
+            const mgt_allreduce_config_t ar{opt.world_size, opt.global_rank, step, P};
+            if (mgt_comm_allreduce_average(comm, &ar, d_grad, compute) != MGT_OK) return EXIT_FAILURE;
+            overlap_chunks = 1;
+        }
+        if (!CUDA_OK(cudaEventRecord(ev_allreduce, compute))) return EXIT_FAILURE;
+        if (!weights_updated) {
+            const mgt_status_t ad = d_w_half != nullptr ? mgt_launch_adamw_with_half_mirror(&adamw, d_w, d_w_half, d_grad, d_m, d_v, compute)
+                                                        : mgt_launch_adamw(&adamw, d_w, d_grad, d_m, d_v, compute);
+            if (ad != MGT_OK) return EXIT_FAILURE;
+        }
+        if (!CUDA_OK(cudaEventRecord(ev_stop, compute)) || !CUDA_OK(cudaEventSynchronize(ev_stop))) return EXIT_FAILURE;
+
+        StepRecord rec{};
+        rec.step = step;
+        if (!CUDA_OK(cudaEventElapsedTime(&rec.step_ms, ev_start, ev_stop)) || !CUDA_OK(cudaEventElapsedTime(&rec.walk_ms, ev_start, ev_walk)) ||
+            !CUDA_OK(cudaEventElapsedTime(&rec.backward_ms, ev_walk, ev_backward)) || !CUDA_OK(cudaEventElapsedTime(&rec.allreduce_ms, ev_backward, ev_allreduce)) ||
+            !CUDA_OK(cudaEventElapsedTime(&rec.adam_ms, ev_allreduce, ev_stop))) return EXIT_FAILURE;
+        if (!CUDA_OK(cudaMemcpy(&last_loss, d_loss, 4, cudaMemcpyDeviceToHost))) return EXIT_FAILURE;
+        int32_t code = 0;
+        if (mgt_engine_check(engine, compute, &code) != MGT_OK || mgt_comm_check(comm, comm_stream, &code) != MGT_OK) {
+            std::cerr << "device wait timed out (code " << code << ")\n";
+            return EXIT_FAILURE;
+        }
+        size_t free_bytes = 0, total_bytes = 0;
+        if (!CUDA_OK(cudaMemGetInfo(&free_bytes, &total_bytes))) return EXIT_FAILURE;
+        rec.loss = last_loss;
+        rec.memory_bytes = total_bytes - free_bytes;
+        rec.overlap_ranges = overlap_ranges;
+        rec.overlap_chunks = overlap_chunks;
+        const float bwv[7] = {bw.input_forward_ms, bw.hidden_forward_ms, bw.residual_forward_ms, bw.output_ms, bw.residual_backward_ms, bw.hidden_backward_ms, bw.input_grad_ms};
+        std::copy(bwv, bwv + 7, rec.bw);
+        log << StepLogLine(plan, rec);
+        profile << StepProfileRow(plan, rec, overlap);
+    }
+
+    if (opt.write_artifacts) {
+        if (!CUDA_OK(cudaMemcpy(weights.data(), d_w, P * 4, cudaMemcpyDeviceToHost)) || !CUDA_OK(cudaMemcpy(adam_m.data(), d_m, P * 4, cudaMemcpyDeviceToHost)) ||
+            !CUDA_OK(cudaMemcpy(adam_v.data(), d_v, P * 4, cudaMemcpyDeviceToHost))) return EXIT_FAILURE;
+        if (!WriteWeights(opt.output_dir, plan, weights) || !WriteCheckpoint(opt.output_dir, plan, weights, adam_m, adam_v)) return EXIT_FAILURE;
+    }
+    if (!WriteMetadataEnv(opt.output_dir, plan, overlap, comm_enabled, resumed) || !WriteLayersJson(opt.output_dir, plan) ||
+        !WriteLinearOpsManifest(opt.output_dir, plan)) return EXIT_FAILURE;
+
+    if (mgt_comm_destroy(comm) != MGT_OK) return EXIT_FAILURE;
+    mgt_engine_destroy(engine);
+    for (cudaEvent_t ev : ready_events) cudaEventDestroy(ev);
+    for (cudaEvent_t ev : {ev_start, ev_walk, ev_backward, ev_allreduce, ev_stop, ev_comm_done}) cudaEventDestroy(ev);
+    for (void* p : {static_cast<void*>(d_target), static_cast<void*>(d_moves), static_cast<void*>(d_meta), static_cast<void*>(d_states), static_cast<void*>(d_v),
+                    static_cast<void*>(d_m), static_cast<void*>(d_ws), static_cast<void*>(d_loss), static_cast<void*>(d_labels), static_cast<void*>(d_walk_labels),
+                    static_cast<void*>(d_w_half), static_cast<void*>(d_w)})
+        if (p != nullptr) cudaFree(p);
+    cudaStreamDestroy(comm_stream);
+    cudaStreamDestroy(compute);
+    std::cout << "native_train_smoke_ok loss=" << last_loss << "\n";
+    return EXIT_SUCCESS;
+}
