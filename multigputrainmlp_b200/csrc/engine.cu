@@ -103,7 +103,7 @@ Workspace PlanWorkspace(const mgt_mlp_shape_t& s, uint32_t B, uint32_t sm_count)
     w.off_partial = take(w.partial_floats * 4);
     w.head_blocks = kHeadBlocks;
     w.off_head = take((uint64_t)kHeadBlocks * (2ULL * s.hd2 + 2) * 4);
-    w.colsum_floats = (uint64_t)sm_count * 4 * (s.hd1 > s.hd2 ? s.hd1 : s.hd2);
+    w.colsum_floats = (uint64_t)sm_count * 8 * (s.hd1 > s.hd2 ? s.hd1 : s.hd2);
     w.off_colsum = take(w.colsum_floats * 4);
     // internal fp16 weight copy (used when the caller's mirror cannot be addressed by TMA as it lies)
     const uint64_t wint_halfs = (uint64_t)(w.IN + 1) * w.p_w1 + (uint64_t)s.hd1 * w.p_w2 + 2ULL * w.R * s.hd2 * w.p_w2 + (uint64_t)s.hd2 * w.p_wout;
@@ -194,14 +194,14 @@ mgt_status_t LaunchGemm(mgt_engine* e, const CUtensorMap& ta, const CUtensorMap&
 }
 
 // Tile configurations. BN = 224 serves the p888 residual width without padded MMA columns.
-template <int BN, Epi EPI> using CfgFwd = GemmCfg<BN, 1, false, BSource::kTmaMN, EPI, 4, 4>;   // act[K-major] x W[K][N]
-template <int BN, Epi EPI> using CfgDx = GemmCfg<BN, 1, false, BSource::kTmaK, EPI, 4, 4>;     // dz[K-major] x W[N][K]
-template <int BN> using CfgDw = GemmCfg<BN, 1, true, BSource::kTmaMN, Epi::kPartialF32, 4, 4>; // act^T x dz
+template <int BN, Epi EPI> using CfgFwd = GemmCfg<BN, 1, false, BSource::kTmaMN, EPI, 3, 3>;   // act[K-major] x W[K][N]
+template <int BN, Epi EPI> using CfgDx = GemmCfg<BN, 1, false, BSource::kTmaK, EPI, 3, 3>;     // dz[K-major] x W[N][K]
+template <int BN> using CfgDw = GemmCfg<BN, 1, true, BSource::kTmaMN, Epi::kPartialF32, 3, 3>; // act^T x dz
 using CfgEmbFwd = GemmCfg<256, 2, true, BSource::kOneHotFwd, Epi::kEmbFwd, 4, 2>;
 using CfgEmbGrad = GemmCfg<256, 2, true, BSource::kOneHotGrad, Epi::kEmbGrad, 4, 2>;
-using CfgDbgKK = GemmCfg<256, 1, false, BSource::kTmaK, Epi::kPartialF32, 4, 4>;
-using CfgDbgKM = GemmCfg<256, 1, false, BSource::kTmaMN, Epi::kPartialF32, 4, 4>;
-using CfgDbgMK = GemmCfg<256, 1, true, BSource::kTmaK, Epi::kPartialF32, 4, 4>;
+using CfgDbgKK = GemmCfg<256, 1, false, BSource::kTmaK, Epi::kPartialF32, 3, 3>;
+using CfgDbgKM = GemmCfg<256, 1, false, BSource::kTmaMN, Epi::kPartialF32, 3, 3>;
+using CfgDbgMK = GemmCfg<256, 1, true, BSource::kTmaK, Epi::kPartialF32, 3, 3>;
 
 inline uint32_t PickBN(uint32_t n) { return n <= 224 ? 224U : 256U; }
 
@@ -475,7 +475,7 @@ mgt_status_t GemmBackpropInput(mgt_engine* e, cudaStream_t st, const __half* dz,
     a.add_f32 = epi.add_f32; a.ld_add = epi.ld_add; a.mask = epi.mask; a.ld_mask = epi.ld_mask;
     const uint64_t units = (uint64_t)a.m_tiles * a.n_tiles;
     const uint32_t grid = (uint32_t)(units < (uint64_t)e->sm_count ? units : (uint64_t)e->sm_count);
-    const uint32_t rows = grid * 4U;
+    const uint32_t rows = grid * 8U;  // one row per epilogue warp
     if ((uint64_t)rows * N > colsum_floats) return MGT_CAPACITY_EXCEEDED;
     if (cudaMemsetAsync(colsum, 0, (uint64_t)rows * N * sizeof(float), st) != cudaSuccess) return MGT_CUDA_FAILURE;
     a.colsum = colsum;

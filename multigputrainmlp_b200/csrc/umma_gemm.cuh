@@ -3,8 +3,8 @@
 //   D[M x N] (fp32, TMEM) = A[M x K] * B[K x N]      fp16 operands, 128B-swizzled shared memory
 //
 // One CTA per SM. Warp 0 feeds operands with TMA (plain per-CTA loads, no multicast), warp 1
-// issues tcgen05.mma from one thread and owns TMEM, warps 2-5 drain the accumulator
-// (tcgen05.ld -> registers -> fused epilogue -> global), and, for the embedding layers, warps 6-13
+// issues tcgen05.mma from one thread and owns TMEM, warps 2-9 drain the accumulator
+// (tcgen05.ld -> registers -> fused epilogue -> global), and, for the embedding layers, warps 10-17
 // synthesise the one-hot operand directly in shared memory from the 80-byte puzzle states, so the
 // one-hot matrix never exists in HBM.
 //
@@ -51,8 +51,8 @@ struct GemmArgs {
     uint32_t ld_mask;
     float* partial;
     // Optional fp32 column sums of the values the kMaskF16 / kAddMaskF32F16 epilogues produce
-    // (bias gradients): row (blockIdx.x * 4 + quad) of colsum[gridDim.x * 4][N] accumulates the
-    // rows this warp handled. The buffer must be zero before the launch.
+    // (bias gradients): row (blockIdx.x * 8 + epilogue warp) of colsum[gridDim.x * 8][N] accumulates
+    // what that warp handled. The buffer must be zero before the launch.
     float* colsum;
     // one-hot operand synthesis
     const uint8_t* states;   // [samples][80]
@@ -82,9 +82,16 @@ struct GemmCfg {
     static constexpr int B_STAGE_BYTES = NACC_ * B_ACC_BYTES;
     static constexpr int ACC_BUFS = 2 / NACC_;
     static constexpr int ACC_COLS = 256;  // TMEM columns reserved per accumulator
+    static constexpr int EPI_WARPS = 8;
     static constexpr int SYNTH_WARPS = 8;
-    static constexpr int THREADS = kOneHot ? 192 + 32 * SYNTH_WARPS : 192;
-    static constexpr int SMEM_BYTES = 1024 + SA_ * A_STAGE_BYTES + SB_ * B_STAGE_BYTES + 256;
+    static constexpr int FIRST_SYNTH_THREAD = 64 + 32 * EPI_WARPS;
+    static constexpr int THREADS = FIRST_SYNTH_THREAD + (kOneHot ? 32 * SYNTH_WARPS : 0);
+    static constexpr int EPI_TILE_PITCH = 36;
+    // per epilogue warp: a padded 32x32 fp32 tile plus 32 words of ReLU-mask bits (the embedding
+    // epilogues write transposed and need no staging)
+    static constexpr int EPI_WARP_BYTES = kOneHot ? 0 : (32 * EPI_TILE_PITCH * 4 + 128);
+    static constexpr int EPI_STAGE_BYTES = EPI_WARPS * EPI_WARP_BYTES;
+    static constexpr int SMEM_BYTES = 1024 + SA_ * A_STAGE_BYTES + SB_ * B_STAGE_BYTES + 256 + EPI_STAGE_BYTES;
     static_assert(BN_ % 16 == 0 && BN_ >= 16 && BN_ <= 256, "UMMA N");
     static_assert(BN_ % 32 == 0, "epilogue drains 32 columns at a time");
     static_assert(NACC_ == 1 || NACC_ == 2, "one or two accumulators");
@@ -172,21 +179,6 @@ __device__ __forceinline__ uint32_t load_mask32(const __half* src, uint32_t vali
     return bits;
 }
 
-// Sums v[j] over the 32 lanes of the warp for every j; lane l returns the total of column l.
-__device__ __forceinline__ float warp_column_sums(float (&v)[32], uint32_t lane) {
-#pragma unroll
-    for (int step = 16; step >= 1; step >>= 1) {
-        const bool upper = (lane & step) != 0U;
-#pragma unroll
-        for (int j = 0; j < step; ++j) {
-            const float send = upper ? v[j] : v[j + step];
-            const float recv = __shfl_xor_sync(0xFFFFFFFFU, send, step);
-            v[j] = (upper ? v[j + step] : v[j]) + recv;
-        }
-    }
-    return v[0];
-}
-
 }  // namespace detail
 
 template <class Cfg>
@@ -211,6 +203,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     uint64_t* acc_empty = acc_full + ACC_BUFS;
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + ACC_BUFS);
     volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_holder + 1);
+    float* epi_stage = reinterpret_cast<float*>(b_ring + SB * Cfg::B_STAGE_BYTES + 256);
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31U;
@@ -227,7 +220,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
         for (int s = 0; s < ACC_BUFS; ++s) {
             mbar_init(&acc_full[s], 1);
-            mbar_init(&acc_empty[s], 128);
+            mbar_init(&acc_empty[s], 32 * Cfg::EPI_WARPS);
         }
         *cta_abort = 0;
         fence_barrier_init();
@@ -349,9 +342,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             }
         }
         __syncwarp();
-    } else if (warp < 6) {
+    } else if (warp < 2U + Cfg::EPI_WARPS) {
         // ------------------------------- epilogue -----------------------------------------
-        const uint32_t quad = warp & 3U;  // TMEM lanes [32*quad, 32*quad+32) belong to this warp
+        // Eight warps: TMEM lanes [32*quad, 32*quad+32) can only be read by warps with warp%4 == quad, so two
+        // warps share a quadrant and take alternate 32-column chunks.
+        const uint32_t ew = warp - 2U;
+        const uint32_t quad = warp & 3U;
+        const uint32_t chunk_parity = ew >> 2;
+        constexpr uint32_t TP = Cfg::EPI_TILE_PITCH;  // floats per staged row (16-byte aligned, bank-friendly)
+        float* tile = epi_stage + ew * (Cfg::EPI_WARP_BYTES / 4);
+        uint32_t* mask_words = reinterpret_cast<uint32_t*>(tile + 32 * TP);
         uint32_t unit_iter = 0;
         bool ok = true;
         for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++unit_iter) {
@@ -361,17 +361,20 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             // the TMEM loads below are warp-collective, so the whole warp takes the same way out
             if (!__all_sync(0xFFFFFFFFU, mbar_wait(&acc_full[ab], aph, cta_abort, kAbortEpilogueWait))) { ok = false; break; }
             tc_fence_after();
-            const uint32_t m = mt * BM + quad * 32U + lane;
+            const uint32_t m_base = mt * BM + quad * 32U;
+            const uint32_t m = m_base + lane;
             const bool m_ok = m < args.M;
+            const uint32_t rows_ok = m_base < args.M ? min(32U, args.M - m_base) : 0U;
 #pragma unroll 1
             for (int acc = 0; acc < NACC; ++acc) {
 #pragma unroll 1
                 for (int cc = 0; cc < BN / 32; ++cc) {
+                    if ((static_cast<uint32_t>(cc) & 1U) != chunk_parity) continue;
+                    const uint32_t n0 = (nt * NACC + acc) * BN + cc * 32;
+                    if (n0 >= args.N) continue;
                     uint32_t r[32];
                     tmem_ld_32x32(tmem_base + ((quad * 32U) << 16) + ab * (NACC * Cfg::ACC_COLS) + acc * Cfg::ACC_COLS + cc * 32, r);
                     tmem_ld_wait();
-                    const uint32_t n0 = (nt * NACC + acc) * BN + cc * 32;
-                    if (n0 >= args.N) continue;
                     const uint32_t valid = min(32U, args.N - n0);
                     float v[32];
 #pragma unroll
@@ -393,48 +396,140 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                                     if (args.splits > 1U) atomicAdd(dst, v[j]); else *dst = v[j];
                                 }
                         }
-                    } else if constexpr (Cfg::EPI == Epi::kPartialF32) {
-                        if (m_ok) {
-                            float* dst = args.partial + (static_cast<uint64_t>(sp) * args.M + m) * args.N + n0;
-                            detail::store_f32x32(dst, v, valid, (args.N & 3U) == 0U);
-                        }
                     } else {
-                        if (m_ok) {
-                            if constexpr (Cfg::EPI == Epi::kBiasReluF16 || Cfg::EPI == Epi::kBiasReluF32F16 || Cfg::EPI == Epi::kBiasResReluF32F16) {
+                        // Row-major tensors: a TMEM lane holds one row, but global memory wants a warp on whole rows.
+                        // Each warp stages operands and results through its own padded 32x32 fp32 tile in shared
+                        // memory, so that every global access is a full 64/128-byte row segment: 16-byte vectors,
+                        // four (fp32) or eight (fp16) rows per instruction. Ragged shapes take the scalar form.
+                        constexpr bool kHasBias = Cfg::EPI == Epi::kBiasReluF16 || Cfg::EPI == Epi::kBiasReluF32F16 || Cfg::EPI == Epi::kBiasResReluF32F16;
+                        constexpr bool kHasAdd = Cfg::EPI == Epi::kBiasResReluF32F16 || Cfg::EPI == Epi::kAddMaskF32F16;
+                        constexpr bool kHasMask = Cfg::EPI == Epi::kMaskF16 || Cfg::EPI == Epi::kAddMaskF32F16;
+                        constexpr bool kOutF32 = Cfg::EPI == Epi::kBiasReluF32F16 || Cfg::EPI == Epi::kBiasResReluF32F16 || Cfg::EPI == Epi::kAddMaskF32F16;
+                        constexpr bool kPartial = Cfg::EPI == Epi::kPartialF32;
+                        const bool vec = valid == 32U && (!kHasAdd || (args.ld_add & 3U) == 0U) && (!kHasMask || (args.ld_mask & 7U) == 0U) &&
+                                         (!kOutF32 || (args.ld_f32 & 3U) == 0U) && (kPartial ? (args.N & 3U) == 0U : (args.ld_f16 & 7U) == 0U);
+                        const bool col_ok = lane < valid;
+                        const uint32_t r4 = lane >> 3, c4 = (lane & 7U) * 4U;  // fp32 vectors: 4 rows x 8 lanes
+                        const uint32_t r8 = lane >> 2, c8 = (lane & 3U) * 8U;  // fp16 vectors: 8 rows x 4 lanes
+                        if constexpr (kHasBias) {
+                            const float bias_l = col_ok ? __ldg(args.bias + n0 + lane) : 0.0f;
 #pragma unroll
-                                for (int j = 0; j < 32; ++j)
-                                    if (static_cast<uint32_t>(j) < valid) v[j] += __ldg(args.bias + n0 + j);
-                            }
-                            if constexpr (Cfg::EPI == Epi::kBiasResReluF32F16 || Cfg::EPI == Epi::kAddMaskF32F16) {
-                                float a[32];
-                                detail::load_f32x32(args.add_f32 + static_cast<uint64_t>(m) * args.ld_add + n0, a, valid, (args.ld_add & 3U) == 0U);
-#pragma unroll
-                                for (int j = 0; j < 32; ++j) v[j] = a[j] + v[j];
-                            }
-                            if constexpr (Cfg::EPI == Epi::kMaskF16 || Cfg::EPI == Epi::kAddMaskF32F16) {
-                                const uint32_t bits = detail::load_mask32(args.mask + static_cast<uint64_t>(m) * args.ld_mask + n0, valid, (args.ld_mask & 7U) == 0U);
-#pragma unroll
-                                for (int j = 0; j < 32; ++j) v[j] = ((bits >> j) & 1U) ? v[j] : 0.0f;
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
-                            }
-                            if constexpr (Cfg::EPI == Epi::kBiasReluF32F16 || Cfg::EPI == Epi::kBiasResReluF32F16 || Cfg::EPI == Epi::kAddMaskF32F16)
-                                detail::store_f32x32(args.out_f32 + static_cast<uint64_t>(m) * args.ld_f32 + n0, v, valid, (args.ld_f32 & 3U) == 0U);
-                            detail::store_f16x32(args.out_f16 + static_cast<uint64_t>(m) * args.ld_f16 + n0, v, valid, (args.ld_f16 & 7U) == 0U);
+                            for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xFFFFFFFFU, bias_l, j);
                         }
-                        if constexpr (Cfg::EPI == Epi::kMaskF16 || Cfg::EPI == Epi::kAddMaskF32F16) {
-                            if (args.colsum != nullptr) {
+                        if constexpr (kHasAdd) {
+                            if (vec) {
 #pragma unroll
-                                for (int j = 0; j < 32; ++j)
-                                    if (!m_ok || static_cast<uint32_t>(j) >= valid) v[j] = 0.0f;
-                                const float total = detail::warp_column_sums(v, lane);
-                                if (lane < valid) {
-                                    float* dst = args.colsum + (static_cast<uint64_t>(blockIdx.x) * 4U + quad) * args.N + n0 + lane;
+                                for (uint32_t i = 0; i < 8U; ++i) {
+                                    const uint32_t rr = r4 + 4U * i;
+                                    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+                                    if (rr < rows_ok) x = *reinterpret_cast<const float4*>(args.add_f32 + static_cast<uint64_t>(m_base + rr) * args.ld_add + n0 + c4);
+                                    *reinterpret_cast<float4*>(tile + rr * TP + c4) = x;
+                                }
+                            } else {
+                                for (uint32_t rr = 0; rr < 32U; ++rr)
+                                    tile[rr * TP + lane] = (rr < rows_ok && col_ok) ? args.add_f32[static_cast<uint64_t>(m_base + rr) * args.ld_add + n0 + lane] : 0.0f;
+                            }
+                            __syncwarp();
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                const float4 x = *reinterpret_cast<const float4*>(tile + lane * TP + q * 4);
+                                v[q * 4] = x.x + v[q * 4];
+                                v[q * 4 + 1] = x.y + v[q * 4 + 1];
+                                v[q * 4 + 2] = x.z + v[q * 4 + 2];
+                                v[q * 4 + 3] = x.w + v[q * 4 + 3];
+                            }
+                            __syncwarp();
+                        }
+                        if constexpr (kHasMask) {
+                            uint32_t bits = 0;
+                            if (vec) {
+                                uint8_t* mask_bytes = reinterpret_cast<uint8_t*>(mask_words);
+#pragma unroll
+                                for (uint32_t i = 0; i < 4U; ++i) {
+                                    const uint32_t rr = r8 + 8U * i;
+                                    uint4 h = make_uint4(0, 0, 0, 0);
+                                    if (rr < rows_ok) h = *reinterpret_cast<const uint4*>(args.mask + static_cast<uint64_t>(m_base + rr) * args.ld_mask + n0 + c8);
+                                    const uint32_t w4[4] = {h.x, h.y, h.z, h.w};
+                                    uint32_t byte = 0;
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e) {
+                                        // a positive non-zero half: sign clear, magnitude non-zero
+                                        const uint32_t lo = w4[e] & 0xFFFFU, hi = w4[e] >> 16;
+                                        byte |= (lo != 0U && lo < 0x8000U) ? (1U << (2 * e)) : 0U;
+                                        byte |= (hi != 0U && hi < 0x8000U) ? (1U << (2 * e + 1)) : 0U;
+                                    }
+                                    mask_bytes[rr * 4U + (lane & 3U)] = static_cast<uint8_t>(byte);
+                                }
+                                __syncwarp();
+                                bits = mask_words[lane];
+                                __syncwarp();
+                            } else {
+                                for (uint32_t rr = 0; rr < 32U; ++rr) {
+                                    const bool positive = (rr < rows_ok && col_ok) ? (__half2float(args.mask[static_cast<uint64_t>(m_base + rr) * args.ld_mask + n0 + lane]) > 0.0f) : false;
+                                    const uint32_t row_bits = __ballot_sync(0xFFFFFFFFU, positive);
+                                    if (lane == rr) bits = row_bits;
+                                }
+                            }
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = ((bits >> j) & 1U) ? v[j] : 0.0f;
+                        } else if constexpr (!kPartial) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+                        }
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            *reinterpret_cast<float4*>(tile + lane * TP + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+                        __syncwarp();
+                        if constexpr (kPartial || kOutF32) {
+                            float* base = kPartial ? args.partial + (static_cast<uint64_t>(sp) * args.M + m_base) * args.N + n0
+                                                   : args.out_f32 + static_cast<uint64_t>(m_base) * args.ld_f32 + n0;
+                            const uint64_t ld = kPartial ? args.N : args.ld_f32;
+                            if (vec) {
+#pragma unroll
+                                for (uint32_t i = 0; i < 8U; ++i) {
+                                    const uint32_t rr = r4 + 4U * i;
+                                    if (rr < rows_ok) *reinterpret_cast<float4*>(base + rr * ld + c4) = *reinterpret_cast<const float4*>(tile + rr * TP + c4);
+                                }
+                            } else {
+                                for (uint32_t rr = 0; rr < rows_ok; ++rr)
+                                    if (col_ok) base[rr * ld + lane] = tile[rr * TP + lane];
+                            }
+                        }
+                        if constexpr (!kPartial) {
+                            if (vec) {
+#pragma unroll
+                                for (uint32_t i = 0; i < 4U; ++i) {
+                                    const uint32_t rr = r8 + 8U * i;
+                                    if (rr < rows_ok) {
+                                        const float4 x0 = *reinterpret_cast<const float4*>(tile + rr * TP + c8);
+                                        const float4 x1 = *reinterpret_cast<const float4*>(tile + rr * TP + c8 + 4U);
+                                        const __half2 h0 = __floats2half2_rn(x0.x, x0.y), h1 = __floats2half2_rn(x0.z, x0.w);
+                                        const __half2 h2 = __floats2half2_rn(x1.x, x1.y), h3 = __floats2half2_rn(x1.z, x1.w);
+                                        uint4 u;
+                                        u.x = *reinterpret_cast<const uint32_t*>(&h0);
+                                        u.y = *reinterpret_cast<const uint32_t*>(&h1);
+                                        u.z = *reinterpret_cast<const uint32_t*>(&h2);
+                                        u.w = *reinterpret_cast<const uint32_t*>(&h3);
+                                        *reinterpret_cast<uint4*>(args.out_f16 + static_cast<uint64_t>(m_base + rr) * args.ld_f16 + n0 + c8) = u;
+                                    }
+                                }
+                            } else {
+                                for (uint32_t rr = 0; rr < rows_ok; ++rr)
+                                    if (col_ok) args.out_f16[static_cast<uint64_t>(m_base + rr) * args.ld_f16 + n0 + lane] = __float2half_rn(tile[rr * TP + lane]);
+                            }
+                        }
+                        if constexpr (kHasMask) {
+                            if (args.colsum != nullptr) {
+                                float total = 0.0f;  // column `lane` of the staged tile, rows in order
+#pragma unroll 8
+                                for (uint32_t rr = 0; rr < 32U; ++rr) total += rr < rows_ok ? tile[rr * TP + lane] : 0.0f;
+                                if (col_ok) {
+                                    float* dst = args.colsum + (static_cast<uint64_t>(blockIdx.x) * Cfg::EPI_WARPS + ew) * args.N + n0 + lane;
                                     *dst += total;  // this warp is the only writer of its row
                                 }
                             }
                         }
+                        __syncwarp();
                     }
                 }
             }
@@ -447,7 +542,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             // Every non-zero place of the operand is owned by one warp (set and later cleared by it),
             // so the synth warps never wait for one another: each warp polls the stage barrier itself
             // and arrives once when its share is in place.
-            const uint32_t t = threadIdx.x - 192U;  // 0 .. 32*SYNTH_WARPS-1
+            const uint32_t t = threadIdx.x - Cfg::FIRST_SYNTH_THREAD;  // 0 .. 32*SYNTH_WARPS-1
             constexpr uint32_t NT = 32U * Cfg::SYNTH_WARPS;
             const uint32_t V = args.value_pad, L = args.state_len, IN = args.in_rows;
             constexpr uint32_t ROWS = NACC * BN;  // rows of the synthesised operand per stage
@@ -496,24 +591,169 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 }
             };
             static_assert(Cfg::BSRC != BSource::kOneHotGrad || NT == 256U, "64 samples x 4 threads");
-            uint32_t it = 0;
-            uint32_t h_nt[2] = {0, 0}, h_c[2] = {0, 0};  // what each of the two stages currently holds
-            bool ok = true;
-            for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
-                uint32_t mt, nt, sp;
-                decode(unit, mt, nt, sp);
-                const uint32_t c0 = chunk_begin(sp), c1 = chunk_begin(sp + 1);
-                for (uint32_t c = c0; c < c1; ++c, ++it) {
-                    const uint32_t sb = it & 1U, pb = (it >> 1) & 1U;
-                    if (!__all_sync(0xFFFFFFFFU, mbar_wait(&empty_b[sb], pb ^ 1U, cta_abort, kAbortSynthWait))) { ok = false; break; }
-                    uint8_t* buf = b_ring + sb * Cfg::B_STAGE_BYTES;
-                    if (it >= 2U) apply(buf, sb ? h_nt[1] : h_nt[0], sb ? h_c[1] : h_c[0], 0);
-                    __syncwarp();  // a place cleared by one lane may be set by another lane of this warp
-                    apply(buf, nt, c, 0x3C00);
-                    if (sb) { h_nt[1] = nt; h_c[1] = c; } else { h_nt[0] = nt; h_c[0] = c; }
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&full_b[sb]);
+            // One stage hand-over: wait until the MMAs that read stage `sb` are done (warp-uniform).
+            auto acquire = [&](uint32_t it) -> bool {
+                return __all_sync(0xFFFFFFFFU, mbar_wait(&empty_b[it & 1U], ((it >> 1) & 1U) ^ 1U, cta_abort, kAbortSynthWait));
+            };
+            auto publish = [&](uint32_t it) {
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full_b[it & 1U]);
+            };
+            bool fast = false;
+            if constexpr (Cfg::BSRC == BSource::kOneHotFwd) {
+                // ---- forward, streaming form: a row's ones sit at k_p = p*V + s[p], increasing in p, and the
+                // chunks of a unit are visited in increasing k. Each row keeps a cursor for setting and one for
+                // clearing (two items behind); the state byte of the next position is fetched when a cursor
+                // advances, one or more chunks before it is needed, so no chunk waits for a load.
+                fast = args.splits == 1U;
+                if (fast) {
+                    constexpr uint32_t RPT = ROWS / NT;
+                    struct Cursor { uint32_t p, s0, s1; };
+                    Cursor setc[RPT], clrc[RPT];
+                    auto rewind = [&](Cursor& q, uint32_t sample) {
+                        const bool active = sample < args.samples;
+                        const uint8_t* st = args.states + static_cast<uint64_t>(sample) * 80U;
+                        q.p = active ? 0U : L;
+                        q.s0 = active ? __ldg(st) : 0U;
+                        q.s1 = (active && L > 1U) ? __ldg(st + 1) : 0U;
+                    };
+                    auto sweep = [&](Cursor& q, uint32_t sample, uint8_t* buf, uint32_t n, uint32_t k0, uint16_t value) {
+                        const uint8_t* st = args.states + static_cast<uint64_t>(sample) * 80U;
+                        while (q.p < L) {
+                            const uint32_t k = q.p * V + q.s0 - k0;  // never below the chunk: earlier chunks consumed those
+                            if (k >= 64U) break;
+                            *place(buf, n, k) = value;
+                            ++q.p;
+                            q.s0 = q.s1;
+                            q.s1 = (q.p + 1U < L) ? __ldg(st + q.p + 1U) : 0U;
+                        }
+                        const uint32_t kb = IN - k0;  // the all-ones column that multiplies the bias row
+                        if (kb < 64U && sample < args.samples) *place(buf, n, kb) = value;
+                    };
+                    uint32_t it = 0, h_nt[2] = {0, 0}, h_c[2] = {0, 0};
+                    bool ok = true;
+                    for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+                        uint32_t mt, nt, sp;
+                        decode(unit, mt, nt, sp);
+                        for (uint32_t c = 0; c < args.k_chunks; ++c, ++it) {
+                            const uint32_t sb = it & 1U;
+                            if (!acquire(it)) { ok = false; break; }
+                            uint8_t* buf = b_ring + sb * Cfg::B_STAGE_BYTES;
+                            if (it >= 2U) {
+                                const uint32_t ont = sb ? h_nt[1] : h_nt[0], oc = sb ? h_c[1] : h_c[0];
+#pragma unroll
+                                for (uint32_t i = 0; i < RPT; ++i) {
+                                    const uint32_t n = t + i * NT, sample = ont * ROWS + n;
+                                    if (oc == 0U) rewind(clrc[i], sample);
+                                    sweep(clrc[i], sample, buf, n, oc * 64U, 0);
+                                }
+                            }
+#pragma unroll
+                            for (uint32_t i = 0; i < RPT; ++i) {
+                                const uint32_t n = t + i * NT, sample = nt * ROWS + n;
+                                if (c == 0U) rewind(setc[i], sample);
+                                sweep(setc[i], sample, buf, n, c * 64U, 0x3C00);
+                            }
+                            if (sb) { h_nt[1] = nt; h_c[1] = c; } else { h_nt[0] = nt; h_c[0] = c; }
+                            publish(it);
+                        }
+                    }
+                }
+            } else {
+                // ---- gradient, pipelined form: thread (sample k = t/4, quarter q = t%4) owns up to three of
+                // the tile's positions of its sample. The state bytes of the NEXT item are fetched while the
+                // current one is published; what was set in a stage is remembered and cleared from registers.
+                const uint32_t max_positions = (ROWS + V - 1U) / V + 1U;
+                fast = max_positions <= 12U;
+                if (fast) {
+                    constexpr uint32_t kNone = 0xFFFFFFFFU;
+                    const uint32_t k = t >> 2, q = t & 3U;
+                    uint32_t cur[3];
+                    uint32_t hist0[4] = {kNone, kNone, kNone, kNone}, hist1[4] = {kNone, kNone, kNone, kNone};
+                    auto fetch = [&](uint32_t nt, uint32_t c) {
+                        const uint32_t sample = c * 64U + k, r0 = nt * ROWS;
+                        const uint32_t p_lo = r0 / V, p_hi = min((r0 + ROWS - 1U) / V, L - 1U);
+                        const uint8_t* st = args.states + static_cast<uint64_t>(sample) * 80U;
+#pragma unroll
+                        for (uint32_t j = 0; j < 3U; ++j) {
+                            const uint32_t p = p_lo + q + 4U * j;
+                            cur[j] = (sample < args.samples && p <= p_hi && p < L) ? __ldg(st + p) : kNone;
+                        }
+                    };
+                    auto offset_of = [&](uint32_t n) -> uint32_t {
+                        return (n / BN) * Cfg::B_ACC_BYTES + (n % BN) * 128U + ((((k >> 3) ^ (n & 7U)) << 4) | ((k & 7U) << 1));
+                    };
+                    uint32_t unit = blockIdx.x, mt, nt, sp;
+                    decode(unit, mt, nt, sp);
+                    uint32_t c = chunk_begin(sp), c_end = chunk_begin(sp + 1);
+                    bool have = unit < total_units && c < c_end;
+                    if (have) fetch(nt, c);
+                    uint32_t it = 0;
+                    while (have) {
+                        // coordinates of the item after this one
+                        uint32_t unit2 = unit, nt2 = nt, c2 = c + 1U, c_end2 = c_end;
+                        bool have2 = true;
+                        if (c2 >= c_end2) {
+                            unit2 += gridDim.x;
+                            have2 = unit2 < total_units;
+                            if (have2) {
+                                uint32_t mt2, sp2;
+                                decode(unit2, mt2, nt2, sp2);
+                                c2 = chunk_begin(sp2);
+                                c_end2 = chunk_begin(sp2 + 1);
+                                have2 = c2 < c_end2;
+                            }
+                        }
+                        const uint32_t sb = it & 1U;
+                        if (!acquire(it)) break;
+                        uint8_t* buf = b_ring + sb * Cfg::B_STAGE_BYTES;
+#pragma unroll
+                        for (uint32_t j = 0; j < 4U; ++j) {
+                            const uint32_t off = sb ? hist1[j] : hist0[j];
+                            if (off != kNone) *reinterpret_cast<uint16_t*>(buf + off) = 0;
+                        }
+                        __syncwarp();  // a place cleared by one lane may be set by another lane of this warp
+                        const uint32_t r0 = nt * ROWS, p_lo = r0 / V;
+                        uint32_t offs[4];
+#pragma unroll
+                        for (uint32_t j = 0; j < 3U; ++j) {
+                            const uint32_t n = (p_lo + q + 4U * j) * V + cur[j] - r0;
+                            offs[j] = (cur[j] != kNone && n < ROWS) ? offset_of(n) : kNone;
+                        }
+                        const uint32_t nb = IN - r0;  // optional all-ones row
+                        offs[3] = (q == 0U && nb < ROWS && c * 64U + k < args.samples) ? offset_of(nb) : kNone;
+#pragma unroll
+                        for (uint32_t j = 0; j < 4U; ++j) {
+                            if (offs[j] != kNone) *reinterpret_cast<uint16_t*>(buf + offs[j]) = 0x3C00;
+                            if (sb) hist1[j] = offs[j]; else hist0[j] = offs[j];
+                        }
+                        if (have2) fetch(nt2, c2);
+                        publish(it);
+                        unit = unit2; nt = nt2; c = c2; c_end = c_end2; have = have2;
+                        ++it;
+                    }
+                }
+            }
+            if (!fast) {
+                // generic form (any class count, any split): recompute the places of an item from the states
+                uint32_t it = 0;
+                uint32_t h_nt[2] = {0, 0}, h_c[2] = {0, 0};  // what each of the two stages currently holds
+                bool ok = true;
+                for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+                    uint32_t mt, nt, sp;
+                    decode(unit, mt, nt, sp);
+                    const uint32_t c0 = chunk_begin(sp), c1 = chunk_begin(sp + 1);
+                    for (uint32_t c = c0; c < c1; ++c, ++it) {
+                        const uint32_t sb = it & 1U;
+                        if (!acquire(it)) { ok = false; break; }
+                        uint8_t* buf = b_ring + sb * Cfg::B_STAGE_BYTES;
+                        if (it >= 2U) apply(buf, sb ? h_nt[1] : h_nt[0], sb ? h_c[1] : h_c[0], 0);
+                        __syncwarp();  // a place cleared by one lane may be set by another lane of this warp
+                        apply(buf, nt, c, 0x3C00);
+                        if (sb) { h_nt[1] = nt; h_c[1] = c; } else { h_nt[0] = nt; h_c[0] = c; }
+                        publish(it);
+                    }
                 }
             }
         }
