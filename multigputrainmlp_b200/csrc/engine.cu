@@ -18,6 +18,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -148,6 +149,7 @@ struct mgt_engine {
     std::mutex mu;
     cudaEvent_t ev_last = nullptr, ev_now = nullptr;
     uint64_t launches = 0;  // kernels launched through this engine (host-side count)
+    uint32_t debug_skip = 0;  // MGT_DEBUG_SKIP: timing experiments only (results are wrong when set)
 
     // fp16 2-D tensor map with 128-byte swizzle: `inner` contiguous elements per row, `outer` rows.
     bool Map(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch_elems, uint32_t box_inner, uint32_t box_outer) {
@@ -186,8 +188,14 @@ mgt_status_t LaunchGemm(mgt_engine* e, const CUtensorMap& ta, const CUtensorMap&
     }
     const uint64_t units = (uint64_t)args.m_tiles * args.n_tiles * args.splits;
     if (units == 0) return MGT_INVALID_CONFIG;
-    const uint32_t grid = (uint32_t)(units < (uint64_t)e->sm_count ? units : (uint64_t)e->sm_count);
+    uint32_t grid = (uint32_t)(units < (uint64_t)e->sm_count ? units : (uint64_t)e->sm_count);
+    if (Cfg::BSTAT) {
+        // every unit of a CTA must share the N tile: unit = mt * n_tiles + nt advances by the grid size
+        if (args.splits != 1 || args.k_chunks > (uint32_t)Cfg::SB || args.n_tiles > (uint32_t)e->sm_count) return MGT_INVALID_CONFIG;
+        if (grid >= args.n_tiles) grid = grid / args.n_tiles * args.n_tiles;
+    }
     args.status = e->status_word;
+    args.debug_skip = e->debug_skip;
     umma_gemm_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, args);
     ++e->launches;
     return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
@@ -196,6 +204,9 @@ mgt_status_t LaunchGemm(mgt_engine* e, const CUtensorMap& ta, const CUtensorMap&
 // Tile configurations. BN = 224 serves the p888 residual width without padded MMA columns.
 template <int BN, Epi EPI> using CfgFwd = GemmCfg<BN, 1, false, BSource::kTmaMN, EPI, 3, 3>;   // act[K-major] x W[K][N]
 template <int BN, Epi EPI> using CfgDx = GemmCfg<BN, 1, false, BSource::kTmaK, EPI, 3, 3>;     // dz[K-major] x W[N][K]
+// B-stationary forms for reductions of at most 256 (the residual width): weights stay in shared memory
+template <int BN, Epi EPI> using CfgFwdS = GemmCfg<BN, 1, false, BSource::kTmaMN, EPI, 3, 4, true>;
+template <int BN, Epi EPI> using CfgDxS = GemmCfg<BN, 1, false, BSource::kTmaK, EPI, 3, 4, true>;
 template <int BN> using CfgDw = GemmCfg<BN, 1, true, BSource::kTmaMN, Epi::kPartialF32, 3, 3>; // act^T x dz
 using CfgEmbFwd = GemmCfg<256, 2, true, BSource::kOneHotFwd, Epi::kEmbFwd, 4, 2>;
 using CfgEmbGrad = GemmCfg<256, 2, true, BSource::kOneHotGrad, Epi::kEmbGrad, 4, 2>;
@@ -227,42 +238,53 @@ __global__ void RepackHalfKernel(const float* __restrict__ src, uint32_t rows, u
     }
 }
 
-// grad[i] = sum over splits (fixed order) of partial[split][i]
-__global__ void ReducePartialsKernel(const float* __restrict__ partial, uint32_t splits, uint64_t count, float* __restrict__ out) {
+// grad[i] = sum over splits (fixed order) of partial[split][i]; loads of eight splits are in flight at once
+__global__ void __launch_bounds__(256)
+ReducePartialsKernel(const float* __restrict__ partial, uint32_t splits, uint64_t count, float* __restrict__ out) {
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
         float sum = partial[i];
-        for (uint32_t s = 1; s < splits; ++s) sum += partial[(uint64_t)s * count + i];
+        uint32_t s = 1;
+        for (; s + 8U <= splits; s += 8U) {
+            float x[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) x[q] = partial[(uint64_t)(s + q) * count + i];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) sum += x[q];
+        }
+        for (; s < splits; ++s) sum += partial[(uint64_t)s * count + i];
         out[i] = sum;
     }
 }
 
-// dst[c] = sum over rows r of src[r * row_stride + col_offset + c], in a fixed order: each of 8 row
-// groups adds its rows (r = g, g+8, ...) and the groups are then added 0..7. One CTA per 32 columns.
+// dst[c] = sum over rows r of src[r * row_stride + col_offset + c], in a fixed order: each of 32 row
+// groups adds its rows (r = g, g+32, ...) and the groups are then added 0..31. One CTA per 8 columns,
+// so that a few-hundred-column reduction still spreads over dozens of SMs.
+constexpr uint32_t kReduceCols = 8;
 __global__ void __launch_bounds__(256)
 ReduceRowsKernel(const float* __restrict__ src, uint32_t rows, uint64_t row_stride, uint32_t col_offset, uint32_t cols, float* __restrict__ dst) {
-    __shared__ float s_part[8][33];
-    const uint32_t lane = threadIdx.x & 31U, g = threadIdx.x >> 5;
-    const uint32_t c = blockIdx.x * 32U + lane;
+    __shared__ float s_part[32][kReduceCols + 1];
+    const uint32_t cl = threadIdx.x & (kReduceCols - 1U), g = threadIdx.x / kReduceCols;
+    const uint32_t c = blockIdx.x * kReduceCols + cl;
     float sum = 0.0f;
     if (c < cols) {
         const float* p = src + col_offset + c;
         uint32_t r = g;
-        for (; r + 24U < rows; r += 32U) {
+        for (; r + 96U < rows; r += 128U) {
             const float a0 = p[(uint64_t)r * row_stride];
-            const float a1 = p[(uint64_t)(r + 8U) * row_stride];
-            const float a2 = p[(uint64_t)(r + 16U) * row_stride];
-            const float a3 = p[(uint64_t)(r + 24U) * row_stride];
+            const float a1 = p[(uint64_t)(r + 32U) * row_stride];
+            const float a2 = p[(uint64_t)(r + 64U) * row_stride];
+            const float a3 = p[(uint64_t)(r + 96U) * row_stride];
             sum += a0; sum += a1; sum += a2; sum += a3;
         }
-        for (; r < rows; r += 8U) sum += p[(uint64_t)r * row_stride];
+        for (; r < rows; r += 32U) sum += p[(uint64_t)r * row_stride];
     }
-    s_part[g][lane] = sum;
+    s_part[g][cl] = sum;
     __syncthreads();
     if (g == 0 && c < cols) {
-        float total = s_part[0][lane];
+        float total = s_part[0][cl];
 #pragma unroll
-        for (int q = 1; q < 8; ++q) total += s_part[q][lane];
+        for (int q = 1; q < 32; ++q) total += s_part[q][cl];
         dst[c] = total;
     }
 }
@@ -461,6 +483,7 @@ mgt_status_t GemmForward(mgt_engine* e, cudaStream_t st, const __half* act, uint
     CUtensorMap ta, tb;
     MGT_MAP(e->Map(&ta, act, K, M, act_pitch, 64, 128));
     MGT_MAP(e->Map(&tb, w, N, K, w_pitch, 64, 64));
+    if (a.k_chunks <= 4) return bn == 224 ? LaunchGemm<CfgFwdS<224, EPI>>(e, ta, tb, a, st) : LaunchGemm<CfgFwdS<256, EPI>>(e, ta, tb, a, st);
     return bn == 224 ? LaunchGemm<CfgFwd<224, EPI>>(e, ta, tb, a, st) : LaunchGemm<CfgFwd<256, EPI>>(e, ta, tb, a, st);
 }
 
@@ -474,7 +497,9 @@ mgt_status_t GemmBackpropInput(mgt_engine* e, cudaStream_t st, const __half* dz,
     a.out_f32 = epi.out_f32; a.ld_f32 = epi.ld_f32; a.out_f16 = epi.out_f16; a.ld_f16 = epi.ld_f16;
     a.add_f32 = epi.add_f32; a.ld_add = epi.ld_add; a.mask = epi.mask; a.ld_mask = epi.ld_mask;
     const uint64_t units = (uint64_t)a.m_tiles * a.n_tiles;
-    const uint32_t grid = (uint32_t)(units < (uint64_t)e->sm_count ? units : (uint64_t)e->sm_count);
+    const bool stationary = a.k_chunks <= 4 && a.n_tiles <= (uint32_t)e->sm_count;
+    uint32_t grid = (uint32_t)(units < (uint64_t)e->sm_count ? units : (uint64_t)e->sm_count);
+    if (stationary && grid >= a.n_tiles) grid = grid / a.n_tiles * a.n_tiles;  // as LaunchGemm picks it
     const uint32_t rows = grid * 8U;  // one row per epilogue warp
     if ((uint64_t)rows * N > colsum_floats) return MGT_CAPACITY_EXCEEDED;
     if (cudaMemsetAsync(colsum, 0, (uint64_t)rows * N * sizeof(float), st) != cudaSuccess) return MGT_CUDA_FAILURE;
@@ -482,8 +507,12 @@ mgt_status_t GemmBackpropInput(mgt_engine* e, cudaStream_t st, const __half* dz,
     CUtensorMap ta, tb;
     MGT_MAP(e->Map(&ta, dz, K, M, dz_pitch, 64, 128));
     MGT_MAP(e->Map(&tb, w, K, N, w_pitch, 64, bn));
-    MGT_TRY(bn == 224 ? LaunchGemm<CfgDx<224, EPI>>(e, ta, tb, a, st) : LaunchGemm<CfgDx<256, EPI>>(e, ta, tb, a, st));
-    ReduceRowsKernel<<<(N + 31) / 32, 256, 0, st>>>(colsum, rows, N, 0, N, bias_grad);
+    if (stationary) {
+        MGT_TRY(bn == 224 ? LaunchGemm<CfgDxS<224, EPI>>(e, ta, tb, a, st) : LaunchGemm<CfgDxS<256, EPI>>(e, ta, tb, a, st));
+    } else {
+        MGT_TRY(bn == 224 ? LaunchGemm<CfgDx<224, EPI>>(e, ta, tb, a, st) : LaunchGemm<CfgDx<256, EPI>>(e, ta, tb, a, st));
+    }
+    ReduceRowsKernel<<<(N + kReduceCols - 1) / kReduceCols, 256, 0, st>>>(colsum, rows, N, 0, N, bias_grad);
     ++e->launches;
     return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
 }
@@ -565,6 +594,7 @@ mgt_status_t mgt_engine_create(int32_t device_id, mgt_engine_t** out_engine) {
         return MGT_CUDA_FAILURE;
     }
     e->encode = reinterpret_cast<EncodeTiledFn>(fn);
+    if (const char* dbg = std::getenv("MGT_DEBUG_SKIP")) e->debug_skip = static_cast<uint32_t>(std::atoi(dbg));
     if (cudaMalloc(&e->status_word, sizeof(int)) != cudaSuccess || cudaMemset(e->status_word, 0, sizeof(int)) != cudaSuccess) {
         delete e;
         return MGT_CUDA_FAILURE;
@@ -715,9 +745,9 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     if (OUT == 1U) {
         HeadOut1Kernel<<<kHeadBlocks, kHeadThreads, 0, st>>>(w + OutputWeight(s), w + OutputBias(s), labels, x_f32, ws.p_f32, B, H2, dzf, dz_cur, ws.p_dz, head_partial);
         const uint32_t items = 2 * H2 + 2;
-        ReduceRowsKernel<<<(H2 + 1 + 31) / 32, 256, 0, st>>>(head_partial, kHeadBlocks, items, 0, H2 + 1, grad + OutputWeight(s));
+        ReduceRowsKernel<<<(H2 + 1 + kReduceCols - 1) / kReduceCols, 256, 0, st>>>(head_partial, kHeadBlocks, items, 0, H2 + 1, grad + OutputWeight(s));
         ReduceRowsKernel<<<1, 256, 0, st>>>(head_partial, kHeadBlocks, items, H2 + 1, 1, loss);
-        ReduceRowsKernel<<<(H2 + 31) / 32, 256, 0, st>>>(head_partial, kHeadBlocks, items, H2 + 2, H2, head_bias_dst);
+        ReduceRowsKernel<<<(H2 + kReduceCols - 1) / kReduceCols, 256, 0, st>>>(head_partial, kHeadBlocks, items, H2 + 2, H2, head_bias_dst);
         e->launches += 4;
     } else {
         float* dy = reinterpret_cast<float*>(base + ws.off_dy);
@@ -727,7 +757,7 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
         const uint32_t items = H2 * OUT + OUT;
         HeadOutNGradKernel<<<(items + 127) / 128, 128, 0, st>>>(x_h(R), ws.p_act, dy_h, hw.pout, dy, B, H2, OUT, grad + OutputWeight(s), grad + OutputBias(s));
         ReduceRowsKernel<<<1, 256, 0, st>>>(head_partial, kHeadBlocks, H2 + 1, 0, 1, loss);
-        ReduceRowsKernel<<<(H2 + 31) / 32, 256, 0, st>>>(head_partial, kHeadBlocks, H2 + 1, 1, H2, head_bias_dst);
+        ReduceRowsKernel<<<(H2 + kReduceCols - 1) / kReduceCols, 256, 0, st>>>(head_partial, kHeadBlocks, H2 + 1, 1, H2, head_bias_dst);
         e->launches += 4;
     }
     if (cudaGetLastError() != cudaSuccess) return MGT_CUDA_FAILURE;

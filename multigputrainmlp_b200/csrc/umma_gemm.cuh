@@ -61,10 +61,14 @@ struct GemmArgs {
     uint32_t samples;
     uint32_t in_rows;        // state_len * value_pad; row `in_rows` is the all-ones (bias) row
     int* status;             // device status word, 0 = ok
+    uint32_t debug_skip;     // diagnostics only: bit 0 = synth writes nothing, bit 1 = embedding epilogue stores nothing
 };
 
-template <int BN_, int NACC_, bool A_MN_, BSource BSRC_, Epi EPI_, int SA_, int SB_>
+// BSTAT_: "B-stationary" - for short reductions (K <= 64*SB_) the whole B operand of the CTA's N tile is loaded
+// once and stays in shared memory while the CTA streams its M tiles (all units of a CTA then share the N tile).
+template <int BN_, int NACC_, bool A_MN_, BSource BSRC_, Epi EPI_, int SA_, int SB_, bool BSTAT_ = false>
 struct GemmCfg {
+    static constexpr bool BSTAT = BSTAT_;
     static constexpr int BM = 128;
     static constexpr int BK = 64;
     static constexpr int BN = BN_;
@@ -97,6 +101,7 @@ struct GemmCfg {
     static_assert(NACC_ == 1 || NACC_ == 2, "one or two accumulators");
     static_assert(B_ACC_BYTES % 1024 == 0, "swizzle atoms must stay 1024-byte aligned");
     static_assert(!kOneHot || SB_ == 2, "the one-hot ring keeps a two-item history");
+    static_assert(!BSTAT_ || (!kOneHot && NACC_ == 1), "B-stationary applies to TMA-fed single-accumulator tiles");
     static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
@@ -204,6 +209,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + ACC_BUFS);
     volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_holder + 1);
     float* epi_stage = reinterpret_cast<float*>(b_ring + SB * Cfg::B_STAGE_BYTES + 256);
+    uint8_t* epi_stage_dummy = b_ring + SB * Cfg::B_STAGE_BYTES + 240;  // 16 spare bytes after the barriers
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31U;
@@ -279,9 +285,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     } else {
                         tma_load_2d(a_dst, &tma_a, static_cast<int32_t>(c * 64), static_cast<int32_t>(mt * BM), &full_a[sa]);
                     }
-                    if (!Cfg::kOneHot) {
-                        const uint32_t sb = it % SB, pb = (it / SB) & 1U;
-                        if (!mbar_wait(&empty_b[sb], pb ^ 1U, cta_abort, kAbortProducerWait)) { ok = false; break; }
+                    if (!Cfg::kOneHot && (!Cfg::BSTAT || unit == blockIdx.x)) {
+                        // B-stationary: chunk c of B lives in stage c for the whole kernel, loaded with the first unit
+                        const uint32_t sb = Cfg::BSTAT ? (c - c0) : it % SB, pb = Cfg::BSTAT ? 0U : (it / SB) & 1U;
+                        if (!Cfg::BSTAT && !mbar_wait(&empty_b[sb], pb ^ 1U, cta_abort, kAbortProducerWait)) { ok = false; break; }
                         uint8_t* b_dst = b_ring + sb * Cfg::B_STAGE_BYTES;
                         mbar_arrive_expect_tx(&full_b[sb], Cfg::B_STAGE_BYTES);
 #pragma unroll
@@ -317,9 +324,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 const uint32_t d_base = tmem_base + ab * (NACC * Cfg::ACC_COLS);
                 for (uint32_t c = c0; c < c1; ++c, ++it) {
                     const uint32_t sa = it % SA, pa = (it / SA) & 1U;
-                    const uint32_t sb = it % SB, pb = (it / SB) & 1U;
+                    const uint32_t sb = Cfg::BSTAT ? (c - c0) : it % SB, pb = Cfg::BSTAT ? 0U : (it / SB) & 1U;
                     if (!mbar_wait(&full_a[sa], pa, cta_abort, kAbortMmaWait)) { ok = false; break; }
-                    if (!mbar_wait(&full_b[sb], pb, cta_abort, kAbortMmaWait)) { ok = false; break; }
+                    if ((!Cfg::BSTAT || unit == blockIdx.x) && !mbar_wait(&full_b[sb], pb, cta_abort, kAbortMmaWait)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(a_ring + sa * Cfg::A_STAGE_BYTES);
                     const uint32_t b_addr = smem_u32(b_ring + sb * Cfg::B_STAGE_BYTES);
@@ -336,7 +343,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                         }
                     }
                     umma_commit(&empty_a[sa]);
-                    umma_commit(&empty_b[sb]);
+                    if (!Cfg::BSTAT) umma_commit(&empty_b[sb]);
                 }
                 if (ok) umma_commit(&acc_full[ab]);
             }
@@ -349,192 +356,234 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         const uint32_t ew = warp - 2U;
         const uint32_t quad = warp & 3U;
         const uint32_t chunk_parity = ew >> 2;
-        constexpr uint32_t TP = Cfg::EPI_TILE_PITCH;  // floats per staged row (16-byte aligned, bank-friendly)
-        float* tile = epi_stage + ew * (Cfg::EPI_WARP_BYTES / 4);
-        uint32_t* mask_words = reinterpret_cast<uint32_t*>(tile + 32 * TP);
         uint32_t unit_iter = 0;
         bool ok = true;
-        for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++unit_iter) {
-            uint32_t mt, nt, sp;
-            decode(unit, mt, nt, sp);
-            const uint32_t ab = unit_iter % ACC_BUFS, aph = (unit_iter / ACC_BUFS) & 1U;
-            // the TMEM loads below are warp-collective, so the whole warp takes the same way out
-            if (!__all_sync(0xFFFFFFFFU, mbar_wait(&acc_full[ab], aph, cta_abort, kAbortEpilogueWait))) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t m_base = mt * BM + quad * 32U;
-            const uint32_t m = m_base + lane;
-            const bool m_ok = m < args.M;
-            const uint32_t rows_ok = m_base < args.M ? min(32U, args.M - m_base) : 0U;
+        if constexpr (Cfg::kOneHot) {
+            // Embedding layers: D is the transposed result, so a TMEM lane (row of D) is a column of the
+            // row-major tensor and the 32 lanes of a warp already write consecutive addresses.
+            for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++unit_iter) {
+                uint32_t mt, nt, sp;
+                decode(unit, mt, nt, sp);
+                const uint32_t ab = unit_iter % ACC_BUFS, aph = (unit_iter / ACC_BUFS) & 1U;
+                if (!__all_sync(0xFFFFFFFFU, mbar_wait(&acc_full[ab], aph, cta_abort, kAbortEpilogueWait))) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t m = mt * BM + quad * 32U + lane;
+                const bool m_ok = m < args.M && !(args.debug_skip & 2U);
 #pragma unroll 1
-            for (int acc = 0; acc < NACC; ++acc) {
+                for (int acc = 0; acc < NACC; ++acc) {
 #pragma unroll 1
-                for (int cc = 0; cc < BN / 32; ++cc) {
-                    if ((static_cast<uint32_t>(cc) & 1U) != chunk_parity) continue;
-                    const uint32_t n0 = (nt * NACC + acc) * BN + cc * 32;
-                    if (n0 >= args.N) continue;
+                    for (int cc = static_cast<int>(chunk_parity); cc < BN / 32; cc += 2) {
+                        const uint32_t n0 = (nt * NACC + acc) * BN + cc * 32;
+                        if (n0 >= args.N) continue;
+                        uint32_t r[32];
+                        tmem_ld_32x32(tmem_base + ((quad * 32U) << 16) + ab * (NACC * Cfg::ACC_COLS) + acc * Cfg::ACC_COLS + cc * 32, r);
+                        tmem_ld_wait();
+                        const uint32_t valid = min(32U, args.N - n0);
+                        if (m_ok) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                if (static_cast<uint32_t>(j) < valid) {
+                                    const float x = __uint_as_float(r[j]);
+                                    if constexpr (Cfg::EPI == Epi::kEmbFwd) {
+                                        args.out_f16[static_cast<uint64_t>(n0 + j) * args.ld_f16 + m] = __float2half_rn(fmaxf(x, 0.0f));
+                                    } else {
+                                        float* dst = args.out_f32 + static_cast<uint64_t>(n0 + j) * args.ld_f32 + m;
+                                        if (args.splits > 1U) atomicAdd(dst, x); else *dst = x;
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(&acc_empty[ab]);
+            }
+        } else {
+            // Row-major tensors: a TMEM lane holds one row, but global memory wants a warp on whole rows. Each warp
+            // stages operands and results through its own padded 32x32 fp32 tile in shared memory, so that every
+            // global access is a full 64/128-byte row segment: 16-byte vectors, four (fp32) or eight (fp16) rows per
+            // instruction. The global operands of a chunk (residual/skip values, ReLU mask source, bias) are
+            // requested one chunk ahead - for the first chunk of a tile before the tile's MMAs have even finished -
+            // so their latency is off the critical path. Ragged shapes take a scalar form without prefetch.
+            constexpr bool kHasBias = Cfg::EPI == Epi::kBiasReluF16 || Cfg::EPI == Epi::kBiasReluF32F16 || Cfg::EPI == Epi::kBiasResReluF32F16;
+            constexpr bool kHasAdd = Cfg::EPI == Epi::kBiasResReluF32F16 || Cfg::EPI == Epi::kAddMaskF32F16;
+            constexpr bool kHasMask = Cfg::EPI == Epi::kMaskF16 || Cfg::EPI == Epi::kAddMaskF32F16;
+            constexpr bool kOutF32 = Cfg::EPI == Epi::kBiasReluF32F16 || Cfg::EPI == Epi::kBiasResReluF32F16 || Cfg::EPI == Epi::kAddMaskF32F16;
+            constexpr bool kPartial = Cfg::EPI == Epi::kPartialF32;
+            constexpr uint32_t TP = Cfg::EPI_TILE_PITCH;  // floats per staged row (16-byte aligned, bank-friendly)
+            float* tile = epi_stage + ew * (Cfg::EPI_WARP_BYTES / 4);
+            uint32_t* mask_words = reinterpret_cast<uint32_t*>(tile + 32 * TP);
+            const uint32_t r4 = lane >> 3, c4 = (lane & 7U) * 4U;  // fp32 vectors: 4 rows x 8 lanes
+            const uint32_t r8 = lane >> 2, c8 = (lane & 3U) * 8U;  // fp16 vectors: 8 rows x 4 lanes
+            const bool ld_vec = (!kHasAdd || (args.ld_add & 3U) == 0U) && (!kHasMask || (args.ld_mask & 7U) == 0U) &&
+                                (!kOutF32 || (args.ld_f32 & 3U) == 0U) && (kPartial ? (args.N & 3U) == 0U : (args.ld_f16 & 7U) == 0U);
+            struct Operands {
+                float4 add[kHasAdd ? 8 : 1];
+                uint4 mask[kHasMask ? 4 : 1];
+                float bias;
+            };
+            // requests the global operands of chunk n0 of the tile whose first row is m_base (vector form only)
+            auto request = [&](Operands& o, uint32_t m_base, uint32_t rows_ok, uint32_t n0) {
+                if (n0 + 32U > args.N || !ld_vec) return;
+                if constexpr (kHasBias) o.bias = __ldg(args.bias + n0 + lane);
+                if constexpr (kHasAdd) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 8U; ++i) {
+                        const uint32_t rr = r4 + 4U * i;
+                        o.add[i] = rr < rows_ok ? *reinterpret_cast<const float4*>(args.add_f32 + static_cast<uint64_t>(m_base + rr) * args.ld_add + n0 + c4)
+                                                : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                }
+                if constexpr (kHasMask) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 4U; ++i) {
+                        const uint32_t rr = r8 + 8U * i;
+                        o.mask[i] = rr < rows_ok ? *reinterpret_cast<const uint4*>(args.mask + static_cast<uint64_t>(m_base + rr) * args.ld_mask + n0 + c8)
+                                                 : make_uint4(0, 0, 0, 0);
+                    }
+                }
+            };
+            for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++unit_iter) {
+                uint32_t mt, nt, sp;
+                decode(unit, mt, nt, sp);
+                const uint32_t ab = unit_iter % ACC_BUFS, aph = (unit_iter / ACC_BUFS) & 1U;
+                const uint32_t m_base = mt * BM + quad * 32U;
+                const uint32_t rows_ok = m_base < args.M ? min(32U, args.M - m_base) : 0U;
+                Operands next{};
+                request(next, m_base, rows_ok, nt * BN + chunk_parity * 32U);
+                // the TMEM loads below are warp-collective, so the whole warp takes the same way out
+                if (!__all_sync(0xFFFFFFFFU, mbar_wait(&acc_full[ab], aph, cta_abort, kAbortEpilogueWait))) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll 1
+                for (int cc = static_cast<int>(chunk_parity); cc < BN / 32; cc += 2) {
+                    const uint32_t n0 = nt * BN + cc * 32;
+                    if (n0 >= args.N) break;
+                    const Operands cur = next;
+                    if (cc + 2 < BN / 32) request(next, m_base, rows_ok, n0 + 64U);
                     uint32_t r[32];
-                    tmem_ld_32x32(tmem_base + ((quad * 32U) << 16) + ab * (NACC * Cfg::ACC_COLS) + acc * Cfg::ACC_COLS + cc * 32, r);
+                    tmem_ld_32x32(tmem_base + ((quad * 32U) << 16) + ab * Cfg::ACC_COLS + cc * 32, r);
                     tmem_ld_wait();
                     const uint32_t valid = min(32U, args.N - n0);
+                    const bool vec = valid == 32U && ld_vec;
+                    const bool col_ok = lane < valid;
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-
-                    if constexpr (Cfg::EPI == Epi::kEmbFwd) {
-                        if (m_ok) {
+                    if constexpr (kHasBias) {
+                        const float bias_l = vec ? cur.bias : (col_ok ? __ldg(args.bias + n0 + lane) : 0.0f);
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (static_cast<uint32_t>(j) < valid)
-                                    args.out_f16[static_cast<uint64_t>(n0 + j) * args.ld_f16 + m] = __float2half_rn(fmaxf(v[j], 0.0f));
+                        for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xFFFFFFFFU, bias_l, j);
+                    }
+                    if constexpr (kHasAdd) {
+                        if (vec) {
+#pragma unroll
+                            for (uint32_t i = 0; i < 8U; ++i) *reinterpret_cast<float4*>(tile + (r4 + 4U * i) * TP + c4) = cur.add[i];
+                        } else {
+                            for (uint32_t rr = 0; rr < 32U; ++rr)
+                                tile[rr * TP + lane] = (rr < rows_ok && col_ok) ? args.add_f32[static_cast<uint64_t>(m_base + rr) * args.ld_add + n0 + lane] : 0.0f;
                         }
-                    } else if constexpr (Cfg::EPI == Epi::kEmbGrad) {
-                        if (m_ok) {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (static_cast<uint32_t>(j) < valid) {
-                                    float* dst = args.out_f32 + static_cast<uint64_t>(n0 + j) * args.ld_f32 + m;
-                                    if (args.splits > 1U) atomicAdd(dst, v[j]); else *dst = v[j];
-                                }
-                        }
-                    } else {
-                        // Row-major tensors: a TMEM lane holds one row, but global memory wants a warp on whole rows.
-                        // Each warp stages operands and results through its own padded 32x32 fp32 tile in shared
-                        // memory, so that every global access is a full 64/128-byte row segment: 16-byte vectors,
-                        // four (fp32) or eight (fp16) rows per instruction. Ragged shapes take the scalar form.
-                        constexpr bool kHasBias = Cfg::EPI == Epi::kBiasReluF16 || Cfg::EPI == Epi::kBiasReluF32F16 || Cfg::EPI == Epi::kBiasResReluF32F16;
-                        constexpr bool kHasAdd = Cfg::EPI == Epi::kBiasResReluF32F16 || Cfg::EPI == Epi::kAddMaskF32F16;
-                        constexpr bool kHasMask = Cfg::EPI == Epi::kMaskF16 || Cfg::EPI == Epi::kAddMaskF32F16;
-                        constexpr bool kOutF32 = Cfg::EPI == Epi::kBiasReluF32F16 || Cfg::EPI == Epi::kBiasResReluF32F16 || Cfg::EPI == Epi::kAddMaskF32F16;
-                        constexpr bool kPartial = Cfg::EPI == Epi::kPartialF32;
-                        const bool vec = valid == 32U && (!kHasAdd || (args.ld_add & 3U) == 0U) && (!kHasMask || (args.ld_mask & 7U) == 0U) &&
-                                         (!kOutF32 || (args.ld_f32 & 3U) == 0U) && (kPartial ? (args.N & 3U) == 0U : (args.ld_f16 & 7U) == 0U);
-                        const bool col_ok = lane < valid;
-                        const uint32_t r4 = lane >> 3, c4 = (lane & 7U) * 4U;  // fp32 vectors: 4 rows x 8 lanes
-                        const uint32_t r8 = lane >> 2, c8 = (lane & 3U) * 8U;  // fp16 vectors: 8 rows x 4 lanes
-                        if constexpr (kHasBias) {
-                            const float bias_l = col_ok ? __ldg(args.bias + n0 + lane) : 0.0f;
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xFFFFFFFFU, bias_l, j);
-                        }
-                        if constexpr (kHasAdd) {
-                            if (vec) {
-#pragma unroll
-                                for (uint32_t i = 0; i < 8U; ++i) {
-                                    const uint32_t rr = r4 + 4U * i;
-                                    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-                                    if (rr < rows_ok) x = *reinterpret_cast<const float4*>(args.add_f32 + static_cast<uint64_t>(m_base + rr) * args.ld_add + n0 + c4);
-                                    *reinterpret_cast<float4*>(tile + rr * TP + c4) = x;
-                                }
-                            } else {
-                                for (uint32_t rr = 0; rr < 32U; ++rr)
-                                    tile[rr * TP + lane] = (rr < rows_ok && col_ok) ? args.add_f32[static_cast<uint64_t>(m_base + rr) * args.ld_add + n0 + lane] : 0.0f;
-                            }
-                            __syncwarp();
-#pragma unroll
-                            for (int q = 0; q < 8; ++q) {
-                                const float4 x = *reinterpret_cast<const float4*>(tile + lane * TP + q * 4);
-                                v[q * 4] = x.x + v[q * 4];
-                                v[q * 4 + 1] = x.y + v[q * 4 + 1];
-                                v[q * 4 + 2] = x.z + v[q * 4 + 2];
-                                v[q * 4 + 3] = x.w + v[q * 4 + 3];
-                            }
-                            __syncwarp();
-                        }
-                        if constexpr (kHasMask) {
-                            uint32_t bits = 0;
-                            if (vec) {
-                                uint8_t* mask_bytes = reinterpret_cast<uint8_t*>(mask_words);
-#pragma unroll
-                                for (uint32_t i = 0; i < 4U; ++i) {
-                                    const uint32_t rr = r8 + 8U * i;
-                                    uint4 h = make_uint4(0, 0, 0, 0);
-                                    if (rr < rows_ok) h = *reinterpret_cast<const uint4*>(args.mask + static_cast<uint64_t>(m_base + rr) * args.ld_mask + n0 + c8);
-                                    const uint32_t w4[4] = {h.x, h.y, h.z, h.w};
-                                    uint32_t byte = 0;
-#pragma unroll
-                                    for (int e = 0; e < 4; ++e) {
-                                        // a positive non-zero half: sign clear, magnitude non-zero
-                                        const uint32_t lo = w4[e] & 0xFFFFU, hi = w4[e] >> 16;
-                                        byte |= (lo != 0U && lo < 0x8000U) ? (1U << (2 * e)) : 0U;
-                                        byte |= (hi != 0U && hi < 0x8000U) ? (1U << (2 * e + 1)) : 0U;
-                                    }
-                                    mask_bytes[rr * 4U + (lane & 3U)] = static_cast<uint8_t>(byte);
-                                }
-                                __syncwarp();
-                                bits = mask_words[lane];
-                                __syncwarp();
-                            } else {
-                                for (uint32_t rr = 0; rr < 32U; ++rr) {
-                                    const bool positive = (rr < rows_ok && col_ok) ? (__half2float(args.mask[static_cast<uint64_t>(m_base + rr) * args.ld_mask + n0 + lane]) > 0.0f) : false;
-                                    const uint32_t row_bits = __ballot_sync(0xFFFFFFFFU, positive);
-                                    if (lane == rr) bits = row_bits;
-                                }
-                            }
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) v[j] = ((bits >> j) & 1U) ? v[j] : 0.0f;
-                        } else if constexpr (!kPartial) {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
-                        }
-#pragma unroll
-                        for (int q = 0; q < 8; ++q)
-                            *reinterpret_cast<float4*>(tile + lane * TP + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
                         __syncwarp();
-                        if constexpr (kPartial || kOutF32) {
-                            float* base = kPartial ? args.partial + (static_cast<uint64_t>(sp) * args.M + m_base) * args.N + n0
-                                                   : args.out_f32 + static_cast<uint64_t>(m_base) * args.ld_f32 + n0;
-                            const uint64_t ld = kPartial ? args.N : args.ld_f32;
-                            if (vec) {
 #pragma unroll
-                                for (uint32_t i = 0; i < 8U; ++i) {
-                                    const uint32_t rr = r4 + 4U * i;
-                                    if (rr < rows_ok) *reinterpret_cast<float4*>(base + rr * ld + c4) = *reinterpret_cast<const float4*>(tile + rr * TP + c4);
-                                }
-                            } else {
-                                for (uint32_t rr = 0; rr < rows_ok; ++rr)
-                                    if (col_ok) base[rr * ld + lane] = tile[rr * TP + lane];
-                            }
-                        }
-                        if constexpr (!kPartial) {
-                            if (vec) {
-#pragma unroll
-                                for (uint32_t i = 0; i < 4U; ++i) {
-                                    const uint32_t rr = r8 + 8U * i;
-                                    if (rr < rows_ok) {
-                                        const float4 x0 = *reinterpret_cast<const float4*>(tile + rr * TP + c8);
-                                        const float4 x1 = *reinterpret_cast<const float4*>(tile + rr * TP + c8 + 4U);
-                                        const __half2 h0 = __floats2half2_rn(x0.x, x0.y), h1 = __floats2half2_rn(x0.z, x0.w);
-                                        const __half2 h2 = __floats2half2_rn(x1.x, x1.y), h3 = __floats2half2_rn(x1.z, x1.w);
-                                        uint4 u;
-                                        u.x = *reinterpret_cast<const uint32_t*>(&h0);
-                                        u.y = *reinterpret_cast<const uint32_t*>(&h1);
-                                        u.z = *reinterpret_cast<const uint32_t*>(&h2);
-                                        u.w = *reinterpret_cast<const uint32_t*>(&h3);
-                                        *reinterpret_cast<uint4*>(args.out_f16 + static_cast<uint64_t>(m_base + rr) * args.ld_f16 + n0 + c8) = u;
-                                    }
-                                }
-                            } else {
-                                for (uint32_t rr = 0; rr < rows_ok; ++rr)
-                                    if (col_ok) args.out_f16[static_cast<uint64_t>(m_base + rr) * args.ld_f16 + n0 + lane] = __float2half_rn(tile[rr * TP + lane]);
-                            }
-                        }
-                        if constexpr (kHasMask) {
-                            if (args.colsum != nullptr) {
-                                float total = 0.0f;  // column `lane` of the staged tile, rows in order
-#pragma unroll 8
-                                for (uint32_t rr = 0; rr < 32U; ++rr) total += rr < rows_ok ? tile[rr * TP + lane] : 0.0f;
-                                if (col_ok) {
-                                    float* dst = args.colsum + (static_cast<uint64_t>(blockIdx.x) * Cfg::EPI_WARPS + ew) * args.N + n0 + lane;
-                                    *dst += total;  // this warp is the only writer of its row
-                                }
-                            }
+                        for (int q = 0; q < 8; ++q) {
+                            const float4 x = *reinterpret_cast<const float4*>(tile + lane * TP + q * 4);
+                            v[q * 4] = x.x + v[q * 4];
+                            v[q * 4 + 1] = x.y + v[q * 4 + 1];
+                            v[q * 4 + 2] = x.z + v[q * 4 + 2];
+                            v[q * 4 + 3] = x.w + v[q * 4 + 3];
                         }
                         __syncwarp();
                     }
+                    if constexpr (kHasMask) {
+                        uint32_t bits = 0;
+                        if (vec) {
+                            uint8_t* mask_bytes = reinterpret_cast<uint8_t*>(mask_words);
+#pragma unroll
+                            for (uint32_t i = 0; i < 4U; ++i) {
+                                const uint32_t w4[4] = {cur.mask[i].x, cur.mask[i].y, cur.mask[i].z, cur.mask[i].w};
+                                uint32_t byte = 0;
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    // a positive non-zero half: sign clear, magnitude non-zero
+                                    const uint32_t lo = w4[e] & 0xFFFFU, hi = w4[e] >> 16;
+                                    byte |= (lo != 0U && lo < 0x8000U) ? (1U << (2 * e)) : 0U;
+                                    byte |= (hi != 0U && hi < 0x8000U) ? (1U << (2 * e + 1)) : 0U;
+                                }
+                                mask_bytes[(r8 + 8U * i) * 4U + (lane & 3U)] = static_cast<uint8_t>(byte);
+                            }
+                            __syncwarp();
+                            bits = mask_words[lane];
+                            __syncwarp();
+                        } else {
+                            for (uint32_t rr = 0; rr < 32U; ++rr) {
+                                const bool positive = (rr < rows_ok && col_ok) ? (__half2float(args.mask[static_cast<uint64_t>(m_base + rr) * args.ld_mask + n0 + lane]) > 0.0f) : false;
+                                const uint32_t row_bits = __ballot_sync(0xFFFFFFFFU, positive);
+                                if (lane == rr) bits = row_bits;
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = ((bits >> j) & 1U) ? v[j] : 0.0f;
+                    } else if constexpr (!kPartial) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+                    }
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        *reinterpret_cast<float4*>(tile + lane * TP + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+                    __syncwarp();
+                    if constexpr (kPartial || kOutF32) {
+                        float* base = kPartial ? args.partial + (static_cast<uint64_t>(sp) * args.M + m_base) * args.N + n0
+                                               : args.out_f32 + static_cast<uint64_t>(m_base) * args.ld_f32 + n0;
+                        const uint64_t ld = kPartial ? args.N : args.ld_f32;
+                        if (vec) {
+#pragma unroll
+                            for (uint32_t i = 0; i < 8U; ++i) {
+                                const uint32_t rr = r4 + 4U * i;
+                                if (rr < rows_ok) *reinterpret_cast<float4*>(base + rr * ld + c4) = *reinterpret_cast<const float4*>(tile + rr * TP + c4);
+                            }
+                        } else {
+                            for (uint32_t rr = 0; rr < rows_ok; ++rr)
+                                if (col_ok) base[rr * ld + lane] = tile[rr * TP + lane];
+                        }
+                    }
+                    if constexpr (!kPartial) {
+                        if (vec) {
+#pragma unroll
+                            for (uint32_t i = 0; i < 4U; ++i) {
+                                const uint32_t rr = r8 + 8U * i;
+                                if (rr < rows_ok) {
+                                    const float4 x0 = *reinterpret_cast<const float4*>(tile + rr * TP + c8);
+                                    const float4 x1 = *reinterpret_cast<const float4*>(tile + rr * TP + c8 + 4U);
+                                    const __half2 h0 = __floats2half2_rn(x0.x, x0.y), h1 = __floats2half2_rn(x0.z, x0.w);
+                                    const __half2 h2 = __floats2half2_rn(x1.x, x1.y), h3 = __floats2half2_rn(x1.z, x1.w);
+                                    uint4 u;
+                                    u.x = *reinterpret_cast<const uint32_t*>(&h0);
+                                    u.y = *reinterpret_cast<const uint32_t*>(&h1);
+                                    u.z = *reinterpret_cast<const uint32_t*>(&h2);
+                                    u.w = *reinterpret_cast<const uint32_t*>(&h3);
+                                    *reinterpret_cast<uint4*>(args.out_f16 + static_cast<uint64_t>(m_base + rr) * args.ld_f16 + n0 + c8) = u;
+                                }
+                            }
+                        } else {
+                            for (uint32_t rr = 0; rr < rows_ok; ++rr)
+                                if (col_ok) args.out_f16[static_cast<uint64_t>(m_base + rr) * args.ld_f16 + n0 + lane] = __float2half_rn(tile[rr * TP + lane]);
+                        }
+                    }
+                    if constexpr (kHasMask) {
+                        if (args.colsum != nullptr) {
+                            float total = 0.0f;  // column `lane` of the staged tile, rows in order
+#pragma unroll 8
+                            for (uint32_t rr = 0; rr < 32U; ++rr) total += rr < rows_ok ? tile[rr * TP + lane] : 0.0f;
+                            if (col_ok) {
+                                float* dst = args.colsum + (static_cast<uint64_t>(blockIdx.x) * Cfg::EPI_WARPS + ew) * args.N + n0 + lane;
+                                *dst += total;  // this warp is the only writer of its row
+                            }
+                        }
+                    }
+                    __syncwarp();
                 }
+                tc_fence_before();
+                mbar_arrive(&acc_empty[ab]);
             }
-            tc_fence_before();
-            mbar_arrive(&acc_empty[ab]);
         }
     } else {
         // ------------------------------- one-hot synthesis --------------------------------
@@ -547,6 +596,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             const uint32_t V = args.value_pad, L = args.state_len, IN = args.in_rows;
             constexpr uint32_t ROWS = NACC * BN;  // rows of the synthesised operand per stage
             auto place = [&](uint8_t* buf, uint32_t n, uint32_t k) -> uint16_t* {
+                if (args.debug_skip & 1U) return reinterpret_cast<uint16_t*>(epi_stage_dummy);
                 uint8_t* row = buf + (n / BN) * Cfg::B_ACC_BYTES + (n % BN) * 128U;
                 return reinterpret_cast<uint16_t*>(row + ((((k >> 3) ^ (n & 7U)) << 4) | ((k & 7U) << 1)));
             };
@@ -711,7 +761,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll
                         for (uint32_t j = 0; j < 4U; ++j) {
                             const uint32_t off = sb ? hist1[j] : hist0[j];
-                            if (off != kNone) *reinterpret_cast<uint16_t*>(buf + off) = 0;
+                            if (off != kNone && !(args.debug_skip & 1U)) *reinterpret_cast<uint16_t*>(buf + off) = 0;
                         }
                         __syncwarp();  // a place cleared by one lane may be set by another lane of this warp
                         const uint32_t r0 = nt * ROWS, p_lo = r0 / V;
@@ -725,7 +775,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                         offs[3] = (q == 0U && nb < ROWS && c * 64U + k < args.samples) ? offset_of(nb) : kNone;
 #pragma unroll
                         for (uint32_t j = 0; j < 4U; ++j) {
-                            if (offs[j] != kNone) *reinterpret_cast<uint16_t*>(buf + offs[j]) = 0x3C00;
+                            if (offs[j] != kNone && !(args.debug_skip & 1U)) *reinterpret_cast<uint16_t*>(buf + offs[j]) = 0x3C00;
                             if (sb) hist1[j] = offs[j]; else hist0[j] = offs[j];
                         }
                         if (have2) fetch(nt2, c2);
