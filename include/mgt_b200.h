@@ -235,6 +235,27 @@ mgt_status_t mgt_debug_gemm(mgt_engine_t* engine, const uint16_t* a, uint32_t ld
                             const uint16_t* b, uint32_t ldb, int32_t b_mn_major, float* d, uint32_t m, uint32_t n,
                             uint32_t k, uint32_t splits, float* partial_scratch, void* stream);
 
+/* Split-K GEMM that allocates nothing. No counterpart in the reference.
+ *
+ * Same computation and arguments as mgt_debug_gemm, for callers that cannot obtain device memory
+ * themselves: a host application that has handed all of HBM to its own memory pool, or a
+ * latency-critical loop in which a cudaMalloc (which synchronises the whole device) is not
+ * acceptable. Such a caller has nowhere to put the split-K partial sums, so they live in a buffer
+ * that is part of the library image: MGT_STATIC_SCRATCH_FLOATS floats (16 MiB) of device memory
+ * on every GPU that loads the library, held until the process exits. No engine handle is needed
+ * and neither this call nor anything it calls uses cudaMalloc, cudaFree or another device allocator.
+ *
+ * Limit: min(splits, ceil(k/64)) * m * n <= MGT_STATIC_SCRATCH_FLOATS when more than one split is
+ * used; beyond that the call returns MGT_CAPACITY_EXCEEDED and says why on stderr.
+ * The first call on each device looks up the device addresses of the built-in buffers and the
+ * tensor-map encoder (host work only); make that first call before starting any stream capture.
+ * All calls on a device share the one buffer: calls that may overlap on the GPU (different
+ * streams) race on it - keep them on one stream or order them with events. */
+#define MGT_STATIC_SCRATCH_FLOATS (4u << 20)
+mgt_status_t mgt_gemm_split_k_static_scratch(const uint16_t* a, uint32_t lda, int32_t a_mn_major, const uint16_t* b,
+                                             uint32_t ldb, int32_t b_mn_major, float* d, uint32_t m, uint32_t n,
+                                             uint32_t k, uint32_t splits, void* stream);
+
 const char* mgt_status_name(mgt_status_t status);
 const char* mgt_version(void);
 

@@ -843,3 +843,71 @@ mgt_status_t mgt_debug_gemm(mgt_engine_t* e, const uint16_t* a, uint32_t lda, in
 }
 
 }  // extern "C"
+
+// ---- split-K GEMM whose scratch is part of the library image ------------------------------------
+// Device memory that this library reserves at load time on every GPU that uses it: the split-K
+// partial sums of mgt_gemm_split_k_static_scratch and that entry point's status word.
+static __device__ __align__(256) float g_static_partials[MGT_STATIC_SCRATCH_FLOATS];
+static __device__ int g_static_status;
+
+namespace {
+struct StaticSlot {
+    mgt_engine* engine = nullptr;   // host-side object only: descriptor cache, SM count, status-word address
+    float* partials = nullptr;      // device address of g_static_partials on that device
+};
+StaticSlot g_static_slots[64];
+std::mutex g_static_mu;
+
+// One-time set-up per device, with that device current: resolve the DEVICE addresses of the two
+// symbols above (in host code their names are only host-side handles) and look up the tensor-map
+// encoder. Allocates no device memory.
+mgt_status_t StaticSlotFor(int device, StaticSlot** out) {
+    if (device < 0 || device >= 64) return MGT_INVALID_CONFIG;
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    StaticSlot& slot = g_static_slots[device];
+    if (slot.engine == nullptr) {
+        void* partials = nullptr;
+        void* status = nullptr;
+        if (cudaGetSymbolAddress(&partials, g_static_partials) != cudaSuccess || partials == nullptr) return MGT_CUDA_FAILURE;
+        if (cudaGetSymbolAddress(&status, g_static_status) != cudaSuccess || status == nullptr) return MGT_CUDA_FAILURE;
+        cudaDeviceProp prop{};
+        if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return MGT_CUDA_FAILURE;
+        if (prop.major != 10) {
+            std::fprintf(stderr, "mgt_b200: device %d is sm_%d%d; this library only runs on sm_100a (B200)\n", device, prop.major, prop.minor);
+            return MGT_CUDA_FAILURE;
+        }
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || fn == nullptr) return MGT_CUDA_FAILURE;
+        auto* e = new mgt_engine();
+        e->device = device;
+        e->sm_count = prop.multiProcessorCount;
+        e->encode = reinterpret_cast<EncodeTiledFn>(fn);
+        e->status_word = static_cast<int*>(status);
+        slot.engine = e;
+        slot.partials = static_cast<float*>(partials);
+    }
+    *out = &slot;
+    return MGT_OK;
+}
+}  // namespace
+
+extern "C" mgt_status_t mgt_gemm_split_k_static_scratch(const uint16_t* a, uint32_t lda, int32_t a_mn, const uint16_t* b, uint32_t ldb, int32_t b_mn,
+                                                        float* d, uint32_t m, uint32_t n, uint32_t k, uint32_t splits, void* stream) {
+    if (a == nullptr || b == nullptr || d == nullptr || m == 0 || n == 0 || k == 0 || splits == 0) return MGT_INVALID_CONFIG;
+    const uint32_t k_chunks = (k + 63U) / 64U;
+    const uint64_t used_splits = splits > k_chunks ? k_chunks : splits;
+    if (used_splits > 1 && used_splits * m * n > static_cast<uint64_t>(MGT_STATIC_SCRATCH_FLOATS)) {
+        std::fprintf(stderr, "mgt_gemm_split_k_static_scratch: %llu splits of a %u x %u result need %llu floats of scratch, the built-in buffer holds %u\n",
+                     static_cast<unsigned long long>(used_splits), m, n, static_cast<unsigned long long>(used_splits * m * n),
+                     static_cast<unsigned>(MGT_STATIC_SCRATCH_FLOATS));
+        return MGT_CAPACITY_EXCEEDED;
+    }
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return MGT_CUDA_FAILURE;
+    StaticSlot* slot = nullptr;
+    MGT_TRY(StaticSlotFor(device, &slot));
+    // every valid element of the partial planes is written before the reduction reads it, so nothing
+    // needs clearing between calls; what an earlier call left beyond that is never read
+    return mgt_debug_gemm(slot->engine, a, lda, a_mn, b, ldb, b_mn, d, m, n, k, splits, slot->partials, stream);
+}
