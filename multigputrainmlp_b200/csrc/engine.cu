@@ -59,8 +59,8 @@ struct Workspace {
     uint32_t p_dz1;   // pitch (halfs) of dz1 over H1
     uint32_t p_f32;   // pitch (floats) of the fp32 residual / gradient streams
     uint32_t p_w1, p_w2, p_wout;  // pitches of the internal fp16 weight copy
-    uint64_t off_a1, off_x, off_r1, off_xf, off_dzf, off_dza, off_dzb, off_dz1, off_partial, off_head, off_wint, off_dy, off_dyh, off_colsum;
-    uint64_t colsum_floats;
+    uint64_t off_a1, off_x, off_r1, off_xf, off_dzf, off_dz2, off_dz1t, off_dz1, off_partial, off_head, off_wint, off_dy, off_dyh, off_colsum;
+    uint64_t colsum_floats, colsum_slot_floats, off_colsum_h1, dz_stride;
     uint64_t x_stride, r1_stride;  // bytes between consecutive blocks' tensors
     uint64_t partial_floats, head_blocks;
     uint64_t total_bytes;
@@ -90,8 +90,12 @@ Workspace PlanWorkspace(const mgt_mlp_shape_t& s, uint32_t B, uint32_t sm_count)
     w.off_r1 = take(w.r1_stride * (w.R > 0 ? w.R : 1));
     w.off_xf = take((uint64_t)B * w.p_f32 * 4);
     w.off_dzf = take((uint64_t)B * w.p_f32 * 4);
-    w.off_dza = take((uint64_t)B * w.p_dz * 2);
-    w.off_dzb = take((uint64_t)B * w.p_dz * 2);
+    // gradients w.r.t. pre-activations, kept for the whole backward pass so that the weight gradients of all
+    // residual blocks can be computed by two grouped GEMMs at the end: tape[0] belongs to the hidden layer,
+    // tape[k+1] to fc2 of block k; dz1t[k] to fc1 of block k
+    w.dz_stride = RoundUp((uint64_t)B * w.p_dz * 2, 1024);
+    w.off_dz2 = take(w.dz_stride * (w.R + 1));
+    w.off_dz1t = take(w.dz_stride * (w.R > 0 ? w.R : 1));
     w.off_dz1 = take((uint64_t)B * w.p_dz1 * 2);
     // split-K partials: at most one CTA wave of [128 x 256] fp32 tiles plus slack for tile padding
     const uint64_t hidden_units = (uint64_t)((s.hd1 + 127) / 128) * ((s.hd2 + 255) / 256);
@@ -99,13 +103,19 @@ Workspace PlanWorkspace(const mgt_mlp_shape_t& s, uint32_t B, uint32_t sm_count)
     const uint64_t hidden_splits = hidden_units >= sm_count ? 1 : sm_count / hidden_units;
     const uint64_t resid_splits = resid_units >= sm_count ? 1 : sm_count / resid_units;
     const uint64_t p1 = hidden_splits * (uint64_t)s.hd1 * s.hd2;
-    const uint64_t p2 = resid_splits * (uint64_t)s.hd2 * s.hd2;
+    const uint64_t group_units = resid_units * (w.R > 0 ? w.R : 1);
+    const uint64_t group_splits = group_units >= sm_count ? 1 : sm_count / group_units;
+    const uint64_t p2 = group_splits * (w.R > 0 ? w.R : 1) * (uint64_t)s.hd2 * s.hd2;
+    (void)resid_splits;
     w.partial_floats = p1 > p2 ? p1 : p2;
     w.off_partial = take(w.partial_floats * 4);
     w.head_blocks = kHeadBlocks;
     w.off_head = take((uint64_t)kHeadBlocks * (2ULL * s.hd2 + 2) * 4);
-    w.colsum_floats = (uint64_t)sm_count * 8 * (s.hd1 > s.hd2 ? s.hd1 : s.hd2);
+    // per-warp column sums: one slot per residual dX GEMM (2R of them), one wider slot for the hidden dX GEMM
+    w.colsum_slot_floats = (uint64_t)sm_count * 8 * s.hd2;
+    w.colsum_floats = w.colsum_slot_floats * 2 * (w.R > 0 ? w.R : 1);
     w.off_colsum = take(w.colsum_floats * 4);
+    w.off_colsum_h1 = take((uint64_t)sm_count * 8 * s.hd1 * 4);
     // internal fp16 weight copy (used when the caller's mirror cannot be addressed by TMA as it lies)
     const uint64_t wint_halfs = (uint64_t)(w.IN + 1) * w.p_w1 + (uint64_t)s.hd1 * w.p_w2 + 2ULL * w.R * s.hd2 * w.p_w2 + (uint64_t)s.hd2 * w.p_wout;
     w.off_wint = take(wint_halfs * 2 + 1024ULL * (2 * w.R + 4));
@@ -124,15 +134,17 @@ struct MapKey {
     const void* base;
     uint64_t inner, outer, pitch;
     uint32_t box_inner, box_outer;
+    uint64_t layers = 0, layer_stride = 0;  // 3-D maps only
     bool operator==(const MapKey& o) const {
-        return base == o.base && inner == o.inner && outer == o.outer && pitch == o.pitch && box_inner == o.box_inner && box_outer == o.box_outer;
+        return base == o.base && inner == o.inner && outer == o.outer && pitch == o.pitch && box_inner == o.box_inner && box_outer == o.box_outer &&
+               layers == o.layers && layer_stride == o.layer_stride;
     }
 };
 struct MapKeyHash {
     size_t operator()(const MapKey& k) const {
         uint64_t h = reinterpret_cast<uint64_t>(k.base);
         auto mix = [&](uint64_t v) { h ^= v + 0x9e3779b97f4a7c15ULL + (h << 6) + (h >> 2); };
-        mix(k.inner); mix(k.outer); mix(k.pitch); mix(k.box_inner); mix(k.box_outer);
+        mix(k.inner); mix(k.outer); mix(k.pitch); mix(k.box_inner); mix(k.box_outer); mix(k.layers); mix(k.layer_stride);
         return (size_t)h;
     }
 };
@@ -150,6 +162,31 @@ struct mgt_engine {
     cudaEvent_t ev_last = nullptr, ev_now = nullptr;
     uint64_t launches = 0;  // kernels launched through this engine (host-side count)
     uint32_t debug_skip = 0;  // MGT_DEBUG_SKIP: timing experiments only (results are wrong when set)
+
+    // fp16 3-D tensor map (a stack of `layers` equal matrices `layer_stride_bytes` apart), 128-byte swizzle, box depth 1
+    bool Map3D(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t layers, uint64_t pitch_elems, uint64_t layer_stride_bytes,
+               uint32_t box_inner, uint32_t box_outer) {
+        mgt::MapKey key{base, inner, outer, pitch_elems, box_inner, box_outer};
+        key.layers = layers;
+        key.layer_stride = layer_stride_bytes;
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = maps.find(key);
+        if (it != maps.end()) { *out = it->second; return true; }
+        if ((reinterpret_cast<uintptr_t>(base) & 15U) != 0 || ((pitch_elems * 2) & 15U) != 0 || (layer_stride_bytes & 15U) != 0 || box_inner * 2 > 128 || box_outer > 256) return false;
+        const cuuint64_t dims[3] = {inner, outer, layers};
+        const cuuint64_t strides[2] = {pitch_elems * 2, layer_stride_bytes};
+        const cuuint32_t box[3] = {box_inner, box_outer, 1};
+        const cuuint32_t elem[3] = {1, 1, 1};
+        CUtensorMap m;
+        const CUresult r = encode(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return false;
+        if (maps.size() > 4096) maps.clear();
+        maps.emplace(key, m);
+        *out = m;
+        return true;
+    }
 
     // fp16 2-D tensor map with 128-byte swizzle: `inner` contiguous elements per row, `outer` rows.
     bool Map(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch_elems, uint32_t box_inner, uint32_t box_outer) {
@@ -186,7 +223,7 @@ mgt_status_t LaunchGemm(mgt_engine* e, const CUtensorMap& ta, const CUtensorMap&
         if (cudaFuncSetAttribute(umma_gemm_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return MGT_CUDA_FAILURE;
         attr_done[e->device] = true;
     }
-    const uint64_t units = (uint64_t)args.m_tiles * args.n_tiles * args.splits;
+    const uint64_t units = (uint64_t)args.m_tiles * args.n_tiles * args.splits * (Cfg::GROUPED ? args.groups : 1U);
     if (units == 0) return MGT_INVALID_CONFIG;
     uint32_t grid = (uint32_t)(units < (uint64_t)e->sm_count ? units : (uint64_t)e->sm_count);
     if (Cfg::BSTAT) {
@@ -208,6 +245,7 @@ template <int BN, Epi EPI> using CfgDx = GemmCfg<BN, 1, false, BSource::kTmaK, E
 template <int BN, Epi EPI> using CfgFwdS = GemmCfg<BN, 1, false, BSource::kTmaMN, EPI, 3, 4, true>;
 template <int BN, Epi EPI> using CfgDxS = GemmCfg<BN, 1, false, BSource::kTmaK, EPI, 3, 4, true>;
 template <int BN> using CfgDw = GemmCfg<BN, 1, true, BSource::kTmaMN, Epi::kPartialF32, 3, 3>; // act^T x dz
+template <int BN> using CfgDwG = GemmCfg<BN, 1, true, BSource::kTmaMN, Epi::kPartialF32, 3, 3, false, true>; // R stacked act^T x dz
 using CfgEmbFwd = GemmCfg<256, 2, true, BSource::kOneHotFwd, Epi::kEmbFwd, 4, 2>;
 using CfgEmbGrad = GemmCfg<256, 2, true, BSource::kOneHotGrad, Epi::kEmbGrad, 4, 2>;
 using CfgDbgKK = GemmCfg<256, 1, false, BSource::kTmaK, Epi::kPartialF32, 3, 3>;
@@ -222,6 +260,7 @@ GemmArgs BaseArgs(uint32_t M, uint32_t N, uint32_t K, uint32_t bn_total, uint32_
     a.m_tiles = (M + 127) / 128;
     a.n_tiles = (N + bn_total - 1) / bn_total;
     a.k_chunks = (K + 63) / 64;
+    a.groups = 1;
     a.splits = splits < 1 ? 1 : (splits > a.k_chunks ? a.k_chunks : splits);
     return a;
 }
@@ -286,6 +325,49 @@ ReduceRowsKernel(const float* __restrict__ src, uint32_t rows, uint64_t row_stri
 #pragma unroll
         for (int q = 1; q < 32; ++q) total += s_part[q][cl];
         dst[c] = total;
+    }
+}
+
+// The two reducers above for a stack of problems: blockIdx.y selects the problem.
+__global__ void __launch_bounds__(256)
+ReducePartialsGroupedKernel(const float* __restrict__ partial, uint32_t splits, uint64_t count, float* __restrict__ out, uint64_t out_group_stride) {
+    const float* src = partial + (uint64_t)blockIdx.y * splits * count;
+    float* dst = out + (uint64_t)blockIdx.y * out_group_stride;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+        float sum = src[i];
+        for (uint32_t s = 1; s < splits; ++s) sum += src[(uint64_t)s * count + i];
+        dst[i] = sum;
+    }
+}
+
+struct ReduceDestinations { uint64_t offset[2 * MGT_MAX_RESIDUAL_BLOCKS]; };  // element offsets into the gradient array
+
+__global__ void __launch_bounds__(256)
+ReduceRowsGroupedKernel(const float* __restrict__ src, uint32_t rows, uint32_t cols, uint64_t slot_stride, float* __restrict__ grad, ReduceDestinations dst) {
+    __shared__ float s_part[32][kReduceCols + 1];
+    const uint32_t cl = threadIdx.x & (kReduceCols - 1U), g = threadIdx.x / kReduceCols;
+    const uint32_t c = blockIdx.x * kReduceCols + cl;
+    float sum = 0.0f;
+    if (c < cols) {
+        const float* p = src + (uint64_t)blockIdx.y * slot_stride + c;
+        uint32_t r = g;
+        for (; r + 96U < rows; r += 128U) {
+            const float a0 = p[(uint64_t)r * cols];
+            const float a1 = p[(uint64_t)(r + 32U) * cols];
+            const float a2 = p[(uint64_t)(r + 64U) * cols];
+            const float a3 = p[(uint64_t)(r + 96U) * cols];
+            sum += a0; sum += a1; sum += a2; sum += a3;
+        }
+        for (; r < rows; r += 32U) sum += p[(uint64_t)r * cols];
+    }
+    s_part[g][cl] = sum;
+    __syncthreads();
+    if (g == 0 && c < cols) {
+        float total = s_part[0][cl];
+#pragma unroll
+        for (int q = 1; q < 32; ++q) total += s_part[q][cl];
+        grad[dst.offset[blockIdx.y] + c] = total;
     }
 }
 
@@ -487,22 +569,27 @@ mgt_status_t GemmForward(mgt_engine* e, cudaStream_t st, const __half* act, uint
     return bn == 224 ? LaunchGemm<CfgFwd<224, EPI>>(e, ta, tb, a, st) : LaunchGemm<CfgFwd<256, EPI>>(e, ta, tb, a, st);
 }
 
-// dX[M x N] = dz[M x K, K-major] * W[N x K, row-major]^T with a backward epilogue that produces the
-// next dz tensor; its fp32 column sums (a bias gradient) are reduced into bias_grad[N].
-template <Epi EPI>
-mgt_status_t GemmBackpropInput(mgt_engine* e, cudaStream_t st, const __half* dz, uint32_t dz_pitch, const __half* w, uint32_t w_pitch,
-                               uint32_t M, uint32_t N, uint32_t K, GemmArgs epi, float* colsum, uint64_t colsum_floats, float* bias_grad) {
-    const uint32_t bn = PickBN(N);
-    GemmArgs a = BaseArgs(M, N, K, bn, 1);
-    a.out_f32 = epi.out_f32; a.ld_f32 = epi.ld_f32; a.out_f16 = epi.out_f16; a.ld_f16 = epi.ld_f16;
-    a.add_f32 = epi.add_f32; a.ld_add = epi.ld_add; a.mask = epi.mask; a.ld_mask = epi.ld_mask;
+// Grid the dX GEMMs run on (the column-sum scratch has one row per epilogue warp of every CTA).
+uint32_t BackpropGrid(const mgt_engine* e, uint32_t M, uint32_t N, uint32_t K) {
+    const GemmArgs a = BaseArgs(M, N, K, PickBN(N), 1);
     const uint64_t units = (uint64_t)a.m_tiles * a.n_tiles;
     const bool stationary = a.k_chunks <= 4 && a.n_tiles <= (uint32_t)e->sm_count;
     uint32_t grid = (uint32_t)(units < (uint64_t)e->sm_count ? units : (uint64_t)e->sm_count);
     if (stationary && grid >= a.n_tiles) grid = grid / a.n_tiles * a.n_tiles;  // as LaunchGemm picks it
-    const uint32_t rows = grid * 8U;  // one row per epilogue warp
-    if ((uint64_t)rows * N > colsum_floats) return MGT_CAPACITY_EXCEEDED;
-    if (cudaMemsetAsync(colsum, 0, (uint64_t)rows * N * sizeof(float), st) != cudaSuccess) return MGT_CUDA_FAILURE;
+    return grid;
+}
+
+// dX[M x N] = dz[M x K, K-major] * W[N x K, row-major]^T with a backward epilogue that produces the
+// next dz tensor; its fp32 column sums (a bias gradient) go to `colsum` (zeroed by the caller,
+// BackpropGrid()*8 rows of N) and, if bias_grad is given, are reduced into bias_grad[N] right away.
+template <Epi EPI>
+mgt_status_t GemmBackpropInput(mgt_engine* e, cudaStream_t st, const __half* dz, uint32_t dz_pitch, const __half* w, uint32_t w_pitch,
+                               uint32_t M, uint32_t N, uint32_t K, GemmArgs epi, float* colsum, float* bias_grad) {
+    const uint32_t bn = PickBN(N);
+    GemmArgs a = BaseArgs(M, N, K, bn, 1);
+    a.out_f32 = epi.out_f32; a.ld_f32 = epi.ld_f32; a.out_f16 = epi.out_f16; a.ld_f16 = epi.ld_f16;
+    a.add_f32 = epi.add_f32; a.ld_add = epi.ld_add; a.mask = epi.mask; a.ld_mask = epi.ld_mask;
+    const bool stationary = a.k_chunks <= 4 && a.n_tiles <= (uint32_t)e->sm_count;
     a.colsum = colsum;
     CUtensorMap ta, tb;
     MGT_MAP(e->Map(&ta, dz, K, M, dz_pitch, 64, 128));
@@ -512,7 +599,36 @@ mgt_status_t GemmBackpropInput(mgt_engine* e, cudaStream_t st, const __half* dz,
     } else {
         MGT_TRY(bn == 224 ? LaunchGemm<CfgDx<224, EPI>>(e, ta, tb, a, st) : LaunchGemm<CfgDx<256, EPI>>(e, ta, tb, a, st));
     }
-    ReduceRowsKernel<<<(N + kReduceCols - 1) / kReduceCols, 256, 0, st>>>(colsum, rows, N, 0, N, bias_grad);
+    if (bias_grad != nullptr) {
+        ReduceRowsKernel<<<(N + kReduceCols - 1) / kReduceCols, 256, 0, st>>>(colsum, BackpropGrid(e, M, N, K) * 8U, N, 0, N, bias_grad);
+        ++e->launches;
+    }
+    return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
+}
+
+// The weight gradients of all residual blocks for one of the two linear layers in ONE launch:
+// grad_g[in x out] = act_g^T * dz_g for g = 0..groups-1, where act_g / dz_g are slices of two tapes and
+// grad_g lie `grad_group_stride` floats apart. Split-K with a fixed-order reduction.
+mgt_status_t GemmGradWeightsGrouped(mgt_engine* e, cudaStream_t st, const __half* act_tape, uint32_t act_pitch, uint64_t act_stride_bytes,
+                                    const __half* dz_tape, uint32_t dz_pitch, uint64_t dz_stride_bytes, uint32_t groups, uint32_t samples,
+                                    uint32_t in_dim, uint32_t out_dim, float* partial, uint64_t partial_floats, float* grad_first, uint64_t grad_group_stride) {
+    const uint32_t M = in_dim, N = out_dim, K = samples;
+    const uint32_t bn = PickBN(N);
+    GemmArgs a = BaseArgs(M, N, K, bn, 1);
+    const uint64_t tiles = (uint64_t)a.m_tiles * a.n_tiles * groups;
+    uint32_t splits = tiles >= (uint64_t)e->sm_count ? 1U : (uint32_t)(e->sm_count / tiles);
+    const uint64_t per_split = (uint64_t)M * N;
+    if ((uint64_t)splits * groups * per_split > partial_floats) splits = (uint32_t)(partial_floats / (per_split * groups));
+    if (splits < 1) return MGT_CAPACITY_EXCEEDED;
+    a = BaseArgs(M, N, K, bn, splits);
+    a.groups = groups;
+    a.partial = partial;
+    CUtensorMap ta, tb;
+    MGT_MAP(e->Map3D(&ta, act_tape, M, K, groups, act_pitch, act_stride_bytes, 64, 64));
+    MGT_MAP(e->Map3D(&tb, dz_tape, N, K, groups, dz_pitch, dz_stride_bytes, 64, 64));
+    MGT_TRY(bn == 224 ? LaunchGemm<CfgDwG<224>>(e, ta, tb, a, st) : LaunchGemm<CfgDwG<256>>(e, ta, tb, a, st));
+    const dim3 grid(GridFor(per_split, 256, e->sm_count) / (groups > 4 ? 4 : 1) + 1, groups);
+    ReducePartialsGroupedKernel<<<grid, 256, 0, st>>>(partial, a.splits, per_split, grad_first, grad_group_stride);
     ++e->launches;
     return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
 }
@@ -659,12 +775,13 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     auto r1_h = [&](uint32_t k) { return reinterpret_cast<__half*>(base + ws.off_r1 + ws.r1_stride * k); };
     float* x_f32 = reinterpret_cast<float*>(base + ws.off_xf);
     float* dzf = reinterpret_cast<float*>(base + ws.off_dzf);
-    __half* dz_a = reinterpret_cast<__half*>(base + ws.off_dza);
-    __half* dz_b = reinterpret_cast<__half*>(base + ws.off_dzb);
+    auto dz_tape = [&](uint32_t k) { return reinterpret_cast<__half*>(base + ws.off_dz2 + ws.dz_stride * k); };   // [0] hidden, [k+1] fc2 of block k
+    auto dz1_tape = [&](uint32_t k) { return reinterpret_cast<__half*>(base + ws.off_dz1t + ws.dz_stride * k); };  // fc1 of block k
     __half* dz1_h = reinterpret_cast<__half*>(base + ws.off_dz1);
     float* partial = reinterpret_cast<float*>(base + ws.off_partial);
     float* head_partial = reinterpret_cast<float*>(base + ws.off_head);
     float* colsum = reinterpret_cast<float*>(base + ws.off_colsum);
+    float* colsum_h1 = reinterpret_cast<float*>(base + ws.off_colsum_h1);
     const uint32_t H1 = s.hd1, H2 = s.hd2, R = s.residual_blocks, OUT = s.output_dim, IN = ws.IN;
 
     StageTimer timer{e, st, profile};
@@ -738,8 +855,7 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     if (!timer.Mark(profile ? &profile->residual_forward_ms : nullptr)) return MGT_CUDA_FAILURE;
 
     // ---- output head, loss and the gradient entering the last block (mlp_backward.cu:1327-1364)
-    __half* dz_cur = dz_a;   // fp16 copy of the gradient w.r.t. the pre-activation being processed
-    __half* dz_other = dz_b;
+    __half* dz_cur = dz_tape(R);   // fp16 copy of the gradient w.r.t. the pre-activation the head feeds
     // the head also yields the fp32 column sums of dz: the bias gradient of the layer below it
     float* head_bias_dst = grad + (R > 0 ? Fc2B(s, R - 1) : HiddenBias(s));
     if (OUT == 1U) {
@@ -764,32 +880,52 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     MGT_TRY(notify(OutputWeight(s), (uint64_t)H2 * OUT + OUT));
     if (!timer.Mark(profile ? &profile->output_ms : nullptr)) return MGT_CUDA_FAILURE;
 
-    // ---- residual blocks backward (mlp_backward.cu:1367-1413). dz_cur holds dz2 of block k in fp16,
-    // dzf the same values in fp32 (they are added to the fc1 input gradient: the skip connection).
+    // ---- residual blocks backward (mlp_backward.cu:1367-1413). First the chain of input-gradient GEMMs,
+    // block R-1 down to 0; every dz tensor is kept. dzf holds the running fp32 gradient (skip connection).
+    const uint32_t dx_rows = BackpropGrid(e, B, H2, H2) * 8U;
+    if (R > 0 && cudaMemsetAsync(colsum, 0, ws.colsum_floats * sizeof(float), st) != cudaSuccess) return MGT_CUDA_FAILURE;
     for (uint32_t rb = R; rb > 0; --rb) {
         const uint32_t k = rb - 1U;
-        MGT_TRY(GemmGradWeights(e, st, r1_h(k), ws.p_act, dz_cur, ws.p_dz, B, H2, H2, partial, ws.partial_floats, grad + Fc2W(s, k)));
-        MGT_TRY(notify(Fc2W(s, k), (uint64_t)H2 * H2 + H2));
         GemmArgs d2{};  // dz1 = (dz2 * W2^T) * [r1 > 0]
-        d2.mask = r1_h(k); d2.ld_mask = ws.p_act; d2.out_f16 = dz_other; d2.ld_f16 = ws.p_dz;
-        MGT_TRY(GemmBackpropInput<Epi::kMaskF16>(e, st, dz_cur, ws.p_dz, hw.w2[k], hw.p2, B, H2, H2, d2, colsum, ws.colsum_floats, grad + Fc1B(s, k)));
-        MGT_TRY(GemmGradWeights(e, st, x_h(k), ws.p_act, dz_other, ws.p_dz, B, H2, H2, partial, ws.partial_floats, grad + Fc1W(s, k)));
-        MGT_TRY(notify(Fc1W(s, k), (uint64_t)H2 * H2 + H2));
+        d2.mask = r1_h(k); d2.ld_mask = ws.p_act; d2.out_f16 = dz1_tape(k); d2.ld_f16 = ws.p_dz;
+        MGT_TRY(GemmBackpropInput<Epi::kMaskF16>(e, st, dz_tape(k + 1), ws.p_dz, hw.w2[k], hw.p2, B, H2, H2, d2, colsum + ws.colsum_slot_floats * k, nullptr));
         GemmArgs d1{};  // next dz = (dz1 * W1^T + dz2) * [x_k > 0]: ReLU of the previous block (or of the hidden layer)
         d1.add_f32 = dzf; d1.ld_add = ws.p_f32; d1.out_f32 = dzf; d1.ld_f32 = ws.p_f32; d1.mask = x_h(k); d1.ld_mask = ws.p_act;
-        d1.out_f16 = dz_cur; d1.ld_f16 = ws.p_dz;
-        MGT_TRY(GemmBackpropInput<Epi::kAddMaskF32F16>(e, st, dz_other, ws.p_dz, hw.w1[k], hw.p2, B, H2, H2, d1, colsum, ws.colsum_floats,
-                                                        grad + (k > 0 ? Fc2B(s, k - 1) : HiddenBias(s))));
+        d1.out_f16 = dz_tape(k); d1.ld_f16 = ws.p_dz;
+        MGT_TRY(GemmBackpropInput<Epi::kAddMaskF32F16>(e, st, dz1_tape(k), ws.p_dz, hw.w1[k], hw.p2, B, H2, H2, d1,
+                                                        colsum + ws.colsum_slot_floats * (R + k), nullptr));
+    }
+    if (R > 0) {
+        // weight gradients of all blocks: two grouped split-K GEMMs (fc2: r1_k^T dz2_k, fc1: x_k^T dz1_k)
+        MGT_TRY(GemmGradWeightsGrouped(e, st, r1_h(0), ws.p_act, ws.r1_stride, dz_tape(1), ws.p_dz, ws.dz_stride, R, B, H2, H2, partial,
+                                       ws.partial_floats, grad + Fc2W(s, 0), BlockParams(s)));
+        MGT_TRY(GemmGradWeightsGrouped(e, st, x_h(0), ws.p_act, ws.x_stride, dz1_tape(0), ws.p_dz, ws.dz_stride, R, B, H2, H2, partial,
+                                       ws.partial_floats, grad + Fc1W(s, 0), BlockParams(s)));
+        // bias gradients: column sums of dz1_k -> b1_k, of the dz each fc1 GEMM produced -> b2_{k-1} (hidden bias for k = 0)
+        ReduceDestinations dst{};
+        for (uint32_t k = 0; k < R; ++k) {
+            dst.offset[k] = Fc1B(s, k);
+            dst.offset[R + k] = k > 0 ? Fc2B(s, k - 1) : HiddenBias(s);
+        }
+        ReduceRowsGroupedKernel<<<dim3((H2 + kReduceCols - 1) / kReduceCols, 2 * R), 256, 0, st>>>(colsum, dx_rows, H2, ws.colsum_slot_floats, grad, dst);
+        ++e->launches;
+        if (cudaGetLastError() != cudaSuccess) return MGT_CUDA_FAILURE;
+        for (uint32_t rb = R; rb > 0; --rb) {
+            MGT_TRY(notify(Fc2W(s, rb - 1U), (uint64_t)H2 * H2 + H2));
+            MGT_TRY(notify(Fc1W(s, rb - 1U), (uint64_t)H2 * H2 + H2));
+        }
     }
     if (!timer.Mark(profile ? &profile->residual_backward_ms : nullptr)) return MGT_CUDA_FAILURE;
 
-    // ---- hidden layer backward (mlp_backward.cu:1417-1438): dz_cur = dcur * [x0 > 0]
+    // ---- hidden layer backward (mlp_backward.cu:1417-1438): dz_tape(0) = dcur * [x0 > 0]
+    dz_cur = dz_tape(0);
     MGT_TRY(GemmGradWeights(e, st, a1_h, ws.p_a1, dz_cur, ws.p_dz, B, H1, H2, partial, ws.partial_floats, grad + HiddenWeight(s)));
     MGT_TRY(notify(HiddenWeight(s), (uint64_t)H1 * H2 + H2));
     {
         GemmArgs d{};  // dz1 = (dzh * Wh^T) * [a1 > 0]
         d.mask = a1_h; d.ld_mask = ws.p_a1; d.out_f16 = dz1_h; d.ld_f16 = ws.p_dz1;
-        MGT_TRY(GemmBackpropInput<Epi::kMaskF16>(e, st, dz_cur, ws.p_dz, hw.wh, hw.p2, B, H1, H2, d, colsum, ws.colsum_floats, grad + InputBias(s)));
+        if (cudaMemsetAsync(colsum_h1, 0, (uint64_t)BackpropGrid(e, B, H1, H2) * 8U * H1 * sizeof(float), st) != cudaSuccess) return MGT_CUDA_FAILURE;
+        MGT_TRY(GemmBackpropInput<Epi::kMaskF16>(e, st, dz_cur, ws.p_dz, hw.wh, hw.p2, B, H1, H2, d, colsum_h1, grad + InputBias(s)));
     }
     if (!timer.Mark(profile ? &profile->hidden_backward_ms : nullptr)) return MGT_CUDA_FAILURE;
 

@@ -101,6 +101,14 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* map, int
         : "memory");
 }
 
+// The same for a 3-D tensor (x innermost): used when one descriptor spans a stack of equally shaped matrices.
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* map, int32_t x, int32_t y, int32_t z, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
 // ---- tcgen05 / TMEM -------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_holder, uint32_t columns) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_holder)), "r"(columns) : "memory");

@@ -40,6 +40,7 @@ enum class Epi : int {
 struct GemmArgs {
     uint32_t M, N, K;
     uint32_t m_tiles, n_tiles, splits, k_chunks;
+    uint32_t groups;         // number of stacked problems (grouped form), else 1
     const float* bias;
     float* out_f32;
     uint32_t ld_f32;
@@ -66,9 +67,12 @@ struct GemmArgs {
 
 // BSTAT_: "B-stationary" - for short reductions (K <= 64*SB_) the whole B operand of the CTA's N tile is loaded
 // once and stays in shared memory while the CTA streams its M tiles (all units of a CTA then share the N tile).
-template <int BN_, int NACC_, bool A_MN_, BSource BSRC_, Epi EPI_, int SA_, int SB_, bool BSTAT_ = false>
+// GROUPED_: one launch computes args.groups independent products of the same shape; operand g is slice g
+// (third coordinate) of the 3-D tensors behind the two descriptors, result g goes to its own partial planes.
+template <int BN_, int NACC_, bool A_MN_, BSource BSRC_, Epi EPI_, int SA_, int SB_, bool BSTAT_ = false, bool GROUPED_ = false>
 struct GemmCfg {
     static constexpr bool BSTAT = BSTAT_;
+    static constexpr bool GROUPED = GROUPED_;
     static constexpr int BM = 128;
     static constexpr int BK = 64;
     static constexpr int BN = BN_;
@@ -101,6 +105,7 @@ struct GemmCfg {
     static_assert(NACC_ == 1 || NACC_ == 2, "one or two accumulators");
     static_assert(B_ACC_BYTES % 1024 == 0, "swizzle atoms must stay 1024-byte aligned");
     static_assert(!kOneHot || SB_ == 2, "the one-hot ring keeps a two-item history");
+    static_assert(!GROUPED_ || (EPI_ == Epi::kPartialF32 && A_MN_ && BSRC_ == BSource::kTmaMN && !BSTAT_), "grouped form: split-K weight gradients");
     static_assert(!BSTAT_ || (!kOneHot && NACC_ == 1), "B-stationary applies to TMA-fed single-accumulator tiles");
     static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
@@ -213,7 +218,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31U;
-    const uint32_t total_units = args.m_tiles * args.n_tiles * args.splits;
+    const uint32_t units_per_group = args.m_tiles * args.n_tiles * args.splits;
+    const uint32_t total_units = units_per_group * (Cfg::GROUPED ? args.groups : 1U);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < SA; ++s) {
@@ -250,7 +256,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
     // unit -> (m tile, n tile, split): splits of one tile are neighbours for TMA-fed GEMMs; for the
     // embedding layers units that share the A stream (same m tile and split) are neighbours.
+    auto group_of = [&](uint32_t unit) { return Cfg::GROUPED ? unit / units_per_group : 0U; };
     auto decode = [&](uint32_t unit, uint32_t& mt, uint32_t& nt, uint32_t& sp) {
+        if (Cfg::GROUPED) unit %= units_per_group;
         if (Cfg::kOneHot) {
             nt = unit % args.n_tiles;
             const uint32_t rest = unit / args.n_tiles;
@@ -279,7 +287,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     if (!mbar_wait(&empty_a[sa], pa ^ 1U, cta_abort, kAbortProducerWait)) { ok = false; break; }
                     uint8_t* a_dst = a_ring + sa * Cfg::A_STAGE_BYTES;
                     mbar_arrive_expect_tx(&full_a[sa], Cfg::A_STAGE_BYTES);
-                    if (Cfg::A_MN) {
+                    if (Cfg::GROUPED) {
+                        const int32_t g = static_cast<int32_t>(group_of(unit));
+                        tma_load_3d(a_dst, &tma_a, static_cast<int32_t>(mt * BM), static_cast<int32_t>(c * 64), g, &full_a[sa]);
+                        tma_load_3d(a_dst + 8192, &tma_a, static_cast<int32_t>(mt * BM + 64), static_cast<int32_t>(c * 64), g, &full_a[sa]);
+                    } else if (Cfg::A_MN) {
                         tma_load_2d(a_dst, &tma_a, static_cast<int32_t>(mt * BM), static_cast<int32_t>(c * 64), &full_a[sa]);
                         tma_load_2d(a_dst + 8192, &tma_a, static_cast<int32_t>(mt * BM + 64), static_cast<int32_t>(c * 64), &full_a[sa]);
                     } else {
@@ -294,7 +306,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll
                         for (int acc = 0; acc < NACC; ++acc) {
                             const uint32_t n0 = (nt * NACC + acc) * BN;
-                            if (Cfg::B_MN) {
+                            if (Cfg::GROUPED) {
+                                const int32_t z = static_cast<int32_t>(group_of(unit));
+#pragma unroll
+                                for (int g = 0; g < Cfg::N_GROUPS; ++g)
+                                    tma_load_3d(b_dst + acc * Cfg::B_ACC_BYTES + g * 8192, &tma_b, static_cast<int32_t>(n0 + g * 64),
+                                                static_cast<int32_t>(c * 64), z, &full_b[sb]);
+                            } else if (Cfg::B_MN) {
 #pragma unroll
                                 for (int g = 0; g < Cfg::N_GROUPS; ++g)
                                     tma_load_2d(b_dst + acc * Cfg::B_ACC_BYTES + g * 8192, &tma_b, static_cast<int32_t>(n0 + g * 64),
@@ -531,7 +549,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                         *reinterpret_cast<float4*>(tile + lane * TP + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
                     __syncwarp();
                     if constexpr (kPartial || kOutF32) {
-                        float* base = kPartial ? args.partial + (static_cast<uint64_t>(sp) * args.M + m_base) * args.N + n0
+                        float* base = kPartial ? args.partial + ((static_cast<uint64_t>(group_of(unit)) * args.splits + sp) * args.M + m_base) * args.N + n0
                                                : args.out_f32 + static_cast<uint64_t>(m_base) * args.ld_f32 + n0;
                         const uint64_t ld = kPartial ? args.N : args.ld_f32;
                         if (vec) {
