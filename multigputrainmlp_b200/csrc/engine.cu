@@ -11,6 +11,7 @@
 //     still reach the bias), reduced over CTAs in a fixed order;
 //   * activations are kept once (fp16 tape + one in-place fp32 residual stream).
 #include "../../include/mgt_b200.h"
+#include "tower_chain.cuh"
 #include "umma_gemm.cuh"
 
 #include <cuda.h>
@@ -61,6 +62,7 @@ struct Workspace {
     uint32_t p_w1, p_w2, p_wout;  // pitches of the internal fp16 weight copy
     uint64_t off_a1, off_x, off_r1, off_xf, off_dzf, off_dz2, off_dz1t, off_dz1, off_partial, off_head, off_wint, off_dy, off_dyh, off_colsum;
     uint64_t colsum_floats, colsum_slot_floats, off_colsum_h1, dz_stride;
+    uint64_t off_bits, bits_stride;  // ReLU sign bits of the residual tower: 2R+1 entries of bits_stride words
     uint64_t x_stride, r1_stride;  // bytes between consecutive blocks' tensors
     uint64_t partial_floats, head_blocks;
     uint64_t total_bytes;
@@ -112,10 +114,14 @@ Workspace PlanWorkspace(const mgt_mlp_shape_t& s, uint32_t B, uint32_t sm_count)
     w.head_blocks = kHeadBlocks;
     w.off_head = take((uint64_t)kHeadBlocks * (2ULL * s.hd2 + 2) * 4);
     // per-warp column sums: one slot per residual dX GEMM (2R of them), one wider slot for the hidden dX GEMM
-    w.colsum_slot_floats = (uint64_t)sm_count * 8 * s.hd2;
+    const uint64_t chain_tiles = (B + 127) / 128;
+    const uint64_t slot_rows = (uint64_t)sm_count * 8 > chain_tiles * 4 ? (uint64_t)sm_count * 8 : chain_tiles * 4;
+    w.colsum_slot_floats = slot_rows * s.hd2;
     w.colsum_floats = w.colsum_slot_floats * 2 * (w.R > 0 ? w.R : 1);
     w.off_colsum = take(w.colsum_floats * 4);
     w.off_colsum_h1 = take((uint64_t)sm_count * 8 * s.hd1 * 4);
+    w.bits_stride = chain_tiles * 128 * 8;
+    w.off_bits = take(w.bits_stride * 4 * (2 * w.R + 1));
     // internal fp16 weight copy (used when the caller's mirror cannot be addressed by TMA as it lies)
     const uint64_t wint_halfs = (uint64_t)(w.IN + 1) * w.p_w1 + (uint64_t)s.hd1 * w.p_w2 + 2ULL * w.R * s.hd2 * w.p_w2 + (uint64_t)s.hd2 * w.p_wout;
     w.off_wint = take(wint_halfs * 2 + 1024ULL * (2 * w.R + 4));
@@ -161,7 +167,7 @@ struct mgt_engine {
     std::mutex mu;
     cudaEvent_t ev_last = nullptr, ev_now = nullptr;
     uint64_t launches = 0;  // kernels launched through this engine (host-side count)
-    uint32_t debug_skip = 0;  // MGT_DEBUG_SKIP: timing experiments only (results are wrong when set)
+    uint32_t debug_skip = 0;  // MGT_DEBUG_SKIP: bits 0-1 are timing experiments (results are wrong when set); bit 2 selects the per-layer residual path
 
     // fp16 3-D tensor map (a stack of `layers` equal matrices `layer_stride_bytes` apart), 128-byte swizzle, box depth 1
     bool Map3D(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t layers, uint64_t pitch_elems, uint64_t layer_stride_bytes,
@@ -655,6 +661,31 @@ mgt_status_t GemmGradWeights(mgt_engine* e, cudaStream_t st, const __half* act, 
     return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
 }
 
+// The residual tower in one launch per direction; see tower_chain.cuh. Shapes it takes: hd2 a multiple of 32 up to 256.
+bool ChainEligible(const mgt_engine* e, const mgt_mlp_shape_t& s) {
+    return s.residual_blocks > 0 && s.hd2 % 32U == 0 && s.hd2 >= 32U && s.hd2 <= 256U && (e->debug_skip & 4U) == 0U;
+}
+
+template <bool BWD>
+mgt_status_t LaunchChain(mgt_engine* e, cudaStream_t st, const __half* w_first, uint32_t w_pitch, uint64_t w_layer_stride_bytes, ChainArgs a) {
+    static std::mutex attr_mu;
+    static bool attr_done[64] = {};
+    {
+        std::lock_guard<std::mutex> lock(attr_mu);
+        if (e->device >= 0 && e->device < 64 && !attr_done[e->device]) {
+            if (cudaFuncSetAttribute(tower_chain_kernel<BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize, ChainCfg::SMEM_BYTES) != cudaSuccess) return MGT_CUDA_FAILURE;
+            attr_done[e->device] = true;
+        }
+    }
+    CUtensorMap tw;
+    MGT_MAP(e->Map3D(&tw, w_first, a.H, a.H, 2ULL * a.R, w_pitch, w_layer_stride_bytes, 64, BWD ? a.H : 64));
+    a.status = e->status_word;
+    const uint32_t grid = a.tiles < (uint32_t)e->sm_count ? a.tiles : (uint32_t)e->sm_count;
+    tower_chain_kernel<BWD><<<grid, ChainCfg::THREADS, ChainCfg::SMEM_BYTES, st>>>(tw, a);
+    ++e->launches;
+    return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
+}
+
 struct HalfWeights {
     const __half* in_table; uint32_t p1;     // [(IN+1)][p1], row IN is the input bias
     const __half* wh; uint32_t p2;            // [H1][p2]
@@ -843,7 +874,23 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     if (!timer.Mark(profile ? &profile->hidden_forward_ms : nullptr)) return MGT_CUDA_FAILURE;
 
     // ---- residual blocks forward (mlp_backward.cu:1294-1323)
-    for (uint32_t k = 0; k < R; ++k) {
+    const bool chain = ChainEligible(e, s);
+    const uint64_t w_layer_stride = R > 0 ? (uint64_t)(reinterpret_cast<const uint8_t*>(hw.w2[0]) - reinterpret_cast<const uint8_t*>(hw.w1[0])) : 16;
+    ChainArgs ca{};
+    ca.samples = B; ca.H = H2; ca.R = R; ca.tiles = (B + 127U) / 128U;
+    ca.ld_f32 = ws.p_f32;
+    ca.bits_s = reinterpret_cast<uint32_t*>(base + ws.off_bits);
+    ca.bits_t = ca.bits_s + ws.bits_stride * (R + 1);
+    ca.bits_stride = ws.bits_stride;
+    if (chain) {
+        ChainArgs f = ca;
+        f.state_f32 = x_f32;
+        f.bias = w + Fc1B(s, 0); f.bias_stride = (uint64_t)H2 * H2 + H2;
+        f.tape_s = x_h(0); f.tape_s_stride = ws.x_stride / 2; f.ld_s = ws.p_act;
+        f.tape_t = r1_h(0); f.tape_t_stride = ws.r1_stride / 2; f.ld_t = ws.p_act;
+        MGT_TRY(LaunchChain<false>(e, st, hw.w1[0], hw.p2, w_layer_stride, f));
+    }
+    for (uint32_t k = 0; k < R && !chain; ++k) {
         GemmArgs e1{};
         e1.bias = w + Fc1B(s, k); e1.out_f16 = r1_h(k); e1.ld_f16 = ws.p_act;
         MGT_TRY(GemmForward<Epi::kBiasReluF16>(e, st, x_h(k), ws.p_act, hw.w1[k], hw.p2, B, H2, H2, e1));
@@ -883,8 +930,18 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     // ---- residual blocks backward (mlp_backward.cu:1367-1413). First the chain of input-gradient GEMMs,
     // block R-1 down to 0; every dz tensor is kept. dzf holds the running fp32 gradient (skip connection).
     const uint32_t dx_rows = BackpropGrid(e, B, H2, H2) * 8U;
-    if (R > 0 && cudaMemsetAsync(colsum, 0, ws.colsum_floats * sizeof(float), st) != cudaSuccess) return MGT_CUDA_FAILURE;
-    for (uint32_t rb = R; rb > 0; --rb) {
+    if (R > 0 && !chain && cudaMemsetAsync(colsum, 0, ws.colsum_floats * sizeof(float), st) != cudaSuccess) return MGT_CUDA_FAILURE;
+    uint32_t colsum_rows = dx_rows;
+    if (chain) {
+        ChainArgs b = ca;
+        b.state_f32 = dzf;
+        b.tape_s = dz_tape(0); b.tape_s_stride = ws.dz_stride / 2; b.ld_s = ws.p_dz;
+        b.tape_t = dz1_tape(0); b.tape_t_stride = ws.dz_stride / 2; b.ld_t = ws.p_dz;
+        b.colsum = colsum; b.colsum_stride = ws.colsum_slot_floats;
+        MGT_TRY(LaunchChain<true>(e, st, hw.w1[0], hw.p2, w_layer_stride, b));
+        colsum_rows = ca.tiles * 4U;
+    }
+    for (uint32_t rb = R; rb > 0 && !chain; --rb) {
         const uint32_t k = rb - 1U;
         GemmArgs d2{};  // dz1 = (dz2 * W2^T) * [r1 > 0]
         d2.mask = r1_h(k); d2.ld_mask = ws.p_act; d2.out_f16 = dz1_tape(k); d2.ld_f16 = ws.p_dz;
@@ -907,7 +964,7 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
             dst.offset[k] = Fc1B(s, k);
             dst.offset[R + k] = k > 0 ? Fc2B(s, k - 1) : HiddenBias(s);
         }
-        ReduceRowsGroupedKernel<<<dim3((H2 + kReduceCols - 1) / kReduceCols, 2 * R), 256, 0, st>>>(colsum, dx_rows, H2, ws.colsum_slot_floats, grad, dst);
+        ReduceRowsGroupedKernel<<<dim3((H2 + kReduceCols - 1) / kReduceCols, 2 * R), 256, 0, st>>>(colsum, colsum_rows, H2, ws.colsum_slot_floats, grad, dst);
         ++e->launches;
         if (cudaGetLastError() != cudaSuccess) return MGT_CUDA_FAILURE;
         for (uint32_t rb = R; rb > 0; --rb) {

@@ -108,6 +108,41 @@ def test_walk_batch_medium_model(oracle, engine):
     assert order == want
 
 
+def _walk_case(oracle, dims, n, seed):
+    moves, target = oracle.cyclic_puzzle(72, 18)
+    _, states, labels, _ = oracle.random_walks(moves, target, seed=seed, epoch=0, step=0, rank=0, k_min=1, k_max=29, samples=n)
+    shape = MlpShape(*dims)
+    rng = np.random.default_rng(seed)
+    w = (rng.standard_normal(shape.param_count) * 0.03).astype(np.float32)
+    lab = labels.reshape(-1, 1).astype(np.float32)
+    if shape.output_dim > 1:
+        lab = np.repeat(lab, shape.output_dim, axis=1) * np.linspace(0.5, 1.5, shape.output_dim, dtype=np.float32)
+    return shape, w, states, np.ascontiguousarray(lab)
+
+
+# hidden widths the fused residual-tower kernels take (multiples of 32 up to 256), ragged last tiles included
+@pytest.mark.parametrize("dims,n", [((72, 72, 128, 224, 3, 1), 900), ((72, 72, 64, 256, 2, 1), 300), ((72, 72, 64, 96, 5, 3), 260),
+                                     ((72, 72, 64, 160, 1, 1), 128)])
+def test_residual_tower_fused(oracle, engine, dims, n):
+    shape, w, states, labels = _walk_case(oracle, dims, n, seed=77)
+    check_against_oracle(oracle, engine, shape, w, states, labels)
+
+
+def test_residual_tower_layered_matches_fused(oracle, engine, monkeypatch):
+    # the per-layer GEMM path (taken for other widths) on a width both paths accept
+    shape, w, states, labels = _walk_case(oracle, (72, 72, 64, 64, 3, 1), 500, seed=5)
+    loss_f, grad_f = run_engine(engine, shape, w, states, labels)
+    monkeypatch.setenv("MGT_DEBUG_SKIP", "4")
+    layered = mgt.Engine(0)
+    try:
+        check_against_oracle(oracle, layered, shape, w, states, labels)
+        loss_l, grad_l = run_engine(layered, shape, w, states, labels)
+    finally:
+        layered.close()
+    assert abs(loss_f - loss_l) <= 1e-5 * abs(loss_l)
+    assert rel_l2(grad_f, grad_l) <= 1e-4
+
+
 def test_trainer_init_weights_first_step(oracle, engine):
     # the trainer's deterministic initial weights (tool:648-650) on a walk batch, physical dims of a padded model
     moves, target = oracle.cyclic_puzzle(72, 18)
