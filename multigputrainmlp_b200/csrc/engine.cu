@@ -667,7 +667,8 @@ bool ChainEligible(const mgt_engine* e, const mgt_mlp_shape_t& s) {
 }
 
 template <bool BWD>
-mgt_status_t LaunchChain(mgt_engine* e, cudaStream_t st, const __half* w_first, uint32_t w_pitch, uint64_t w_layer_stride_bytes, ChainArgs a) {
+mgt_status_t LaunchChain(mgt_engine* e, cudaStream_t st, const __half* w_first, uint32_t w_pitch, uint64_t w_layer_stride_bytes, uint32_t tape_s_entries,
+                         uint32_t tape_t_entries, ChainArgs a) {
     static std::mutex attr_mu;
     static bool attr_done[64] = {};
     {
@@ -677,11 +678,15 @@ mgt_status_t LaunchChain(mgt_engine* e, cudaStream_t st, const __half* w_first, 
             attr_done[e->device] = true;
         }
     }
-    CUtensorMap tw;
+    CUtensorMap tw, ts, tt;
     MGT_MAP(e->Map3D(&tw, w_first, a.H, a.H, 2ULL * a.R, w_pitch, w_layer_stride_bytes, 64, BWD ? a.H : 64));
+    // the tapes as stacks of [samples][H] matrices; a store box is one operand panel: 64 columns x 128 rows
+    MGT_MAP(e->Map3D(&ts, a.tape_s, a.H, a.samples, tape_s_entries, a.ld_s, a.tape_s_stride * 2, 64, 128));
+    MGT_MAP(e->Map3D(&tt, a.tape_t, a.H, a.samples, tape_t_entries, a.ld_t, a.tape_t_stride * 2, 64, 128));
     a.status = e->status_word;
+    a.debug = e->debug_skip;
     const uint32_t grid = a.tiles < (uint32_t)e->sm_count ? a.tiles : (uint32_t)e->sm_count;
-    tower_chain_kernel<BWD><<<grid, ChainCfg::THREADS, ChainCfg::SMEM_BYTES, st>>>(tw, a);
+    tower_chain_kernel<BWD><<<grid, ChainCfg::THREADS, ChainCfg::SMEM_BYTES, st>>>(tw, ts, tt, a);
     ++e->launches;
     return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
 }
@@ -888,7 +893,7 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
         f.bias = w + Fc1B(s, 0); f.bias_stride = (uint64_t)H2 * H2 + H2;
         f.tape_s = x_h(0); f.tape_s_stride = ws.x_stride / 2; f.ld_s = ws.p_act;
         f.tape_t = r1_h(0); f.tape_t_stride = ws.r1_stride / 2; f.ld_t = ws.p_act;
-        MGT_TRY(LaunchChain<false>(e, st, hw.w1[0], hw.p2, w_layer_stride, f));
+        MGT_TRY(LaunchChain<false>(e, st, hw.w1[0], hw.p2, w_layer_stride, R + 1, R, f));
     }
     for (uint32_t k = 0; k < R && !chain; ++k) {
         GemmArgs e1{};
@@ -938,7 +943,7 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
         b.tape_s = dz_tape(0); b.tape_s_stride = ws.dz_stride / 2; b.ld_s = ws.p_dz;
         b.tape_t = dz1_tape(0); b.tape_t_stride = ws.dz_stride / 2; b.ld_t = ws.p_dz;
         b.colsum = colsum; b.colsum_stride = ws.colsum_slot_floats;
-        MGT_TRY(LaunchChain<true>(e, st, hw.w1[0], hw.p2, w_layer_stride, b));
+        MGT_TRY(LaunchChain<true>(e, st, hw.w1[0], hw.p2, w_layer_stride, R + 1, R, b));
         colsum_rows = ca.tiles * 4U;
     }
     for (uint32_t rb = R; rb > 0 && !chain; --rb) {

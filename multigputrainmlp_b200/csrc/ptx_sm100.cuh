@@ -70,6 +70,35 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     return true;
 }
 
+// The same bound, but polling with the non-suspending test_wait: for hand-overs on a latency-critical chain,
+// where the time try_wait may take to resume a waiter matters.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* cta_abort, int code) {
+    if (mbar_test_wait(bar, parity)) return true;
+    const uint64_t start = global_timer_ns();
+    uint32_t spins = 0;
+    while (!mbar_test_wait(bar, parity)) {
+        if ((++spins & 1023U) == 0U) {
+            if (*cta_abort != 0) return false;
+            if (global_timer_ns() - start > kWaitLimitNs) {
+                *cta_abort = code;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
 // Named barrier over `threads` threads (a multiple of 32); id 0 is __syncthreads' own barrier.
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
@@ -109,6 +138,18 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* map, int
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
         : "memory");
 }
+
+// 3-D tiled TMA store from this CTA's shared memory (bulk-group completion); rows/columns outside the tensor are clipped.
+__device__ __forceinline__ void tma_store_3d(const void* map, const void* smem_src, int32_t x, int32_t y, int32_t z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+        ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all bulk stores of this thread have finished READING shared memory / have completed
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // ---- tcgen05 / TMEM -------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_holder, uint32_t columns) {

@@ -44,14 +44,16 @@ struct ChainArgs {
     float* colsum;             // backward: slot j at colsum + j * colsum_stride, [tiles*4][H] partial column sums
     uint64_t colsum_stride;
     int* status;
+    uint32_t debug;            // timing experiments only: 8 = no global stores, 16 = no bias/mask, 32 = weights loaded once
 };
 
 struct ChainCfg {
-    static constexpr int THREADS = 320;
+    static constexpr int EPI_WARPS = 16;            // a multiple of four: EPI_WARPS/4 warps share a TMEM lane quadrant
+    static constexpr int THREADS = 64 + 32 * EPI_WARPS;
     static constexpr int SW = 3;                    // weight ring stages
     static constexpr int ACT_BYTES = 4 * 16384;     // one operand: up to four 64-column panels of 128 rows x 128 bytes
     static constexpr int W_STAGE_BYTES = 32768;
-    static constexpr int SMEM_BYTES = 1024 + 2 * ACT_BYTES + SW * W_STAGE_BYTES + 512;
+    static constexpr int SMEM_BYTES = 1024 + 2 * ACT_BYTES + SW * W_STAGE_BYTES + 256 + 1024;  // + barriers + bias slices
     static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
@@ -95,7 +97,8 @@ __device__ __forceinline__ uint32_t pack_halfs(const float (&v)[32], uint32_t (&
 
 template <bool BWD>
 __global__ void __launch_bounds__(ChainCfg::THREADS, 1)
-tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const ChainArgs args) {
+tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_tape_s,
+                   const __grid_constant__ CUtensorMap tma_tape_t, const ChainArgs args) {
     using namespace ptx;
     constexpr int SW = ChainCfg::SW;
     constexpr uint32_t kStateCol = 256;  // first TMEM column of S
@@ -114,6 +117,7 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const ChainArgs ar
     uint64_t* mma_done = ready_t + 4;   // [2] D complete / S complete
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(mma_done + 2);
     volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_holder + 1);
+    float* bias_slots = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);  // [warps per quadrant][chunks per warp][32]
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31U;
     const uint32_t H = args.H, R = args.R;
@@ -136,6 +140,8 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const ChainArgs ar
         *cta_abort = 0;
         fence_barrier_init();
         prefetch_tensormap(&tma_w);
+        prefetch_tensormap(&tma_tape_s);
+        prefetch_tensormap(&tma_tape_t);
     }
     if (warp == 1) {
         tmem_alloc(tmem_holder, 512);
@@ -158,6 +164,7 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const ChainArgs ar
                     const int32_t z = static_cast<int32_t>(BWD ? (2U * (R - 1U - (l >> 1)) + ((l & 1U) ^ 1U)) : l);
                     for (uint32_t c = 0; c < KC; ++c, ++it) {
                         const uint32_t s = it % SW, ph = (it / SW) & 1U;
+                        if ((args.debug & 32U) && it >= SW) continue;
                         if (!mbar_wait(&w_empty[s], ph ^ 1U, cta_abort, kAbortChainWait)) { ok = false; break; }
                         uint8_t* dst = w_ring + s * ChainCfg::W_STAGE_BYTES;
                         mbar_arrive_expect_tx(&w_full[s], stage_bytes);
@@ -189,7 +196,7 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const ChainArgs ar
                         for (uint32_t c = 0; c < KC; ++c, ++it) {
                             const uint32_t s = it % SW, ph = (it / SW) & 1U;
                             if (!mbar_wait(&ready[c], uses & 1U, cta_abort, kAbortChainWait)) { ok = false; break; }
-                            if (!mbar_wait(&w_full[s], ph, cta_abort, kAbortChainWait)) { ok = false; break; }
+                            if (!((args.debug & 32U) && it >= SW) && !mbar_wait(&w_full[s], ph, cta_abort, kAbortChainWait)) { ok = false; break; }
                             tc_fence_after();
                             const uint32_t a_addr = a_base + c * 16384U;
                             const uint32_t b_addr = smem_u32(w_ring + s * ChainCfg::W_STAGE_BYTES);
@@ -199,21 +206,37 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const ChainArgs ar
                                 const uint64_t a_desc = make_smem_desc(a_addr + kk * 32U, 16U, 1024U);
                                 const uint64_t b_desc = BWD ? make_smem_desc(b_addr + kk * 32U, 16U, 1024U) : make_smem_desc(b_addr + kk * 2048U, 8192U, 1024U);
                                 // the second product of a block adds onto the state that already sits in TMEM
-                                umma_f16(d_addr, a_desc, b_desc, idesc, (half != 0U || c > 0U || kk > 0U) ? 1U : 0U);
+                                if (!(args.debug & 64U)) umma_f16(d_addr, a_desc, b_desc, idesc, (half != 0U || c > 0U || kk > 0U) ? 1U : 0U);
                             }
-                            umma_commit(&w_empty[s]);
+                            if (!(args.debug & 32U)) umma_commit(&w_empty[s]);
                         }
+                        // the epilogue this commit releases overwrites the operand the PREVIOUS phase read and stored
+                        bulk_wait_read_all();
                         if (ok) umma_commit(&mma_done[half]);
+                        // Each operand panel is also a 64-column slice of a tape entry: T of this block, or the S the previous
+                        // block produced (the S a tile starts with is on its tape already). Issued here, after the commit,
+                        // the stores cost the MMA stream nothing.
+                        if (ok && (half != 0U || kb > 0U) && !(args.debug & 8U)) {
+                            const uint32_t k = BWD ? R - 1U - kb : kb;
+                            const uint32_t entry = half ? k : (BWD ? k + 1U : k);
+                            for (uint32_t c = 0; c < KC; ++c)
+                                tma_store_3d(half ? &tma_tape_t : &tma_tape_s, (half ? act_t : act_s) + c * 16384U, static_cast<int32_t>(c * 64U),
+                                             static_cast<int32_t>(tile * 128U), static_cast<int32_t>(entry));
+                            bulk_commit_group();
+                        }
                     }
                 }
             }
+            bulk_wait_all();  // the tape stores read this CTA's shared memory until they complete
         }
         __syncwarp();
     } else {
         // ------------------------------- epilogue -----------------------------------------
         const uint32_t ew = warp - 2U;
         const uint32_t quad = warp & 3U;       // TMEM lanes [32*quad, 32*quad+32)
-        const uint32_t par = ew >> 2;          // this warp takes 32-column chunks par, par+2, ...
+        constexpr uint32_t SUBS = ChainCfg::EPI_WARPS / 4;  // warps per quadrant
+        constexpr uint32_t WPW = 8U / SUBS;                  // 32-column chunks (and sign-bit words) per warp at most
+        const uint32_t par = ew >> 2;          // this warp takes 32-column chunks par, par+SUBS, ...
         const uint32_t r = quad * 32U + lane;  // row inside the tile
         const uint32_t lane_addr = (quad * 32U) << 16;
         // byte offset of 16-byte unit u (0..7) of this row inside a 64-column panel, 128B swizzle
@@ -229,25 +252,61 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const ChainArgs ar
 #pragma unroll
             for (uint32_t q = 0; q < 4U; ++q) dst[q] = make_uint4(h[4 * q], h[4 * q + 1], h[4 * q + 2], h[4 * q + 3]);
         };
+        // lane 0 polls, the warp follows: the result is warp-uniform
+        auto warp_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+            uint32_t done = 0;
+            if (lane == 0) done = mbar_wait(bar, parity, cta_abort, kAbortChainWait) ? 1U : 0U;
+            return __shfl_sync(0xFFFFFFFFU, done, 0) != 0U;
+        };
         auto publish = [&](uint64_t* bar) {
             fence_proxy_async_smem();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar);
         };
-        auto add_bias_relu = [&](float (&v)[32], const float* b) {
-            if ((reinterpret_cast<uintptr_t>(b) & 15U) == 0U) {
+        // Bias of a layer: each lane fetches one value per chunk of its warp before the warp waits for the MMAs (the
+        // load flies during the wait); after the wait the values go through a shared-memory slot so that every
+        // thread can read all 32 of a chunk as broadcast vectors. The warps of one quadrant set share slots and write
+        // identical values; a slot is rewritten only after the MMAs that needed every warp's previous epilogue.
+        float bias_reg[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        auto fetch_bias = [&](uint32_t layer) {
+            if (!BWD && !(args.debug & 16U)) {
 #pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                    const float4 f = __ldg(reinterpret_cast<const float4*>(b) + q);
-                    v[4 * q] = fmaxf(v[4 * q] + f.x, 0.0f);
-                    v[4 * q + 1] = fmaxf(v[4 * q + 1] + f.y, 0.0f);
-                    v[4 * q + 2] = fmaxf(v[4 * q + 2] + f.z, 0.0f);
-                    v[4 * q + 3] = fmaxf(v[4 * q + 3] + f.w, 0.0f);
+                for (uint32_t ci = 0; ci < WPW; ++ci) {
+                    const uint32_t cc = par + SUBS * ci;
+                    if (cc < NC) bias_reg[ci] = __ldg(args.bias + layer * args.bias_stride + cc * 32U + lane);
                 }
-            } else {
+            }
+        };
+        auto stage_bias = [&]() {
+            if (!BWD) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j] + __ldg(b + j), 0.0f);
+                for (uint32_t ci = 0; ci < WPW; ++ci) bias_slots[(par * WPW + ci) * 32U + lane] = bias_reg[ci];
+                __syncwarp();
+            }
+        };
+        auto add_bias_relu = [&](float (&v)[32], uint32_t ci) {
+            const float4* b = reinterpret_cast<const float4*>(bias_slots + (par * WPW + ci) * 32U);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const float4 f = b[q];
+                v[4 * q] = fmaxf(v[4 * q] + f.x, 0.0f);
+                v[4 * q + 1] = fmaxf(v[4 * q + 1] + f.y, 0.0f);
+                v[4 * q + 2] = fmaxf(v[4 * q + 2] + f.z, 0.0f);
+                v[4 * q + 3] = fmaxf(v[4 * q + 3] + f.w, 0.0f);
+            }
+        };
+        auto store_words = [&](uint32_t* dst, const uint32_t (&wd)[4]) {
+            if (WPW == 4U) *reinterpret_cast<uint4*>(dst) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+            else *reinterpret_cast<uint2*>(dst) = make_uint2(wd[0], wd[1]);
+        };
+        auto load_words = [&](const uint32_t* src, uint32_t (&wd)[4]) {
+            if (WPW == 4U) {
+                const uint4 m = *reinterpret_cast<const uint4*>(src);
+                wd[0] = m.x; wd[1] = m.y; wd[2] = m.z; wd[3] = m.w;
+            } else {
+                const uint2 m = *reinterpret_cast<const uint2*>(src);
+                wd[0] = m.x; wd[1] = m.y;
             }
         };
         auto apply_mask = [&](float (&v)[32], uint32_t bits) {
@@ -260,14 +319,15 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const ChainArgs ar
         for (uint32_t tile = blockIdx.x; tile < args.tiles && ok; tile += gridDim.x) {
             const uint64_t row = static_cast<uint64_t>(tile) * 128U + r;
             const bool row_ok = row < args.samples;
-            const uint64_t bits_row = row * 8U + par * 4U;  // this warp's four words of the row
+            const bool st_ok = row_ok && !(args.debug & 8U);
+            const uint64_t bits_row = row * 8U + par * WPW;  // this warp's words of the row
 
             // ---- load the state: TMEM S, fp16 operand, (forward) sign bits of x_0
             {
-                uint32_t words[4] = {0, 0, 0, 0};
+                uint32_t words[4] = {0, 0, 0, 0};  // the first WPW are used
 #pragma unroll
-                for (uint32_t ci = 0; ci < 4U; ++ci) {
-                    const uint32_t cc = par + 2U * ci;
+                for (uint32_t ci = 0; ci < WPW; ++ci) {
+                    const uint32_t cc = par + SUBS * ci;
                     if (cc >= NC) break;
                     float v[32];
                     if (row_ok) {
@@ -291,7 +351,7 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const ChainArgs ar
                     tmem_st_wait();
                     publish(&ready_s[cc >> 1]);
                 }
-                if (!BWD) *reinterpret_cast<uint4*>(args.bits_s + bits_row) = make_uint4(words[0], words[1], words[2], words[3]);
+                if (!BWD) store_words(args.bits_s + bits_row, words);
             }
 
             for (uint32_t kb = 0; kb < R && ok; ++kb, ++uses) {
@@ -299,16 +359,16 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const ChainArgs ar
                 const bool last = kb + 1U == R;
                 // ================= first epilogue: T from D =================
                 {
-                    uint4 mb = make_uint4(0, 0, 0, 0);
-                    if (BWD) mb = *reinterpret_cast<const uint4*>(args.bits_t + k * args.bits_stride + bits_row);
-                    const uint32_t mwords[4] = {mb.x, mb.y, mb.z, mb.w};
-                    uint32_t words[4] = {0, 0, 0, 0};
-                    if (!__all_sync(0xFFFFFFFFU, mbar_wait(&mma_done[0], uses & 1U, cta_abort, kAbortChainWait))) { ok = false; break; }
+                    uint32_t mwords[4] = {0, 0, 0, 0};
+                    if (BWD) load_words(args.bits_t + k * args.bits_stride + bits_row, mwords);
+                    uint32_t words[4] = {0, 0, 0, 0};  // the first WPW are used
+                    fetch_bias(2U * k);
+                    if (!warp_wait(&mma_done[0], uses & 1U)) { ok = false; break; }
                     tc_fence_after();
-                    __half* tape_row = args.tape_t + k * args.tape_t_stride + row * args.ld_t;
+                    stage_bias();
 #pragma unroll
-                    for (uint32_t ci = 0; ci < 4U; ++ci) {
-                        const uint32_t cc = par + 2U * ci;
+                    for (uint32_t ci = 0; ci < WPW; ++ci) {
+                        const uint32_t cc = par + SUBS * ci;
                         if (cc >= NC) break;
                         uint32_t raw[32];
                         tmem_ld_32x32(tmem_base + lane_addr + cc * 32U, raw);
@@ -316,33 +376,34 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const ChainArgs ar
                         float v[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
-                        if (BWD) apply_mask(v, mwords[ci]);
-                        else add_bias_relu(v, args.bias + (2U * k) * args.bias_stride + cc * 32U);
+                        if (args.debug & 16U) {
+                        } else if (BWD) apply_mask(v, mwords[ci]);
+                        else add_bias_relu(v, ci);
                         uint32_t h[16];
                         words[ci] = detail::pack_halfs(v, h);
                         store_operand(act_t, cc, h);
                         publish(&ready_t[cc >> 1]);
-                        if (row_ok) store_tape(tape_row, cc, h);
-                        if (BWD) {
+                        if (BWD && !(args.debug & 8U)) {
                             const float total = detail::warp_column_sums(v, lane);
                             args.colsum[k * args.colsum_stride + (static_cast<uint64_t>(tile) * 4U + quad) * H + cc * 32U + lane] = total;
                         }
                     }
-                    if (!BWD) *reinterpret_cast<uint4*>(args.bits_t + k * args.bits_stride + bits_row) = make_uint4(words[0], words[1], words[2], words[3]);
+                    if (!BWD) store_words(args.bits_t + k * args.bits_stride + bits_row, words);
                 }
                 // ================= second epilogue: new S =================
                 {
-                    uint4 mb = make_uint4(0, 0, 0, 0);
-                    if (BWD) mb = *reinterpret_cast<const uint4*>(args.bits_s + k * args.bits_stride + bits_row);
-                    const uint32_t mwords[4] = {mb.x, mb.y, mb.z, mb.w};
-                    uint32_t words[4] = {0, 0, 0, 0};
-                    if (!__all_sync(0xFFFFFFFFU, mbar_wait(&mma_done[1], uses & 1U, cta_abort, kAbortChainWait))) { ok = false; break; }
+                    uint32_t mwords[4] = {0, 0, 0, 0};
+                    if (BWD) load_words(args.bits_s + k * args.bits_stride + bits_row, mwords);
+                    uint32_t words[4] = {0, 0, 0, 0};  // the first WPW are used
+                    fetch_bias(2U * k + 1U);
+                    if (!warp_wait(&mma_done[1], uses & 1U)) { ok = false; break; }
                     tc_fence_after();
+                    stage_bias();
                     const uint32_t entry = BWD ? k : k + 1U;
                     __half* tape_row = args.tape_s + entry * args.tape_s_stride + row * args.ld_s;
 #pragma unroll
-                    for (uint32_t ci = 0; ci < 4U; ++ci) {
-                        const uint32_t cc = par + 2U * ci;
+                    for (uint32_t ci = 0; ci < WPW; ++ci) {
+                        const uint32_t cc = par + SUBS * ci;
                         if (cc >= NC) break;
                         uint32_t raw[32];
                         tmem_ld_32x32(tmem_base + lane_addr + kStateCol + cc * 32U, raw);
@@ -350,8 +411,9 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const ChainArgs ar
                         float v[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
-                        if (BWD) apply_mask(v, mwords[ci]);
-                        else add_bias_relu(v, args.bias + (2U * k + 1U) * args.bias_stride + cc * 32U);
+                        if (args.debug & 16U) {
+                        } else if (BWD) apply_mask(v, mwords[ci]);
+                        else add_bias_relu(v, ci);
                         uint32_t h[16];
                         words[ci] = detail::pack_halfs(v, h);
                         if (!last) {
@@ -362,20 +424,20 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const ChainArgs ar
                             tmem_st_wait();
                             publish(&ready_s[cc >> 1]);
                         }
-                        if (row_ok) {
+                        if (st_ok && last) {  // no MMA consumes the last S of a tile, so no panel store either
                             store_tape(tape_row, cc, h);
-                            if (!BWD && last) {
+                            if (!BWD) {
                                 float4* dst = reinterpret_cast<float4*>(args.state_f32 + row * args.ld_f32 + cc * 32U);
 #pragma unroll
                                 for (int q = 0; q < 8; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
                             }
                         }
-                        if (BWD) {
+                        if (BWD && !(args.debug & 8U)) {
                             const float total = detail::warp_column_sums(v, lane);
                             args.colsum[(R + k) * args.colsum_stride + (static_cast<uint64_t>(tile) * 4U + quad) * H + cc * 32U + lane] = total;
                         }
                     }
-                    if (!BWD) *reinterpret_cast<uint4*>(args.bits_s + (k + 1U) * args.bits_stride + bits_row) = make_uint4(words[0], words[1], words[2], words[3]);
+                    if (!BWD) store_words(args.bits_s + (k + 1U) * args.bits_stride + bits_row, words);
                     if (last) tc_fence_before();  // the next tile's state load overwrites the TMEM columns read here
                 }
             }
