@@ -670,62 +670,98 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             };
             bool fast = false;
             if constexpr (Cfg::BSRC == BSource::kOneHotFwd) {
-                // ---- forward, streaming form: a row's ones sit at k_p = p*V + s[p], increasing in p, and the
-                // chunks of a unit are visited in increasing k. Each row keeps a cursor for setting and one for
-                // clearing (two items behind); the state byte of the next position is fetched when a cursor
-                // advances, one or more chunks before it is needed, so no chunk waits for a load.
-                fast = args.splits == 1U;
+                // ---- forward, pipelined form: a row's ones sit at k_p = p*V + s[p], increasing in p, and the chunks of
+                // a unit are visited in increasing k, so each row keeps a cursor. With V >= 64 a 64-wide chunk holds at
+                // most two of a row's ones (plus the all-ones column that multiplies the bias row, in the last chunk).
+                // Everything that needs arithmetic or a load - the places of the NEXT item - is worked out while the
+                // MMAs of the current items run; between "stage released" and "stage published" the warp only stores:
+                // zeros at the places it remembers from two items ago, ones at the new places.
+                fast = args.splits == 1U && V >= 64U;
                 if (fast) {
                     constexpr uint32_t RPT = ROWS / NT;
+                    constexpr uint32_t kNone = 0xFFFFFFFFU;
                     struct Cursor { uint32_t p, s0, s1; };
-                    Cursor setc[RPT], clrc[RPT];
-                    auto rewind = [&](Cursor& q, uint32_t sample) {
-                        const bool active = sample < args.samples;
-                        const uint8_t* st = args.states + static_cast<uint64_t>(sample) * 80U;
-                        q.p = active ? 0U : L;
-                        q.s0 = active ? __ldg(st) : 0U;
-                        q.s1 = (active && L > 1U) ? __ldg(st + 1) : 0U;
-                    };
-                    auto sweep = [&](Cursor& q, uint32_t sample, uint8_t* buf, uint32_t n, uint32_t k0, uint16_t value) {
-                        const uint8_t* st = args.states + static_cast<uint64_t>(sample) * 80U;
-                        while (q.p < L) {
-                            const uint32_t k = q.p * V + q.s0 - k0;  // never below the chunk: earlier chunks consumed those
-                            if (k >= 64U) break;
-                            *place(buf, n, k) = value;
-                            ++q.p;
-                            q.s0 = q.s1;
-                            q.s1 = (q.p + 1U < L) ? __ldg(st + q.p + 1U) : 0U;
-                        }
-                        const uint32_t kb = IN - k0;  // the all-ones column that multiplies the bias row
-                        if (kb < 64U && sample < args.samples) *place(buf, n, kb) = value;
-                    };
-                    uint32_t it = 0, h_nt[2] = {0, 0}, h_c[2] = {0, 0};
-                    bool ok = true;
-                    for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
-                        uint32_t mt, nt, sp;
-                        decode(unit, mt, nt, sp);
-                        for (uint32_t c = 0; c < args.k_chunks; ++c, ++it) {
-                            const uint32_t sb = it & 1U;
-                            if (!acquire(it)) { ok = false; break; }
-                            uint8_t* buf = b_ring + sb * Cfg::B_STAGE_BYTES;
-                            if (it >= 2U) {
-                                const uint32_t ont = sb ? h_nt[1] : h_nt[0], oc = sb ? h_c[1] : h_c[0];
+                    Cursor cur[RPT];
+                    uint32_t next[RPT][3], hist0[RPT][3], hist1[RPT][3];
 #pragma unroll
-                                for (uint32_t i = 0; i < RPT; ++i) {
-                                    const uint32_t n = t + i * NT, sample = ont * ROWS + n;
-                                    if (oc == 0U) rewind(clrc[i], sample);
-                                    sweep(clrc[i], sample, buf, n, oc * 64U, 0);
+                    for (uint32_t i = 0; i < RPT; ++i)
+#pragma unroll
+                        for (uint32_t j = 0; j < 3U; ++j) hist0[i][j] = hist1[i][j] = kNone;
+                    auto offset_of = [&](uint32_t n, uint32_t k) -> uint32_t {
+                        return (n / BN) * Cfg::B_ACC_BYTES + (n % BN) * 128U + ((((k >> 3) ^ (n & 7U)) << 4) | ((k & 7U) << 1));
+                    };
+                    // places of item (nt, c) -> next[][]; advances the cursors (rewound at the first chunk of a unit)
+                    auto prepare = [&](uint32_t nt, uint32_t c) {
+                        const uint32_t k0 = c * 64U;
+                        const uint32_t kb = IN - k0;
+#pragma unroll
+                        for (uint32_t i = 0; i < RPT; ++i) {
+                            const uint32_t n = t + i * NT, sample = nt * ROWS + n;
+                            const bool active = sample < args.samples;
+                            const uint8_t* st = args.states + static_cast<uint64_t>(sample) * 80U;
+                            Cursor& q = cur[i];
+                            if (c == 0U) {
+                                q.p = active ? 0U : L;
+                                q.s0 = active ? __ldg(st) : 0U;
+                                q.s1 = (active && L > 1U) ? __ldg(st + 1) : 0U;
+                            }
+#pragma unroll
+                            for (uint32_t j = 0; j < 2U; ++j) {
+                                const uint32_t k = q.p * V + q.s0 - k0;  // never below the chunk: earlier chunks consumed those
+                                const bool hit = q.p < L && k < 64U;
+                                next[i][j] = hit ? offset_of(n, k) : kNone;
+                                if (hit) {
+                                    ++q.p;
+                                    q.s0 = q.s1;
+                                    q.s1 = (q.p + 1U < L) ? __ldg(st + q.p + 1U) : 0U;
                                 }
                             }
-#pragma unroll
-                            for (uint32_t i = 0; i < RPT; ++i) {
-                                const uint32_t n = t + i * NT, sample = nt * ROWS + n;
-                                if (c == 0U) rewind(setc[i], sample);
-                                sweep(setc[i], sample, buf, n, c * 64U, 0x3C00);
-                            }
-                            if (sb) { h_nt[1] = nt; h_c[1] = c; } else { h_nt[0] = nt; h_c[0] = c; }
-                            publish(it);
+                            next[i][2] = (kb < 64U && active) ? offset_of(n, kb) : kNone;
                         }
+                    };
+                    uint32_t unit = blockIdx.x, mt, nt, sp;
+                    bool have = unit < total_units && args.k_chunks > 0U;
+                    uint32_t c = 0;
+                    if (have) {
+                        decode(unit, mt, nt, sp);
+                        prepare(nt, 0);
+                    }
+                    uint32_t it = 0;
+                    const bool dry = (args.debug_skip & 1U) != 0U;
+                    while (have) {
+                        uint32_t unit2 = unit, nt2 = nt, c2 = c + 1U;
+                        bool have2 = true;
+                        if (c2 >= args.k_chunks) {
+                            unit2 += gridDim.x;
+                            c2 = 0;
+                            have2 = unit2 < total_units;
+                            if (have2) {
+                                uint32_t mt2, sp2;
+                                decode(unit2, mt2, nt2, sp2);
+                            }
+                        }
+                        const uint32_t sb = it & 1U;
+                        if (!acquire(it)) break;
+                        uint8_t* buf = b_ring + sb * Cfg::B_STAGE_BYTES;
+#pragma unroll
+                        for (uint32_t i = 0; i < RPT; ++i)
+#pragma unroll
+                            for (uint32_t j = 0; j < 3U; ++j) {
+                                const uint32_t old = sb ? hist1[i][j] : hist0[i][j];
+                                if (old != kNone && !dry) *reinterpret_cast<uint16_t*>(buf + old) = 0;
+                            }
+#pragma unroll
+                        for (uint32_t i = 0; i < RPT; ++i)
+#pragma unroll
+                            for (uint32_t j = 0; j < 3U; ++j) {
+                                const uint32_t off = next[i][j];
+                                if (off != kNone && !dry) *reinterpret_cast<uint16_t*>(buf + off) = 0x3C00;
+                                if (sb) hist1[i][j] = off; else hist0[i][j] = off;
+                            }
+                        publish(it);
+                        if (have2) prepare(nt2, c2);
+                        unit = unit2; nt = nt2; c = c2; have = have2;
+                        ++it;
                     }
                 }
             } else {
