@@ -39,6 +39,9 @@ LR = 1e-4
 FLOP_PER_CANDIDATE = 13_444_416          # 3*(2*H1*H2 + 4R*H2^2 + 2*H2*OUT) + 2*L*H1 at the physical dims
 EMB_ALGO_FLOP_PER_CANDIDATE = 72 * 2560   # the embedding forward counted as the sparse work it is (72 row adds)
 EMB_EXEC_FLOP_PER_CANDIDATE = 2 * (72 * 72 + 1) * 2560  # what the one-hot GEMM executes on the tensor cores
+# dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch of the one-hot forward kernel (single-pass ncu
+# capture, profiles/training_step_p888_launch_list.md): 31.4 MB read + 218.9 MB written
+EMB_FWD_DRAM_BYTES_PER_LAUNCH = 250_300_000
 
 
 def workload_config(n_gpus: int) -> dict:
@@ -61,54 +64,79 @@ def load_peaks() -> dict:
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: NVML queries (read-only) every
+    10 ms from a thread of this process, or `nvidia-smi -lms 100` when the NVML module is missing."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
-    def __init__(self, index: int):
-        self.rows = []
+    def __init__(self, index: int, uuid: str | None = None):
+        self.rows = []          # (time, sm_mhz, set of active reasons)
+        self.smax = None
         self.proc = None
+        self.stop_flag = threading.Event()
+        self.thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            try:  # CUDA_VISIBLE_DEVICES renumbers CUDA devices, NVML keeps the board order: go by UUID when it is known
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode() if isinstance(uuid, str) else uuid)
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.smax = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread = threading.Thread(target=self._read_smi, daemon=True)
             self.thread.start()
         except OSError:
             self.proc = None
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append((time.time(), line.strip()))
+    def _poll_nvml(self):
+        n = self.nvml
+        masks = {"hw_slowdown": getattr(n, "nvmlClocksEventReasonHwSlowdown", 0x8), "hw_thermal_slowdown": getattr(n, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(n, "nvmlClocksEventReasonSwThermalSlowdown", 0x20), "sw_power_cap": getattr(n, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        get_reasons = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or getattr(n, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        while not self.stop_flag.is_set():
+            try:
+                mhz = float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
+                bits = int(get_reasons(self.handle))
+                self.rows.append((time.time(), mhz, {name for name, mask in masks.items() if bits & mask}))
+            except Exception:
+                pass
+            time.sleep(0.01)
 
-    def stop(self, t0: float, t1: float) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        sm, smax, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ts, line in self.rows:
+    def _read_smi(self):
+        for line in self.proc.stdout:
             parts = [x.strip() for x in line.split(",")]
             if len(parts) < 7:
                 continue
             try:
-                smax = float(parts[1])
-                if t0 - 0.05 <= ts <= t1 + 0.05:
-                    sm.append(float(parts[0]))
-                    for name, val in zip(names, parts[3:7]):
-                        if val.lower().startswith("active"):
-                            reasons.add(name)
+                self.smax = float(parts[1])
+                self.rows.append((time.time(), float(parts[0]), {name for name, val in zip(self.NAMES, parts[3:7]) if val.lower().startswith("active")}))
             except ValueError:
                 continue
-        if not sm:  # very short regions: take what was seen
-            for ts, line in self.rows[-3:]:
-                parts = [x.strip() for x in line.split(",")]
-                try:
-                    sm.append(float(parts[0]))
-                except (ValueError, IndexError):
-                    pass
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm)}
+
+    def stop(self, t0: float, t1: float) -> dict:
+        if self.thread is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["clock sampling unavailable"]}
+        time.sleep(0.05 if self.proc is None else 0.15)
+        self.stop_flag.set()
+        if self.proc is not None:
+            self.proc.terminate()
+        inside = [r for r in self.rows if t0 <= r[0] <= t1] or self.rows[-3:]  # very short regions: take what was seen
+        sm = [r[1] for r in inside]
+        reasons = set()
+        for r in inside:
+            reasons |= r[2]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": self.smax, "reasons": sorted(reasons), "samples": len(sm)}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -182,7 +210,7 @@ def run_reference_cpu(args, steps: int, warmup: int) -> dict:
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--comm", default="peer", choices=["peer", "nccl"], help="gradient exchange at N>1: the library's NVLink peer kernels, or NCCL + AdamW (the reference's scheme, for comparison)")
@@ -293,7 +321,11 @@ def main():
     assert st == 0, f"device status {code}"
 
     # ---- device-timed region: K steps, resident inputs --------------------------------------
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    try:
+        gpu_uuid = "GPU-" + str(torch.cuda.get_device_properties(local_rank).uuid)
+    except Exception:
+        gpu_uuid = None
+    sampler = ClockSampler(local_rank, gpu_uuid) if rank == 0 else None
     if sampler is not None:
         time.sleep(0.3)
     launches0 = engine.launch_count + other_launches
@@ -354,7 +386,8 @@ def main():
     exec_tflops = EMB_EXEC_FLOP_PER_CANDIDATE * batch / (emb * 1e-3) / 1e12
     roofline = {
         "kernel": "umma_gemm_kernel<one-hot forward> (embedding layer)", "bound": "tensor", "achieved": algo_tflops,
-        "peak": peaks["tflops_burst"], "unit": "TFLOP/s", "frac": algo_tflops / peaks["tflops_burst"], "traffic": None,
+        "peak": peaks["tflops_burst"], "unit": "TFLOP/s", "frac": algo_tflops / peaks["tflops_burst"],
+        "traffic": EMB_FWD_DRAM_BYTES_PER_LAUNCH if batch == BATCH else None,
         "peak_source": peaks["source"] + " (cuBLAS bf16 burst)", "ms_per_launch": emb,
         "executed_tflops": exec_tflops, "executed_frac": exec_tflops / peaks["tflops_burst"],
         "note": "achieved counts the 72 row-adds per candidate the layer needs; executed counts the dense one-hot MMA work",

@@ -39,6 +39,7 @@ class GradientRangeScheduler:
     bucket_params: int = (4 << 20) // 4
     expected_ranges: Optional[int] = None
     lag: int = 1                                     # notifications a range is held back (1 when the update is fused)
+    whole_tail: bool = True                          # ranges left at finish() go out unchunked: nothing remains to overlap with
     scheduled_ranges: int = 0
     scheduled_chunks: int = 0
     log: List[ScheduledChunk] = field(default_factory=list)
@@ -50,7 +51,7 @@ class GradientRangeScheduler:
         self.log = []
         self._pending = []
 
-    def _flush(self, keep: int) -> None:
+    def _flush(self, keep: int, whole: bool = False) -> None:
         if len(self._pending) <= keep:
             return
         self.wait_for_producer()
@@ -58,7 +59,7 @@ class GradientRangeScheduler:
             ready_id, offset, count = self._pending.pop(0)
             remaining = count
             while remaining > 0:
-                chunk = min(remaining, max(1, self.bucket_params))
+                chunk = remaining if whole else min(remaining, max(1, self.bucket_params))
                 self.launch(offset, chunk)
                 self.log.append(ScheduledChunk(ready_id, offset, chunk))
                 offset += chunk
@@ -74,7 +75,7 @@ class GradientRangeScheduler:
         return 0
 
     def finish(self) -> None:
-        self._flush(0)
+        self._flush(0, whole=self.whole_tail)
         if self.expected_ranges is not None and self.scheduled_ranges != self.expected_ranges:
             raise RuntimeError(f"gradient-ready ranges: got {self.scheduled_ranges}, expected {self.expected_ranges}")  # tool:817
 

@@ -168,7 +168,32 @@ __device__ void ReduceRange(const CommDev& c, uint64_t begin, uint64_t end, floa
                 if (p != c.rank) c.grad[p][i] = avg;
         Finish1<kAdam>(avg, i, own, a, sc);
     }
-    for (uint64_t i = head_end + tid * 4ULL; i < body_end; i += nthreads * 4ULL) {
+    // four vectors per thread and pass: 4 x world peer loads are in flight before the first sum, which is what it takes
+    // to cover the NVLink round trip with 148 x 256 threads
+    constexpr uint32_t kUnroll = 4;
+    uint64_t i = head_end + tid * 4ULL;
+    for (; i + (kUnroll - 1ULL) * nthreads * 4ULL < body_end; i += nthreads * 4ULL * kUnroll) {
+        float4 acc[kUnroll];
+#pragma unroll
+        for (uint32_t u = 0; u < kUnroll; ++u) acc[u] = ld_peer_f4(c.grad[0] + i + u * nthreads * 4ULL);
+        for (uint32_t p = 1; p < c.world; ++p) {
+            float4 x[kUnroll];
+#pragma unroll
+            for (uint32_t u = 0; u < kUnroll; ++u) x[u] = ld_peer_f4(c.grad[p] + i + u * nthreads * 4ULL);
+#pragma unroll
+            for (uint32_t u = 0; u < kUnroll; ++u) { acc[u].x += x[u].x; acc[u].y += x[u].y; acc[u].z += x[u].z; acc[u].w += x[u].w; }
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < kUnroll; ++u) {
+            const uint64_t j = i + u * nthreads * 4ULL;
+            const float4 avg = make_float4(acc[u].x * inv_w, acc[u].y * inv_w, acc[u].z * inv_w, acc[u].w * inv_w);
+            if (kWritePeers)
+                for (uint32_t p = 0; p < c.world; ++p)
+                    if (p != c.rank) *reinterpret_cast<float4*>(c.grad[p] + j) = avg;
+            Finish4<kAdam>(avg, j, own, a, sc);
+        }
+    }
+    for (; i < body_end; i += nthreads * 4ULL) {
         const float4 avg = Average4(c, i, inv_w);
         if (kWritePeers)
             for (uint32_t p = 0; p < c.world; ++p)
@@ -189,7 +214,12 @@ __device__ void AdamRange(const CommDev& c, uint64_t begin, uint64_t end, const 
     float* own = c.grad[c.rank];
     const uint64_t tid = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     const uint64_t nthreads = static_cast<uint64_t>(gridDim.x) * blockDim.x;
-    for (uint64_t i = begin + tid; i < end; i += nthreads) Finish1<true>(__ldcg(own + i), i, own, a, sc);
+    const uint64_t head_up = (begin + 3ULL) & ~3ULL;
+    const uint64_t head_end = end < head_up ? end : head_up;
+    const uint64_t body_end = head_end + ((end - head_end) & ~3ULL);
+    for (uint64_t i = begin + tid; i < head_end; i += nthreads) Finish1<true>(__ldcg(own + i), i, own, a, sc);
+    for (uint64_t i = head_end + tid * 4ULL; i < body_end; i += nthreads * 4ULL) Finish4<true>(__ldcg(reinterpret_cast<const float4*>(own + i)), i, own, a, sc);
+    for (uint64_t i = body_end + tid; i < end; i += nthreads) Finish1<true>(__ldcg(own + i), i, own, a, sc);
 }
 
 template <bool kAdam>

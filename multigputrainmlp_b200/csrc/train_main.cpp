@@ -44,11 +44,12 @@ struct ExchangeContext {
     uint64_t pending_offset = 0, pending_count = 0;
     bool failed = false;
 
-    bool LaunchRange(uint64_t offset, uint64_t count, cudaStream_t producer) {
+    // `whole`: no chunking - for the range(s) left when backward has ended and nothing remains to overlap with
+    bool LaunchRange(uint64_t offset, uint64_t count, cudaStream_t producer, bool whole) {
         cudaEvent_t ev = (*events)[next_event++ % events->size()];
         if (!CUDA_OK(cudaEventRecord(ev, producer)) || !CUDA_OK(cudaStreamWaitEvent(comm_stream, ev, 0))) return false;
         while (count > 0) {
-            const uint64_t chunk = std::min<uint64_t>(count, bucket_params);
+            const uint64_t chunk = whole ? count : std::min<uint64_t>(count, bucket_params);
             if (mgt_comm_allreduce_average_adamw(comm, offset, chunk, &adamw, w, w_half, m, v, comm_stream) != MGT_OK) return false;
             offset += chunk;
             count -= chunk;
@@ -56,10 +57,10 @@ struct ExchangeContext {
         }
         return true;
     }
-    bool Flush(cudaStream_t producer) {
+    bool Flush(cudaStream_t producer, bool whole = false) {
         if (!have_pending) return true;
         have_pending = false;
-        return LaunchRange(pending_offset, pending_count, producer);
+        return LaunchRange(pending_offset, pending_count, producer, whole);
     }
 };
 
@@ -196,7 +197,7 @@ int main(int argc, char** argv) {
         uint32_t overlap_ranges = 0, overlap_chunks = 0;
         bool weights_updated = false;
         if (overlap) {
-            if (exchange.failed || exchange.scheduled_ranges != expected_ranges || !exchange.Flush(compute)) return EXIT_FAILURE;
+            if (exchange.failed || exchange.scheduled_ranges != expected_ranges || !exchange.Flush(compute, true)) return EXIT_FAILURE;
             overlap_ranges = exchange.scheduled_ranges;
             overlap_chunks = exchange.scheduled_chunks;
             if (!CUDA_OK(cudaEventRecord(ev_comm_done, comm_stream)) || !CUDA_OK(cudaStreamWaitEvent(compute, ev_comm_done, 0))) return EXIT_FAILURE;

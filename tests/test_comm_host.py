@@ -53,7 +53,8 @@ def test_schedule_matches_reference_chunking():
 
 def test_fused_update_is_held_back_one_notification():
     sched, launches, waits, seen_before = run_scheduler(lag=1)
-    assert sched.scheduled_chunks == 47
+    # the range still pending when backward ends (the embedding table) goes out whole: 34 chunks + 1 instead of + 13
+    assert sched.scheduled_chunks == 35 and launches[-1] == (0, 72 * 72 * 2560 + 2560)
     ranges = p888_ranges()
     # after notification i only ranges 0..i-1 may have been launched: the GEMM that still reads the
     # weights of range i is enqueued between notification i and i+1
