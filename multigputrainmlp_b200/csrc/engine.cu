@@ -11,6 +11,7 @@
 //     still reach the bias), reduced over CTAs in a fixed order;
 //   * activations are kept once (fp16 tape + one in-place fp32 residual stream).
 #include "../../include/mgt_b200.h"
+#include "fp32_path.cuh"
 #include "tower_chain.cuh"
 #include "umma_gemm.cuh"
 
@@ -691,6 +692,116 @@ mgt_status_t LaunchChain(mgt_engine* e, cudaStream_t st, const __half* w_first, 
     return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
 }
 
+// ---- the fp32 data flow (use_half_linear == 0), mlp_backward.cu:1273-1510 without the fp16 copies -----------------
+struct Fp32Workspace {
+    uint64_t a1, x, r1, z, y, dy, d0, d1, dz1, lossp, total;  // float offsets
+};
+Fp32Workspace PlanFp32(const mgt_mlp_shape_t& s, uint32_t B) {
+    Fp32Workspace w{};
+    uint64_t off = 0;
+    auto take = [&](uint64_t n) { const uint64_t at = off; off += (n + 63) & ~63ULL; return at; };
+    const uint64_t bh2 = (uint64_t)B * s.hd2, bh1 = (uint64_t)B * s.hd1;
+    w.a1 = take(bh1);
+    w.x = take(bh2 * (s.residual_blocks + 1ULL));
+    w.r1 = take(bh2 * (s.residual_blocks > 0 ? s.residual_blocks : 1ULL));
+    w.z = take(bh2);
+    w.y = take((uint64_t)B * s.output_dim);
+    w.dy = take((uint64_t)B * s.output_dim);
+    w.d0 = take(bh2);
+    w.d1 = take(bh2);
+    w.dz1 = take(bh1);
+    w.lossp = take(1024);
+    w.total = off + 64;
+    return w;
+}
+uint64_t Fp32WorkspaceFloats(const mgt_mlp_shape_t& s, uint32_t B) { return PlanFp32(s, B).total; }
+
+template <class F>
+mgt_status_t LaunchFp32Path(mgt_engine* e, const mgt_mlp_shape_t& s, const float* w, const uint8_t* states, const float* labels, uint32_t B, float* loss,
+                            float* grad, float* workspace, bool half_ig, mgt_backward_profile_t* profile, F&& notify, cudaStream_t st) {
+    using namespace mgt::fp32path;
+    const Fp32Workspace ws = PlanFp32(s, B);
+    float* base = reinterpret_cast<float*>(RoundUp(reinterpret_cast<uintptr_t>(workspace), 256));
+    const uint32_t H1 = s.hd1, H2 = s.hd2, R = s.residual_blocks, OUT = s.output_dim, L = s.state_len, V = s.state_value_pad;
+    const uint64_t bh2 = (uint64_t)B * H2, bh1 = (uint64_t)B * H1;
+    float* a1 = base + ws.a1;
+    auto x = [&](uint32_t k) { return base + ws.x + bh2 * k; };
+    auto r1 = [&](uint32_t k) { return base + ws.r1 + bh2 * k; };
+    float *z = base + ws.z, *y = base + ws.y, *dy = base + ws.dy, *d0 = base + ws.d0, *d1 = base + ws.d1, *dz1 = base + ws.dz1, *lossp = base + ws.lossp;
+    const int sm = e->sm_count;
+    auto blocks = [&](uint64_t n) { return GridFor(n, 256, sm); };
+    auto ok = [&]() { return cudaGetLastError() == cudaSuccess; };
+    auto colsum = [&](const float* src, uint32_t cols, float* dst) {
+        ColumnSumKernel<<<(cols + 7) / 8, 256, 0, st>>>(src, B, cols, dst);
+        ++e->launches;
+    };
+    StageTimer timer{e, st, profile};
+    if (!timer.Start()) return MGT_CUDA_FAILURE;
+
+    InputForwardKernel<<<blocks(bh1), 256, 0, st>>>(states, w, w + InputBias(s), B, L, V, H1, a1);
+    ++e->launches;
+    if (!ok() || !timer.Mark(profile ? &profile->input_forward_ms : nullptr)) return MGT_CUDA_FAILURE;
+    // hidden layer and residual blocks (y = x W, weights row-major [in][out])
+    if (Sgemm<false, false>(st, B, H2, H1, a1, H1, w + HiddenWeight(s), H2, z, H2) != cudaSuccess) return MGT_CUDA_FAILURE;
+    BiasReluKernel<<<blocks(bh2), 256, 0, st>>>(z, w + HiddenBias(s), nullptr, H2, bh2, x(0));
+    e->launches += 2;
+    if (!ok() || !timer.Mark(profile ? &profile->hidden_forward_ms : nullptr)) return MGT_CUDA_FAILURE;
+    for (uint32_t k = 0; k < R; ++k) {
+        if (Sgemm<false, false>(st, B, H2, H2, x(k), H2, w + Fc1W(s, k), H2, z, H2) != cudaSuccess) return MGT_CUDA_FAILURE;
+        BiasReluKernel<<<blocks(bh2), 256, 0, st>>>(z, w + Fc1B(s, k), nullptr, H2, bh2, r1(k));
+        if (Sgemm<false, false>(st, B, H2, H2, r1(k), H2, w + Fc2W(s, k), H2, z, H2) != cudaSuccess) return MGT_CUDA_FAILURE;
+        BiasReluKernel<<<blocks(bh2), 256, 0, st>>>(z, w + Fc2B(s, k), x(k), H2, bh2, x(k + 1));
+        e->launches += 4;
+    }
+    if (!ok() || !timer.Mark(profile ? &profile->residual_forward_ms : nullptr)) return MGT_CUDA_FAILURE;
+    // output layer, loss, dL/dy, gradients of the output layer, gradient entering the tower
+    const uint64_t by = (uint64_t)B * OUT;
+    if (Sgemm<false, false>(st, B, OUT, H2, x(R), H2, w + OutputWeight(s), OUT, y, OUT) != cudaSuccess) return MGT_CUDA_FAILURE;
+    AddBiasKernel<<<blocks(by), 256, 0, st>>>(y, w + OutputBias(s), OUT, by);
+    const uint32_t loss_blocks = (uint32_t)(blocks(by) < 1024 ? blocks(by) : 1024);
+    LossKernel<<<loss_blocks, 256, 0, st>>>(y, labels, by, 1.0f / (float)by, dy, lossp);
+    FinishLossKernel<<<1, 32, 0, st>>>(lossp, loss_blocks, loss);
+    if (Sgemm<true, false>(st, H2, OUT, B, x(R), H2, dy, OUT, grad + OutputWeight(s), OUT) != cudaSuccess) return MGT_CUDA_FAILURE;
+    colsum(dy, OUT, grad + OutputBias(s));
+    if (Sgemm<false, true>(st, B, H2, OUT, dy, OUT, w + OutputWeight(s), OUT, d0, H2) != cudaSuccess) return MGT_CUDA_FAILURE;
+    e->launches += 6;
+    MGT_TRY(notify(OutputWeight(s), (uint64_t)H2 * OUT + OUT));
+    if (!ok() || !timer.Mark(profile ? &profile->output_ms : nullptr)) return MGT_CUDA_FAILURE;
+    // residual blocks backward: d0 holds dL/dx_{k+1}
+    for (uint32_t rb = R; rb > 0; --rb) {
+        const uint32_t k = rb - 1U;
+        MaskKernel<float><<<blocks(bh2), 256, 0, st>>>(d0, nullptr, x(k + 1), H2, H2, bh2, false, d0);  // dz2, in place
+        colsum(d0, H2, grad + Fc2B(s, k));
+        if (Sgemm<true, false>(st, H2, H2, B, r1(k), H2, d0, H2, grad + Fc2W(s, k), H2) != cudaSuccess) return MGT_CUDA_FAILURE;
+        MGT_TRY(notify(Fc2W(s, k), (uint64_t)H2 * H2 + H2));
+        if (Sgemm<false, true>(st, B, H2, H2, d0, H2, w + Fc2W(s, k), H2, z, H2) != cudaSuccess) return MGT_CUDA_FAILURE;
+        MaskKernel<float><<<blocks(bh2), 256, 0, st>>>(z, nullptr, r1(k), H2, H2, bh2, false, d1);       // dz1 of the block
+        colsum(d1, H2, grad + Fc1B(s, k));
+        if (Sgemm<true, false>(st, H2, H2, B, x(k), H2, d1, H2, grad + Fc1W(s, k), H2) != cudaSuccess) return MGT_CUDA_FAILURE;
+        MGT_TRY(notify(Fc1W(s, k), (uint64_t)H2 * H2 + H2));
+        if (Sgemm<false, true>(st, B, H2, H2, d1, H2, w + Fc1W(s, k), H2, z, H2) != cudaSuccess) return MGT_CUDA_FAILURE;
+        AddIntoKernel<<<blocks(bh2), 256, 0, st>>>(d0, z, bh2);  // dL/dx_k = dz2 + dz1 W1^T
+        e->launches += 7;
+    }
+    if (!ok() || !timer.Mark(profile ? &profile->residual_backward_ms : nullptr)) return MGT_CUDA_FAILURE;
+    // hidden layer backward
+    MaskKernel<float><<<blocks(bh2), 256, 0, st>>>(d0, nullptr, x(0), H2, H2, bh2, false, d0);  // dzh
+    colsum(d0, H2, grad + HiddenBias(s));
+    if (Sgemm<true, false>(st, H1, H2, B, a1, H1, d0, H2, grad + HiddenWeight(s), H2) != cudaSuccess) return MGT_CUDA_FAILURE;
+    MGT_TRY(notify(HiddenWeight(s), (uint64_t)H1 * H2 + H2));
+    if (Sgemm<false, true>(st, B, H1, H2, d0, H2, w + HiddenWeight(s), H2, dz1, H1) != cudaSuccess) return MGT_CUDA_FAILURE;
+    MaskKernel<float><<<blocks(bh1), 256, 0, st>>>(dz1, nullptr, a1, H1, H1, bh1, false, dz1);
+    colsum(dz1, H1, grad + InputBias(s));  // the reference sums the fp32 dz1 (mlp_backward.cu:1505)
+    if (half_ig) MaskKernel<float><<<blocks(bh1), 256, 0, st>>>(dz1, nullptr, a1, H1, H1, bh1, true, dz1);  // fp16 operand of the embedding gradient
+    e->launches += 5;
+    if (!ok() || !timer.Mark(profile ? &profile->hidden_backward_ms : nullptr)) return MGT_CUDA_FAILURE;
+    EmbeddingGradKernel<float><<<dim3(L, (H1 + 63) / 64), 128, 2ULL * V * 64 * sizeof(float), st>>>(states, dz1, H1, B, V, H1, grad);
+    ++e->launches;
+    MGT_TRY(notify(0, (uint64_t)L * V * H1 + H1));
+    if (!ok() || !timer.Mark(profile ? &profile->input_grad_ms : nullptr)) return MGT_CUDA_FAILURE;
+    return MGT_OK;
+}
+
 struct HalfWeights {
     const __half* in_table; uint32_t p1;     // [(IN+1)][p1], row IN is the input bias
     const __half* wh; uint32_t p2;            // [H1][p2]
@@ -782,10 +893,11 @@ mgt_status_t mgt_engine_check(mgt_engine_t* e, void* stream, int32_t* out_device
 uint64_t mgt_mlp_loss_grad_workspace_floats(const mgt_mlp_shape_t* shape, uint32_t sample_count, uint32_t chunks,
                                             int32_t use_half_input_grad, int32_t use_half_linear) {
     if (!ValidShape(shape) || sample_count == 0 || chunks == 0) return 0;
-    (void)use_half_input_grad;
-    (void)use_half_linear;
+    if (!use_half_linear) return Fp32WorkspaceFloats(*shape, sample_count);
     const Workspace w = PlanWorkspace(*shape, sample_count, 148);
-    return (w.total_bytes + 3) / 4;
+    // fp32 embedding-gradient operand: da1 and dz1 [samples][hd1] in fp32 behind the tensor-core workspace
+    const uint64_t extra = use_half_input_grad ? 0 : 2ULL * sample_count * shape->hd1;
+    return (w.total_bytes + 3) / 4 + extra + (extra ? 256 : 0);
 }
 
 mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* shape, const float* w, const uint16_t* w_half_u16,
@@ -798,14 +910,25 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
         B == 0 || workspace == nullptr || chunks == 0 || ppb == 0) {
         return MGT_INVALID_CONFIG;
     }
-    // The tensor-core engine computes the reference's fp16 data flow; the fp32/TF32 variant of the
-    // reference (both switches off) and the mixed combinations are not provided.
-    if (!half_ig || !half_lin) return MGT_INVALID_CONFIG;
     const mgt_mlp_shape_t s = *shape;
+    if (!half_lin) {
+        // fp32 linear layers: the CUDA-core path (fp32_path.cuh); half_ig only selects the rounding of its embedding-gradient operand
+        if (workspace_floats < Fp32WorkspaceFloats(s, B)) return MGT_CAPACITY_EXCEEDED;
+        uint32_t id = 0;
+        auto tell = [&](uint64_t off, uint64_t count) -> mgt_status_t {
+            if (ready == nullptr) return MGT_OK;
+            return ready(ready_user, id++, off, count, stream_v) == MGT_OK ? MGT_OK : MGT_CUDA_FAILURE;
+        };
+        return LaunchFp32Path(e, s, w, reinterpret_cast<const uint8_t*>(states), labels, B, loss, grad, workspace, half_ig != 0, profile, tell,
+                              static_cast<cudaStream_t>(stream_v));
+    }
     const Workspace ws = PlanWorkspace(s, B, 148);
-    if (workspace_floats < (ws.total_bytes + 3) / 4) return MGT_CAPACITY_EXCEEDED;
+    const uint64_t f32_extra = half_ig ? 0 : 2ULL * B * s.hd1;  // da1, dz1 in fp32 for the fp32 embedding gradient
+    if (workspace_floats < (ws.total_bytes + 3) / 4 + f32_extra + (f32_extra ? 256 : 0)) return MGT_CAPACITY_EXCEEDED;
     cudaStream_t st = static_cast<cudaStream_t>(stream_v);
     uint8_t* base = reinterpret_cast<uint8_t*>(RoundUp(reinterpret_cast<uintptr_t>(workspace), 1024));
+    float* da1_f32 = reinterpret_cast<float*>(RoundUp(reinterpret_cast<uintptr_t>(workspace + (ws.total_bytes + 3) / 4), 256));  // behind the tensor-core workspace
+    float* dz1_f32 = da1_f32 + (uint64_t)B * s.hd1;
     __half* a1_h = reinterpret_cast<__half*>(base + ws.off_a1);
     auto x_h = [&](uint32_t k) { return reinterpret_cast<__half*>(base + ws.off_x + ws.x_stride * k); };
     auto r1_h = [&](uint32_t k) { return reinterpret_cast<__half*>(base + ws.off_r1 + ws.r1_stride * k); };
@@ -983,17 +1106,33 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     dz_cur = dz_tape(0);
     MGT_TRY(GemmGradWeights(e, st, a1_h, ws.p_a1, dz_cur, ws.p_dz, B, H1, H2, partial, ws.partial_floats, grad + HiddenWeight(s)));
     MGT_TRY(notify(HiddenWeight(s), (uint64_t)H1 * H2 + H2));
-    {
+    if (half_ig) {
         GemmArgs d{};  // dz1 = (dzh * Wh^T) * [a1 > 0]
         d.mask = a1_h; d.ld_mask = ws.p_a1; d.out_f16 = dz1_h; d.ld_f16 = ws.p_dz1;
         if (cudaMemsetAsync(colsum_h1, 0, (uint64_t)BackpropGrid(e, B, H1, H2) * 8U * H1 * sizeof(float), st) != cudaSuccess) return MGT_CUDA_FAILURE;
         MGT_TRY(GemmBackpropInput<Epi::kMaskF16>(e, st, dz_cur, ws.p_dz, hw.wh, hw.p2, B, H1, H2, d, colsum_h1, grad + InputBias(s)));
+    } else {
+        // --input-grad-fp16 0: the embedding gradient wants dz1 in fp32 (mlp_backward.cu:1433-1504, float one-hot GEMM).
+        // da1 from the same fp16 operands with fp32 accumulation, masked in fp32, then the table gradient on CUDA cores.
+        using namespace mgt::fp32path;
+        const uint64_t bh1 = (uint64_t)B * H1;
+        if (Sgemm<false, true>(st, B, H1, H2, dz_cur, ws.p_dz, hw.wh, hw.p2, da1_f32, H1) != cudaSuccess) return MGT_CUDA_FAILURE;
+        MaskKernel<__half><<<GridFor(bh1, 256, e->sm_count), 256, 0, st>>>(da1_f32, nullptr, a1_h, H1, ws.p_a1, bh1, false, dz1_f32);
+        ColumnSumKernel<<<(H1 + 7) / 8, 256, 0, st>>>(dz1_f32, B, H1, grad + InputBias(s));
+        e->launches += 3;
+        if (cudaGetLastError() != cudaSuccess) return MGT_CUDA_FAILURE;
     }
     if (!timer.Mark(profile ? &profile->hidden_backward_ms : nullptr)) return MGT_CUDA_FAILURE;
 
     // ---- embedding gradient: grad W_in = onehot^T * dz1  (mlp_backward.cu:1440-1504); the input-bias
     // gradient (mlp_backward.cu:1505) is the column sum written by the GEMM above
-    {
+    if (!half_ig) {
+        using namespace mgt::fp32path;
+        EmbeddingGradKernel<float><<<dim3(s.state_len, (H1 + 63) / 64), 128, 2ULL * s.state_value_pad * 64 * sizeof(float), st>>>(
+            reinterpret_cast<const uint8_t*>(states), dz1_f32, H1, B, s.state_value_pad, H1, grad);
+        ++e->launches;
+        if (cudaGetLastError() != cudaSuccess) return MGT_CUDA_FAILURE;
+    } else {
         GemmArgs a = BaseArgs(H1, IN, B, 512, 1);
         const uint64_t tiles = (uint64_t)a.m_tiles * a.n_tiles;
         // Two splits keep fp32 atomics order-independent (0 + a + b == 0 + b + a); use them when one

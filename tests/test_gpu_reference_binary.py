@@ -45,11 +45,16 @@ def test_losses_match_reference_gpu_fixture(tmp_path, case):
     ["--steps", 6, "--batch-size", 1536, "--k-min", 1, "--k-max", 29, "--hd1", 256, "--hd2", 64, "--nrd", 2, "--lr", 0.001],
     ["--steps", 10, "--batch-size", 53248, "--k-min", 1, "--k-max", 29, "--hd1", 2556, "--hd2", 218, "--nrd", 16,
      "--input-grad-fp16", 1, "--input-grad-position-tile", 36, "--linear-fp16", 1],
-], ids=["small", "p888"])
+    # the reference's ctest native_train_input_grad_float_backend, and its TF32 linears (our fp32 path is the more exact one)
+    ["--steps", 6, "--batch-size", 1536, "--k-min", 1, "--k-max", 29, "--hd1", 256, "--hd2", 64, "--nrd", 2, "--lr", 0.001, "--input-grad-fp16", 0],
+    ["--steps", 6, "--batch-size", 1536, "--k-min", 1, "--k-max", 29, "--hd1", 256, "--hd2", 64, "--nrd", 2, "--lr", 0.001, "--linear-fp16", 0,
+     "--input-grad-fp16", 0],
+], ids=["small", "p888", "small_ig_fp32", "small_all_fp32"])
 def test_side_by_side_with_reference_binary(tmp_path, flags):
     ref_rows = run(REF, tmp_path / "ref", ["--write-artifacts", 1, *flags])
     our_rows = run(OURS, tmp_path / "ours", ["--write-artifacts", 1, *flags])
     assert len(ref_rows) == len(our_rows)
+    assert [r["input_grad_backend"] for r in ref_rows] == [r["input_grad_backend"] for r in our_rows]
     for a, b in zip(ref_rows, our_rows):
         assert abs(a["loss"] - b["loss"]) <= TOL * abs(a["loss"]), (a["step"], a["loss"], b["loss"])
     # final weights, m, v as the two binaries checkpoint them (checkpoint/state.f32.bin: w | m | v)
