@@ -120,7 +120,10 @@ typedef struct {
 
 /* mlp_backward.cuh:21-25. Called synchronously on the launching thread, 2*residual_blocks+3 times
  * per launch, in the reference's order: output, (fc2, fc1) of each block from last to first,
- * hidden, embedding+input bias. */
+ * hidden, embedding+input bias. Stronger than the reference: when a range is announced, every kernel of
+ * this launch that reads the WEIGHTS of that range has already been enqueued on producer_stream, so a
+ * caller may exchange the gradient range and update those weights in place behind an event recorded at
+ * that moment (the reference announces a layer before the GEMM that back-propagates through it). */
 typedef mgt_status_t (*mgt_gradient_ready_fn)(void* user, uint32_t ready_id, uint64_t param_offset,
                                               uint64_t param_count, void* producer_stream);
 

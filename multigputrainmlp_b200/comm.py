@@ -4,9 +4,10 @@
 reference's ScheduleGradientAllreduce (native/tools/mgt_native_train_smoke.cu:494-523): ranges
 arrive through the gradient-ready callback in backward order, each is cut into chunks of at most
 `allreduce_bucket_bytes`, and the exchange runs on a second stream behind an event so that it
-overlaps the rest of backward. Because the exchange is fused with the AdamW update here, a range
-is launched one notification late: the backward GEMM that still reads a layer's weights is
-enqueued right after that layer's notification and before the next one.
+overlaps the rest of backward. The exchange is fused with the AdamW update here; that is safe without
+holding ranges back because the engine announces a range only after the last kernel that reads its
+weights has been enqueued (include/mgt_b200.h). `lag` remains for engines that announce earlier, as the
+reference does.
 
 Back-ends:
   PeerBackend  - the library's NVLink peer-to-peer kernels (mgt_comm_* in include/mgt_b200.h)
@@ -38,7 +39,7 @@ class GradientRangeScheduler:
     wait_for_producer: Callable[[], None]            # make the exchange stream wait for what the compute stream has enqueued so far
     bucket_params: int = (4 << 20) // 4
     expected_ranges: Optional[int] = None
-    lag: int = 1                                     # notifications a range is held back (1 when the update is fused)
+    lag: int = 0                                     # notifications a range is held back (1 = fused update behind an engine that announces a layer before its dX GEMM)
     whole_tail: bool = True                          # ranges left at finish() go out unchunked: nothing remains to overlap with
     scheduled_ranges: int = 0
     scheduled_chunks: int = 0
@@ -71,7 +72,9 @@ class GradientRangeScheduler:
             return 1  # invalid_config, as the reference's callback does (tool:501-504)
         self.scheduled_ranges += 1
         self._pending.append((ready_id, param_offset, param_count))
-        self._flush(self.lag)
+        # the range that closes backward waits for finish(), where it goes out whole
+        last = self.whole_tail and self.expected_ranges is not None and self.scheduled_ranges == self.expected_ranges
+        self._flush(max(self.lag, 1 if last else 0))
         return 0
 
     def finish(self) -> None:
@@ -156,7 +159,7 @@ class OverlappedGradientExchange:
         self.adamw: Optional[AdamWKernelConfig] = None
         self.state = None
         self.scheduler = GradientRangeScheduler(self._launch, self._wait_for_producer, bucket_params=max(1, bucket_bytes // 4),
-                                                expected_ranges=2 * residual_blocks + 3, lag=1 if fused_adamw else 0)
+                                                expected_ranges=2 * residual_blocks + 3, lag=0)
 
     def _wait_for_producer(self):
         ev = self.events[self._ev % len(self.events)]

@@ -419,7 +419,17 @@ static mgt_status_t LaunchAllreduce(mgt_comm_t* c, uint64_t offset, uint64_t cou
     }
     const uint64_t quads = (count + 3ULL) / 4ULL;
     const uint64_t want = (quads + kCommThreads - 1ULL) / kCommThreads;  // one-shot ranges: one float4 per thread (at most 64 CTAs)
-    const uint64_t cap = static_cast<uint64_t>(c->sm_count);
+    // All CTAs of a launch wait for the peers, so the grid must be able to be resident at once: at most what the
+    // occupancy calculator allows per SM (and 4 per SM is plenty to cover the NVLink round trip).
+    static int per_sm_adam = 0, per_sm_plain = 0;
+    int& per_sm = adam != nullptr ? per_sm_adam : per_sm_plain;
+    if (per_sm == 0) {
+        int n = 1;
+        const cudaError_t q = adam != nullptr ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, AllreduceAverageKernel<true>, kCommThreads, 0)
+                                              : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, AllreduceAverageKernel<false>, kCommThreads, 0);
+        per_sm = (q == cudaSuccess && n >= 1) ? (n > 4 ? 4 : n) : 1;
+    }
+    const uint64_t cap = static_cast<uint64_t>(c->sm_count) * static_cast<uint64_t>(per_sm);
     if (count <= kOneShotMaxFloats && want > cap) return MGT_CAPACITY_EXCEEDED;
     const uint32_t grid = static_cast<uint32_t>(want < 1 ? 1 : (want < cap ? want : cap));
     const uint32_t seq = ++c->seq;

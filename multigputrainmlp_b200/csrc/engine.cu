@@ -773,13 +773,13 @@ mgt_status_t LaunchFp32Path(mgt_engine* e, const mgt_mlp_shape_t& s, const float
         MaskKernel<float><<<blocks(bh2), 256, 0, st>>>(d0, nullptr, x(k + 1), H2, H2, bh2, false, d0);  // dz2, in place
         colsum(d0, H2, grad + Fc2B(s, k));
         if (Sgemm<true, false>(st, H2, H2, B, r1(k), H2, d0, H2, grad + Fc2W(s, k), H2) != cudaSuccess) return MGT_CUDA_FAILURE;
-        MGT_TRY(notify(Fc2W(s, k), (uint64_t)H2 * H2 + H2));
         if (Sgemm<false, true>(st, B, H2, H2, d0, H2, w + Fc2W(s, k), H2, z, H2) != cudaSuccess) return MGT_CUDA_FAILURE;
+        MGT_TRY(notify(Fc2W(s, k), (uint64_t)H2 * H2 + H2));  // after the last reader of W2_k
         MaskKernel<float><<<blocks(bh2), 256, 0, st>>>(z, nullptr, r1(k), H2, H2, bh2, false, d1);       // dz1 of the block
         colsum(d1, H2, grad + Fc1B(s, k));
         if (Sgemm<true, false>(st, H2, H2, B, x(k), H2, d1, H2, grad + Fc1W(s, k), H2) != cudaSuccess) return MGT_CUDA_FAILURE;
-        MGT_TRY(notify(Fc1W(s, k), (uint64_t)H2 * H2 + H2));
         if (Sgemm<false, true>(st, B, H2, H2, d1, H2, w + Fc1W(s, k), H2, z, H2) != cudaSuccess) return MGT_CUDA_FAILURE;
+        MGT_TRY(notify(Fc1W(s, k), (uint64_t)H2 * H2 + H2));
         AddIntoKernel<<<blocks(bh2), 256, 0, st>>>(d0, z, bh2);  // dL/dx_k = dz2 + dz1 W1^T
         e->launches += 7;
     }
@@ -788,8 +788,8 @@ mgt_status_t LaunchFp32Path(mgt_engine* e, const mgt_mlp_shape_t& s, const float
     MaskKernel<float><<<blocks(bh2), 256, 0, st>>>(d0, nullptr, x(0), H2, H2, bh2, false, d0);  // dzh
     colsum(d0, H2, grad + HiddenBias(s));
     if (Sgemm<true, false>(st, H1, H2, B, a1, H1, d0, H2, grad + HiddenWeight(s), H2) != cudaSuccess) return MGT_CUDA_FAILURE;
-    MGT_TRY(notify(HiddenWeight(s), (uint64_t)H1 * H2 + H2));
     if (Sgemm<false, true>(st, B, H1, H2, d0, H2, w + HiddenWeight(s), H2, dz1, H1) != cudaSuccess) return MGT_CUDA_FAILURE;
+    MGT_TRY(notify(HiddenWeight(s), (uint64_t)H1 * H2 + H2));
     MaskKernel<float><<<blocks(bh1), 256, 0, st>>>(dz1, nullptr, a1, H1, H1, bh1, false, dz1);
     colsum(dz1, H1, grad + InputBias(s));  // the reference sums the fp32 dz1 (mlp_backward.cu:1505)
     if (half_ig) MaskKernel<float><<<blocks(bh1), 256, 0, st>>>(dz1, nullptr, a1, H1, H1, bh1, true, dz1);  // fp16 operand of the embedding gradient
@@ -1105,7 +1105,6 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     // ---- hidden layer backward (mlp_backward.cu:1417-1438): dz_tape(0) = dcur * [x0 > 0]
     dz_cur = dz_tape(0);
     MGT_TRY(GemmGradWeights(e, st, a1_h, ws.p_a1, dz_cur, ws.p_dz, B, H1, H2, partial, ws.partial_floats, grad + HiddenWeight(s)));
-    MGT_TRY(notify(HiddenWeight(s), (uint64_t)H1 * H2 + H2));
     if (half_ig) {
         GemmArgs d{};  // dz1 = (dzh * Wh^T) * [a1 > 0]
         d.mask = a1_h; d.ld_mask = ws.p_a1; d.out_f16 = dz1_h; d.ld_f16 = ws.p_dz1;
@@ -1122,6 +1121,9 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
         e->launches += 3;
         if (cudaGetLastError() != cudaSuccess) return MGT_CUDA_FAILURE;
     }
+    // announced only now, after the last kernel that reads the hidden weights: a caller may update a range in place as
+    // soon as it is announced
+    MGT_TRY(notify(HiddenWeight(s), (uint64_t)H1 * H2 + H2));
     if (!timer.Mark(profile ? &profile->hidden_backward_ms : nullptr)) return MGT_CUDA_FAILURE;
 
     // ---- embedding gradient: grad W_in = onehot^T * dz1  (mlp_backward.cu:1440-1504); the input-bias

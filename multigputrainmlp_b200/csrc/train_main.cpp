@@ -26,8 +26,8 @@ namespace {
 #define CUDA_OK(expr) ((expr) == cudaSuccess)
 
 // Gradient-ready ranges -> exchange launches (the role of ScheduleGradientAllreduce, tool:494-523).
-// The exchange is fused with the AdamW update, so a range is launched one notification late: the
-// backward GEMM that still reads a layer's weights is enqueued right after that layer's notification.
+// The exchange is fused with the AdamW update; the engine announces a range only after the last kernel that
+// reads its weights is enqueued, so ranges go out as they are announced.
 struct ExchangeContext {
     bool enabled = false;
     mgt_comm_t* comm = nullptr;
@@ -39,7 +39,7 @@ struct ExchangeContext {
     uint16_t* w_half = nullptr;
     float* m = nullptr;
     float* v = nullptr;
-    uint32_t scheduled_ranges = 0, scheduled_chunks = 0, next_event = 0;
+    uint32_t scheduled_ranges = 0, scheduled_chunks = 0, next_event = 0, expected_ranges = 0;
     bool have_pending = false;
     uint64_t pending_offset = 0, pending_count = 0;
     bool failed = false;
@@ -70,10 +70,17 @@ mgt_status_t OnGradientReady(void* user, uint32_t ready_id, uint64_t offset, uin
     if (ctx->comm == nullptr || ctx->comm_stream == nullptr || ctx->events == nullptr || ctx->bucket_params == 0 || count == 0) return MGT_INVALID_CONFIG;
     (void)ready_id;
     ++ctx->scheduled_ranges;
+    // The engine announces a range after the last kernel that reads its weights, so the fused exchange + update can go
+    // out at once. The range that closes backward (the embedding table) is kept for Flush(whole): nothing is left to
+    // overlap with, so it is not cut into buckets.
     if (!ctx->Flush(static_cast<cudaStream_t>(producer_stream))) { ctx->failed = true; return MGT_NCCL_FAILURE; }
-    ctx->have_pending = true;
-    ctx->pending_offset = offset;
-    ctx->pending_count = count;
+    if (ctx->expected_ranges != 0 && ctx->scheduled_ranges == ctx->expected_ranges) {
+        ctx->have_pending = true;
+        ctx->pending_offset = offset;
+        ctx->pending_count = count;
+        return MGT_OK;
+    }
+    if (!ctx->LaunchRange(offset, count, static_cast<cudaStream_t>(producer_stream), false)) { ctx->failed = true; return MGT_NCCL_FAILURE; }
     return MGT_OK;
 }
 
@@ -181,6 +188,7 @@ int main(int argc, char** argv) {
             exchange.events = &ready_events;
             exchange.bucket_params = std::max<uint64_t>(1ULL, opt.allreduce_bucket_bytes / sizeof(float));
             exchange.adamw = adamw;
+            exchange.expected_ranges = expected_ranges;
             exchange.w = d_w; exchange.w_half = d_w_half; exchange.m = d_m; exchange.v = d_v;
         }
         mgt_backward_profile_t bw{};

@@ -26,10 +26,10 @@ def p888_ranges():
     return out
 
 
-def run_scheduler(lag, bucket_bytes=4 << 20):
+def run_scheduler(lag, bucket_bytes=4 << 20, whole_tail=True):
     launches, waits = [], []
     sched = GradientRangeScheduler(lambda off, cnt: launches.append((off, cnt)), lambda: waits.append(len(launches)),
-                                   bucket_params=bucket_bytes // 4, expected_ranges=35, lag=lag)
+                                   bucket_params=bucket_bytes // 4, expected_ranges=35, lag=lag, whole_tail=whole_tail)
     sched.begin_step()
     seen_before = []
     for i, (off, cnt) in enumerate(p888_ranges()):
@@ -40,7 +40,7 @@ def run_scheduler(lag, bucket_bytes=4 << 20):
 
 
 def test_schedule_matches_reference_chunking():
-    sched, launches, waits, _ = run_scheduler(lag=0)
+    sched, launches, waits, _ = run_scheduler(lag=0, whole_tail=False)
     # 35 ranges; at 4 MiB buckets the embedding range (13 273 600 floats) needs 13 chunks: 47 launches
     assert sched.scheduled_ranges == 35 and sched.scheduled_chunks == 47 == len(launches)
     assert launches[0] == (15460064, 225)
@@ -62,6 +62,16 @@ def test_fused_update_is_held_back_one_notification():
         launched = seen_before[i]
         assert launched == sum(-(-ranges[j][1] // ((4 << 20) // 4)) for j in range(i))
     assert len(waits) == 35  # one producer event per flush
+
+
+def test_default_schedule_launches_at_once_and_keeps_the_closing_range_whole():
+    sched, launches, waits, seen_before = run_scheduler(lag=0)
+    ranges = p888_ranges()
+    assert sched.scheduled_chunks == 35 and launches[-1] == (0, 72 * 72 * 2560 + 2560)
+    # range i is launched inside notification i (the engine announces it after the last reader of its weights) ...
+    assert seen_before[:34] == list(range(1, 35)) and launches[:34] == ranges[:34]
+    # ... except the one that closes backward, which finish() sends unchunked
+    assert seen_before[34] == 34
 
 
 def test_scheduler_rejects_unexpected_ranges():
