@@ -253,6 +253,9 @@ template <int BN, Epi EPI> using CfgFwdS = GemmCfg<BN, 1, false, BSource::kTmaMN
 template <int BN, Epi EPI> using CfgDxS = GemmCfg<BN, 1, false, BSource::kTmaK, EPI, 3, 4, true>;
 template <int BN> using CfgDw = GemmCfg<BN, 1, true, BSource::kTmaMN, Epi::kPartialF32, 3, 3>; // act^T x dz
 template <int BN> using CfgDwG = GemmCfg<BN, 1, true, BSource::kTmaMN, Epi::kPartialF32, 3, 3, false, true>; // R stacked act^T x dz
+// Two 256-column accumulators per unit (all of TMEM) and a two-stage one-hot ring. Measured alternatives at p888: 2 x 192
+// columns with a three-stage ring 1.44 ms, one double-buffered 256-column accumulator (epilogue under the next unit's
+// MMAs, but the table tile re-read twice as often) 1.37 ms, this form 1.14 ms: the K loop already issues MMAs back to back.
 using CfgEmbFwd = GemmCfg<256, 2, true, BSource::kOneHotFwd, Epi::kEmbFwd, 4, 2>;
 using CfgEmbGrad = GemmCfg<256, 2, true, BSource::kOneHotGrad, Epi::kEmbGrad, 4, 2>;
 using CfgDbgKK = GemmCfg<256, 1, false, BSource::kTmaK, Epi::kPartialF32, 3, 3>;
@@ -984,7 +987,7 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
 
     // ---- embedding forward: a1 = relu([onehot | 1] * [W_in ; b_in])  (mlp_backward.cu:755-832)
     {
-        GemmArgs a = BaseArgs(H1, B, IN + 1, 512, 1);
+        GemmArgs a = BaseArgs(H1, B, IN + 1, CfgEmbFwd::NACC * CfgEmbFwd::BN, 1);
         a.out_f16 = a1_h; a.ld_f16 = ws.p_a1;
         a.states = reinterpret_cast<const uint8_t*>(states); a.state_len = s.state_len; a.value_pad = s.state_value_pad; a.samples = B; a.in_rows = IN;
         CUtensorMap ta;
@@ -1135,14 +1138,14 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
         ++e->launches;
         if (cudaGetLastError() != cudaSuccess) return MGT_CUDA_FAILURE;
     } else {
-        GemmArgs a = BaseArgs(H1, IN, B, 512, 1);
+        GemmArgs a = BaseArgs(H1, IN, B, CfgEmbGrad::NACC * CfgEmbGrad::BN, 1);
         const uint64_t tiles = (uint64_t)a.m_tiles * a.n_tiles;
         // Two splits keep fp32 atomics order-independent (0 + a + b == 0 + b + a); use them when one
         // split would leave a large part of the last wave idle.
         const uint64_t waves1 = (tiles + e->sm_count - 1) / e->sm_count;
         const uint64_t waves2 = (2 * tiles + e->sm_count - 1) / e->sm_count;
         const uint32_t splits = (a.k_chunks >= 2 && waves2 < 2 * waves1) ? 2U : 1U;
-        a = BaseArgs(H1, IN, B, 512, splits);
+        a = BaseArgs(H1, IN, B, CfgEmbGrad::NACC * CfgEmbGrad::BN, splits);
         a.out_f32 = grad; a.ld_f32 = H1;
         a.states = reinterpret_cast<const uint8_t*>(states); a.state_len = s.state_len; a.value_pad = s.state_value_pad; a.samples = B;
         a.in_rows = 0xFFFFFFFFU;  // no all-ones row in this direction

@@ -95,16 +95,16 @@ struct GemmCfg {
     static constexpr int FIRST_SYNTH_THREAD = 64 + 32 * EPI_WARPS;
     static constexpr int THREADS = FIRST_SYNTH_THREAD + (kOneHot ? 32 * SYNTH_WARPS : 0);
     static constexpr int EPI_TILE_PITCH = 36;
-    // per epilogue warp: a padded 32x32 fp32 tile plus 32 words of ReLU-mask bits (the embedding
-    // epilogues write transposed and need no staging)
-    static constexpr int EPI_WARP_BYTES = kOneHot ? 0 : (32 * EPI_TILE_PITCH * 4 + 128);
+    // per epilogue warp: a padded 32x32 fp32 tile, 32 words of ReLU-mask bits and four rows of column-sum accumulators
+    // (the embedding epilogues write transposed and need no staging)
+    static constexpr int EPI_WARP_BYTES = kOneHot ? 0 : (32 * EPI_TILE_PITCH * 4 + 128 + 4 * 32 * 4);
     static constexpr int EPI_STAGE_BYTES = EPI_WARPS * EPI_WARP_BYTES;
     static constexpr int SMEM_BYTES = 1024 + SA_ * A_STAGE_BYTES + SB_ * B_STAGE_BYTES + 256 + EPI_STAGE_BYTES;
     static_assert(BN_ % 16 == 0 && BN_ >= 16 && BN_ <= 256, "UMMA N");
     static_assert(BN_ % 32 == 0, "epilogue drains 32 columns at a time");
     static_assert(NACC_ == 1 || NACC_ == 2, "one or two accumulators");
     static_assert(B_ACC_BYTES % 1024 == 0, "swizzle atoms must stay 1024-byte aligned");
-    static_assert(!kOneHot || SB_ == 2, "the one-hot ring keeps a two-item history");
+    static_assert(!kOneHot || (SB_ >= 2 && SB_ <= 4), "one-hot ring depth");
     static_assert(!GROUPED_ || (EPI_ == Epi::kPartialF32 && A_MN_ && BSRC_ == BSource::kTmaMN && !BSTAT_), "grouped form: split-K weight gradients");
     static_assert(!BSTAT_ || (!kOneHot && NACC_ == 1), "B-stationary applies to TMA-fed single-accumulator tiles");
     static_assert(SMEM_BYTES <= 232448, "shared memory budget");
@@ -431,6 +431,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             constexpr uint32_t TP = Cfg::EPI_TILE_PITCH;  // floats per staged row (16-byte aligned, bank-friendly)
             float* tile = epi_stage + ew * (Cfg::EPI_WARP_BYTES / 4);
             uint32_t* mask_words = reinterpret_cast<uint32_t*>(tile + 32 * TP);
+            // B-stationary kernels keep one N tile per CTA, so a warp meets the same (at most four) column chunks in every
+            // unit: their column sums are accumulated here and written once at the end instead of a global
+            // read-modify-write per chunk
+            float* col_acc = reinterpret_cast<float*>(mask_words + 32);
+            constexpr bool kColsumLocal = Cfg::BSTAT && kHasMask && BN / 64 <= 4;
+            if (kColsumLocal) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) col_acc[i * 32 + lane] = 0.0f;
+                __syncwarp();
+            }
             const uint32_t r4 = lane >> 3, c4 = (lane & 7U) * 4U;  // fp32 vectors: 4 rows x 8 lanes
             const uint32_t r8 = lane >> 2, c8 = (lane & 3U) * 8U;  // fp16 vectors: 8 rows x 4 lanes
             const bool ld_vec = (!kHasAdd || (args.ld_add & 3U) == 0U) && (!kHasMask || (args.ld_mask & 7U) == 0U) &&
@@ -591,7 +601,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                             float total = 0.0f;  // column `lane` of the staged tile, rows in order
 #pragma unroll 8
                             for (uint32_t rr = 0; rr < 32U; ++rr) total += rr < rows_ok ? tile[rr * TP + lane] : 0.0f;
-                            if (col_ok) {
+                            if (kColsumLocal) {
+                                col_acc[(cc >> 1) * 32 + lane] += total;  // this lane is the only user of the slot
+                            } else if (col_ok) {
                                 float* dst = args.colsum + (static_cast<uint64_t>(blockIdx.x) * Cfg::EPI_WARPS + ew) * args.N + n0 + lane;
                                 *dst += total;  // this warp is the only writer of its row
                             }
@@ -601,6 +613,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 }
                 tc_fence_before();
                 mbar_arrive(&acc_empty[ab]);
+            }
+            if (kColsumLocal && args.colsum != nullptr && blockIdx.x < total_units) {
+                const uint32_t nt = blockIdx.x % args.n_tiles;  // the N tile of every unit of this CTA
+                for (int cc = static_cast<int>(chunk_parity); cc < BN / 32; cc += 2) {
+                    const uint32_t n = nt * BN + cc * 32 + lane;
+                    if (n < args.N) args.colsum[(static_cast<uint64_t>(blockIdx.x) * Cfg::EPI_WARPS + ew) * args.N + n] = col_acc[(cc >> 1) * 32 + lane];
+                }
             }
         }
     } else {
@@ -627,10 +646,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     const uint32_t p_hi = min((k0 + 63U) / V, L - 1U);
                     const uint32_t kb = IN - k0;  // the all-ones column that multiplies the bias row
 #pragma unroll
-                    for (uint32_t i = 0; i < ROWS / NT; ++i) {
+                    for (uint32_t i = 0; i < (ROWS + NT - 1U) / NT; ++i) {
                         const uint32_t n = t + i * NT;
                         const uint32_t sample = nt * ROWS + n;
-                        if (sample < args.samples) {
+                        if (sample < args.samples && n < ROWS) {
                             const uint8_t* st = args.states + static_cast<uint64_t>(sample) * 80U;
                             for (uint32_t p = p_lo; p <= p_hi && p < L; ++p) {
                                 const uint32_t k = p * V + __ldg(st + p) - k0;
@@ -661,12 +680,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             static_assert(Cfg::BSRC != BSource::kOneHotGrad || NT == 256U, "64 samples x 4 threads");
             // One stage hand-over: wait until the MMAs that read stage `sb` are done (warp-uniform).
             auto acquire = [&](uint32_t it) -> bool {
-                return __all_sync(0xFFFFFFFFU, mbar_wait(&empty_b[it & 1U], ((it >> 1) & 1U) ^ 1U, cta_abort, kAbortSynthWait));
+                return __all_sync(0xFFFFFFFFU, mbar_wait(&empty_b[it % SB], ((it / SB) & 1U) ^ 1U, cta_abort, kAbortSynthWait));
             };
             auto publish = [&](uint32_t it) {
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&full_b[it & 1U]);
+                if (lane == 0) mbar_arrive(&full_b[it % SB]);
             };
             bool fast = false;
             if constexpr (Cfg::BSRC == BSource::kOneHotFwd) {
@@ -678,15 +697,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 // zeros at the places it remembers from two items ago, ones at the new places.
                 fast = args.splits == 1U && V >= 64U;
                 if (fast) {
-                    constexpr uint32_t RPT = ROWS / NT;
+                    constexpr uint32_t RPT = (ROWS + NT - 1U) / NT;
                     constexpr uint32_t kNone = 0xFFFFFFFFU;
                     struct Cursor { uint32_t p, s0, s1; };
                     Cursor cur[RPT];
-                    uint32_t next[RPT][3], hist0[RPT][3], hist1[RPT][3];
+                    uint32_t next[RPT][3], hist[SB][RPT][3];  // hist[0]: what this thread set in the stage that comes round now
 #pragma unroll
                     for (uint32_t i = 0; i < RPT; ++i)
 #pragma unroll
-                        for (uint32_t j = 0; j < 3U; ++j) hist0[i][j] = hist1[i][j] = kNone;
+                        for (uint32_t j = 0; j < 3U; ++j)
+#pragma unroll
+                            for (int q = 0; q < SB; ++q) hist[q][i][j] = kNone;
                     auto offset_of = [&](uint32_t n, uint32_t k) -> uint32_t {
                         return (n / BN) * Cfg::B_ACC_BYTES + (n % BN) * 128U + ((((k >> 3) ^ (n & 7U)) << 4) | ((k & 7U) << 1));
                     };
@@ -697,7 +718,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll
                         for (uint32_t i = 0; i < RPT; ++i) {
                             const uint32_t n = t + i * NT, sample = nt * ROWS + n;
-                            const bool active = sample < args.samples;
+                            const bool active = sample < args.samples && n < ROWS;
                             const uint8_t* st = args.states + static_cast<uint64_t>(sample) * 80U;
                             Cursor& q = cur[i];
                             if (c == 0U) {
@@ -740,14 +761,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                                 decode(unit2, mt2, nt2, sp2);
                             }
                         }
-                        const uint32_t sb = it & 1U;
                         if (!acquire(it)) break;
-                        uint8_t* buf = b_ring + sb * Cfg::B_STAGE_BYTES;
+                        uint8_t* buf = b_ring + (it % SB) * Cfg::B_STAGE_BYTES;
 #pragma unroll
                         for (uint32_t i = 0; i < RPT; ++i)
 #pragma unroll
                             for (uint32_t j = 0; j < 3U; ++j) {
-                                const uint32_t old = sb ? hist1[i][j] : hist0[i][j];
+                                const uint32_t old = hist[0][i][j];
                                 if (old != kNone && !dry) *reinterpret_cast<uint16_t*>(buf + old) = 0;
                             }
 #pragma unroll
@@ -756,7 +776,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                             for (uint32_t j = 0; j < 3U; ++j) {
                                 const uint32_t off = next[i][j];
                                 if (off != kNone && !dry) *reinterpret_cast<uint16_t*>(buf + off) = 0x3C00;
-                                if (sb) hist1[i][j] = off; else hist0[i][j] = off;
+#pragma unroll
+                                for (int q = 0; q + 1 < SB; ++q) hist[q][i][j] = hist[q + 1][i][j];
+                                hist[SB - 1][i][j] = off;
                             }
                         publish(it);
                         if (have2) prepare(nt2, c2);
@@ -774,7 +796,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     constexpr uint32_t kNone = 0xFFFFFFFFU;
                     const uint32_t k = t >> 2, q = t & 3U;
                     uint32_t cur[3];
-                    uint32_t hist0[4] = {kNone, kNone, kNone, kNone}, hist1[4] = {kNone, kNone, kNone, kNone};
+                    uint32_t hist[SB][4];  // hist[0]: what this thread set in the stage that comes round now
+#pragma unroll
+                    for (int q2 = 0; q2 < SB; ++q2)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) hist[q2][j] = kNone;
                     auto fetch = [&](uint32_t nt, uint32_t c) {
                         const uint32_t sample = c * 64U + k, r0 = nt * ROWS;
                         const uint32_t p_lo = r0 / V, p_hi = min((r0 + ROWS - 1U) / V, L - 1U);
@@ -809,12 +835,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                                 have2 = c2 < c_end2;
                             }
                         }
-                        const uint32_t sb = it & 1U;
                         if (!acquire(it)) break;
-                        uint8_t* buf = b_ring + sb * Cfg::B_STAGE_BYTES;
+                        uint8_t* buf = b_ring + (it % SB) * Cfg::B_STAGE_BYTES;
 #pragma unroll
                         for (uint32_t j = 0; j < 4U; ++j) {
-                            const uint32_t off = sb ? hist1[j] : hist0[j];
+                            const uint32_t off = hist[0][j];
                             if (off != kNone && !(args.debug_skip & 1U)) *reinterpret_cast<uint16_t*>(buf + off) = 0;
                         }
                         __syncwarp();  // a place cleared by one lane may be set by another lane of this warp
@@ -830,7 +855,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll
                         for (uint32_t j = 0; j < 4U; ++j) {
                             if (offs[j] != kNone && !(args.debug_skip & 1U)) *reinterpret_cast<uint16_t*>(buf + offs[j]) = 0x3C00;
-                            if (sb) hist1[j] = offs[j]; else hist0[j] = offs[j];
+#pragma unroll
+                            for (int q2 = 0; q2 + 1 < SB; ++q2) hist[q2][j] = hist[q2 + 1][j];
+                            hist[SB - 1][j] = offs[j];
                         }
                         if (have2) fetch(nt2, c2);
                         publish(it);
@@ -842,20 +869,21 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             if (!fast) {
                 // generic form (any class count, any split): recompute the places of an item from the states
                 uint32_t it = 0;
-                uint32_t h_nt[2] = {0, 0}, h_c[2] = {0, 0};  // what each of the two stages currently holds
+                uint32_t h_nt[SB] = {}, h_c[SB] = {};  // the last SB items, oldest first: [0] is what the stage coming round now holds
                 bool ok = true;
                 for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
                     uint32_t mt, nt, sp;
                     decode(unit, mt, nt, sp);
                     const uint32_t c0 = chunk_begin(sp), c1 = chunk_begin(sp + 1);
                     for (uint32_t c = c0; c < c1; ++c, ++it) {
-                        const uint32_t sb = it & 1U;
                         if (!acquire(it)) { ok = false; break; }
-                        uint8_t* buf = b_ring + sb * Cfg::B_STAGE_BYTES;
-                        if (it >= 2U) apply(buf, sb ? h_nt[1] : h_nt[0], sb ? h_c[1] : h_c[0], 0);
+                        uint8_t* buf = b_ring + (it % SB) * Cfg::B_STAGE_BYTES;
+                        if (it >= static_cast<uint32_t>(SB)) apply(buf, h_nt[0], h_c[0], 0);
                         __syncwarp();  // a place cleared by one lane may be set by another lane of this warp
                         apply(buf, nt, c, 0x3C00);
-                        if (sb) { h_nt[1] = nt; h_c[1] = c; } else { h_nt[0] = nt; h_c[0] = c; }
+#pragma unroll
+                        for (int q2 = 0; q2 + 1 < SB; ++q2) { h_nt[q2] = h_nt[q2 + 1]; h_c[q2] = h_c[q2 + 1]; }
+                        h_nt[SB - 1] = nt; h_c[SB - 1] = c;
                         publish(it);
                     }
                 }
