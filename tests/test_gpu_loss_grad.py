@@ -128,6 +128,13 @@ def test_residual_tower_fused(oracle, engine, dims, n):
     check_against_oracle(oracle, engine, shape, w, states, labels)
 
 
+def test_reference_hard_caps(oracle, engine):
+    # hd1 4096, hd2 512 are the reference's compile-time caps (native/cuda/mlp_forward.cu:7-9); 29 outputs as in the
+    # depth-classification variant; hd2 > 256 takes the per-layer residual path
+    shape, w, states, labels = _walk_case(oracle, (72, 72, 4096, 512, 2, 29), 96, seed=3)
+    check_against_oracle(oracle, engine, shape, w * 0.3, states, labels)
+
+
 def test_residual_tower_layered_matches_fused(oracle, engine, monkeypatch):
     # the per-layer GEMM path (taken for other widths) on a width both paths accept
     shape, w, states, labels = _walk_case(oracle, (72, 72, 64, 64, 3, 1), 500, seed=5)
