@@ -26,6 +26,10 @@ struct TrainOptions {
     float lr = 0.0001f, weight_decay = 0.0f;
     bool write_artifacts = true, backward_profile = false, overlap_allreduce = true;
     std::string nccl_id_file, resume_checkpoint;
+    // beyond the reference's flag set (both default to its behaviour): write the checkpoint every N steps, and let a
+    // resumed run continue the step count the checkpoint was written at instead of restarting it at 0
+    uint32_t checkpoint_period_steps = 0;
+    bool resume_step = false;
 };
 
 // Every flag takes exactly one value; unknown flags, missing values and unparsable values fail

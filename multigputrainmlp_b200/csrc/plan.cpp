@@ -83,6 +83,7 @@ bool ParseTrainOptions(int argc, const char* const* argv, TrainOptions* o) {
         {"--write-artifacts", flag(&o->write_artifacts)}, {"--backward-profile", flag(&o->backward_profile)},
         {"--overlap-allreduce", flag(&o->overlap_allreduce)}, {"--nccl-id-file", text(&o->nccl_id_file)},
         {"--resume-checkpoint", text(&o->resume_checkpoint)},
+        {"--checkpoint-period-steps", u32(&o->checkpoint_period_steps)}, {"--resume-step", flag(&o->resume_step)},
     };
     for (int i = 1; i < argc; i += 2) {
         if (i + 1 >= argc) return false;

@@ -88,7 +88,8 @@ const char kUsage[] =
     "usage: mgt_native_train --output-dir DIR --steps N --device-id ID --world-size N --global-rank R --local-rank R "
     "[--batch-size N --k-min N --k-max N --hd1 N --hd2 N --nrd N --write-artifacts 0|1 --backward-profile 0|1 --overlap-allreduce 0|1 "
     "--input-grad-partial-chunks N --input-grad-positions-per-block N --input-grad-position-tile N --input-grad-fp16 0|1 --linear-fp16 0|1 "
-    "--persistent-half-weights 0|1 --lt-workspace-bytes N --nccl-id-file PATH --resume-checkpoint DIR]\n";
+    "--persistent-half-weights 0|1 --lt-workspace-bytes N --nccl-id-file PATH --resume-checkpoint DIR "
+    "--checkpoint-period-steps N --resume-step 0|1]\n";
 
 }  // namespace
 
@@ -118,6 +119,17 @@ int main(int argc, char** argv) {
     InitialWeights(&weights);
     const bool resumed = !opt.resume_checkpoint.empty();
     if (resumed && !ReadCheckpoint(opt.resume_checkpoint, &weights, &adam_m, &adam_v)) return EXIT_FAILURE;
+    // Step numbering of a resumed run: the reference restarts at 0 (tool:765,830), which replays the first walk batches
+    // and AdamW bias corrections. With --resume-step 1 the count written beside the checkpoint (checkpoint/step.txt; the
+    // manifest itself stays byte-compatible) is continued, so that N + M steps in two runs equal N + M steps in one.
+    uint32_t first_step = 0;
+    if (resumed && opt.resume_step) {
+        std::ifstream in(opt.resume_checkpoint + "/step.txt");
+        if (!(in >> first_step)) {
+            std::cerr << "--resume-step 1: " << opt.resume_checkpoint << "/step.txt not found or unreadable\n";
+            return EXIT_FAILURE;
+        }
+    }
     uint8_t moves[18 * 80], target[80];
     BuildCyclicPuzzle(plan, moves, target);
 
@@ -171,7 +183,16 @@ int main(int argc, char** argv) {
 
     const mgt_random_walk_config_t walk_cfg{B, opt.k_min, opt.k_max, opt.move_count, opt.state_len, plan.padded_state_dim};
     float last_loss = 0.0f;
-    for (uint32_t step = 0; step < opt.steps; ++step) {
+    auto write_checkpoint = [&](uint32_t steps_done, bool with_weights) -> bool {
+        if (!CUDA_OK(cudaMemcpy(weights.data(), d_w, P * 4, cudaMemcpyDeviceToHost)) || !CUDA_OK(cudaMemcpy(adam_m.data(), d_m, P * 4, cudaMemcpyDeviceToHost)) ||
+            !CUDA_OK(cudaMemcpy(adam_v.data(), d_v, P * 4, cudaMemcpyDeviceToHost))) return false;
+        if (with_weights && !WriteWeights(opt.output_dir, plan, weights)) return false;
+        if (!WriteCheckpoint(opt.output_dir, plan, weights, adam_m, adam_v)) return false;
+        std::ofstream out(opt.output_dir + "/checkpoint/step.txt", std::ios::trunc);
+        out << steps_done << "\n";
+        return static_cast<bool>(out);
+    };
+    for (uint32_t step = first_step; step < first_step + opt.steps; ++step) {
         if (!CUDA_OK(cudaEventRecord(ev_start, compute))) return EXIT_FAILURE;
         float* walk_labels = opt.output_dim == 1 ? d_labels : d_walk_labels;
         if (mgt_launch_random_walk(&walk_cfg, opt.seed, 0, step, opt.global_rank, d_moves, d_target, d_states, walk_labels, d_meta, compute) != MGT_OK) return EXIT_FAILURE;
@@ -244,13 +265,12 @@ int main(int argc, char** argv) {
         std::copy(bwv, bwv + 7, rec.bw);
         log << StepLogLine(plan, rec);
         profile << StepProfileRow(plan, rec, overlap);
+        const uint32_t done = step + 1U;
+        if (opt.write_artifacts && opt.checkpoint_period_steps != 0 && done % opt.checkpoint_period_steps == 0 && done != first_step + opt.steps &&
+            !write_checkpoint(done, false)) return EXIT_FAILURE;
     }
 
-    if (opt.write_artifacts) {
-        if (!CUDA_OK(cudaMemcpy(weights.data(), d_w, P * 4, cudaMemcpyDeviceToHost)) || !CUDA_OK(cudaMemcpy(adam_m.data(), d_m, P * 4, cudaMemcpyDeviceToHost)) ||
-            !CUDA_OK(cudaMemcpy(adam_v.data(), d_v, P * 4, cudaMemcpyDeviceToHost))) return EXIT_FAILURE;
-        if (!WriteWeights(opt.output_dir, plan, weights) || !WriteCheckpoint(opt.output_dir, plan, weights, adam_m, adam_v)) return EXIT_FAILURE;
-    }
+    if (opt.write_artifacts && !write_checkpoint(first_step + opt.steps, true)) return EXIT_FAILURE;
     if (!WriteMetadataEnv(opt.output_dir, plan, overlap, comm_enabled, resumed) || !WriteLayersJson(opt.output_dir, plan) ||
         !WriteLinearOpsManifest(opt.output_dir, plan)) return EXIT_FAILURE;
 

@@ -2,16 +2,20 @@
 // (seed, epoch, step, rank, sample): native/cuda/random_walk_kernel.cu:7-64 and
 // native/src/random_walk_cpu.cpp:32-66. Integer-only; HBM traffic is 100 bytes per sample.
 //
-// One thread walks one sample. The 18 move permutations live in shared memory; each thread keeps
-// its two 72-byte state buffers in shared memory as well, laid out position-major so that the
-// threads of a warp touch neighbouring bytes.
+// One thread walks one sample. The 18 move permutations live in shared memory; each thread keeps its two 72-byte
+// state buffers in shared memory as words of four positions, words of neighbouring threads next to each other:
+// byte gathers of a warp then fall into 32 different banks and a move writes 18 words per thread instead of 72 bytes.
+// The generator's `rng % bound` on the full 64-bit state is computed exactly with 32-bit multiplies
+// (x mod b = ((hi mod b) * (2^32 mod b) + lo mod b) mod b, each step by a multiply-high with ceil(2^32 / b) and one
+// correction), which is several times cheaper than a 64-bit remainder.
 #include "../../include/mgt_b200.h"
 
 #include <cuda_runtime.h>
 
 namespace {
 
-constexpr int kWalkThreads = 128;
+constexpr int kWalkThreads = 64;
+constexpr int kStateWords = MGT_STATE_STORAGE_LEN / 4;  // 20 words hold the 72 positions (and the 8 pad bytes)
 
 __host__ __device__ inline uint64_t Mix64(uint64_t x) {
     x += 0x9e3779b97f4a7c15ULL;
@@ -20,26 +24,52 @@ __host__ __device__ inline uint64_t Mix64(uint64_t x) {
     return x ^ (x >> 31);
 }
 
+struct Bound {
+    uint32_t b, magic, r32;  // magic = ceil(2^32 / b), r32 = 2^32 mod b; valid for 2 <= b <= 65535
+};
+__device__ inline Bound MakeBound(uint32_t b) {
+    Bound q{b, 0U, 0U};
+    if (b >= 2U && b <= 65535U) {
+        q.magic = 0xFFFFFFFFU / b + 1U;
+        q.r32 = (0xFFFFFFFFU % b + 1U) % b;
+    }
+    return q;
+}
+__device__ inline uint32_t Mod32(uint32_t n, const Bound& q) {
+    if (q.magic == 0U) return q.b <= 1U ? 0U : n % q.b;
+    uint32_t r = n - __umulhi(n, q.magic) * q.b;  // the quotient estimate is exact or one too large
+    return r >= q.b ? r + q.b : r;
+}
 // rng = Mix64(rng); value = rng % bound on the full 64-bit state
-__device__ inline uint32_t NextBounded(uint64_t* state, uint32_t bound) {
+__device__ inline uint32_t NextBounded(uint64_t* state, const Bound& q) {
     *state = Mix64(*state);
-    return static_cast<uint32_t>(*state % bound);
+    const uint64_t x = *state;
+    if (q.b <= 1U) return 0U;  // (a bound of 0 is a division by zero in the reference; never reached with valid configurations)
+    if (q.magic == 0U) return static_cast<uint32_t>(x % q.b);
+    const uint32_t h = Mod32(static_cast<uint32_t>(x >> 32), q), l = Mod32(static_cast<uint32_t>(x), q);
+    return Mod32(h * q.r32 + l, q);
 }
 
 __global__ void __launch_bounds__(kWalkThreads)
 RandomWalkKernel(mgt_random_walk_config_t config, uint64_t base_seed, uint64_t epoch, uint64_t step, uint32_t global_rank,
                  const mgt_train_state_t* __restrict__ moves, const mgt_train_state_t* __restrict__ target,
                  mgt_train_state_t* __restrict__ states, float* __restrict__ labels, mgt_walk_meta_t* __restrict__ meta) {
-    __shared__ uint8_t s_moves[MGT_MOVE_COUNT * MGT_STATE_LEN];
-    __shared__ uint8_t s_state[2][MGT_STATE_LEN][kWalkThreads];
-    __shared__ __align__(16) uint8_t s_out[kWalkThreads][MGT_STATE_STORAGE_LEN];
+    __shared__ __align__(4) uint8_t s_moves[MGT_MOVE_COUNT * MGT_STATE_STORAGE_LEN];  // pad positions map to themselves
+    __shared__ uint32_t s_state[2][kStateWords][kWalkThreads];
 
     const uint32_t tid = threadIdx.x;
-    for (uint32_t i = tid; i < config.move_count * config.state_len; i += kWalkThreads) {
-        const uint32_t mv = i / config.state_len, pos = i - mv * config.state_len;
-        s_moves[mv * MGT_STATE_LEN + pos] = moves[mv].v[pos];
+    for (uint32_t i = tid; i < MGT_MOVE_COUNT * MGT_STATE_STORAGE_LEN; i += kWalkThreads) {
+        const uint32_t mv = i / MGT_STATE_STORAGE_LEN, pos = i - mv * MGT_STATE_STORAGE_LEN;
+        s_moves[i] = (mv < config.move_count && pos < config.state_len) ? moves[mv].v[pos] : static_cast<uint8_t>(pos);
     }
-    for (uint32_t pos = 0; pos < config.state_len; ++pos) s_state[0][pos][tid] = target->v[pos];
+    for (uint32_t wd = 0; wd < kStateWords; ++wd) {
+        uint32_t packed = 0;
+        for (uint32_t k = 0; k < 4U; ++k) {
+            const uint32_t pos = wd * 4U + k;
+            packed |= static_cast<uint32_t>(pos < config.state_len ? target->v[pos] : 0U) << (8U * k);
+        }
+        s_state[0][wd][tid] = packed;
+    }
     __syncthreads();
 
     const uint32_t sample = blockIdx.x * kWalkThreads + tid;
@@ -51,27 +81,47 @@ RandomWalkKernel(mgt_random_walk_config_t config, uint64_t base_seed, uint64_t e
     rng ^= Mix64(static_cast<uint64_t>(global_rank) << 32);
     rng ^= Mix64(sample);
 
-    const uint32_t depth_span = config.k_max - config.k_min + 1U;
-    const uint32_t depth = active ? config.k_min + NextBounded(&rng, depth_span) : 0U;
+    const Bound span = MakeBound(config.k_max - config.k_min + 1U), all_moves = MakeBound(config.move_count), other_moves = MakeBound(config.move_count - 1U);
+    const uint32_t depth = active ? config.k_min + NextBounded(&rng, span) : 0U;
+    const uint32_t words = (config.state_len + 3U) / 4U;
     uint32_t last_move = config.move_count;
     uint32_t cur = 0;
     for (uint32_t d = 0; d < depth; ++d) {
-        uint32_t move = NextBounded(&rng, config.move_count);
+        uint32_t move = NextBounded(&rng, all_moves);
         if (last_move != config.move_count && move == last_move) {
-            move = (move + 1U + NextBounded(&rng, config.move_count - 1U)) % config.move_count;
+            move = Mod32(move + 1U + NextBounded(&rng, other_moves), all_moves);
         }
-        const uint8_t* def = s_moves + move * MGT_STATE_LEN;
-        for (uint32_t i = 0; i < config.state_len; ++i) s_state[cur ^ 1U][i][tid] = s_state[cur][def[i]][tid];
+        const uint32_t* def = reinterpret_cast<const uint32_t*>(s_moves + move * MGT_STATE_STORAGE_LEN);
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(&s_state[cur][0][0]);
+        for (uint32_t wd = 0; wd < words; ++wd) {
+            const uint32_t from = def[wd];  // four source positions
+            uint32_t packed = 0;
+#pragma unroll
+            for (uint32_t k = 0; k < 4U; ++k) {
+                const uint32_t pos = (from >> (8U * k)) & 0xFFU;
+                packed |= static_cast<uint32_t>(src[((pos >> 2) * kWalkThreads + tid) * 4U + (pos & 3U)]) << (8U * k);
+            }
+            s_state[cur ^ 1U][wd][tid] = packed;
+        }
         cur ^= 1U;
         last_move = move;
     }
-    // stage the 80-byte record (pad bytes zero) and write it with 16-byte stores
-    for (uint32_t i = 0; i < MGT_STATE_STORAGE_LEN; ++i) s_out[tid][i] = i < config.state_len ? s_state[cur][i][tid] : 0;
     if (active) {
-        const uint4* src = reinterpret_cast<const uint4*>(s_out[tid]);
+        // the 80-byte record (pad bytes zero) as five 16-byte stores
         uint4* dst = reinterpret_cast<uint4*>(states + sample);
 #pragma unroll
-        for (int q = 0; q < MGT_STATE_STORAGE_LEN / 16; ++q) dst[q] = src[q];
+        for (int q = 0; q < kStateWords / 4; ++q) {
+            uint32_t wv[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t wd = q * 4 + k;
+                uint32_t x = wd < words ? s_state[cur][wd][tid] : 0U;
+                const uint32_t first = wd * 4U;  // positions at or beyond state_len are padding
+                if (first + 4U > config.state_len) x &= first >= config.state_len ? 0U : (0xFFFFFFFFU >> (8U * (first + 4U - config.state_len)));
+                wv[k] = x;
+            }
+            dst[q] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+        }
         labels[sample] = static_cast<float>(depth);
         mgt_walk_meta_t m;
         m.depth = depth;

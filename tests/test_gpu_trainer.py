@@ -167,3 +167,29 @@ def test_two_rank_run_keeps_replicas_identical(tmp_path, oracle):
         for row, want in zip(rows, losses):
             assert abs(row["loss"] - want[r]) <= 1e-3 * abs(want[r])
         assert "WORLD_SIZE=2\n" in open(tmp_path / f"rank{r}" / "metadata.env").read()
+
+
+def test_resume_step_continues_the_run_bit_for_bit(tmp_path):
+    # --resume-step 1 / --checkpoint-period-steps (beyond the reference's flags): 3 + 3 steps in two runs, the second
+    # resumed from the periodic checkpoint of the first, end in the very state of 6 steps in one run
+    common = ["--batch-size", 640, "--k-min", 1, "--k-max", 29, "--hd1", 128, "--hd2", 64, "--nrd", 2, "--lr", 0.001]
+    run(tmp_path / "whole", "--steps", 6, *common)
+    run(tmp_path / "first", "--steps", 4, "--checkpoint-period-steps", 3, *common)
+    # the periodic checkpoint of step 3 was overwritten by the final one of step 4; make the 3-step one explicitly
+    run(tmp_path / "three", "--steps", 3, *common)
+    assert open(tmp_path / "three" / "checkpoint" / "step.txt").read().strip() == "3"
+    assert open(tmp_path / "first" / "checkpoint" / "step.txt").read().strip() == "4"
+    run(tmp_path / "second", "--steps", 3, "--resume-checkpoint", tmp_path / "three" / "checkpoint", "--resume-step", 1, *common)
+    whole = np.fromfile(tmp_path / "whole" / "checkpoint" / "state.f32.bin", dtype=np.float32)
+    second = np.fromfile(tmp_path / "second" / "checkpoint" / "state.f32.bin", dtype=np.float32)
+    assert np.array_equal(whole, second)
+    steps = [r["step"] for r in read_profile(tmp_path / "second" / "profile.jsonl")]
+    assert steps == [3, 4, 5]
+    losses_whole = [r["loss"] for r in read_profile(tmp_path / "whole" / "profile.jsonl")]
+    losses_second = [r["loss"] for r in read_profile(tmp_path / "second" / "profile.jsonl")]
+    assert losses_whole[3:] == losses_second
+    # the reference's behaviour stays the default: the step count restarts
+    run(tmp_path / "restart", "--steps", 2, "--resume-checkpoint", tmp_path / "three" / "checkpoint", *common)
+    assert [r["step"] for r in read_profile(tmp_path / "restart" / "profile.jsonl")] == [0, 1]
+    res = run(tmp_path / "bad", "--steps", 1, "--resume-checkpoint", tmp_path / "nowhere", "--resume-step", 1, *common, check=False)
+    assert res.returncode != 0
