@@ -116,11 +116,11 @@ Workspace PlanWorkspace(const mgt_mlp_shape_t& s, uint32_t B, uint32_t sm_count)
     w.off_head = take((uint64_t)kHeadBlocks * (2ULL * s.hd2 + 2) * 4);
     // per-warp column sums: one slot per residual dX GEMM (2R of them), one wider slot for the hidden dX GEMM
     const uint64_t chain_tiles = (B + 127) / 128;
-    const uint64_t slot_rows = (uint64_t)sm_count * 8 > chain_tiles * 4 ? (uint64_t)sm_count * 8 : chain_tiles * 4;
+    const uint64_t slot_rows = (uint64_t)sm_count * 16 > chain_tiles * 4 ? (uint64_t)sm_count * 16 : chain_tiles * 4;  // up to 16 epilogue warps per CTA
     w.colsum_slot_floats = slot_rows * s.hd2;
     w.colsum_floats = w.colsum_slot_floats * 2 * (w.R > 0 ? w.R : 1);
     w.off_colsum = take(w.colsum_floats * 4);
-    w.off_colsum_h1 = take((uint64_t)sm_count * 8 * s.hd1 * 4);
+    w.off_colsum_h1 = take((uint64_t)sm_count * 16 * s.hd1 * 4);
     w.bits_stride = chain_tiles * 128 * 8;
     w.off_bits = take(w.bits_stride * 4 * (2 * w.R + 1));
     // internal fp16 weight copy (used when the caller's mirror cannot be addressed by TMA as it lies)
@@ -251,6 +251,8 @@ template <int BN, Epi EPI> using CfgDx = GemmCfg<BN, 1, false, BSource::kTmaK, E
 // B-stationary forms for reductions of at most 256 (the residual width): weights stay in shared memory
 template <int BN, Epi EPI> using CfgFwdS = GemmCfg<BN, 1, false, BSource::kTmaMN, EPI, 3, 4, true>;
 template <int BN, Epi EPI> using CfgDxS = GemmCfg<BN, 1, false, BSource::kTmaK, EPI, 3, 4, true>;
+// wide outputs (the hidden layer's dX): 128-column tiles drained by sixteen epilogue warps, one 32-column chunk each
+template <Epi EPI> using CfgDxW = GemmCfg<128, 1, false, BSource::kTmaK, EPI, 3, 4, true, false, 16>;
 template <int BN> using CfgDw = GemmCfg<BN, 1, true, BSource::kTmaMN, Epi::kPartialF32, 3, 3>; // act^T x dz
 template <int BN> using CfgDwG = GemmCfg<BN, 1, true, BSource::kTmaMN, Epi::kPartialF32, 3, 3, false, true>; // R stacked act^T x dz
 // Two 256-column accumulators per unit (all of TMEM) and a two-stage one-hot ring. Measured alternatives at p888: 2 x 192
@@ -579,38 +581,49 @@ mgt_status_t GemmForward(mgt_engine* e, cudaStream_t st, const __half* act, uint
     return bn == 224 ? LaunchGemm<CfgFwd<224, EPI>>(e, ta, tb, a, st) : LaunchGemm<CfgFwd<256, EPI>>(e, ta, tb, a, st);
 }
 
-// Grid the dX GEMMs run on (the column-sum scratch has one row per epilogue warp of every CTA).
-uint32_t BackpropGrid(const mgt_engine* e, uint32_t M, uint32_t N, uint32_t K) {
-    const GemmArgs a = BaseArgs(M, N, K, PickBN(N), 1);
+// How a dX GEMM is run: tile width, form, grid, and the rows of its column-sum scratch (one per epilogue warp of every CTA).
+struct BackpropPlan {
+    uint32_t bn;
+    bool stationary, wide;
+    uint32_t grid, rows;
+};
+BackpropPlan PlanBackprop(const mgt_engine* e, uint32_t M, uint32_t N, uint32_t K) {
+    BackpropPlan p{};
+    const uint32_t sm = (uint32_t)e->sm_count;
+    p.wide = (K + 63) / 64 <= 4 && N % 128U == 0 && N >= 512U && N / 128U <= sm;
+    p.bn = p.wide ? 128U : PickBN(N);
+    const GemmArgs a = BaseArgs(M, N, K, p.bn, 1);
+    p.stationary = p.wide || (a.k_chunks <= 4 && a.n_tiles <= sm);
     const uint64_t units = (uint64_t)a.m_tiles * a.n_tiles;
-    const bool stationary = a.k_chunks <= 4 && a.n_tiles <= (uint32_t)e->sm_count;
-    uint32_t grid = (uint32_t)(units < (uint64_t)e->sm_count ? units : (uint64_t)e->sm_count);
-    if (stationary && grid >= a.n_tiles) grid = grid / a.n_tiles * a.n_tiles;  // as LaunchGemm picks it
-    return grid;
+    p.grid = (uint32_t)(units < (uint64_t)sm ? units : (uint64_t)sm);
+    if (p.stationary && p.grid >= a.n_tiles) p.grid = p.grid / a.n_tiles * a.n_tiles;  // as LaunchGemm picks it
+    p.rows = p.grid * (p.wide ? 16U : 8U);
+    return p;
 }
 
 // dX[M x N] = dz[M x K, K-major] * W[N x K, row-major]^T with a backward epilogue that produces the
 // next dz tensor; its fp32 column sums (a bias gradient) go to `colsum` (zeroed by the caller,
-// BackpropGrid()*8 rows of N) and, if bias_grad is given, are reduced into bias_grad[N] right away.
+// PlanBackprop().rows rows of N) and, if bias_grad is given, are reduced into bias_grad[N] right away.
 template <Epi EPI>
 mgt_status_t GemmBackpropInput(mgt_engine* e, cudaStream_t st, const __half* dz, uint32_t dz_pitch, const __half* w, uint32_t w_pitch,
                                uint32_t M, uint32_t N, uint32_t K, GemmArgs epi, float* colsum, float* bias_grad) {
-    const uint32_t bn = PickBN(N);
-    GemmArgs a = BaseArgs(M, N, K, bn, 1);
+    const BackpropPlan p = PlanBackprop(e, M, N, K);
+    GemmArgs a = BaseArgs(M, N, K, p.bn, 1);
     a.out_f32 = epi.out_f32; a.ld_f32 = epi.ld_f32; a.out_f16 = epi.out_f16; a.ld_f16 = epi.ld_f16;
     a.add_f32 = epi.add_f32; a.ld_add = epi.ld_add; a.mask = epi.mask; a.ld_mask = epi.ld_mask;
-    const bool stationary = a.k_chunks <= 4 && a.n_tiles <= (uint32_t)e->sm_count;
     a.colsum = colsum;
     CUtensorMap ta, tb;
     MGT_MAP(e->Map(&ta, dz, K, M, dz_pitch, 64, 128));
-    MGT_MAP(e->Map(&tb, w, K, N, w_pitch, 64, bn));
-    if (stationary) {
-        MGT_TRY(bn == 224 ? LaunchGemm<CfgDxS<224, EPI>>(e, ta, tb, a, st) : LaunchGemm<CfgDxS<256, EPI>>(e, ta, tb, a, st));
+    MGT_MAP(e->Map(&tb, w, K, N, w_pitch, 64, p.bn));
+    if (p.wide) {
+        MGT_TRY(LaunchGemm<CfgDxW<EPI>>(e, ta, tb, a, st));
+    } else if (p.stationary) {
+        MGT_TRY(p.bn == 224 ? LaunchGemm<CfgDxS<224, EPI>>(e, ta, tb, a, st) : LaunchGemm<CfgDxS<256, EPI>>(e, ta, tb, a, st));
     } else {
-        MGT_TRY(bn == 224 ? LaunchGemm<CfgDx<224, EPI>>(e, ta, tb, a, st) : LaunchGemm<CfgDx<256, EPI>>(e, ta, tb, a, st));
+        MGT_TRY(p.bn == 224 ? LaunchGemm<CfgDx<224, EPI>>(e, ta, tb, a, st) : LaunchGemm<CfgDx<256, EPI>>(e, ta, tb, a, st));
     }
     if (bias_grad != nullptr) {
-        ReduceRowsKernel<<<(N + kReduceCols - 1) / kReduceCols, 256, 0, st>>>(colsum, BackpropGrid(e, M, N, K) * 8U, N, 0, N, bias_grad);
+        ReduceRowsKernel<<<(N + kReduceCols - 1) / kReduceCols, 256, 0, st>>>(colsum, p.rows, N, 0, N, bias_grad);
         ++e->launches;
     }
     return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
@@ -1060,7 +1073,7 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
 
     // ---- residual blocks backward (mlp_backward.cu:1367-1413). First the chain of input-gradient GEMMs,
     // block R-1 down to 0; every dz tensor is kept. dzf holds the running fp32 gradient (skip connection).
-    const uint32_t dx_rows = BackpropGrid(e, B, H2, H2) * 8U;
+    const uint32_t dx_rows = PlanBackprop(e, B, H2, H2).rows;
     if (R > 0 && !chain && cudaMemsetAsync(colsum, 0, ws.colsum_floats * sizeof(float), st) != cudaSuccess) return MGT_CUDA_FAILURE;
     uint32_t colsum_rows = dx_rows;
     if (chain) {
@@ -1111,7 +1124,7 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     if (half_ig) {
         GemmArgs d{};  // dz1 = (dzh * Wh^T) * [a1 > 0]
         d.mask = a1_h; d.ld_mask = ws.p_a1; d.out_f16 = dz1_h; d.ld_f16 = ws.p_dz1;
-        if (cudaMemsetAsync(colsum_h1, 0, (uint64_t)BackpropGrid(e, B, H1, H2) * 8U * H1 * sizeof(float), st) != cudaSuccess) return MGT_CUDA_FAILURE;
+        if (cudaMemsetAsync(colsum_h1, 0, (uint64_t)PlanBackprop(e, B, H1, H2).rows * H1 * sizeof(float), st) != cudaSuccess) return MGT_CUDA_FAILURE;
         MGT_TRY(GemmBackpropInput<Epi::kMaskF16>(e, st, dz_cur, ws.p_dz, hw.wh, hw.p2, B, H1, H2, d, colsum_h1, grad + InputBias(s)));
     } else {
         // --input-grad-fp16 0: the embedding gradient wants dz1 in fp32 (mlp_backward.cu:1433-1504, float one-hot GEMM).

@@ -69,7 +69,7 @@ struct GemmArgs {
 // once and stays in shared memory while the CTA streams its M tiles (all units of a CTA then share the N tile).
 // GROUPED_: one launch computes args.groups independent products of the same shape; operand g is slice g
 // (third coordinate) of the 3-D tensors behind the two descriptors, result g goes to its own partial planes.
-template <int BN_, int NACC_, bool A_MN_, BSource BSRC_, Epi EPI_, int SA_, int SB_, bool BSTAT_ = false, bool GROUPED_ = false>
+template <int BN_, int NACC_, bool A_MN_, BSource BSRC_, Epi EPI_, int SA_, int SB_, bool BSTAT_ = false, bool GROUPED_ = false, int EPI_WARPS_ = 8>
 struct GemmCfg {
     static constexpr bool BSTAT = BSTAT_;
     static constexpr bool GROUPED = GROUPED_;
@@ -90,7 +90,8 @@ struct GemmCfg {
     static constexpr int B_STAGE_BYTES = NACC_ * B_ACC_BYTES;
     static constexpr int ACC_BUFS = 2 / NACC_;
     static constexpr int ACC_COLS = 256;  // TMEM columns reserved per accumulator
-    static constexpr int EPI_WARPS = 8;
+    static constexpr int EPI_WARPS = EPI_WARPS_;        // a multiple of four: EPI_WARPS/4 warps share a TMEM lane quadrant
+    static constexpr int EPI_STRIDE = EPI_WARPS_ / 4;  // ... and take every EPI_STRIDE-th 32-column chunk
     static constexpr int SYNTH_WARPS = 8;
     static constexpr int FIRST_SYNTH_THREAD = 64 + 32 * EPI_WARPS;
     static constexpr int THREADS = FIRST_SYNTH_THREAD + (kOneHot ? 32 * SYNTH_WARPS : 0);
@@ -103,6 +104,8 @@ struct GemmCfg {
     static_assert(BN_ % 16 == 0 && BN_ >= 16 && BN_ <= 256, "UMMA N");
     static_assert(BN_ % 32 == 0, "epilogue drains 32 columns at a time");
     static_assert(NACC_ == 1 || NACC_ == 2, "one or two accumulators");
+    static_assert(EPI_WARPS_ == 8 || EPI_WARPS_ == 16, "epilogue warps");
+    static_assert(!kOneHot || EPI_WARPS_ == 8, "the synthesis warps follow eight epilogue warps");
     static_assert(B_ACC_BYTES % 1024 == 0, "swizzle atoms must stay 1024-byte aligned");
     static_assert(!kOneHot || (SB_ >= 2 && SB_ <= 4), "one-hot ring depth");
     static_assert(!GROUPED_ || (EPI_ == Epi::kPartialF32 && A_MN_ && BSRC_ == BSource::kTmaMN && !BSTAT_), "grouped form: split-K weight gradients");
@@ -390,7 +393,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll 1
                 for (int acc = 0; acc < NACC; ++acc) {
 #pragma unroll 1
-                    for (int cc = static_cast<int>(chunk_parity); cc < BN / 32; cc += 2) {
+                    for (int cc = static_cast<int>(chunk_parity); cc < BN / 32; cc += Cfg::EPI_STRIDE) {
                         const uint32_t n0 = (nt * NACC + acc) * BN + cc * 32;
                         if (n0 >= args.N) continue;
                         uint32_t r[32];
@@ -435,7 +438,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             // unit: their column sums are accumulated here and written once at the end instead of a global
             // read-modify-write per chunk
             float* col_acc = reinterpret_cast<float*>(mask_words + 32);
-            constexpr bool kColsumLocal = Cfg::BSTAT && kHasMask && BN / 64 <= 4;
+            constexpr bool kColsumLocal = Cfg::BSTAT && kHasMask && BN / (32 * Cfg::EPI_STRIDE) <= 4;
             if (kColsumLocal) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) col_acc[i * 32 + lane] = 0.0f;
@@ -483,11 +486,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 if (!__all_sync(0xFFFFFFFFU, mbar_wait(&acc_full[ab], aph, cta_abort, kAbortEpilogueWait))) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll 1
-                for (int cc = static_cast<int>(chunk_parity); cc < BN / 32; cc += 2) {
+                for (int cc = static_cast<int>(chunk_parity); cc < BN / 32; cc += Cfg::EPI_STRIDE) {
                     const uint32_t n0 = nt * BN + cc * 32;
                     if (n0 >= args.N) break;
                     const Operands cur = next;
-                    if (cc + 2 < BN / 32) request(next, m_base, rows_ok, n0 + 64U);
+                    if (cc + Cfg::EPI_STRIDE < BN / 32) request(next, m_base, rows_ok, n0 + 32U * Cfg::EPI_STRIDE);
                     uint32_t r[32];
                     tmem_ld_32x32(tmem_base + ((quad * 32U) << 16) + ab * Cfg::ACC_COLS + cc * 32, r);
                     tmem_ld_wait();
@@ -602,7 +605,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll 8
                             for (uint32_t rr = 0; rr < 32U; ++rr) total += rr < rows_ok ? tile[rr * TP + lane] : 0.0f;
                             if (kColsumLocal) {
-                                col_acc[(cc >> 1) * 32 + lane] += total;  // this lane is the only user of the slot
+                                col_acc[(cc / Cfg::EPI_STRIDE) * 32 + lane] += total;  // this lane is the only user of the slot
                             } else if (col_ok) {
                                 float* dst = args.colsum + (static_cast<uint64_t>(blockIdx.x) * Cfg::EPI_WARPS + ew) * args.N + n0 + lane;
                                 *dst += total;  // this warp is the only writer of its row
@@ -616,9 +619,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             }
             if (kColsumLocal && args.colsum != nullptr && blockIdx.x < total_units) {
                 const uint32_t nt = blockIdx.x % args.n_tiles;  // the N tile of every unit of this CTA
-                for (int cc = static_cast<int>(chunk_parity); cc < BN / 32; cc += 2) {
+                for (int cc = static_cast<int>(chunk_parity); cc < BN / 32; cc += Cfg::EPI_STRIDE) {
                     const uint32_t n = nt * BN + cc * 32 + lane;
-                    if (n < args.N) args.colsum[(static_cast<uint64_t>(blockIdx.x) * Cfg::EPI_WARPS + ew) * args.N + n] = col_acc[(cc >> 1) * 32 + lane];
+                    if (n < args.N) args.colsum[(static_cast<uint64_t>(blockIdx.x) * Cfg::EPI_WARPS + ew) * args.N + n] = col_acc[(cc / Cfg::EPI_STRIDE) * 32 + lane];
                 }
             }
         }
