@@ -168,7 +168,7 @@ struct mgt_engine {
     std::mutex mu;
     cudaEvent_t ev_last = nullptr, ev_now = nullptr;
     uint64_t launches = 0;  // kernels launched through this engine (host-side count)
-    uint32_t debug_skip = 0;  // MGT_DEBUG_SKIP: bits 0-1 are timing experiments (results are wrong when set); bit 2 selects the per-layer residual path
+    bool layered_tower = false;  // MGT_RESIDUAL_PATH=layered: per-layer GEMMs instead of the fused residual-tower kernels (both are tested)
 
     // fp16 3-D tensor map (a stack of `layers` equal matrices `layer_stride_bytes` apart), 128-byte swizzle, box depth 1
     bool Map3D(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t layers, uint64_t pitch_elems, uint64_t layer_stride_bytes,
@@ -239,7 +239,6 @@ mgt_status_t LaunchGemm(mgt_engine* e, const CUtensorMap& ta, const CUtensorMap&
         if (grid >= args.n_tiles) grid = grid / args.n_tiles * args.n_tiles;
     }
     args.status = e->status_word;
-    args.debug_skip = e->debug_skip;
     umma_gemm_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, args);
     ++e->launches;
     return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
@@ -252,7 +251,7 @@ template <int BN, Epi EPI> using CfgDx = GemmCfg<BN, 1, false, BSource::kTmaK, E
 template <int BN, Epi EPI> using CfgFwdS = GemmCfg<BN, 1, false, BSource::kTmaMN, EPI, 3, 4, true>;
 template <int BN, Epi EPI> using CfgDxS = GemmCfg<BN, 1, false, BSource::kTmaK, EPI, 3, 4, true>;
 // wide outputs (the hidden layer's dX): 128-column tiles drained by sixteen epilogue warps, one 32-column chunk each
-template <Epi EPI> using CfgDxW = GemmCfg<128, 1, false, BSource::kTmaK, EPI, 3, 4, true, false, 16>;
+template <Epi EPI> using CfgDxW = GemmCfg<128, 1, false, BSource::kTmaK, EPI, 4, 4, true, false, 16>;
 template <int BN> using CfgDw = GemmCfg<BN, 1, true, BSource::kTmaMN, Epi::kPartialF32, 3, 3>; // act^T x dz
 template <int BN> using CfgDwG = GemmCfg<BN, 1, true, BSource::kTmaMN, Epi::kPartialF32, 3, 3, false, true>; // R stacked act^T x dz
 // Two 256-column accumulators per unit (all of TMEM) and a two-stage one-hot ring. Measured alternatives at p888: 2 x 192
@@ -680,7 +679,7 @@ mgt_status_t GemmGradWeights(mgt_engine* e, cudaStream_t st, const __half* act, 
 
 // The residual tower in one launch per direction; see tower_chain.cuh. Shapes it takes: hd2 a multiple of 32 up to 256.
 bool ChainEligible(const mgt_engine* e, const mgt_mlp_shape_t& s) {
-    return s.residual_blocks > 0 && s.hd2 % 32U == 0 && s.hd2 >= 32U && s.hd2 <= 256U && (e->debug_skip & 4U) == 0U;
+    return s.residual_blocks > 0 && s.hd2 % 32U == 0 && s.hd2 >= 32U && s.hd2 <= 256U && !e->layered_tower;
 }
 
 template <bool BWD>
@@ -701,7 +700,6 @@ mgt_status_t LaunchChain(mgt_engine* e, cudaStream_t st, const __half* w_first, 
     MGT_MAP(e->Map3D(&ts, a.tape_s, a.H, a.samples, tape_s_entries, a.ld_s, a.tape_s_stride * 2, 64, 128));
     MGT_MAP(e->Map3D(&tt, a.tape_t, a.H, a.samples, tape_t_entries, a.ld_t, a.tape_t_stride * 2, 64, 128));
     a.status = e->status_word;
-    a.debug = e->debug_skip;
     const uint32_t grid = a.tiles < (uint32_t)e->sm_count ? a.tiles : (uint32_t)e->sm_count;
     tower_chain_kernel<BWD><<<grid, ChainCfg::THREADS, ChainCfg::SMEM_BYTES, st>>>(tw, ts, tt, a);
     ++e->launches;
@@ -873,7 +871,7 @@ mgt_status_t mgt_engine_create(int32_t device_id, mgt_engine_t** out_engine) {
         return MGT_CUDA_FAILURE;
     }
     e->encode = reinterpret_cast<EncodeTiledFn>(fn);
-    if (const char* dbg = std::getenv("MGT_DEBUG_SKIP")) e->debug_skip = static_cast<uint32_t>(std::atoi(dbg));
+    if (const char* path = std::getenv("MGT_RESIDUAL_PATH")) e->layered_tower = std::strcmp(path, "layered") == 0;
     if (cudaMalloc(&e->status_word, sizeof(int)) != cudaSuccess || cudaMemset(e->status_word, 0, sizeof(int)) != cudaSuccess) {
         delete e;
         return MGT_CUDA_FAILURE;

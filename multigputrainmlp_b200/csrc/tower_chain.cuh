@@ -44,7 +44,6 @@ struct ChainArgs {
     float* colsum;             // backward: slot j at colsum + j * colsum_stride, [tiles*4][H] partial column sums
     uint64_t colsum_stride;
     int* status;
-    uint32_t debug;            // timing experiments only: 8 = no global stores, 16 = no bias/mask, 32 = weights loaded once
 };
 
 struct ChainCfg {
@@ -164,7 +163,6 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
                     const int32_t z = static_cast<int32_t>(BWD ? (2U * (R - 1U - (l >> 1)) + ((l & 1U) ^ 1U)) : l);
                     for (uint32_t c = 0; c < KC; ++c, ++it) {
                         const uint32_t s = it % SW, ph = (it / SW) & 1U;
-                        if ((args.debug & 32U) && it >= SW) continue;
                         if (!mbar_wait(&w_empty[s], ph ^ 1U, cta_abort, kAbortChainWait)) { ok = false; break; }
                         uint8_t* dst = w_ring + s * ChainCfg::W_STAGE_BYTES;
                         mbar_arrive_expect_tx(&w_full[s], stage_bytes);
@@ -196,7 +194,7 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
                         for (uint32_t c = 0; c < KC; ++c, ++it) {
                             const uint32_t s = it % SW, ph = (it / SW) & 1U;
                             if (!mbar_wait(&ready[c], uses & 1U, cta_abort, kAbortChainWait)) { ok = false; break; }
-                            if (!((args.debug & 32U) && it >= SW) && !mbar_wait(&w_full[s], ph, cta_abort, kAbortChainWait)) { ok = false; break; }
+                            if (!mbar_wait(&w_full[s], ph, cta_abort, kAbortChainWait)) { ok = false; break; }
                             tc_fence_after();
                             const uint32_t a_addr = a_base + c * 16384U;
                             const uint32_t b_addr = smem_u32(w_ring + s * ChainCfg::W_STAGE_BYTES);
@@ -206,9 +204,9 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
                                 const uint64_t a_desc = make_smem_desc(a_addr + kk * 32U, 16U, 1024U);
                                 const uint64_t b_desc = BWD ? make_smem_desc(b_addr + kk * 32U, 16U, 1024U) : make_smem_desc(b_addr + kk * 2048U, 8192U, 1024U);
                                 // the second product of a block adds onto the state that already sits in TMEM
-                                if (!(args.debug & 64U)) umma_f16(d_addr, a_desc, b_desc, idesc, (half != 0U || c > 0U || kk > 0U) ? 1U : 0U);
+                                umma_f16(d_addr, a_desc, b_desc, idesc, (half != 0U || c > 0U || kk > 0U) ? 1U : 0U);
                             }
-                            if (!(args.debug & 32U)) umma_commit(&w_empty[s]);
+                            umma_commit(&w_empty[s]);
                         }
                         // the epilogue this commit releases overwrites the operand the PREVIOUS phase read and stored
                         bulk_wait_read_all();
@@ -216,7 +214,7 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
                         // Each operand panel is also a 64-column slice of a tape entry: T of this block, or the S the previous
                         // block produced (the S a tile starts with is on its tape already). Issued here, after the commit,
                         // the stores cost the MMA stream nothing.
-                        if (ok && (half != 0U || kb > 0U) && !(args.debug & 8U)) {
+                        if (ok && (half != 0U || kb > 0U)) {
                             const uint32_t k = BWD ? R - 1U - kb : kb;
                             const uint32_t entry = half ? k : (BWD ? k + 1U : k);
                             for (uint32_t c = 0; c < KC; ++c)
@@ -270,7 +268,7 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         // identical values; a slot is rewritten only after the MMAs that needed every warp's previous epilogue.
         float bias_reg[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         auto fetch_bias = [&](uint32_t layer) {
-            if (!BWD && !(args.debug & 16U)) {
+            if (!BWD) {
 #pragma unroll
                 for (uint32_t ci = 0; ci < WPW; ++ci) {
                     const uint32_t cc = par + SUBS * ci;
@@ -319,7 +317,6 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         for (uint32_t tile = blockIdx.x; tile < args.tiles && ok; tile += gridDim.x) {
             const uint64_t row = static_cast<uint64_t>(tile) * 128U + r;
             const bool row_ok = row < args.samples;
-            const bool st_ok = row_ok && !(args.debug & 8U);
             const uint64_t bits_row = row * 8U + par * WPW;  // this warp's words of the row
 
             // ---- load the state: TMEM S, fp16 operand, (forward) sign bits of x_0
@@ -376,14 +373,13 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
                         float v[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
-                        if (args.debug & 16U) {
-                        } else if (BWD) apply_mask(v, mwords[ci]);
+                        if (BWD) apply_mask(v, mwords[ci]);
                         else add_bias_relu(v, ci);
                         uint32_t h[16];
                         words[ci] = detail::pack_halfs(v, h);
                         store_operand(act_t, cc, h);
                         publish(&ready_t[cc >> 1]);
-                        if (BWD && !(args.debug & 8U)) {
+                        if (BWD) {
                             const float total = detail::warp_column_sums(v, lane);
                             args.colsum[k * args.colsum_stride + (static_cast<uint64_t>(tile) * 4U + quad) * H + cc * 32U + lane] = total;
                         }
@@ -411,8 +407,7 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
                         float v[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
-                        if (args.debug & 16U) {
-                        } else if (BWD) apply_mask(v, mwords[ci]);
+                        if (BWD) apply_mask(v, mwords[ci]);
                         else add_bias_relu(v, ci);
                         uint32_t h[16];
                         words[ci] = detail::pack_halfs(v, h);
@@ -424,7 +419,7 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
                             tmem_st_wait();
                             publish(&ready_s[cc >> 1]);
                         }
-                        if (st_ok && last) {  // no MMA consumes the last S of a tile, so no panel store either
+                        if (row_ok && last) {  // no MMA consumes the last S of a tile, so no panel store either
                             store_tape(tape_row, cc, h);
                             if (!BWD) {
                                 float4* dst = reinterpret_cast<float4*>(args.state_f32 + row * args.ld_f32 + cc * 32U);
@@ -432,7 +427,7 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
                                 for (int q = 0; q < 8; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
                             }
                         }
-                        if (BWD && !(args.debug & 8U)) {
+                        if (BWD) {
                             const float total = detail::warp_column_sums(v, lane);
                             args.colsum[(R + k) * args.colsum_stride + (static_cast<uint64_t>(tile) * 4U + quad) * H + cc * 32U + lane] = total;
                         }

@@ -62,7 +62,6 @@ struct GemmArgs {
     uint32_t samples;
     uint32_t in_rows;        // state_len * value_pad; row `in_rows` is the all-ones (bias) row
     int* status;             // device status word, 0 = ok
-    uint32_t debug_skip;     // diagnostics only: bit 0 = synth writes nothing, bit 1 = embedding epilogue stores nothing
 };
 
 // BSTAT_: "B-stationary" - for short reductions (K <= 64*SB_) the whole B operand of the CTA's N tile is loaded
@@ -217,7 +216,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + ACC_BUFS);
     volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_holder + 1);
     float* epi_stage = reinterpret_cast<float*>(b_ring + SB * Cfg::B_STAGE_BYTES + 256);
-    uint8_t* epi_stage_dummy = b_ring + SB * Cfg::B_STAGE_BYTES + 240;  // 16 spare bytes after the barriers
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31U;
@@ -389,7 +387,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 if (!__all_sync(0xFFFFFFFFU, mbar_wait(&acc_full[ab], aph, cta_abort, kAbortEpilogueWait))) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t m = mt * BM + quad * 32U + lane;
-                const bool m_ok = m < args.M && !(args.debug_skip & 2U);
+                const bool m_ok = m < args.M;
 #pragma unroll 1
                 for (int acc = 0; acc < NACC; ++acc) {
 #pragma unroll 1
@@ -636,7 +634,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             const uint32_t V = args.value_pad, L = args.state_len, IN = args.in_rows;
             constexpr uint32_t ROWS = NACC * BN;  // rows of the synthesised operand per stage
             auto place = [&](uint8_t* buf, uint32_t n, uint32_t k) -> uint16_t* {
-                if (args.debug_skip & 1U) return reinterpret_cast<uint16_t*>(epi_stage_dummy);
                 uint8_t* row = buf + (n / BN) * Cfg::B_ACC_BYTES + (n % BN) * 128U;
                 return reinterpret_cast<uint16_t*>(row + ((((k >> 3) ^ (n & 7U)) << 4) | ((k & 7U) << 1)));
             };
@@ -751,7 +748,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                         prepare(nt, 0);
                     }
                     uint32_t it = 0;
-                    const bool dry = (args.debug_skip & 1U) != 0U;
                     while (have) {
                         uint32_t unit2 = unit, nt2 = nt, c2 = c + 1U;
                         bool have2 = true;
@@ -771,14 +767,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll
                             for (uint32_t j = 0; j < 3U; ++j) {
                                 const uint32_t old = hist[0][i][j];
-                                if (old != kNone && !dry) *reinterpret_cast<uint16_t*>(buf + old) = 0;
+                                if (old != kNone) *reinterpret_cast<uint16_t*>(buf + old) = 0;
                             }
 #pragma unroll
                         for (uint32_t i = 0; i < RPT; ++i)
 #pragma unroll
                             for (uint32_t j = 0; j < 3U; ++j) {
                                 const uint32_t off = next[i][j];
-                                if (off != kNone && !dry) *reinterpret_cast<uint16_t*>(buf + off) = 0x3C00;
+                                if (off != kNone) *reinterpret_cast<uint16_t*>(buf + off) = 0x3C00;
 #pragma unroll
                                 for (int q = 0; q + 1 < SB; ++q) hist[q][i][j] = hist[q + 1][i][j];
                                 hist[SB - 1][i][j] = off;
@@ -843,7 +839,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll
                         for (uint32_t j = 0; j < 4U; ++j) {
                             const uint32_t off = hist[0][j];
-                            if (off != kNone && !(args.debug_skip & 1U)) *reinterpret_cast<uint16_t*>(buf + off) = 0;
+                            if (off != kNone) *reinterpret_cast<uint16_t*>(buf + off) = 0;
                         }
                         __syncwarp();  // a place cleared by one lane may be set by another lane of this warp
                         const uint32_t r0 = nt * ROWS, p_lo = r0 / V;
@@ -857,7 +853,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                         offs[3] = (q == 0U && nb < ROWS && c * 64U + k < args.samples) ? offset_of(nb) : kNone;
 #pragma unroll
                         for (uint32_t j = 0; j < 4U; ++j) {
-                            if (offs[j] != kNone && !(args.debug_skip & 1U)) *reinterpret_cast<uint16_t*>(buf + offs[j]) = 0x3C00;
+                            if (offs[j] != kNone) *reinterpret_cast<uint16_t*>(buf + offs[j]) = 0x3C00;
 #pragma unroll
                             for (int q2 = 0; q2 + 1 < SB; ++q2) hist[q2][j] = hist[q2 + 1][j];
                             hist[SB - 1][j] = offs[j];

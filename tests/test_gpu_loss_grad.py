@@ -139,7 +139,7 @@ def test_residual_tower_layered_matches_fused(oracle, engine, monkeypatch):
     # the per-layer GEMM path (taken for other widths) on a width both paths accept
     shape, w, states, labels = _walk_case(oracle, (72, 72, 64, 64, 3, 1), 500, seed=5)
     loss_f, grad_f = run_engine(engine, shape, w, states, labels)
-    monkeypatch.setenv("MGT_DEBUG_SKIP", "4")
+    monkeypatch.setenv("MGT_RESIDUAL_PATH", "layered")
     layered = mgt.Engine(0)
     try:
         check_against_oracle(oracle, layered, shape, w, states, labels)
