@@ -40,8 +40,8 @@ FLOP_PER_CANDIDATE = 13_444_416          # 3*(2*H1*H2 + 4R*H2^2 + 2*H2*OUT) + 2*
 EMB_ALGO_FLOP_PER_CANDIDATE = 72 * 2560   # the embedding forward counted as the sparse work it is (72 row adds)
 EMB_EXEC_FLOP_PER_CANDIDATE = 2 * (72 * 72 + 1) * 2560  # what the one-hot GEMM executes on the tensor cores
 # dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch of the one-hot forward kernel (single-pass ncu
-# capture, profiles/training_step_p888_launch_list.md): 31.4 MB read + 218.9 MB written
-EMB_FWD_DRAM_BYTES_PER_LAUNCH = 250_300_000
+# capture, profiles/training_step_p888_launch_list.md): 31.1 MB read + 218.7 MB written
+EMB_FWD_DRAM_BYTES_PER_LAUNCH = 249_800_000
 
 
 def workload_config(n_gpus: int) -> dict:
