@@ -229,6 +229,14 @@ mgt_status_t mgt_write_run_artifacts(int32_t argc, const char* const* argv, cons
 /* checkpoint/state.f32.bin = weights | adam_m | adam_v (tool:392-404) */
 mgt_status_t mgt_read_checkpoint(const char* checkpoint_dir, uint64_t param_count, float* weights, float* adam_m, float* adam_v);
 
+/* Replaces LoadPuzzleDefinition (native/include/mgt/puzzle_io.hpp, native/src/puzzle_io.cpp:48-97): the integers of the
+ * JSON text are group id, state length, move count and move_count permutations; the target file holds exactly
+ * state_len bytes. `moves` receives MGT_MOVE_COUNT records (unused ones are the identity), pad positions of a move map
+ * to themselves, pad bytes of the target are 0. The reference fixes group 888 / 72 / 18; here they are arguments.
+ * Returns MGT_OK, MGT_INVALID_PUZZLE or MGT_IO_FAILURE. Host only. */
+mgt_status_t mgt_load_puzzle_definition(const char* group_json, const char* target_bin, uint32_t group_id, uint32_t state_len,
+                                        uint32_t move_count, mgt_train_state_t* moves, mgt_train_state_t* target);
+
 /* ---- diagnostics ---------------------------------------------------------------------------
  * One plain GEMM through the tcgen05 kernel, used by the parity tests to pin each operand form.
  * D[M x N] fp32 = A * B with fp16 operands; a_mn_major: A stored [K][M] (else [M][K]);

@@ -17,6 +17,7 @@ from .api import (  # noqa: F401
     launch_adamw_kernel_with_half_mirror,
     launch_float_to_half,
     launch_random_walk_kernel,
+    load_puzzle_definition,
     mlp_loss_grad_workspace_floats,
     status_name,
     validate_adamw_kernel_config,

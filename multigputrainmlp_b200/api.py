@@ -119,6 +119,18 @@ def launch_random_walk_kernel(config, base_seed, epoch, step, global_rank, devic
                                                   _ptr(device_labels), _ptr(device_meta), _stream(stream)))
 
 
+def load_puzzle_definition(group_json: str, target_bin: str, group_id: int = 888, state_len: int = 72, move_count: int = 18):
+    """LoadPuzzleDefinition (native/src/puzzle_io.cpp:48-97): returns (status, moves[18][80] uint8, target[80] uint8)."""
+    import numpy as np
+    moves = np.zeros((18, 80), np.uint8)
+    target = np.zeros(80, np.uint8)
+    lib = _lib.load()
+    lib.mgt_load_puzzle_definition.argtypes = [C.c_char_p, C.c_char_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]
+    st = int(lib.mgt_load_puzzle_definition(str(group_json).encode(), str(target_bin).encode(), group_id, state_len, move_count,
+                                            moves.ctypes.data_as(C.c_void_p), target.ctypes.data_as(C.c_void_p)))
+    return st, moves, target
+
+
 def validate_cuda_mlp_shape(shape: CudaMlpShape) -> int:
     s = shape.c()
     return int(_lib.load().mgt_validate_mlp_shape(C.byref(s)))

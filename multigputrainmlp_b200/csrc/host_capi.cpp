@@ -53,6 +53,13 @@ mgt_status_t mgt_plan_write_files(int32_t argc, const char* const* argv, const c
 
 uint16_t mgt_export_float_to_fp16(float value) { return ExportFloatToFp16(value); }
 
+mgt_status_t mgt_load_puzzle_definition(const char* group_json, const char* target_bin, uint32_t group_id, uint32_t state_len, uint32_t move_count,
+                                        mgt_train_state_t* moves, mgt_train_state_t* target) {
+    if (group_json == nullptr || target_bin == nullptr || moves == nullptr || target == nullptr) return MGT_INVALID_PUZZLE;
+    return static_cast<mgt_status_t>(LoadPuzzleFiles(group_json, target_bin, group_id, state_len, move_count, reinterpret_cast<uint8_t*>(moves),
+                                                     reinterpret_cast<uint8_t*>(target)));
+}
+
 mgt_status_t mgt_write_run_artifacts(int32_t argc, const char* const* argv, const char* dir, const float* weights, const float* adam_m, const float* adam_v) {
     TrainPlan p;
     if (dir == nullptr || weights == nullptr || adam_m == nullptr || adam_v == nullptr || !PlanFromArgs(argc, argv, &p)) return MGT_INVALID_CONFIG;

@@ -28,6 +28,7 @@ struct TrainOptions {
     std::string nccl_id_file, resume_checkpoint;
     // beyond the reference's flag set (both default to its behaviour): write the checkpoint every N steps, and let a
     // resumed run continue the step count the checkpoint was written at instead of restarting it at 0
+    std::string puzzle_json, target_bin;  // a puzzle definition from files instead of the built-in cyclic shifts
     uint32_t checkpoint_period_steps = 0;
     bool resume_step = false;
 };
@@ -112,6 +113,11 @@ std::string StepProfileRow(const TrainPlan& plan, const StepRecord& r, bool over
 
 // Built-in puzzle of the trainer: cyclic shifts, identity target (tool:117-140). 18 move records + 1 target record of 80 bytes.
 void BuildCyclicPuzzle(const TrainPlan& plan, uint8_t* moves_18x80, uint8_t* target_80);
+// A puzzle definition from files (the format of the reference's LoadPuzzleDefinition, native/src/puzzle_io.cpp:48-97):
+// the integers of the JSON text in order are group id, state length, move count, then move_count permutations of
+// 0..state_len-1; the target is exactly state_len raw bytes. Returns 0 ok, 2 invalid_puzzle, 6 io_failure.
+int LoadPuzzleFiles(const std::string& group_json, const std::string& target_bin, uint32_t group_id, uint32_t state_len, uint32_t move_count,
+                    uint8_t* moves_18x80, uint8_t* target_80);
 // Deterministic initial weights (tool:648-650).
 void InitialWeights(std::vector<float>* weights);
 

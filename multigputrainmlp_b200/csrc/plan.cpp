@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <fstream>
 #include <functional>
 #include <map>
 
@@ -84,6 +85,7 @@ bool ParseTrainOptions(int argc, const char* const* argv, TrainOptions* o) {
         {"--overlap-allreduce", flag(&o->overlap_allreduce)}, {"--nccl-id-file", text(&o->nccl_id_file)},
         {"--resume-checkpoint", text(&o->resume_checkpoint)},
         {"--checkpoint-period-steps", u32(&o->checkpoint_period_steps)}, {"--resume-step", flag(&o->resume_step)},
+        {"--puzzle-json", text(&o->puzzle_json)}, {"--target-bin", text(&o->target_bin)},
     };
     for (int i = 1; i < argc; i += 2) {
         if (i + 1 >= argc) return false;
@@ -246,6 +248,65 @@ void BuildCyclicPuzzle(const TrainPlan& plan, uint8_t* moves, uint8_t* target) {
     for (uint32_t mv = 0; mv < 18; ++mv)
         for (uint32_t i = 0; i < L && i < 80; ++i) moves[mv * 80 + i] = static_cast<uint8_t>(mv < mc ? (i + mv + 1) % L : i);
     for (uint32_t i = 0; i < L && i < 80; ++i) target[i] = static_cast<uint8_t>(i);
+}
+
+int LoadPuzzleFiles(const std::string& group_json, const std::string& target_bin, uint32_t group_id, uint32_t state_len, uint32_t move_count,
+                    uint8_t* moves, uint8_t* target) {
+    if (moves == nullptr || target == nullptr || state_len == 0 || state_len > 72 || move_count == 0 || move_count > 18) return 2;
+    std::ifstream json(group_json, std::ios::binary);
+    if (!json) return 6;
+    // every run of digits (with an optional leading minus) is a value; names and punctuation are skipped
+    std::vector<long long> values;
+    {
+        long long value = 0;
+        bool in_number = false, negative = false;
+        char ch = 0, prev = 0;
+        auto flush = [&]() {
+            if (in_number) values.push_back(negative ? -value : value);
+            in_number = false;
+            negative = false;
+            value = 0;
+        };
+        while (json.get(ch)) {
+            if (ch >= '0' && ch <= '9') {
+                if (!in_number) negative = prev == '-';
+                in_number = true;
+                if (value < (1LL << 40)) value = value * 10 + (ch - '0');
+            } else {
+                flush();
+            }
+            prev = ch;
+        }
+        flush();
+    }
+    const size_t required = 3 + static_cast<size_t>(move_count) * state_len;
+    if (values.size() < required) return 2;
+    if (values[0] != static_cast<long long>(group_id) || values[1] != static_cast<long long>(state_len) || values[2] != static_cast<long long>(move_count)) return 2;
+    std::memset(moves, 0, 18 * 80);
+    size_t pos = 3;
+    for (uint32_t mv = 0; mv < 18; ++mv) {
+        uint8_t* rec = moves + mv * 80;
+        if (mv < move_count) {
+            bool seen[80] = {};
+            for (uint32_t i = 0; i < state_len; ++i) {
+                const long long v = values[pos++];
+                if (v < 0 || v >= static_cast<long long>(state_len) || seen[v]) return 2;  // not a permutation
+                seen[v] = true;
+                rec[i] = static_cast<uint8_t>(v);
+            }
+            for (uint32_t i = state_len; i < 80; ++i) rec[i] = static_cast<uint8_t>(i);  // pad positions stay where they are
+        } else {
+            for (uint32_t i = 0; i < 80; ++i) rec[i] = static_cast<uint8_t>(i);
+        }
+    }
+    std::ifstream bin(target_bin, std::ios::binary);
+    if (!bin) return 6;
+    std::memset(target, 0, 80);
+    bin.read(reinterpret_cast<char*>(target), state_len);
+    if (bin.gcount() != static_cast<std::streamsize>(state_len)) return 2;
+    char extra = 0;
+    if (bin.read(&extra, 1)) return 2;  // longer than one state
+    return 0;
 }
 
 void InitialWeights(std::vector<float>* w) {

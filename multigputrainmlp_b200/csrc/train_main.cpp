@@ -89,7 +89,7 @@ const char kUsage[] =
     "[--batch-size N --k-min N --k-max N --hd1 N --hd2 N --nrd N --write-artifacts 0|1 --backward-profile 0|1 --overlap-allreduce 0|1 "
     "--input-grad-partial-chunks N --input-grad-positions-per-block N --input-grad-position-tile N --input-grad-fp16 0|1 --linear-fp16 0|1 "
     "--persistent-half-weights 0|1 --lt-workspace-bytes N --nccl-id-file PATH --resume-checkpoint DIR "
-    "--checkpoint-period-steps N --resume-step 0|1]\n";
+    "--checkpoint-period-steps N --resume-step 0|1 --puzzle-json PATH --target-bin PATH]\n";
 
 }  // namespace
 
@@ -131,7 +131,19 @@ int main(int argc, char** argv) {
         }
     }
     uint8_t moves[18 * 80], target[80];
-    BuildCyclicPuzzle(plan, moves, target);
+    if (opt.puzzle_json.empty() != opt.target_bin.empty()) {
+        std::cerr << "--puzzle-json and --target-bin go together\n";
+        return EXIT_FAILURE;
+    }
+    if (opt.puzzle_json.empty()) {
+        BuildCyclicPuzzle(plan, moves, target);  // the reference trainer's only puzzle (tool:117-140)
+    } else {
+        const int st = LoadPuzzleFiles(opt.puzzle_json, opt.target_bin, opt.group_id, opt.state_len, opt.move_count, moves, target);
+        if (st != 0) {
+            std::cerr << "puzzle definition: " << mgt_status_name(static_cast<mgt_status_t>(st)) << "\n";
+            return EXIT_FAILURE;
+        }
+    }
 
     mgt_engine_t* engine = nullptr;
     if (mgt_engine_create(static_cast<int32_t>(opt.device_id), &engine) != MGT_OK) return EXIT_FAILURE;

@@ -149,6 +149,13 @@ class Reference:
                                        _p(states), _p(labels), _p(meta))
         return st, states, labels, meta
 
+    def load_puzzle(self, group_json, target_bin):
+        """LoadPuzzleDefinition of the reference: (status, moves[18][80], target[80])."""
+        moves = np.zeros((MAX_MOVES, STATE_STORAGE_LEN), np.uint8)
+        target = np.zeros(STATE_STORAGE_LEN, np.uint8)
+        st = int(self.lib.ref_load_puzzle(str(group_json).encode(), str(target_bin).encode(), _p(moves), _p(target)))
+        return st, moves, target
+
     def param_count(self, shape):
         return int(self.lib.ref_param_count(shape.as_array()))
 

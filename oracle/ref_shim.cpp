@@ -3,6 +3,7 @@
 // oracle/_ref/libmgt_ref.so; used to validate the restatement in oracle.cpp, to generate the
 // golden vectors under tests/golden/ and as the timed CPU baseline. The reference sources are
 // compiled where they lie; nothing of them is copied into this repository.
+#include "mgt/puzzle_io.hpp"
 #include "mgt/allreduce.hpp"
 #include "mgt/mlp_cpu_ref.hpp"
 #include "mgt/random_walk.hpp"
@@ -110,6 +111,17 @@ int ref_plan_linear_op(unsigned state_len, unsigned value_count, unsigned hd1, u
     out[11] = op.logical_tail_masked ? 1U : 0U;
     out[12] = op.lhs_rows;
     out[13] = op.rhs_cols;
+    return 0;
+}
+
+// LoadPuzzleDefinition (native/src/puzzle_io.cpp:48-97): 18 move records and the target, 80 bytes each.
+int ref_load_puzzle(const char* group_json, const char* target_bin, unsigned char* moves, unsigned char* target) {
+    mgt::PuzzleDefinition puzzle{};
+    const mgt::Status st = mgt::LoadPuzzleDefinition(group_json, target_bin, &puzzle);
+    if (st != mgt::Status::kOk) return static_cast<int>(st);
+    for (unsigned mv = 0; mv < mgt::kMoveCount; ++mv)
+        for (unsigned i = 0; i < mgt::kStateStorageLen; ++i) moves[mv * mgt::kStateStorageLen + i] = puzzle.moves[mv].v[i];
+    for (unsigned i = 0; i < mgt::kStateStorageLen; ++i) target[i] = puzzle.target.v[i];
     return 0;
 }
 

@@ -29,10 +29,10 @@ def run(out_dir, *flags, check=True):
     return res
 
 
-def oracle_training(oracle, *, hd1, hd2, nrd, out, batch, steps, k_min, k_max, seed=1234, lr=1e-4, wd=0.0, world=1, start=None):
+def oracle_training(oracle, *, hd1, hd2, nrd, out, batch, steps, k_min, k_max, seed=1234, lr=1e-4, wd=0.0, world=1, start=None, puzzle=None):
     """The reference trainer's loop on the CPU oracle (fp16 data flow), `world` ranks averaged in rank order."""
     shape = MlpShape(72, 72, hd1, hd2, nrd, out)
-    moves, target = oracle.cyclic_puzzle(72, 18)
+    moves, target = oracle.cyclic_puzzle(72, 18) if puzzle is None else puzzle
     w = trainer_init_weights(shape.param_count) if start is None else start[0].copy()
     m = np.zeros_like(w) if start is None else start[1].copy()
     v = np.zeros_like(w) if start is None else start[2].copy()
@@ -193,3 +193,36 @@ def test_resume_step_continues_the_run_bit_for_bit(tmp_path):
     assert [r["step"] for r in read_profile(tmp_path / "restart" / "profile.jsonl")] == [0, 1]
     res = run(tmp_path / "bad", "--steps", 1, "--resume-checkpoint", tmp_path / "nowhere", "--resume-step", 1, *common, check=False)
     assert res.returncode != 0
+
+
+def test_puzzle_from_files_drives_the_walks(tmp_path, oracle):
+    # --puzzle-json / --target-bin (beyond the reference trainer, which only knows its built-in cyclic shifts): a random
+    # generator set in the reference loader's file format; the run must follow the oracle trained on those moves
+    import multigputrainmlp_b200 as mgt
+    rng = np.random.default_rng(21)
+    perms = [rng.permutation(72) for _ in range(18)]
+    jp = tmp_path / "puzzle.json"
+    jp.write_text(json.dumps({"group_id": 888, "state_len": 72, "move_count": 18, "moves": [[int(v) for v in p] for p in perms]}))
+    tp = tmp_path / "target.bin"
+    tp.write_bytes(bytes(range(72)))
+    st, moves, target = mgt.load_puzzle_definition(jp, tp)
+    assert st == 0
+    cfg = dict(hd1=64, hd2=32, nrd=2, out=1, batch=512, steps=3, k_min=1, k_max=29, lr=1e-3)
+    run(tmp_path / "run", "--steps", 3, "--batch-size", 512, "--k-min", 1, "--k-max", 29, "--hd1", 64, "--hd2", 32, "--nrd", 2, "--lr", 0.001,
+        "--puzzle-json", jp, "--target-bin", tp)
+    w, m, v, losses = oracle_training(oracle, puzzle=(moves, target), **cfg)
+    got = [r["loss"] for r in read_profile(tmp_path / "run" / "profile.jsonl")]
+    for a, b in zip(got, losses):
+        assert abs(a - b[0]) <= 1e-3 * abs(b[0])
+    state = np.fromfile(tmp_path / "run" / "checkpoint" / "state.f32.bin", dtype=np.float32)
+    p = w.size
+    # the first moment is linear in the gradients; the weights themselves are looser here: random generators visit every
+    # table row with a few samples, and where such a tiny gradient component changes sign Adam moves the weight the other way
+    assert rel_l2(state[p:2 * p], m) <= 2e-3
+    assert rel_l2(state[:p], w) <= 5e-2
+    # and it is a different run from the built-in puzzle
+    run(tmp_path / "builtin", "--steps", 3, "--batch-size", 512, "--k-min", 1, "--k-max", 29, "--hd1", 64, "--hd2", 32, "--nrd", 2, "--lr", 0.001)
+    builtin = np.fromfile(tmp_path / "builtin" / "checkpoint" / "state.f32.bin", dtype=np.float32)
+    table = 72 * 72 * 64  # depths, hence step-0 losses, do not depend on the moves; which table rows get gradients does
+    assert rel_l2(builtin[p:p + table], m[:table]) > 0.5
+    assert run(tmp_path / "bad", "--steps", 1, "--puzzle-json", jp, check=False).returncode != 0
