@@ -393,6 +393,22 @@ def main():
         "note": "achieved counts the 72 row-adds per candidate the layer needs; executed counts the dense one-hot MMA work",
     }
 
+    # the other single-kernel stages, same live timer: algorithmic work of the stage / its time, against the measured peaks
+    grad_t = float(np.median(grad_ms))
+    tower_fwd_bytes = batch * (224 * 4 + 16 * 2 * 224 * 2 + 17 * 32 + 224 * 4)   # state in, 32 fp16 tape entries, sign bits, state out
+    hidden_fwd_bytes = batch * (2560 * 2 + 224 * 4 + 224 * 2) + 2560 * 224 * 2    # a1 in, x fp32 + fp16 out, weights
+    roofline_other = [
+        {"kernel": "umma_gemm_kernel<one-hot gradient> (embedding table gradient)", "bound": "tensor", "ms_per_launch": grad_t,
+         "achieved": EMB_ALGO_FLOP_PER_CANDIDATE * batch / (grad_t * 1e-3) / 1e12, "executed_tflops": 2 * 72 * 72 * 2560 * batch / (grad_t * 1e-3) / 1e12,
+         "peak": peaks["tflops_burst"], "unit": "TFLOP/s", "executed_frac": 2 * 72 * 72 * 2560 * batch / (grad_t * 1e-3) / 1e12 / peaks["tflops_burst"]},
+        {"kernel": "tower_chain_kernel<forward> (16 residual blocks)", "bound": "hbm", "ms_per_launch": stage_ms["residual_forward_ms"],
+         "achieved": tower_fwd_bytes / (stage_ms["residual_forward_ms"] * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+         "frac": tower_fwd_bytes / (stage_ms["residual_forward_ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"]},
+        {"kernel": "umma_gemm_kernel (hidden layer forward)", "bound": "hbm", "ms_per_launch": stage_ms["hidden_forward_ms"],
+         "achieved": hidden_fwd_bytes / (stage_ms["hidden_forward_ms"] * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+         "frac": hidden_fwd_bytes / (stage_ms["hidden_forward_ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"]},
+    ]
+
     if rank != 0:
         if world > 1:
             import torch.distributed as dist
@@ -406,7 +422,7 @@ def main():
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic", "config": workload_config(world), "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(puzzle_pinned.numel()), "d2h_bytes_per_step": 4},
-        "gpu_launches": int(launches), "roofline": roofline, "comm": (args.comm if world > 1 else "none"),
+        "gpu_launches": int(launches), "roofline": roofline, "roofline_other": roofline_other if batch == BATCH else None, "comm": (args.comm if world > 1 else "none"),
         "step_tflops_algorithmic": FLOP_PER_CANDIDATE * value / world / 1e12,
         "step_frac_of_fp16_peak": FLOP_PER_CANDIDATE * value / world / 1e12 / peaks["tflops_sustained"],
         "stage_ms": stage_ms, "final_loss": final_loss,

@@ -172,3 +172,48 @@ def test_weights_and_checkpoint_files(tmp_path):
     assert np.array_equal(w2, w) and np.array_equal(m2, m) and np.array_equal(v2, v)
     assert lib.mgt_read_checkpoint(str(tmp_path / "nope").encode(), params, p(w2), p(m2), p(v2)) == 6
     assert lib.mgt_read_checkpoint(str(cd).encode(), params + 1, p(np.zeros(params + 1, np.float32)), p(np.zeros(params + 1, np.float32)), p(np.zeros(params + 1, np.float32))) == 6
+
+
+def test_exported_weight_files_rebuild_the_model(tmp_path, oracle):
+    # What the downstream consumer does with weights/ (tool:241-348): every tensor is a row-major [inputs][outputs] fp16
+    # file named in a fixed order, "row-major input activations times weight_hxk". Rebuilding the flat parameter vector
+    # from the files alone and running the forward pass must reproduce the fp32 model up to the fp16 rounding.
+    from oracle import MlpShape
+    lib = _lib.load()
+    hd1, hd2, nrd, out = 16, 8, 2, 3
+    n, arr = _argv({"--hd1": hd1, "--hd2": hd2, "--nrd": nrd, "--output-dim": out})
+    shape = MlpShape(72, 72, hd1, hd2, nrd, out)
+    rng = np.random.default_rng(12)
+    w = (rng.standard_normal(shape.param_count) * 0.05).astype(np.float32)
+    zeros = np.zeros_like(w)
+    p = lambda a: a.ctypes.data_as(C.c_void_p)
+    lib.mgt_write_run_artifacts.argtypes = [C.c_int32, C.c_void_p, C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    assert lib.mgt_write_run_artifacts(n, arr, str(tmp_path).encode(), p(w), p(zeros), p(zeros)) == 0
+    man = json.load(open(tmp_path / "weights" / "manifest.json"))
+    assert (man["hd1"], man["hd2"], man["nrd"], man["output_dim"], man["dtype"]) == (hd1, hd2, nrd, out, "fp16")
+    names = ["input_weight_hxk", "input_bias", "hidden_weight_hxk", "hidden_bias"]
+    for k in range(man["nrd"]):
+        names += [f"residual{k}_fc1_weight_hxk", f"residual{k}_fc1_bias", f"residual{k}_fc2_weight_hxk", f"residual{k}_fc2_bias"]
+    names += ["output_weight_hxk", "output_bias"]
+    bits = np.concatenate([np.fromfile(tmp_path / "weights" / f"{name}.fp16", np.uint16) for name in names])
+    assert bits.size == shape.param_count
+    # the files hold exactly the trainer's software conversion of every parameter, tensors in parameter order
+    lib.mgt_export_float_to_fp16.restype = C.c_uint16
+    lib.mgt_export_float_to_fp16.argtypes = [C.c_float]
+    assert np.array_equal(bits, np.array([lib.mgt_export_float_to_fp16(float(x)) for x in w], np.uint16))
+    rebuilt = bits.view(np.float16).astype(np.float32)
+    # That converter (tool:215-229) ORs the rounded mantissa into the exponent field, so a value that rounds up to a power
+    # of two with an odd half exponent comes out halved; it is reproduced literally. Everything else is fp16 rounding.
+    off = np.abs(rebuilt - w) > 2.0 ** -11 * np.abs(w) + 1e-7
+    assert off.sum() <= 1e-3 * w.size
+    ieee = w[off].astype(np.float16)
+    assert np.all((ieee.view(np.uint16) & 0x3FF) == 0) and np.all(((ieee.view(np.uint16) >> 10) & 1) == 0)  # IEEE result 2^e, carried into an even exponent
+    assert np.allclose(rebuilt[off], 0.5 * ieee.astype(np.float32))
+    states = rng.integers(0, 72, (40, 80)).astype(np.uint8)
+    states[:, 72:] = 0
+    expect = w.copy()
+    expect[off] = rebuilt[off]
+    st_a, y_files = oracle.forward(shape, rebuilt, states)
+    st_b, y_f32 = oracle.forward(shape, expect, states)
+    assert st_a == 0 and st_b == 0
+    assert np.max(np.abs(y_files - y_f32)) <= 5e-3 * max(1.0, np.max(np.abs(y_f32)))
