@@ -46,7 +46,7 @@ EMB_FWD_DRAM_BYTES_PER_LAUNCH = 249_800_000
 
 def workload_config(n_gpus: int) -> dict:
     return {
-        "workload": "p888 training step: walk gen -> fwd/loss/bwd -> grad average -> AdamW (BASELINE config %d)" % (1 if n_gpus == 1 else 2),
+        "workload": "p888 training step: walk gen -> fwd/loss/bwd -> grad average -> AdamW (headline configuration, %s)" % ("one rank" if n_gpus == 1 else "%d ranks" % n_gpus),
         "batch_per_rank": BATCH, "global_batch": BATCH * n_gpus, "hd1": 2556, "physical_hd1": 2560, "hd2": 218,
         "physical_hd2": 224, "nrd": 16, "output_dim": 1, "k_min": 1, "k_max": 29, "seed": SEED,
         "precision": "fp16 operands, fp32 accumulate, fp32 master weights", "parallelism": "dp%d" % n_gpus,
