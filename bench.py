@@ -39,9 +39,24 @@ LR = 1e-4
 FLOP_PER_CANDIDATE = 13_444_416          # 3*(2*H1*H2 + 4R*H2^2 + 2*H2*OUT) + 2*L*H1 at the physical dims
 EMB_ALGO_FLOP_PER_CANDIDATE = 72 * 2560   # the embedding forward counted as the sparse work it is (72 row adds)
 EMB_EXEC_FLOP_PER_CANDIDATE = 2 * (72 * 72 + 1) * 2560  # what the one-hot GEMM executes on the tensor cores
-# dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch of the one-hot forward kernel (single-pass ncu
-# capture, profiles/training_step_p888_launch_list.md): 31.1 MB read + 218.7 MB written
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from an ncu capture (not measured by
+# this run: the source is named in the output next to the figure)
 EMB_FWD_DRAM_BYTES_PER_LAUNCH = 249_800_000
+EMB_FWD_DRAM_SOURCE = "ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch at batch 53248 (31.1 MB read + 218.7 MB written), captured 2026-11-25"
+README_P888_FLAGS = ["--batch-size", "53248", "--k-min", "1", "--k-max", "29", "--hd1", "2556", "--hd2", "218", "--nrd", "16",
+                     "--input-grad-fp16", "1", "--input-grad-position-tile", "36", "--linear-fp16", "1", "--write-artifacts", "0",
+                     "--allreduce-bucket-bytes", "4194304"]  # the reference README's p888 command (README.md:48-64)
+
+
+def cyclic_puzzle(state_len: int = 72, move_count: int = 18):
+    """The trainer's built-in puzzle (native/tools/mgt_native_train_smoke.cu:117-140): move m maps i -> (i + m + 1) mod
+    state_len (unused moves are the identity), the target is the identity; pad bytes are zero."""
+    moves = np.zeros((18, 80), np.uint8)
+    for mv in range(18):
+        moves[mv, :state_len] = (np.arange(state_len) + mv + 1) % state_len if mv < move_count else np.arange(state_len)
+    target = np.zeros(80, np.uint8)
+    target[:state_len] = np.arange(state_len)
+    return moves, target
 
 
 def workload_config(n_gpus: int) -> dict:
@@ -206,6 +221,107 @@ def run_reference_cpu(args, steps: int, warmup: int) -> dict:
     return line
 
 
+
+# ------------------------------------------------------------------------------------------------
+def check_gradient_exchange(torch, dist, mgt, backend, dev, world, params, bucket_bytes, state):
+    """Correctness of the multi-GPU data plane, checked where the number is produced (after the timed regions):
+      avg_bit_exact       the peer exchange on the trainer's real range schedule equals the rank-order sum times 1/W
+                          bit for bit (what ncclAllReduce(sum) + ScaleKernel define, native/cuda/allreduce_nccl.cu:130-148);
+      replicas_identical  weights, fp16 mirror and both AdamW moments have the same checksums on every rank after the
+                          timed steps (identical replicas are what lets the reference skip a broadcast);
+      fused_vs_nccl_rel_l2  one fused exchange+AdamW step against NCCL allreduce + scale + AdamW kernel from the same state."""
+    from bench_collective import p888_schedule
+    w, w_half, m, v = state
+    out = {}
+
+    def checksums(t):
+        bits = t.view(torch.int32) if t.dtype == torch.float32 else t.view(torch.int16)
+        x = bits.to(torch.int64)
+        weights = (torch.arange(x.numel(), device=dev, dtype=torch.int64) % 65521) + 1
+        return [int(x.sum().item()), int((x * weights).sum().item())]
+
+    mine = torch.tensor([c for t in (w, w_half, m, v) for c in checksums(t)], device=dev, dtype=torch.int64)
+    everyone = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(everyone, mine)
+    out["replicas_identical"] = bool(all(torch.equal(everyone[0], e) for e in everyone))
+
+    grad = backend.gradient_tensor(dev)
+    gen = torch.Generator(device=dev).manual_seed(4242 + dist.get_rank())
+    pattern = torch.randn(params, device=dev, generator=gen) * 1e-3
+    ranges, launches = p888_schedule(max(1, bucket_bytes // 4))
+    grad.copy_(pattern)
+    torch.cuda.synchronize()
+    dist.barrier()
+    for off, cnt in launches:
+        st = backend.allreduce_average(off, cnt)
+        assert st == 0, st
+    st, code = backend.check()
+    assert st == 0, f"communicator status {code}"
+    inputs = [torch.empty_like(pattern) for _ in range(world)]
+    dist.all_gather(inputs, pattern)
+    expected = inputs[0].clone()
+    for r in range(1, world):
+        expected += inputs[r]
+    expected *= torch.tensor(1.0, dtype=torch.float32).div(float(world)).item()
+    out["avg_bit_exact"] = bool(torch.equal(grad, expected))
+    out["avg_ranges"] = len(ranges)
+    out["avg_launches"] = len(launches)
+    del inputs
+
+    # one optimizer step both ways from the same state
+    w0, h0, m0, v0 = w.clone(), w_half.clone(), m.clone(), v.clone()
+    cfg = mgt.AdamWKernelConfig(params, 7, LR)
+    grad.copy_(pattern)
+    torch.cuda.synchronize()
+    dist.barrier()
+    for off, cnt in launches:
+        st = backend.allreduce_average_adamw(off, cnt, cfg, w, w_half, m, v)
+        assert st == 0, st
+    st, code = backend.check()
+    assert st == 0, f"communicator status {code}"
+    g2 = pattern.clone()
+    dist.all_reduce(g2, op=dist.ReduceOp.SUM)
+    g2.mul_(1.0 / world)
+    st = mgt.launch_adamw_kernel_with_half_mirror(cfg, w0, h0, g2, m0, v0)
+    assert st == 0, st
+    torch.cuda.synchronize()
+    num = (w.double() - w0.double()).pow(2).sum().sqrt().item()
+    den = w0.double().pow(2).sum().sqrt().item()
+    out["fused_vs_nccl_rel_l2"] = num / max(den, 1e-30)
+    out["fused_vs_nccl_mirror_equal_fraction"] = float((w_half == h0).float().mean().item())
+    flags = torch.tensor([int(out["avg_bit_exact"]), int(out["replicas_identical"]), int(out["fused_vs_nccl_rel_l2"] <= 1e-6)], device=dev)
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)  # a check holds only if it holds on every rank
+    out["avg_bit_exact"], out["replicas_identical"] = bool(flags[0].item()), bool(flags[1].item())
+    out["ok"] = bool(flags.min().item() == 1)
+    return out
+
+
+def run_gpu_trainers_side_by_side(world: int, steps: int) -> dict:
+    """The reference's own GPU trainer (unmodified sources compiled for sm_100 with the cuBLASLt/NCCL of the image, built
+    by oracle/Makefile into oracle/_ref) and bin/mgt_native_train on the README's p888 command, one process per GPU, timed
+    by the reference's throughput formula (kaggle/kernel/run_ranks_2xt4.sh:95-115). A checker leg like cpu_baseline: it runs
+    outside the timed regions and nothing of it is on the product path."""
+    import tempfile
+    from multigputrainmlp_b200.launch import TRAINER, launch
+    ref_bin = os.path.join(ROOT, "oracle", "_ref", "mgt_native_train_ref")
+    if not os.path.exists(ref_bin) or not os.path.exists(TRAINER):
+        return {"unavailable": "oracle/_ref/mgt_native_train_ref or bin/mgt_native_train not built"}
+    flags = README_P888_FLAGS + ["--steps", str(steps)]
+    out = {"flags": " ".join(flags), "world_size": world}
+    with tempfile.TemporaryDirectory(prefix="mgt_bench_") as tmp:
+        for name, binary in (("reference", ref_bin), ("ours", TRAINER)):
+            summary = launch(world, os.path.join(tmp, name), flags, trainer=binary, timeout=600)
+            if summary.get("status") != "ok":
+                return {"unavailable": f"{name} trainer run failed: {summary.get('status')} exit codes {summary.get('exit_codes')}"}
+            steady = summary["steady_steps"]
+            out[name] = {"candidates_s": summary["avg_throughput_states_s"], "ms_per_step": float(np.mean([s["max_rank_ms"] for s in steady])),
+                         "final_loss_rank0": steady[-1]["rank_losses"][0], "steps_timed": len(steady)}
+    out["ratio"] = out["ours"]["candidates_s"] / out["reference"]["candidates_s"]
+    a, b = out["reference"]["final_loss_rank0"], out["ours"]["final_loss_rank0"]
+    out["final_loss_rel_diff"] = abs(a - b) / max(abs(a), 1e-30)
+    return out
+
+
 # ------------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -220,6 +336,10 @@ def main():
     ap.add_argument("--steps-cpu", type=int, default=2)
     ap.add_argument("--warmup-cpu", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-reference-gpu", action="store_true", help="skip the side-by-side run of the reference's GPU trainer and bin/mgt_native_train")
+    ap.add_argument("--reference-gpu-steps", type=int, default=30)
+    ap.add_argument("--workload", default="step", choices=["step", "collective"],
+                    help="step: the p888 training step (headline); collective: the gradient-exchange microbenchmark (bench_collective.py, needs >= 2 ranks)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -231,9 +351,15 @@ def main():
             print(json.dumps(run_reference_cpu(args, args.steps, args.warmup)), flush=True)
         return
 
+    if args.workload == "collective":
+        import bench_collective
+        line = bench_collective.run(args)
+        if line:
+            print(json.dumps(line), flush=True)
+        return
+
     import torch
     import multigputrainmlp_b200 as mgt
-    from oracle import load_oracle
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU fallback")
@@ -242,6 +368,7 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+        host_group = dist.new_group(backend="gloo")  # for waits during which no rank may keep a kernel spinning on its GPU
     batch = args.batch
     shape = mgt.CudaMlpShape(**P888)
     params = shape.param_count
@@ -254,25 +381,24 @@ def main():
     loss = torch.zeros(1, device=dev)
     backend = None
     exchange = None
-    if world > 1:
-        import torch.distributed as dist
-        from multigputrainmlp_b200.comm import NcclBackend, OverlappedGradientExchange, PeerBackend, default_id_file
-        if args.comm == "peer":
-            id_file = default_id_file()
+    from multigputrainmlp_b200.comm import NcclBackend, OverlappedGradientExchange, PeerBackend, default_id_file
+    if world > 1 and args.comm == "nccl":
+        grad = torch.zeros(params, device=dev)
+        backend = NcclBackend(grad, world)
+        exchange = OverlappedGradientExchange(backend, dev, bucket_bytes=args.bucket_bytes, residual_blocks=16, fused_adamw=False)
+    else:
+        # the library's communicator, also for one rank: the per-range "exchange" is then just the AdamW update of each
+        # range on the second stream while backward still runs (what bin/mgt_native_train does)
+        id_file = default_id_file() if world > 1 else None
+        if world > 1:
+            import torch.distributed as dist
             if rank == 0 and os.path.exists(id_file):
                 os.remove(id_file)  # a stale id file of an earlier run must not be picked up
             dist.barrier()
-            backend = PeerBackend(local_rank, world, rank, id_file, params)
-            grad = backend.gradient_tensor(dev)
-            exchange = OverlappedGradientExchange(backend, dev, bucket_bytes=args.bucket_bytes, residual_blocks=16, fused_adamw=True)
-        else:
-            grad = torch.zeros(params, device=dev)
-            backend = NcclBackend(grad, world)
-            exchange = OverlappedGradientExchange(backend, dev, bucket_bytes=args.bucket_bytes, residual_blocks=16, fused_adamw=False)
-    else:
-        grad = torch.zeros(params, device=dev)
-    orc = load_oracle()
-    moves_h, target_h = orc.cyclic_puzzle(72, 18)
+        backend = PeerBackend(local_rank, world, rank, id_file, params)
+        grad = backend.gradient_tensor(dev)
+        exchange = OverlappedGradientExchange(backend, dev, bucket_bytes=args.bucket_bytes, residual_blocks=16, fused_adamw=True)
+    moves_h, target_h = cyclic_puzzle(72, 18)
     puzzle_pinned = torch.from_numpy(np.concatenate([moves_h.reshape(-1), target_h.reshape(-1)])).pin_memory()
     puzzle_dev = torch.empty_like(puzzle_pinned, device=dev)
     puzzle_dev.copy_(puzzle_pinned)
@@ -284,6 +410,8 @@ def main():
     ws_floats = mgt.mlp_loss_grad_workspace_floats(shape, batch)
     workspace = torch.empty(ws_floats, device=dev)
     engine = mgt.Engine(local_rank)
+    if exchange is not None and exchange.fused:
+        assert engine.set_early_range_hook(exchange.early_callback) == 0
     walk_cfg = mgt.RandomWalkKernelConfig(batch, 1, 29)
     loss_pinned = torch.zeros(1).pin_memory()
     other_launches = 0
@@ -329,7 +457,8 @@ def main():
     if sampler is not None:
         time.sleep(0.3)
     launches0 = engine.launch_count + other_launches
-    comm_launches0 = backend.launch_count if (args.comm == "peer" and backend is not None) else 0
+    peer_comm = isinstance(backend, PeerBackend)
+    comm_launches0 = backend.launch_count if peer_comm else 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     t_wall0 = time.time()
@@ -345,7 +474,7 @@ def main():
         dist.all_reduce(ms_total, op=dist.ReduceOp.MAX)
     ms_step = float(ms_total.item()) / args.steps
     launches = engine.launch_count + other_launches - launches0
-    if args.comm == "peer" and backend is not None:
+    if peer_comm:
         launches += backend.launch_count - comm_launches0
         st, code = backend.check()
         assert st == 0, f"communicator status {code}"
@@ -388,6 +517,7 @@ def main():
         "kernel": "umma_gemm_kernel<one-hot forward> (embedding layer)", "bound": "tensor", "achieved": algo_tflops,
         "peak": peaks["tflops_burst"], "unit": "TFLOP/s", "frac": algo_tflops / peaks["tflops_burst"],
         "traffic": EMB_FWD_DRAM_BYTES_PER_LAUNCH if batch == BATCH else None,
+        "traffic_source": EMB_FWD_DRAM_SOURCE if batch == BATCH else None,
         "peak_source": peaks["source"] + " (cuBLAS bf16 burst)", "ms_per_launch": emb,
         "executed_tflops": exec_tflops, "executed_frac": exec_tflops / peaks["tflops_burst"],
         "note": "achieved counts the 72 row-adds per candidate the layer needs; executed counts the dense one-hot MMA work",
@@ -409,11 +539,28 @@ def main():
          "frac": hidden_fwd_bytes / (stage_ms["hidden_forward_ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"]},
     ]
 
+    comm_check = None
+    if world > 1 and args.comm == "peer" and batch == BATCH:
+        import torch.distributed as dist
+        comm_check = check_gradient_exchange(torch, dist, mgt, backend, dev, world, params, args.bucket_bytes, (w, w_half, m, v))
+    barrier()
+    reference_gpu = None
+    if not args.no_reference_gpu and batch == BATCH:
+        # rank 0 starts the trainer processes on all GPUs; the other ranks wait on the host (a NCCL barrier would keep a
+        # kernel polling on their GPUs and time-slice with the trainers)
+        if rank == 0:
+            reference_gpu = run_gpu_trainers_side_by_side(world, max(3, min(args.steps, args.reference_gpu_steps)))
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier(group=host_group)
+
     if rank != 0:
         if world > 1:
             import torch.distributed as dist
             dist.barrier()
             dist.destroy_process_group()
+        if comm_check is not None and not comm_check["ok"]:
+            sys.exit(1)
         return
 
     value = batch * world / (ms_step * 1e-3)
@@ -425,7 +572,7 @@ def main():
         "gpu_launches": int(launches), "roofline": roofline, "roofline_other": roofline_other if batch == BATCH else None, "comm": (args.comm if world > 1 else "none"),
         "step_tflops_algorithmic": FLOP_PER_CANDIDATE * value / world / 1e12,
         "step_frac_of_fp16_peak": FLOP_PER_CANDIDATE * value / world / 1e12 / peaks["tflops_sustained"],
-        "stage_ms": stage_ms, "final_loss": final_loss,
+        "stage_ms": stage_ms, "final_loss": final_loss, "comm_check": comm_check, "reference_gpu": reference_gpu,
     }
     if batch != BATCH:
         line["config"]["batch_per_rank"] = batch
@@ -438,6 +585,8 @@ def main():
         import torch.distributed as dist
         dist.barrier()
         dist.destroy_process_group()
+    if comm_check is not None and not comm_check["ok"]:
+        sys.exit(1)
 
 
 if __name__ == "__main__":

@@ -127,6 +127,16 @@ typedef struct {
 typedef mgt_status_t (*mgt_gradient_ready_fn)(void* user, uint32_t ready_id, uint64_t param_offset,
                                               uint64_t param_count, void* producer_stream);
 
+/* Early-range hook (optional; no counterpart in the reference). The embedding table is 86 % of the p888 parameters and
+ * its gradient is the last thing backward produces. With a hook installed and input_grad_position_tile T (0 < T <
+ * state_len) the table gradient is computed in blocks of T positions (T * state_value_pad rows), one launch each, and
+ * `hook` is called (same signature and rules as gradient_ready; ready_id = the id of the closing announcement) for every
+ * finished block but the last, the moment its kernel is enqueued: blocks come in order, end to end, starting at the
+ * first parameter of the range. A caller can exchange and update a block while the next one is still being computed.
+ * The gradient_ready calls are unchanged - same count, order and ranges as the reference, the whole embedding range
+ * last - so a caller that acted on the hook handles only the rest of the range there. NULL removes the hook. */
+mgt_status_t mgt_engine_set_early_range_hook(mgt_engine_t* engine, mgt_gradient_ready_fn hook, void* user);
+
 /* Number of floats of caller-owned scratch the launch needs (0 = invalid arguments). */
 uint64_t mgt_mlp_loss_grad_workspace_floats(const mgt_mlp_shape_t* shape, uint32_t sample_count,
                                             uint32_t input_grad_partial_chunks, int32_t use_half_input_grad,
@@ -199,9 +209,22 @@ mgt_status_t mgt_comm_allreduce_average(mgt_comm_t* comm, const mgt_allreduce_co
 mgt_status_t mgt_comm_allreduce_average_adamw(mgt_comm_t* comm, uint64_t param_offset, uint64_t param_count,
                                               const mgt_adamw_config_t* adamw, float* device_weights,
                                               uint16_t* device_weights_half, float* device_m, float* device_v, void* stream);
-/* Synchronises `stream`, reads and clears the communicator's status: MGT_OK or MGT_DEVICE_TIMEOUT
- * (a peer did not show up within the wait limit; out_code 1 = ready wait, 2 = done wait). */
+/* Synchronises `stream` and reads the communicator's status: MGT_OK or MGT_DEVICE_TIMEOUT (a peer did
+ * not show up within the wait limit; out_code 1 = ready wait, 2 = done wait). A timeout is final for this
+ * communicator: the ranks' flag state no longer agrees, so every later exchange call and check returns
+ * MGT_DEVICE_TIMEOUT without launching anything, and parameters that a fused update had already touched are
+ * undefined. Destroy it, restore weights/m/v from a checkpoint and create a new one.
+ * (The reference's NCCL call has no timeout at all: a dead peer hangs it, allreduce_nccl.cu:130.) */
 mgt_status_t mgt_comm_check(mgt_comm_t* comm, void* stream, int32_t* out_code);
+/* How long an exchange kernel waits for a peer before it gives up (default 1000 ms, at most 60 000).
+ * The limit also bounds how far apart the ranks may ENTER a collective, so ranks that do unequal host
+ * work between steps (checkpoint files, start-up) meet at mgt_comm_host_barrier first. No counterpart
+ * in the reference. */
+mgt_status_t mgt_comm_set_wait_limit_ms(mgt_comm_t* comm, uint32_t milliseconds);
+/* Host-side rendezvous of all ranks through small files beside the id file (no GPU work, no kernel):
+ * returns when every rank has called it the same number of times, or MGT_IO_FAILURE after timeout_ms.
+ * world_size 1: returns at once. No counterpart in the reference. */
+mgt_status_t mgt_comm_host_barrier(mgt_comm_t* comm, uint32_t timeout_ms);
 uint64_t mgt_comm_launch_count(const mgt_comm_t* comm);
 
 /* ---- run plan and output files (host only, no GPU) --------------------------------------------
@@ -221,6 +244,19 @@ mgt_status_t mgt_plan_linear_op(int32_t argc, const char* const* argv, uint32_t 
 /* metadata.env, layers.json, linear_ops.json (tool:184-214, 888-895) */
 mgt_status_t mgt_plan_write_files(int32_t argc, const char* const* argv, const char* dir, int32_t overlap_allreduce,
                                   int32_t comm_enabled, int32_t resumed);
+/* One step as the trainer logs it: the "phase=start" line of train.log (tool:750-762), the per-step line of train.log
+ * (tool:856-858) and the row of profile.jsonl (tool:859-875), each zero-terminated into a caller buffer of `capacity`
+ * bytes (NULL = not wanted). The trainer binary writes its files through the same formatters. */
+typedef struct {
+    uint32_t step;
+    float loss, step_ms, walk_ms, backward_ms, allreduce_ms, adam_ms;
+    uint64_t memory_bytes;
+    uint32_t overlap_ranges, overlap_chunks;
+    float backward_stage_ms[7]; /* the fields of mgt_backward_profile_t, in its order */
+} mgt_step_record_t;
+mgt_status_t mgt_format_step_record(int32_t argc, const char* const* argv, const mgt_step_record_t* record,
+                                    int32_t overlap_allreduce, int32_t comm_enabled, int32_t resumed, char* start_line,
+                                    char* log_line, char* profile_row, uint32_t capacity);
 /* The trainer's software float->fp16 converter used for weights/ files (tool:215-229). */
 uint16_t mgt_export_float_to_fp16(float value);
 /* weights/ (fp16 per-layer files + manifest + weights.f32.bin) and checkpoint/ (tool:241-390) from host arrays. */
@@ -241,10 +277,21 @@ mgt_status_t mgt_load_puzzle_definition(const char* group_json, const char* targ
  * One plain GEMM through the tcgen05 kernel, used by the parity tests to pin each operand form.
  * D[M x N] fp32 = A * B with fp16 operands; a_mn_major: A stored [K][M] (else [M][K]);
  * b_mn_major: B stored [K][N] (else [N][K]); lda/ldb are row pitches in elements.
+ * d must be 4-byte aligned, and 16-byte aligned when a single split is used (splits == 1 or k <= 64) and
+ * n is a multiple of 4 (the accumulator tiles are then stored to d as 16-byte vectors); partial_scratch must
+ * be 16-byte aligned when n is a multiple of 4. Otherwise MGT_INVALID_CONFIG, nothing is launched.
  * No counterpart in the reference. */
 mgt_status_t mgt_debug_gemm(mgt_engine_t* engine, const uint16_t* a, uint32_t lda, int32_t a_mn_major,
                             const uint16_t* b, uint32_t ldb, int32_t b_mn_major, float* d, uint32_t m, uint32_t n,
                             uint32_t k, uint32_t splits, float* partial_scratch, void* stream);
+
+/* How the embedding-layer GEMMs deal their work to `grid` CTAs (host only, no GPU): the N range [n_begin, n_end) of every
+ * (M tile, K split) is laid end to end, cut into equal shares and each share into units of at most max_cols columns.
+ * out_units receives grid * (*out_stride) records {m tile, n_base, n_count, split}; a CTA's list ends at the first record
+ * with n_count == 0. MGT_INVALID_CONFIG when no such list exists (the kernels then deal whole tiles round-robin).
+ * No counterpart in the reference. */
+mgt_status_t mgt_debug_work_list(uint32_t grid, uint32_t m_tiles, uint32_t splits, uint32_t n_begin, uint32_t n_end,
+                                 uint32_t max_cols, uint32_t* out_units, uint32_t out_capacity_units, uint32_t* out_stride);
 
 /* Split-K GEMM that allocates nothing. No counterpart in the reference.
  *
@@ -261,11 +308,18 @@ mgt_status_t mgt_debug_gemm(mgt_engine_t* engine, const uint16_t* a, uint32_t ld
  * The first call on each device looks up the device addresses of the built-in buffers and the
  * tensor-map encoder (host work only); make that first call before starting any stream capture.
  * All calls on a device share the one buffer: calls that may overlap on the GPU (different
- * streams) race on it - keep them on one stream or order them with events. */
+ * streams) race on it - keep them on one stream or order them with events.
+ * d has the alignment rule of mgt_debug_gemm. The kernels' bounded waits report into a status word that is
+ * built into the library as well; read it with mgt_static_scratch_check. */
 #define MGT_STATIC_SCRATCH_FLOATS (4u << 20)
 mgt_status_t mgt_gemm_split_k_static_scratch(const uint16_t* a, uint32_t lda, int32_t a_mn_major, const uint16_t* b,
                                              uint32_t ldb, int32_t b_mn_major, float* d, uint32_t m, uint32_t n,
                                              uint32_t k, uint32_t splits, void* stream);
+/* What mgt_engine_check is for an engine, for mgt_gemm_split_k_static_scratch on the current device:
+ * synchronises `stream`, reads and clears the built-in status word. MGT_OK, or MGT_DEVICE_TIMEOUT when a
+ * kernel of an earlier call gave up on a bounded wait (d of that call is then undefined). Allocates nothing.
+ * No counterpart in the reference. */
+mgt_status_t mgt_static_scratch_check(void* stream, int32_t* out_device_code);
 
 const char* mgt_status_name(mgt_status_t status);
 const char* mgt_version(void);

@@ -177,6 +177,13 @@ class Engine:
         st = int(self._lib.mgt_engine_check(self.handle, _stream(stream), C.byref(code)))
         return st, int(code.value)
 
+    def set_early_range_hook(self, fn=None) -> int:
+        """mgt_engine_set_early_range_hook: fn(user, ready_id, offset, count, stream) -> status, or None to remove it."""
+        cb = GRADIENT_READY_FN(fn) if fn is not None else None
+        self._early_keepalive = cb
+        self._lib.mgt_engine_set_early_range_hook.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        return int(self._lib.mgt_engine_set_early_range_hook(self.handle, C.cast(cb, C.c_void_p) if cb is not None else None, None))
+
     def launch_mlp_loss_grad(self, shape, device_weights, device_weights_half, device_states, device_labels, sample_count,
                              device_loss, device_grad, workspace, workspace_floats, input_grad_partial_chunks=1,
                              input_grad_positions_per_block=1, use_half_input_grad=True, use_half_linear=True,

@@ -45,12 +45,29 @@ class GradientRangeScheduler:
     scheduled_chunks: int = 0
     log: List[ScheduledChunk] = field(default_factory=list)
     _pending: List[Tuple[int, int, int]] = field(default_factory=list)
+    _early: List[Tuple[int, int]] = field(default_factory=list)   # what the early hook already sent this step
 
     def begin_step(self) -> None:
         self.scheduled_ranges = 0
         self.scheduled_chunks = 0
         self.log = []
         self._pending = []
+        self._early = []
+
+    def on_early(self, ready_id: int, param_offset: int, param_count: int) -> int:
+        """The engine's early-range hook (mgt_engine_set_early_range_hook): a leading block of the range that closes
+        backward (rows of the embedding table) is complete while the kernel that computes the next block still runs.
+        It goes out at once and whole, so that its exchange and update run under that kernel; the closing gradient-ready
+        call then only sends what is left of the range."""
+        if param_count == 0:
+            return 1
+        self._flush(0)
+        self.wait_for_producer()
+        self.launch(param_offset, param_count)
+        self.log.append(ScheduledChunk(ready_id, param_offset, param_count))
+        self.scheduled_chunks += 1
+        self._early.append((param_offset, param_count))
+        return 0
 
     def _flush(self, keep: int, whole: bool = False) -> None:
         if len(self._pending) <= keep:
@@ -71,7 +88,14 @@ class GradientRangeScheduler:
         if param_count == 0 or (self.expected_ranges is not None and ready_id >= self.expected_ranges):
             return 1  # invalid_config, as the reference's callback does (tool:501-504)
         self.scheduled_ranges += 1
-        self._pending.append((ready_id, param_offset, param_count))
+        # leading blocks of this range that the early hook has sent already
+        end = param_offset + param_count
+        for off, cnt in sorted(self._early):
+            if off == param_offset and off + cnt <= end:
+                param_offset += cnt
+        param_count = end - param_offset
+        if param_count > 0:
+            self._pending.append((ready_id, param_offset, param_count))
         # the range that closes backward waits for finish(), where it goes out whole
         last = self.whole_tail and self.expected_ranges is not None and self.scheduled_ranges == self.expected_ranges
         self._flush(max(self.lag, 1 if last else 0))
@@ -103,6 +127,8 @@ class PeerBackend:
         lib.mgt_comm_check.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
         lib.mgt_comm_launch_count.restype = C.c_uint64
         lib.mgt_comm_launch_count.argtypes = [C.c_void_p]
+        lib.mgt_comm_set_wait_limit_ms.argtypes = [C.c_void_p, C.c_uint32]
+        lib.mgt_comm_host_barrier.argtypes = [C.c_void_p, C.c_uint32]
         handle = C.c_void_p()
         st = lib.mgt_comm_create(device_index, world_size, global_rank, id_file.encode() if id_file else None, gradient_floats, C.byref(handle))
         if st != 0:
@@ -131,6 +157,14 @@ class PeerBackend:
         code = C.c_int32(0)
         st = int(self._lib.mgt_comm_check(self.handle, _stream(stream), C.byref(code)))
         return st, int(code.value)
+
+    def set_wait_limit_ms(self, milliseconds: int) -> int:
+        """How long an exchange kernel waits for a peer before it gives up (default 1000 ms)."""
+        return int(self._lib.mgt_comm_set_wait_limit_ms(self.handle, milliseconds))
+
+    def host_barrier(self, timeout_ms: int = 600000) -> int:
+        """Host-side rendezvous of all ranks (files beside the id file); no GPU work."""
+        return int(self._lib.mgt_comm_host_barrier(self.handle, timeout_ms))
 
     @property
     def launch_count(self) -> int:
@@ -183,6 +217,9 @@ class OverlappedGradientExchange:
 
     def callback(self, user, ready_id, offset, count, stream) -> int:
         return self.scheduler.on_ready(int(ready_id), int(offset), int(count))
+
+    def early_callback(self, user, ready_id, offset, count, stream) -> int:
+        return self.scheduler.on_early(int(ready_id), int(offset), int(count))
 
     def finish_step(self):
         self.scheduler.finish()

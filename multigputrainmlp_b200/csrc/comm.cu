@@ -36,7 +36,7 @@ constexpr uint32_t kFlagDone = 8;      // [kMaxWorld] written by peers
 constexpr uint32_t kFlagCounter = 16;  // local: CTAs that finished their writes
 constexpr uint32_t kFlagStatus = 17;   // local: 0 ok, else the wait that gave up
 constexpr uint32_t kFlagWords = 64;
-constexpr uint64_t kWaitLimitNs = 1000ULL * 1000ULL * 1000ULL;
+constexpr uint64_t kDefaultWaitLimitNs = 1000ULL * 1000ULL * 1000ULL;
 constexpr uint32_t kCommThreads = 256;
 constexpr uint64_t kOneShotMaxFloats = 65536;  // 256 KB: below this a single pass over all copies is cheaper than two handshaken phases
 
@@ -45,6 +45,7 @@ struct CommDev {
     uint32_t* flags[kMaxWorld];
     uint32_t world;
     uint32_t rank;
+    uint64_t wait_limit_ns;  // how long a kernel waits for a peer before it gives up
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
@@ -80,7 +81,7 @@ __device__ bool WaitPeers(const CommDev& c, uint32_t base, uint32_t seq, int cod
         uint32_t spins = 0;
         // sequence numbers only grow, so a later value also releases the wait
         while (static_cast<int32_t>(ld_acquire_sys(slot) - seq) < 0) {
-            if ((++spins & 255U) == 0U && timer_ns() - start > kWaitLimitNs) {
+            if ((++spins & 255U) == 0U && timer_ns() - start > c.wait_limit_ns) {
                 s_fail = 1;
                 atomicCAS(reinterpret_cast<int*>(c.flags[c.rank] + kFlagStatus), 0, code);
                 break;
@@ -222,23 +223,30 @@ __device__ void AdamRange(const CommDev& c, uint64_t begin, uint64_t end, const 
     for (uint64_t i = body_end + tid; i < end; i += nthreads) Finish1<true>(__ldcg(own + i), i, own, a, sc);
 }
 
+// One-shot ranges run as ONE launch (kPhaseAll, at most 64 CTAs). Two-shot ranges run as two launches on the same stream:
+// kPhaseReduce (ready handshake, reduce own slice, write it to every rank, last CTA signals "done") and kPhaseFinish
+// (done handshake, AdamW on the slices the peers wrote). Split like this, no CTA of a large grid ever waits for something
+// that another CTA of the SAME launch still has to do, so the grid need not be resident at once - it may queue behind the
+// persistent GEMM kernels it overlaps with.
+enum CommPhase : int { kPhaseAll = 0, kPhaseReduce = 1, kPhaseFinish = 2 };
+
 template <bool kAdam>
 __global__ void __launch_bounds__(kCommThreads)
-AllreduceAverageKernel(CommDev c, uint64_t offset, uint64_t count, uint32_t seq, mgt_adamw_config_t cfg, AdamPtrs a) {
+AllreduceAverageKernel(CommDev c, uint64_t offset, uint64_t count, uint32_t seq, mgt_adamw_config_t cfg, AdamPtrs a, int phase) {
     const float inv_w = 1.0f / static_cast<float>(c.world);
     mgt::AdamWScalars sc{};
     if (kAdam) sc = mgt::MakeAdamWScalars(cfg.step, cfg.learning_rate, cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay);
     uint32_t* my_flags = c.flags[c.rank];
+    const bool one_shot = phase == kPhaseAll;
 
-    // ready handshake: the producer kernels of this rank finished before this kernel started
-    if (blockIdx.x == 0 && threadIdx.x < c.world && threadIdx.x != c.rank) {
-        __threadfence_system();
-        st_release_sys(c.flags[threadIdx.x] + kFlagReady + c.rank, seq);
-    }
-    if (!WaitPeers(c, kFlagReady, seq, 1)) return;
-
-    const bool one_shot = count <= kOneShotMaxFloats;
+    // two-shot slices: boundaries on multiples of 4 floats so that the bulk of every slice is 16-byte aligned
     uint64_t my_begin = offset, my_end = offset + count;
+    if (!one_shot) {
+        const uint64_t first4 = (offset + 3ULL) / 4ULL, last4 = (offset + count) / 4ULL;
+        const uint64_t quads = last4 > first4 ? last4 - first4 : 0ULL;
+        my_begin = c.rank == 0 ? offset : (first4 + quads * c.rank / c.world) * 4ULL;
+        my_end = c.rank + 1 == c.world ? offset + count : (first4 + quads * (c.rank + 1) / c.world) * 4ULL;
+    }
     // one-shot: every rank reads all copies, so nobody may overwrite its own copy before the done
     // handshake; each thread keeps its (at most one) float4 and two edge scalars in registers
     const uint64_t tid = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -248,31 +256,37 @@ AllreduceAverageKernel(CommDev c, uint64_t offset, uint64_t count, uint32_t seq,
     const uint64_t body_end = head_end + ((end - head_end) & ~3ULL);
     float4 keep4 = make_float4(0.f, 0.f, 0.f, 0.f);
     float keep_head = 0.f, keep_tail = 0.f;
-    if (one_shot) {
-        if (offset + tid < head_end) keep_head = Average1(c, offset + tid, inv_w);
-        if (head_end + tid * 4ULL < body_end) keep4 = Average4(c, head_end + tid * 4ULL, inv_w);
-        if (body_end + tid < end) keep_tail = Average1(c, body_end + tid, inv_w);
-    } else {
-        // slice boundaries on multiples of 4 floats so that the bulk of every slice is 16-byte aligned
-        const uint64_t first4 = (offset + 3ULL) / 4ULL, last4 = (offset + count) / 4ULL;
-        const uint64_t quads = last4 > first4 ? last4 - first4 : 0ULL;
-        my_begin = c.rank == 0 ? offset : (first4 + quads * c.rank / c.world) * 4ULL;
-        my_end = c.rank + 1 == c.world ? offset + count : (first4 + quads * (c.rank + 1) / c.world) * 4ULL;
-        ReduceRange<kAdam, true>(c, my_begin, my_end, inv_w, a, sc);
+
+    if (phase != kPhaseFinish) {
+        // ready handshake: the producer kernels of this rank finished before this kernel started
+        if (blockIdx.x == 0 && threadIdx.x < c.world && threadIdx.x != c.rank) {
+            __threadfence_system();
+            st_release_sys(c.flags[threadIdx.x] + kFlagReady + c.rank, seq);
+        }
+        if (!WaitPeers(c, kFlagReady, seq, 1)) return;
+        if (one_shot) {
+            if (offset + tid < head_end) keep_head = Average1(c, offset + tid, inv_w);
+            if (head_end + tid * 4ULL < body_end) keep4 = Average4(c, head_end + tid * 4ULL, inv_w);
+            if (body_end + tid < end) keep_tail = Average1(c, body_end + tid, inv_w);
+        } else {
+            ReduceRange<kAdam, true>(c, my_begin, my_end, inv_w, a, sc);
+        }
+        // the last CTA of this rank to finish tells every peer
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const uint32_t arrived = atomicAdd(my_flags + kFlagCounter, 1U);
+            if (arrived == gridDim.x - 1U) {
+                my_flags[kFlagCounter] = 0U;
+                __threadfence_system();
+                for (uint32_t p = 0; p < c.world; ++p)
+                    if (p != c.rank) st_release_sys(c.flags[p] + kFlagDone + c.rank, seq);
+            }
+        }
+        if (phase == kPhaseReduce) return;
     }
 
-    // done handshake: the last CTA of this rank to finish tells every peer
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const uint32_t arrived = atomicAdd(my_flags + kFlagCounter, 1U);
-        if (arrived == gridDim.x - 1U) {
-            my_flags[kFlagCounter] = 0U;
-            __threadfence_system();
-            for (uint32_t p = 0; p < c.world; ++p)
-                if (p != c.rank) st_release_sys(c.flags[p] + kFlagDone + c.rank, seq);
-        }
-    }
+    // done handshake: nobody goes on (and overwrites its gradients) before all peers are finished
     if (!WaitPeers(c, kFlagDone, seq, 2)) return;
 
     if (one_shot) {
@@ -280,8 +294,7 @@ AllreduceAverageKernel(CommDev c, uint64_t offset, uint64_t count, uint32_t seq,
         if (offset + tid < head_end) Finish1<kAdam>(keep_head, offset + tid, own, a, sc);
         if (head_end + tid * 4ULL < body_end) Finish4<kAdam>(keep4, head_end + tid * 4ULL, own, a, sc);
         if (body_end + tid < end) Finish1<kAdam>(keep_tail, body_end + tid, own, a, sc);
-    }
-    if (kAdam && !one_shot) {
+    } else if (kAdam) {
         AdamRange(c, offset, my_begin, a, sc);
         AdamRange(c, my_end, offset + count, a, sc);
     }
@@ -332,6 +345,8 @@ struct mgt_comm {
     uint64_t launches = 0;
     std::string id_file;
     uint64_t nonce = 0;
+    uint64_t barrier_seq = 0;  // host barriers passed so far
+    bool dead = false;         // a wait ran out: the flag state of the ranks no longer agrees, nothing more is launched
 };
 
 extern "C" {
@@ -356,6 +371,7 @@ mgt_status_t mgt_comm_create(int32_t device_id, uint32_t world_size, uint32_t gl
     }
     c->dev.world = world_size;
     c->dev.rank = global_rank;
+    c->dev.wait_limit_ns = kDefaultWaitLimitNs;
     c->peer_base[global_rank] = c->local;
     if (world_size > 1) {
         c->id_file = id_file;
@@ -408,6 +424,7 @@ uint64_t mgt_comm_launch_count(const mgt_comm_t* c) { return c == nullptr ? 0 : 
 static mgt_status_t LaunchAllreduce(mgt_comm_t* c, uint64_t offset, uint64_t count, const mgt_adamw_config_t* adam, float* w,
                                     uint16_t* w_half, float* m, float* v, void* stream) {
     if (c == nullptr || count == 0 || offset + count > c->gradient_floats) return MGT_INVALID_CONFIG;
+    if (c->dead) return MGT_DEVICE_TIMEOUT;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     AdamPtrs a{w, reinterpret_cast<__half*>(w_half), m, v};
     mgt_adamw_config_t cfg{};
@@ -419,24 +436,26 @@ static mgt_status_t LaunchAllreduce(mgt_comm_t* c, uint64_t offset, uint64_t cou
     }
     const uint64_t quads = (count + 3ULL) / 4ULL;
     const uint64_t want = (quads + kCommThreads - 1ULL) / kCommThreads;  // one-shot ranges: one float4 per thread (at most 64 CTAs)
-    // All CTAs of a launch wait for the peers, so the grid must be able to be resident at once: at most what the
-    // occupancy calculator allows per SM (and 4 per SM is plenty to cover the NVLink round trip).
-    static int per_sm_adam = 0, per_sm_plain = 0;
-    int& per_sm = adam != nullptr ? per_sm_adam : per_sm_plain;
-    if (per_sm == 0) {
-        int n = 1;
-        const cudaError_t q = adam != nullptr ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, AllreduceAverageKernel<true>, kCommThreads, 0)
-                                              : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, AllreduceAverageKernel<false>, kCommThreads, 0);
-        per_sm = (q == cudaSuccess && n >= 1) ? (n > 4 ? 4 : n) : 1;
-    }
-    const uint64_t cap = static_cast<uint64_t>(c->sm_count) * static_cast<uint64_t>(per_sm);
-    if (count <= kOneShotMaxFloats && want > cap) return MGT_CAPACITY_EXCEEDED;
-    const uint32_t grid = static_cast<uint32_t>(want < 1 ? 1 : (want < cap ? want : cap));
+    const bool one_shot = count <= kOneShotMaxFloats;
     const uint32_t seq = ++c->seq;
-    if (adam != nullptr) {
-        AllreduceAverageKernel<true><<<grid, kCommThreads, 0, st>>>(c->dev, offset, count, seq, cfg, a);
+    auto launch = [&](uint32_t grid, int phase) {
+        if (adam != nullptr) {
+            AllreduceAverageKernel<true><<<grid, kCommThreads, 0, st>>>(c->dev, offset, count, seq, cfg, a, phase);
+        } else {
+            AllreduceAverageKernel<false><<<grid, kCommThreads, 0, st>>>(c->dev, offset, count, seq, cfg, a, phase);
+        }
+        ++c->launches;
+    };
+    if (one_shot) {
+        // every CTA waits for the peers' "done" after its own reads, so these (at most 64) CTAs must be able to be resident
+        // together: they are, one per SM, also beside a persistent GEMM CTA (256 threads, no shared memory)
+        launch(static_cast<uint32_t>(want < 1 ? 1 : want), kPhaseAll);
     } else {
-        AllreduceAverageKernel<false><<<grid, kCommThreads, 0, st>>>(c->dev, offset, count, seq, cfg, a);
+        // up to four CTAs per SM cover the NVLink round trip; the grid may queue (see CommPhase)
+        const uint64_t cap = static_cast<uint64_t>(c->sm_count) * 4ULL;
+        launch(static_cast<uint32_t>(want < cap ? want : cap), kPhaseReduce);
+        const uint64_t rest = adam != nullptr ? want : 1ULL;  // without the update the second launch only waits for the peers
+        launch(static_cast<uint32_t>(rest < cap ? rest : cap), kPhaseFinish);
     }
     ++c->launches;
     return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
@@ -465,10 +484,48 @@ mgt_status_t mgt_comm_check(mgt_comm_t* c, void* stream, int32_t* out_code) {
     uint32_t code = 0;
     if (cudaMemcpy(&code, status, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return MGT_CUDA_FAILURE;
     if (out_code) *out_code = static_cast<int32_t>(code);
-    if (code != 0) {
+    if (code != 0 || c->dead) {
+        // CTAs that gave up never reached the arrival counter and the peers' sequence numbers no longer match this
+        // rank's: the communicator stays unusable. Weights that a fused update touched before the wait ran out are
+        // undefined (some slices updated, some not).
         cudaMemset(status, 0, 4);
+        cudaMemset(reinterpret_cast<uint32_t*>(c->local + grad_bytes) + kFlagCounter, 0, 4);
+        c->dead = true;
         return MGT_DEVICE_TIMEOUT;
     }
+    return MGT_OK;
+}
+
+mgt_status_t mgt_comm_set_wait_limit_ms(mgt_comm_t* c, uint32_t milliseconds) {
+    if (c == nullptr || milliseconds == 0 || milliseconds > 60000U) return MGT_INVALID_CONFIG;
+    c->dev.wait_limit_ns = static_cast<uint64_t>(milliseconds) * 1000000ULL;
+    return MGT_OK;
+}
+
+mgt_status_t mgt_comm_host_barrier(mgt_comm_t* c, uint32_t timeout_ms) {
+    if (c == nullptr) return MGT_INVALID_CONFIG;
+    if (c->world <= 1) return MGT_OK;
+    // every rank publishes "<id file>.<nonce>.b<seq>.<rank>" and waits for the files of all the others; a rank removes
+    // its file of the barrier before the last one, which every peer has passed by then
+    const uint64_t seq = ++c->barrier_seq;
+    auto name = [&](uint64_t q, uint32_t r) {
+        char suffix[96];
+        std::snprintf(suffix, sizeof(suffix), ".%016llx.b%llu.%u", static_cast<unsigned long long>(c->nonce), static_cast<unsigned long long>(q), r);
+        return c->id_file + suffix;
+    };
+    const uint8_t mark = 1;
+    if (!WriteFileAtomic(name(seq, c->rank), &mark, 1)) return MGT_IO_FAILURE;
+    const auto start = std::chrono::steady_clock::now();
+    for (uint32_t p = 0; p < c->world; ++p) {
+        if (p == c->rank) continue;
+        for (;;) {
+            std::ifstream in(name(seq, p), std::ios::binary);
+            if (in) break;
+            if (std::chrono::steady_clock::now() - start > std::chrono::milliseconds(timeout_ms)) return MGT_IO_FAILURE;
+            std::this_thread::sleep_for(std::chrono::milliseconds(2));
+        }
+    }
+    if (seq >= 2) std::remove(name(seq - 2, c->rank).c_str());
     return MGT_OK;
 }
 
@@ -480,9 +537,14 @@ mgt_status_t mgt_comm_destroy(mgt_comm_t* c) {
         if (p != c->rank && c->peer_base[p] != nullptr) cudaIpcCloseMemHandle(c->peer_base[p]);
     if (c->local) cudaFree(c->local);
     if (c->world > 1 && !c->id_file.empty()) {
-        char suffix[64];
+        char suffix[96];
         std::snprintf(suffix, sizeof(suffix), ".%016llx.%u", static_cast<unsigned long long>(c->nonce), c->rank);
         std::remove((c->id_file + suffix).c_str());
+        // the file of the last barrier stays: a peer may still be reading it
+        if (c->barrier_seq >= 2) {
+            std::snprintf(suffix, sizeof(suffix), ".%016llx.b%llu.%u", static_cast<unsigned long long>(c->nonce), static_cast<unsigned long long>(c->barrier_seq - 1), c->rank);
+            std::remove((c->id_file + suffix).c_str());
+        }
     }
     delete c;
     return MGT_OK;

@@ -2,7 +2,9 @@
 #include "../../include/mgt_b200.h"
 #include "host_plan.hpp"
 
+#include <algorithm>
 #include <filesystem>
+#include <string>
 #include <vector>
 
 using namespace mgt::host;
@@ -49,6 +51,27 @@ mgt_status_t mgt_plan_write_files(int32_t argc, const char* const* argv, const c
     std::filesystem::create_directories(dir, ec);
     const bool ok = WriteMetadataEnv(dir, p, overlap_allreduce != 0, comm_enabled != 0, resumed != 0) && WriteLayersJson(dir, p) && WriteLinearOpsManifest(dir, p);
     return ok ? MGT_OK : MGT_IO_FAILURE;
+}
+
+mgt_status_t mgt_format_step_record(int32_t argc, const char* const* argv, const mgt_step_record_t* record, int32_t overlap_allreduce, int32_t comm_enabled,
+                                    int32_t resumed, char* start_line, char* log_line, char* profile_row, uint32_t capacity) {
+    TrainPlan p;
+    if (record == nullptr || capacity == 0 || !PlanFromArgs(argc, argv, &p)) return MGT_INVALID_CONFIG;
+    StepRecord r{};
+    r.step = record->step; r.loss = record->loss; r.step_ms = record->step_ms; r.walk_ms = record->walk_ms; r.backward_ms = record->backward_ms;
+    r.allreduce_ms = record->allreduce_ms; r.adam_ms = record->adam_ms; r.memory_bytes = record->memory_bytes;
+    r.overlap_ranges = record->overlap_ranges; r.overlap_chunks = record->overlap_chunks;
+    for (int i = 0; i < 7; ++i) r.bw[i] = record->backward_stage_ms[i];
+    auto put = [&](char* dst, const std::string& text) {
+        if (dst == nullptr) return true;
+        if (text.size() + 1 > capacity) return false;
+        std::copy(text.begin(), text.end(), dst);
+        dst[text.size()] = '\0';
+        return true;
+    };
+    const bool ok = put(start_line, StartLogLine(p, overlap_allreduce != 0, comm_enabled != 0, resumed != 0)) && put(log_line, StepLogLine(p, r)) &&
+                    put(profile_row, StepProfileRow(p, r, overlap_allreduce != 0));
+    return ok ? MGT_OK : MGT_CAPACITY_EXCEEDED;
 }
 
 uint16_t mgt_export_float_to_fp16(float value) { return ExportFloatToFp16(value); }

@@ -4,7 +4,7 @@
 //
 //   per step:  record step_start -> random walks -> forward/loss/backward (gradient-ready
 //              notifications schedule the peer gradient exchange, fused with AdamW, on a second
-//              stream) -> wait for the exchange -> AdamW (single rank or non-overlapped mode)
+//              stream, also with a single rank) -> wait for the exchange -> AdamW (non-overlapped mode only)
 //              -> record step_stop, synchronise, read the loss, write train.log / profile.jsonl
 #include "../../include/mgt_b200.h"
 #include "host_plan.hpp"
@@ -43,6 +43,8 @@ struct ExchangeContext {
     bool have_pending = false;
     uint64_t pending_offset = 0, pending_count = 0;
     bool failed = false;
+    bool have_early = false;  // the early-range hook already sent [early_begin, early_end)
+    uint64_t early_begin = 0, early_end = 0;
 
     // `whole`: no chunking - for the range(s) left when backward has ended and nothing remains to overlap with
     bool LaunchRange(uint64_t offset, uint64_t count, cudaStream_t producer, bool whole) {
@@ -74,6 +76,12 @@ mgt_status_t OnGradientReady(void* user, uint32_t ready_id, uint64_t offset, uin
     // out at once. The range that closes backward (the embedding table) is kept for Flush(whole): nothing is left to
     // overlap with, so it is not cut into buckets.
     if (!ctx->Flush(static_cast<cudaStream_t>(producer_stream))) { ctx->failed = true; return MGT_NCCL_FAILURE; }
+    if (ctx->have_early && ctx->early_begin == offset && ctx->early_end <= offset + count) {
+        // leading blocks of this range went out through the hook: only the rest is left
+        count = offset + count - ctx->early_end;
+        offset = ctx->early_end;
+        if (count == 0) return MGT_OK;
+    }
     if (ctx->expected_ranges != 0 && ctx->scheduled_ranges == ctx->expected_ranges) {
         ctx->have_pending = true;
         ctx->pending_offset = offset;
@@ -81,6 +89,24 @@ mgt_status_t OnGradientReady(void* user, uint32_t ready_id, uint64_t offset, uin
         return MGT_OK;
     }
     if (!ctx->LaunchRange(offset, count, static_cast<cudaStream_t>(producer_stream), false)) { ctx->failed = true; return MGT_NCCL_FAILURE; }
+    return MGT_OK;
+}
+
+// The engine's early-range hook: a leading block of the embedding table's gradient is complete while the kernel that
+// computes the next block still runs, so it goes out now, whole, and is exchanged and updated under that kernel.
+mgt_status_t OnEarlyRange(void* user, uint32_t ready_id, uint64_t offset, uint64_t count, void* producer_stream) {
+    auto* ctx = static_cast<ExchangeContext*>(user);
+    if (ctx == nullptr || !ctx->enabled) return MGT_OK;
+    (void)ready_id;
+    if (ctx->comm == nullptr || ctx->comm_stream == nullptr || ctx->events == nullptr || count == 0) return MGT_INVALID_CONFIG;
+    if (ctx->have_early && offset != ctx->early_end) return MGT_INVALID_CONFIG;  // blocks come in order, end to end
+    if (!ctx->Flush(static_cast<cudaStream_t>(producer_stream)) || !ctx->LaunchRange(offset, count, static_cast<cudaStream_t>(producer_stream), true)) {
+        ctx->failed = true;
+        return MGT_NCCL_FAILURE;
+    }
+    if (!ctx->have_early) ctx->early_begin = offset;
+    ctx->have_early = true;
+    ctx->early_end = offset + count;
     return MGT_OK;
 }
 
@@ -183,10 +209,14 @@ int main(int argc, char** argv) {
     if (!CUDA_OK(cudaEventCreate(&ev_start)) || !CUDA_OK(cudaEventCreate(&ev_walk)) || !CUDA_OK(cudaEventCreate(&ev_backward)) ||
         !CUDA_OK(cudaEventCreate(&ev_allreduce)) || !CUDA_OK(cudaEventCreate(&ev_stop)) ||
         !CUDA_OK(cudaEventCreateWithFlags(&ev_comm_done, cudaEventDisableTiming))) return EXIT_FAILURE;
+    // `overlap` is what the reference calls overlap (tool:737) and what the files report. This trainer also takes the
+    // per-range path with a single rank: the "exchange" is then just the AdamW update of each range on the second stream,
+    // under the rest of backward, instead of one pass over all parameters after it.
     const bool overlap = comm_enabled && opt.overlap_allreduce && opt.world_size > 1;
+    const bool per_range = comm_enabled && opt.overlap_allreduce;
     const uint32_t expected_ranges = 2U * opt.nrd + 3U;
     std::vector<cudaEvent_t> ready_events;
-    if (overlap) {
+    if (per_range) {
         ready_events.resize(expected_ranges + 1U, nullptr);
         for (cudaEvent_t& ev : ready_events)
             if (!CUDA_OK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming))) return EXIT_FAILURE;
@@ -204,6 +234,10 @@ int main(int argc, char** argv) {
         out << steps_done << "\n";
         return static_cast<bool>(out);
     };
+    // The exchange kernels wait at most a second for a peer, so the ranks meet on the host wherever they may have
+    // drifted apart: after start-up (allocations, uploads, module load) and after every checkpoint write.
+    constexpr uint32_t kHostBarrierTimeoutMs = 600000;
+    if (!CUDA_OK(cudaDeviceSynchronize()) || mgt_comm_host_barrier(comm, kHostBarrierTimeoutMs) != MGT_OK) return EXIT_FAILURE;
     for (uint32_t step = first_step; step < first_step + opt.steps; ++step) {
         if (!CUDA_OK(cudaEventRecord(ev_start, compute))) return EXIT_FAILURE;
         float* walk_labels = opt.output_dim == 1 ? d_labels : d_walk_labels;
@@ -214,7 +248,7 @@ int main(int argc, char** argv) {
         // the resumed run restarts its step counter, as the reference does (tool:765,830)
         const mgt_adamw_config_t adamw{P, static_cast<uint64_t>(step) + 1ULL, opt.lr, 0.9f, 0.999f, 1.0e-8f, opt.weight_decay};
         ExchangeContext exchange;
-        if (overlap) {
+        if (per_range) {
             exchange.enabled = true;
             exchange.comm = comm;
             exchange.comm_stream = comm_stream;
@@ -224,11 +258,12 @@ int main(int argc, char** argv) {
             exchange.expected_ranges = expected_ranges;
             exchange.w = d_w; exchange.w_half = d_w_half; exchange.m = d_m; exchange.v = d_v;
         }
+        if (mgt_engine_set_early_range_hook(engine, per_range ? OnEarlyRange : nullptr, per_range ? &exchange : nullptr) != MGT_OK) return EXIT_FAILURE;
         mgt_backward_profile_t bw{};
         const mgt_status_t st = mgt_launch_mlp_loss_grad(engine, &shape, d_w, d_w_half, d_states, d_labels, B, d_loss, d_grad, d_ws, ws_floats,
                                                          opt.input_grad_partial_chunks, opt.input_grad_positions_per_block, opt.input_grad_fp16,
-                                                         opt.linear_fp16, opt.backward_profile ? &bw : nullptr, overlap ? OnGradientReady : nullptr,
-                                                         overlap ? &exchange : nullptr, compute, opt.input_grad_position_tile);
+                                                         opt.linear_fp16, opt.backward_profile ? &bw : nullptr, per_range ? OnGradientReady : nullptr,
+                                                         per_range ? &exchange : nullptr, compute, opt.input_grad_position_tile);
         if (st != MGT_OK) {
             log << "rank=" << opt.global_rank << " step=" << step << " phase=backward status=" << mgt_status_name(st) << " status_code=" << st << "\n";
             std::cerr << "backward failed: " << mgt_status_name(st) << " (" << st << ")\n";
@@ -237,10 +272,10 @@ int main(int argc, char** argv) {
         if (!CUDA_OK(cudaEventRecord(ev_backward, compute))) return EXIT_FAILURE;
         uint32_t overlap_ranges = 0, overlap_chunks = 0;
         bool weights_updated = false;
-        if (overlap) {
+        if (per_range) {
             if (exchange.failed || exchange.scheduled_ranges != expected_ranges || !exchange.Flush(compute, true)) return EXIT_FAILURE;
-            overlap_ranges = exchange.scheduled_ranges;
-            overlap_chunks = exchange.scheduled_chunks;
+            overlap_ranges = overlap ? exchange.scheduled_ranges : 0U;
+            overlap_chunks = overlap ? exchange.scheduled_chunks : 0U;
             if (!CUDA_OK(cudaEventRecord(ev_comm_done, comm_stream)) || !CUDA_OK(cudaStreamWaitEvent(compute, ev_comm_done, 0))) return EXIT_FAILURE;
             weights_updated = true;  // AdamW ran inside the exchange kernels
         } else if (opt.world_size > 1) {
@@ -278,8 +313,11 @@ int main(int argc, char** argv) {
         log << StepLogLine(plan, rec);
         profile << StepProfileRow(plan, rec, overlap);
         const uint32_t done = step + 1U;
-        if (opt.write_artifacts && opt.checkpoint_period_steps != 0 && done % opt.checkpoint_period_steps == 0 && done != first_step + opt.steps &&
-            !write_checkpoint(done, false)) return EXIT_FAILURE;
+        if (opt.checkpoint_period_steps != 0 && done % opt.checkpoint_period_steps == 0 && done != first_step + opt.steps) {
+            // every rank passes here at the same steps, whether or not it writes files itself
+            if (opt.write_artifacts && !write_checkpoint(done, false)) return EXIT_FAILURE;
+            if (mgt_comm_host_barrier(comm, kHostBarrierTimeoutMs) != MGT_OK) return EXIT_FAILURE;
+        }
     }
 
     if (opt.write_artifacts && !write_checkpoint(first_step + opt.steps, true)) return EXIT_FAILURE;

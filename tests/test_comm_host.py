@@ -74,6 +74,40 @@ def test_default_schedule_launches_at_once_and_keeps_the_closing_range_whole():
     assert seen_before[34] == 34
 
 
+def test_early_blocks_go_out_whole_and_the_closing_call_sends_the_rest():
+    # the engine computes the embedding gradient in row blocks and announces every finished block but the last through its
+    # early-range hook; the closing gradient-ready call still names the whole range, as the reference does
+    launches, waits = [], []
+    sched = GradientRangeScheduler(lambda off, cnt: launches.append((off, cnt)), lambda: waits.append(len(launches)),
+                                   bucket_params=(4 << 20) // 4, expected_ranges=35)
+    ranges = p888_ranges()
+    half = 36 * 72 * 2560                                  # 36 of the 72 positions: the README's --input-grad-position-tile
+    for step in range(2):                                  # the second step starts clean
+        launches.clear()
+        sched.begin_step()
+        for i in range(34):
+            assert sched.on_ready(i, *ranges[i]) == 0
+        assert sched.on_early(34, 0, half) == 0
+        assert launches[-1] == (0, half) and len(launches) == 35   # at once and whole: 6 635 520 floats in one launch
+        assert sched.on_ready(34, *ranges[34]) == 0
+        assert len(launches) == 35                          # what is left waits for finish() ...
+        sched.finish()
+        assert launches[-1] == (half, ranges[34][1] - half)  # ... and goes out whole: second block + input bias
+        assert sched.scheduled_ranges == 35 and sched.scheduled_chunks == 36
+        assert sum(c for _, c in launches) == 15460289      # every parameter exactly once
+        covered = sorted(launches)
+        assert all(covered[i][0] + covered[i][1] == covered[i + 1][0] for i in range(len(covered) - 1))
+    # a hook that announced everything leaves nothing for the closing call
+    sched.begin_step()
+    for i in range(34):
+        assert sched.on_ready(i, *ranges[i]) == 0
+    assert sched.on_early(34, 0, half) == 0 and sched.on_early(34, half, ranges[34][1] - half) == 0
+    n = len(launches)
+    assert sched.on_ready(34, *ranges[34]) == 0
+    sched.finish()
+    assert len(launches) == n and sched.on_early(34, 0, 0) == 1
+
+
 def test_scheduler_rejects_unexpected_ranges():
     sched = GradientRangeScheduler(lambda o, c: None, lambda: None, expected_ranges=3)
     sched.begin_step()

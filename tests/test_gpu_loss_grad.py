@@ -161,6 +161,47 @@ def test_trainer_init_weights_first_step(oracle, engine):
     assert prof.input_forward_ms > 0 and prof.input_grad_ms > 0
 
 
+@pytest.mark.parametrize("weights", ["trainer_init", "random"])
+def test_physical_p888_shape(oracle, engine, weights):
+    # the headline model at its physical dims (72 x 72 -> 2560 -> 224, 16 blocks, 1 output: 15 460 289 parameters) on a walk
+    # batch the oracle finishes in seconds: the 224-wide fused tower at its full depth, the 2560-wide embedding and hidden layers
+    moves, target = oracle.cyclic_puzzle(72, 18)
+    _, states, labels, _ = oracle.random_walks(moves, target, seed=1234, epoch=0, step=3, rank=0, k_min=1, k_max=29, samples=512)
+    shape = MlpShape(72, 72, 2560, 224, 16, 1)
+    assert shape.param_count == 15_460_289
+    if weights == "trainer_init":
+        w = trainer_init_weights(shape.param_count)
+    else:
+        # He-like scales per layer keep the activations O(1) through 16 blocks (a flat 0.03 would overflow fp16 here)
+        rng = np.random.default_rng(11)
+        w = np.empty(shape.param_count, np.float32)
+        in_w = 72 * 72 * 2560
+        w[:in_w] = rng.standard_normal(in_w) * 0.08
+        w[in_w:in_w + 2560] = rng.standard_normal(2560) * 0.05
+        lo = in_w + 2560
+        w[lo:lo + 2560 * 224 + 224] = rng.standard_normal(2560 * 224 + 224) * 0.02
+        lo += 2560 * 224 + 224
+        w[lo:] = rng.standard_normal(shape.param_count - lo) * 0.04
+    # With the trainer's 1e-4-scale initial weights the stated 1e-3 holds. With O(1) random weights 33 fp16-rounded layers
+    # amplify every last-bit difference in summation order: the rounding-point model itself sits 4.2e-3 (gradient rel-L2)
+    # from the true-fp32 reference on this case, so two correct fp16 realisations agree only to that order - 5e-3 here,
+    # and the GPU result must be as close to fp32 as the model is.
+    tol = 1e-3 if weights == "trainer_init" else 5e-3
+    loss_g, grad_g, loss_o, grad_o = check_against_oracle(oracle, engine, shape, w, states, labels.reshape(-1, 1), tol=tol)
+    assert abs(loss_g - loss_o) <= 1e-3 * abs(loss_o)
+    # every residual block on its own: weights and biases of fc1/fc2 of block k
+    base = 72 * 72 * 2560 + 2560 + 2560 * 224 + 224
+    blk = 2 * (224 * 224 + 224)
+    for k in range(16):
+        lo, hi = base + k * blk, base + (k + 1) * blk
+        if np.abs(grad_o[lo:hi]).max() > 0:
+            assert rel_l2(grad_g[lo:hi], grad_o[lo:hi]) <= 3 * tol, (k, rel_l2(grad_g[lo:hi], grad_o[lo:hi]))
+    if weights == "random":
+        _, loss_f, grad_f = oracle.loss_grad(shape, w, states, labels.reshape(-1, 1))
+        model_error = rel_l2(grad_o, grad_f)
+        assert rel_l2(grad_g, grad_f) <= 1.5 * model_error + 1e-4, (rel_l2(grad_g, grad_f), model_error)
+
+
 def test_argument_errors(engine):
     cshape = mgt.CudaMlpShape(8, 8, 16, 16, 2, 1)
     t = torch.zeros(4096, device=DEV)

@@ -217,3 +217,49 @@ def test_exported_weight_files_rebuild_the_model(tmp_path, oracle):
     st_b, y_f32 = oracle.forward(shape, expect, states)
     assert st_a == 0 and st_b == 0
     assert np.max(np.abs(y_files - y_f32)) <= 5e-3 * max(1.0, np.max(np.abs(y_f32)))
+
+
+REF_SCRIPTS = "/root/reference/native/tests/scripts"
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(REF_SCRIPTS, "check_native_train_artifacts.sh")),
+                    reason="the reference checkout (with its contract scripts) is not present")
+def test_reference_artifact_script_accepts_our_files(tmp_path):
+    """native/tests/scripts/check_native_train_artifacts.sh, run UNCHANGED (ctest native_train_artifacts, CMakeLists.txt:191)
+    over a run directory written by the trainer's own writers and formatters for the flags of ctest native_train_smoke
+    (defaults: hd1 5, hd2 3, nrd 1). The GPU suite runs the same script over a directory bin/mgt_native_train wrote, where
+    a GPU and the checkout are both present; this leg needs neither a GPU nor the trainer's step loop."""
+    import subprocess
+
+    class Rec(C.Structure):
+        _fields_ = [("step", C.c_uint32), ("loss", C.c_float), ("step_ms", C.c_float), ("walk_ms", C.c_float), ("backward_ms", C.c_float),
+                    ("allreduce_ms", C.c_float), ("adam_ms", C.c_float), ("memory_bytes", C.c_uint64), ("overlap_ranges", C.c_uint32),
+                    ("overlap_chunks", C.c_uint32), ("backward_stage_ms", C.c_float * 7)]
+
+    lib = _lib.load()
+    flags = {"--steps": 2, "--device-id": 0, "--world-size": 1, "--global-rank": 0, "--local-rank": 0}
+    n, arr = _argv(flags)
+    run = tmp_path / "native-train-smoke-run"
+    assert lib.mgt_plan_write_files(n, arr, str(run).encode(), 1, 1, 0) == 0
+    params = 72 * 72 * 8 + 8 + 8 * 8 + 8 + 2 * (8 * 8 + 8) + 8 + 1
+    i = np.arange(params, dtype=np.int64)
+    w = ((i % 29 - 14) * 0.0001).astype(np.float64).astype(np.float32)
+    zeros = np.zeros(params, np.float32)
+    p = lambda a: a.ctypes.data_as(C.c_void_p)
+    lib.mgt_write_run_artifacts.argtypes = [C.c_int32, C.c_void_p, C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    assert lib.mgt_write_run_artifacts(n, arr, str(run).encode(), p(w), p(zeros), p(zeros)) == 0
+    lib.mgt_format_step_record.argtypes = [C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_char_p, C.c_char_p, C.c_char_p, C.c_uint32]
+    start, line, row = (C.create_string_buffer(8192) for _ in range(3))
+    with open(run / "train.log", "w") as log, open(run / "profile.jsonl", "w") as prof:
+        for step in range(2):
+            rec = Rec(step, 30.5 - step, 1.25, 0.02, 1.0, 0.0, 0.1, 123456789, 0, 0, (C.c_float * 7)(*[0.1] * 7))
+            assert lib.mgt_format_step_record(n, arr, C.byref(rec), 0, 1, 0, start if step == 0 else None, line, row, 8192) == 0
+            if step == 0:
+                log.write(start.value.decode())
+            log.write(line.value.decode())
+            prof.write(row.value.decode())
+    for text in open(run / "profile.jsonl"):
+        json.loads(text)  # every row is one JSON object
+    res = subprocess.run(["bash", os.path.join(REF_SCRIPTS, "check_native_train_artifacts.sh"), str(run)], capture_output=True, text=True)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert lib.mgt_format_step_record(n, arr, C.byref(rec), 0, 1, 0, None, line, row, 8) == 3  # capacity_exceeded

@@ -21,6 +21,15 @@ DEV = "cuda:0"
 STATIC_FLOATS = 4 << 20
 
 
+def _static_check():
+    """mgt_static_scratch_check: (status, device code) of the built-in status word, read and cleared."""
+    lib = _lib.load()
+    lib.mgt_static_scratch_check.argtypes = [C.c_void_p, C.POINTER(C.c_int32)]
+    code = C.c_int32(-1)
+    st = int(lib.mgt_static_scratch_check(torch.cuda.current_stream().cuda_stream, C.byref(code)))
+    return st, int(code.value)
+
+
 def _static_gemm(a, lda, a_mn, b, ldb, b_mn, d, m, n, k, splits):
     lib = _lib.load()
     lib.mgt_gemm_split_k_static_scratch.argtypes = [C.c_void_p, C.c_uint32, C.c_int32, C.c_void_p, C.c_uint32, C.c_int32, C.c_void_p,
@@ -48,6 +57,7 @@ def test_static_scratch_gemm_matches_the_ordinary_entry_point_twice_in_a_row():
         assert engine.debug_gemm(a_buf, lda, True, b_buf, ldb, True, want, m, n, k, splits, partial) == 0
         got = torch.full((m, n), float("nan"), device=DEV)
         assert _static_gemm(a_buf, lda, True, b_buf, ldb, True, got, m, n, k, splits) == 0
+        assert _static_check() == (0, 0)  # no bounded wait of its kernels gave up
         torch.cuda.synchronize()
         assert torch.isfinite(got).all()
         # same kernels, same order of additions: identical; the tolerance of the GEMM tests is the outer bound
@@ -66,4 +76,14 @@ def test_static_scratch_gemm_rejects_what_does_not_fit():
     assert _static_gemm(a, k, False, b, k, False, d, m, n, k, 2) == 3      # capacity_exceeded
     assert _static_gemm(a, k, False, b, k, False, d, m, n, k, 1) == 0      # a single split needs no scratch
     assert _static_gemm(a, k, False, b, k, False, d, 0, n, k, 1) == 1
+    # a single split stores 16-byte vectors straight into d when n is a multiple of 4: a d that is only 4-byte aligned is
+    # refused before anything is launched (both entry points share the check)
+    flat = torch.zeros(m * n + 4, device=DEV)
+    odd = flat[1:1 + m * n]
+    assert odd.data_ptr() % 16 == 4
+    assert _static_gemm(a, k, False, b, k, False, odd, m, n, k, 1) == 1
+    engine = mgt.Engine(0)
+    assert engine.debug_gemm(a, k, False, b, k, False, odd, m, n, k, 1, None) == 1
+    engine.close()
+    assert _static_check() == (0, 0)
     torch.cuda.synchronize()
