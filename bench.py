@@ -331,6 +331,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--comm", default="peer", choices=["peer", "nccl"], help="gradient exchange at N>1: the library's NVLink peer kernels, or NCCL + AdamW (the reference's scheme, for comparison)")
     ap.add_argument("--bucket-bytes", type=int, default=4 << 20)
+    ap.add_argument("--no-early-range", action="store_true", help="N>1: exchange the embedding range when backward has ended instead of under the weight-gradient GEMMs")
+    ap.add_argument("--early-fused", action="store_true", help="N>1: also run the AdamW update of the early range under the weight-gradient GEMMs (default: after backward)")
     ap.add_argument("--batch", type=int, default=BATCH, help=argparse.SUPPRESS)  # smaller batches are for ncu captures only
     ap.add_argument("--cpu-samples-per-core", type=int, default=384)
     ap.add_argument("--steps-cpu", type=int, default=2)
@@ -386,18 +388,18 @@ def main():
         grad = torch.zeros(params, device=dev)
         backend = NcclBackend(grad, world)
         exchange = OverlappedGradientExchange(backend, dev, bucket_bytes=args.bucket_bytes, residual_blocks=16, fused_adamw=False)
-    else:
-        # the library's communicator, also for one rank: the per-range "exchange" is then just the AdamW update of each
-        # range on the second stream while backward still runs (what bin/mgt_native_train does)
-        id_file = default_id_file() if world > 1 else None
-        if world > 1:
-            import torch.distributed as dist
-            if rank == 0 and os.path.exists(id_file):
-                os.remove(id_file)  # a stale id file of an earlier run must not be picked up
-            dist.barrier()
+    elif world > 1:
+        import torch.distributed as dist
+        id_file = default_id_file()
+        if rank == 0 and os.path.exists(id_file):
+            os.remove(id_file)  # a stale id file of an earlier run must not be picked up
+        dist.barrier()
         backend = PeerBackend(local_rank, world, rank, id_file, params)
         grad = backend.gradient_tensor(dev)
-        exchange = OverlappedGradientExchange(backend, dev, bucket_bytes=args.bucket_bytes, residual_blocks=16, fused_adamw=True)
+        exchange = OverlappedGradientExchange(backend, dev, bucket_bytes=args.bucket_bytes, residual_blocks=16, fused_adamw=True,
+                                              early_update_after_backward=not args.early_fused)
+    else:
+        grad = torch.zeros(params, device=dev)
     moves_h, target_h = cyclic_puzzle(72, 18)
     puzzle_pinned = torch.from_numpy(np.concatenate([moves_h.reshape(-1), target_h.reshape(-1)])).pin_memory()
     puzzle_dev = torch.empty_like(puzzle_pinned, device=dev)
@@ -410,7 +412,7 @@ def main():
     ws_floats = mgt.mlp_loss_grad_workspace_floats(shape, batch)
     workspace = torch.empty(ws_floats, device=dev)
     engine = mgt.Engine(local_rank)
-    if exchange is not None and exchange.fused:
+    if exchange is not None and not args.no_early_range:
         assert engine.set_early_range_hook(exchange.early_callback) == 0
     walk_cfg = mgt.RandomWalkKernelConfig(batch, 1, 29)
     loss_pinned = torch.zeros(1).pin_memory()

@@ -127,14 +127,13 @@ typedef struct {
 typedef mgt_status_t (*mgt_gradient_ready_fn)(void* user, uint32_t ready_id, uint64_t param_offset,
                                               uint64_t param_count, void* producer_stream);
 
-/* Early-range hook (optional; no counterpart in the reference). The embedding table is 86 % of the p888 parameters and
- * its gradient is the last thing backward produces. With a hook installed and input_grad_position_tile T (0 < T <
- * state_len) the table gradient is computed in blocks of T positions (T * state_value_pad rows), one launch each, and
- * `hook` is called (same signature and rules as gradient_ready; ready_id = the id of the closing announcement) for every
- * finished block but the last, the moment its kernel is enqueued: blocks come in order, end to end, starting at the
- * first parameter of the range. A caller can exchange and update a block while the next one is still being computed.
- * The gradient_ready calls are unchanged - same count, order and ranges as the reference, the whole embedding range
- * last - so a caller that acted on the hook handles only the rest of the range there. NULL removes the hook. */
+/* Early-range hook (optional; no counterpart in the reference). The embedding table and the input bias are 86 % of the
+ * p888 parameters and the reference announces them last. This library computes their gradient BEFORE the weight-gradient
+ * GEMMs of the residual blocks and of the hidden layer, and calls `hook` (same signature and rules as gradient_ready;
+ * ready_id = the id the closing announcement will carry) the moment the kernels producing that range are enqueued, so
+ * that a caller can exchange it while that remaining work runs. The gradient_ready calls are unchanged - same count,
+ * order and ranges as the reference, the embedding range last - so a caller that acted on the hook skips the range
+ * (or handles only what the hook did not name) there. NULL removes the hook. */
 mgt_status_t mgt_engine_set_early_range_hook(mgt_engine_t* engine, mgt_gradient_ready_fn hook, void* user);
 
 /* Number of floats of caller-owned scratch the launch needs (0 = invalid arguments). */
@@ -284,14 +283,6 @@ mgt_status_t mgt_load_puzzle_definition(const char* group_json, const char* targ
 mgt_status_t mgt_debug_gemm(mgt_engine_t* engine, const uint16_t* a, uint32_t lda, int32_t a_mn_major,
                             const uint16_t* b, uint32_t ldb, int32_t b_mn_major, float* d, uint32_t m, uint32_t n,
                             uint32_t k, uint32_t splits, float* partial_scratch, void* stream);
-
-/* How the embedding-layer GEMMs deal their work to `grid` CTAs (host only, no GPU): the N range [n_begin, n_end) of every
- * (M tile, K split) is laid end to end, cut into equal shares and each share into units of at most max_cols columns.
- * out_units receives grid * (*out_stride) records {m tile, n_base, n_count, split}; a CTA's list ends at the first record
- * with n_count == 0. MGT_INVALID_CONFIG when no such list exists (the kernels then deal whole tiles round-robin).
- * No counterpart in the reference. */
-mgt_status_t mgt_debug_work_list(uint32_t grid, uint32_t m_tiles, uint32_t splits, uint32_t n_begin, uint32_t n_end,
-                                 uint32_t max_cols, uint32_t* out_units, uint32_t out_capacity_units, uint32_t* out_stride);
 
 /* Split-K GEMM that allocates nothing. No counterpart in the reference.
  *

@@ -41,6 +41,7 @@ class GradientRangeScheduler:
     expected_ranges: Optional[int] = None
     lag: int = 0                                     # notifications a range is held back (1 = fused update behind an engine that announces a layer before its dX GEMM)
     whole_tail: bool = True                          # ranges left at finish() go out unchunked: nothing remains to overlap with
+    launch_early: Optional[Callable[[int, int], None]] = None   # how a range from the early hook is sent (default: like any other)
     scheduled_ranges: int = 0
     scheduled_chunks: int = 0
     log: List[ScheduledChunk] = field(default_factory=list)
@@ -55,15 +56,15 @@ class GradientRangeScheduler:
         self._early = []
 
     def on_early(self, ready_id: int, param_offset: int, param_count: int) -> int:
-        """The engine's early-range hook (mgt_engine_set_early_range_hook): a leading block of the range that closes
-        backward (rows of the embedding table) is complete while the kernel that computes the next block still runs.
-        It goes out at once and whole, so that its exchange and update run under that kernel; the closing gradient-ready
-        call then only sends what is left of the range."""
+        """The engine's early-range hook (mgt_engine_set_early_range_hook): the range that closes backward in the
+        reference's order (embedding table + input bias), or a leading part of it, is complete while weight-gradient
+        GEMMs of other layers are still to run. It goes out at once and whole, so that its exchange runs under that
+        work; the closing gradient-ready call then only sends what is left of the range, if anything."""
         if param_count == 0:
             return 1
         self._flush(0)
         self.wait_for_producer()
-        self.launch(param_offset, param_count)
+        (self.launch_early or self.launch)(param_offset, param_count)
         self.log.append(ScheduledChunk(ready_id, param_offset, param_count))
         self.scheduled_chunks += 1
         self._early.append((param_offset, param_count))
@@ -180,7 +181,8 @@ class OverlappedGradientExchange:
     """Wires a back-end, a second CUDA stream and the scheduler to the engine's gradient-ready
     callback, the way the reference trainer's step loop does (tool:785-821)."""
 
-    def __init__(self, backend: PeerBackend, device, bucket_bytes: int = 4 << 20, residual_blocks: int = 16, fused_adamw: bool = True):
+    def __init__(self, backend: PeerBackend, device, bucket_bytes: int = 4 << 20, residual_blocks: int = 16, fused_adamw: bool = True,
+                 early_update_after_backward: bool = True):
         import torch
         self.torch = torch
         self.backend = backend
@@ -192,8 +194,13 @@ class OverlappedGradientExchange:
         self.done_event = torch.cuda.Event()
         self.adamw: Optional[AdamWKernelConfig] = None
         self.state = None
+        # The range from the early hook is exchanged while HBM-bound weight-gradient GEMMs run. Its AdamW update (30 bytes of
+        # HBM traffic per parameter) would fight them for bandwidth, so by default only the NVLink exchange overlaps and the
+        # update of that range follows once backward has ended.
+        self.early_update_after_backward = early_update_after_backward and fused_adamw
+        self._deferred = []
         self.scheduler = GradientRangeScheduler(self._launch, self._wait_for_producer, bucket_params=max(1, bucket_bytes // 4),
-                                                expected_ranges=2 * residual_blocks + 3, lag=0)
+                                                expected_ranges=2 * residual_blocks + 3, lag=0, launch_early=self._launch_early)
 
     def _wait_for_producer(self):
         ev = self.events[self._ev % len(self.events)]
@@ -210,9 +217,18 @@ class OverlappedGradientExchange:
         if st != 0:
             raise MgtError(st, "gradient exchange")
 
+    def _launch_early(self, offset: int, count: int):
+        if not self.early_update_after_backward:
+            return self._launch(offset, count)
+        st = self.backend.allreduce_average(offset, count, stream=self.comm_stream)
+        if st != 0:
+            raise MgtError(st, "gradient exchange")
+        self._deferred.append((offset, count))
+
     def begin_step(self, adamw: AdamWKernelConfig, w, w_half, m, v):
         self.adamw = adamw
         self.state = (w, w_half, m, v)
+        self._deferred = []
         self.scheduler.begin_step()
 
     def callback(self, user, ready_id, offset, count, stream) -> int:
@@ -225,6 +241,17 @@ class OverlappedGradientExchange:
         self.scheduler.finish()
         self.done_event.record(self.comm_stream)
         self.torch.cuda.current_stream(self.device).wait_event(self.done_event)  # tool:820-821
+        if self._deferred:
+            from .api import launch_adamw_kernel_with_half_mirror
+            w, w_half, m, v = self.state
+            grad = self.backend.gradient_tensor(self.device)
+            for offset, count in self._deferred:
+                cfg = AdamWKernelConfig(count, self.adamw.step, self.adamw.learning_rate, self.adamw.beta1, self.adamw.beta2, self.adamw.eps,
+                                        self.adamw.weight_decay)
+                hi = offset + count
+                st = launch_adamw_kernel_with_half_mirror(cfg, w[offset:hi], w_half[offset:hi], grad[offset:hi], m[offset:hi], v[offset:hi])
+                if st != 0:
+                    raise MgtError(st, "AdamW")
 
 
 class NcclBackend:

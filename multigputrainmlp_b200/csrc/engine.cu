@@ -65,8 +65,6 @@ struct Workspace {
     uint64_t off_a1, off_x, off_r1, off_xf, off_dzf, off_dz2, off_dz1t, off_dz1, off_partial, off_head, off_wint, off_dy, off_dyh, off_colsum;
     uint64_t colsum_floats, colsum_slot_floats, off_colsum_h1, dz_stride;
     uint64_t off_bits, bits_stride;  // ReLU sign bits of the residual tower: 2R+1 entries of bits_stride words
-    uint64_t off_a1bits;             // sign bits of a1 (embedding output): [B][a1_words]
-    uint32_t a1_words;
     uint64_t x_stride, r1_stride;  // bytes between consecutive blocks' tensors
     uint64_t partial_floats, head_blocks;
     uint64_t total_bytes;
@@ -138,8 +136,6 @@ Workspace PlanWorkspace(const mgt_mlp_shape_t& s, uint32_t B, uint32_t sm_count)
     w.off_colsum_h1 = take((uint64_t)sm_count * 16 * s.hd1 * 4);
     w.bits_stride = chain_tiles * 128 * 8;
     w.off_bits = take(w.bits_stride * 4 * (2 * w.R + 1));
-    w.a1_words = (s.hd1 + 31U) / 32U;
-    w.off_a1bits = take((uint64_t)B * w.a1_words * 4);
     // internal fp16 weight copy (used when the caller's mirror cannot be addressed by TMA as it lies)
     const uint64_t wint_halfs = (uint64_t)(w.IN + 1) * w.p_w1 + (uint64_t)s.hd1 * w.p_w2 + 2ULL * w.R * s.hd2 * w.p_w2 + (uint64_t)s.hd2 * w.p_wout;
     w.off_wint = take(wint_halfs * 2 + 1024ULL * (2 * w.R + 4));
@@ -147,60 +143,6 @@ Workspace PlanWorkspace(const mgt_mlp_shape_t& s, uint32_t B, uint32_t sm_count)
     w.off_dyh = take((uint64_t)B * w.p_wout * 2);
     w.total_bytes = off + 1024;  // slack to align the caller's base
     return w;
-}
-
-// ---- work lists of the one-hot kernels ----------------------------------------------------------
-// The N range [n_begin, n_end) of every (M tile, K split) is laid end to end and cut into `grid` equal shares (multiples
-// of 16 columns), one per CTA; a share is then cut into units of at most `max_cols` columns. So every CTA has the same
-// amount of MMA work - no partly filled last wave - and the first unit of CTA b is shortened by 16 * (b % 16) columns,
-// which spreads the epilogues (bursts of output traffic during which the CTA's tensor pipe idles) over time instead of
-// having all CTAs reach them together.
-struct WorkUnit { uint32_t mt, n_base, n_count, sp; };
-constexpr uint32_t kWorkStride = 96;  // units per CTA, the terminating zero unit included (hd1 4096 at batch 131 072 needs 58)
-
-bool BuildWorkList(uint32_t grid, uint32_t m_tiles, uint32_t splits, uint32_t n_begin, uint32_t n_end, uint32_t max_cols, std::vector<WorkUnit>* out) {
-    out->assign(static_cast<size_t>(grid) * kWorkStride, WorkUnit{0, 0, 0, 0});
-    if (grid == 0 || m_tiles == 0 || splits == 0 || n_end <= n_begin || max_cols < 32) return false;
-    const uint64_t span = n_end - n_begin;
-    const uint64_t total = static_cast<uint64_t>(m_tiles) * splits * span;
-    const uint64_t share = ((total + grid - 1) / grid + 15) / 16 * 16;
-    for (uint32_t b = 0; b < grid; ++b) {
-        uint64_t lo = static_cast<uint64_t>(b) * share;
-        const uint64_t hi = std::min<uint64_t>(total, lo + share);
-        uint32_t used = 0;
-        bool first = true;
-        while (lo < hi) {
-            const uint64_t segment = lo / span;                                   // which (M tile, split)
-            const uint64_t seg_end = std::min<uint64_t>(hi, (segment + 1) * span);
-            uint64_t len = seg_end - lo;
-            const uint32_t pieces = static_cast<uint32_t>((len + max_cols - 1) / max_cols);
-            uint64_t base = (len / pieces + 15) / 16 * 16;                        // near-equal pieces, multiples of 16
-            if (base > max_cols) base = max_cols;
-            uint64_t first_len = base;
-            if (first && pieces >= 2) {
-                // shorten the first piece; the others share what it gives up, as long as they stay within max_cols
-                const uint64_t shift = 16ULL * (b % 16U);
-                if (base > shift + 32 && (len - (base - shift) + (pieces - 2)) / (pieces - 1) <= max_cols) first_len = base - shift;
-            }
-            first = false;
-            uint64_t pos = lo;
-            for (uint32_t piece = 0; piece < pieces && pos < seg_end; ++piece) {
-                uint64_t n = piece == 0 ? first_len : ((seg_end - pos) / (pieces - piece) + 15) / 16 * 16;
-                if (n > max_cols) n = max_cols;
-                if (piece + 1 == pieces || pos + n > seg_end) n = seg_end - pos;
-                if (n > max_cols || used + 1 >= kWorkStride) return false;
-                WorkUnit& u = (*out)[static_cast<size_t>(b) * kWorkStride + used++];
-                u.mt = static_cast<uint32_t>(segment / splits);
-                u.sp = static_cast<uint32_t>(segment % splits);
-                u.n_base = n_begin + static_cast<uint32_t>(pos - segment * span);
-                u.n_count = static_cast<uint32_t>(n);
-                pos += n;
-            }
-            if (pos != seg_end) return false;
-            lo = seg_end;
-        }
-    }
-    return true;
 }
 
 // ---- engine -----------------------------------------------------------------------------------
@@ -240,35 +182,9 @@ struct mgt_engine {
     cudaEvent_t ev_last = nullptr, ev_now = nullptr;
     uint64_t launches = 0;  // kernels launched through this engine (host-side count)
     bool layered_tower = false;  // MGT_RESIDUAL_PATH=layered: per-layer GEMMs instead of the fused residual-tower kernels (both are tested)
+    uint32_t onehot_tune = 0;    // kTune* switches of the embedding-layer GEMMs (MGT_ONEHOT_TUNE overrides the default)
     mgt_gradient_ready_fn early_fn = nullptr;  // mgt_engine_set_early_range_hook
     void* early_user = nullptr;
-    // work lists of the one-hot kernels, built on the host once per shape and kept on the device (slots of one list each)
-    static constexpr uint32_t kWorkSlots = 16;
-    uint4* work_dev = nullptr;
-    struct WorkKey { uint32_t grid, m_tiles, splits, n_begin, n_end, max_cols; };
-    std::vector<WorkKey> work_keys;
-    bool balanced_units = true;  // MGT_ONEHOT_UNITS=tiles: whole tiles dealt round-robin instead (both are tested)
-
-    // Device address of the work list for this cut, uploading it on `stream` the first time (the copy is ordered before the
-    // launch that uses it; an engine is driven from one stream at a time). Null when no list applies.
-    const uint4* WorkList(uint32_t grid, uint32_t m_tiles, uint32_t splits, uint32_t n_begin, uint32_t n_end, uint32_t max_cols, cudaStream_t stream) {
-        if (!balanced_units || work_dev == nullptr) return nullptr;
-        std::lock_guard<std::mutex> lock(mu);
-        for (size_t i = 0; i < work_keys.size(); ++i) {
-            const WorkKey& k = work_keys[i];
-            if (k.grid == grid && k.m_tiles == m_tiles && k.splits == splits && k.n_begin == n_begin && k.n_end == n_end && k.max_cols == max_cols)
-                return work_dev + i * static_cast<size_t>(sm_count) * mgt::kWorkStride;
-        }
-        if (grid > static_cast<uint32_t>(sm_count)) return nullptr;
-        std::vector<mgt::WorkUnit> list;
-        if (!mgt::BuildWorkList(grid, m_tiles, splits, n_begin, n_end, max_cols, &list)) return nullptr;
-        if (work_keys.size() >= kWorkSlots) work_keys.clear();  // slots are reused in order; launches still in flight on `stream` finish first
-        const size_t slot = work_keys.size();
-        uint4* dst = work_dev + slot * static_cast<size_t>(sm_count) * mgt::kWorkStride;
-        if (cudaMemcpyAsync(dst, list.data(), list.size() * sizeof(mgt::WorkUnit), cudaMemcpyHostToDevice, stream) != cudaSuccess) return nullptr;
-        work_keys.push_back(WorkKey{grid, m_tiles, splits, n_begin, n_end, max_cols});
-        return dst;
-    }
 
     // fp16 3-D tensor map (a stack of `layers` equal matrices `layer_stride_bytes` apart), 128-byte swizzle, box depth 1
     bool Map3D(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t layers, uint64_t pitch_elems, uint64_t layer_stride_bytes,
@@ -337,19 +253,18 @@ mgt_status_t LaunchGemm(mgt_engine* e, const CUtensorMap& ta, const CUtensorMap&
     const uint64_t units = (uint64_t)args.m_tiles * args.n_tiles * args.splits * (Cfg::GROUPED ? args.groups : 1U);
     if (units == 0) return MGT_INVALID_CONFIG;
     uint32_t grid = (uint32_t)(units < (uint64_t)e->sm_count ? units : (uint64_t)e->sm_count);
-    if (Cfg::kOneHot) {
-        // equal shares of the N range per CTA instead of whole tiles (see BuildWorkList); without a list the kernel deals tiles
-        const uint32_t n_end = args.n_end != 0U ? args.n_end : args.N;
-        args.work = e->WorkList(grid, args.m_tiles, args.splits, args.n_begin, n_end, Cfg::NACC * Cfg::BN, stream);
-        args.work_stride = kWorkStride;
-        if (args.work == nullptr && (args.n_begin != 0U || n_end != args.N)) return MGT_INVALID_CONFIG;  // a partial range needs a list
-    }
     if (Cfg::BSTAT) {
         // every unit of a CTA must share the N tile: unit = mt * n_tiles + nt advances by the grid size
         if (args.splits != 1 || args.k_chunks > (uint32_t)Cfg::SB || args.n_tiles > (uint32_t)e->sm_count) return MGT_INVALID_CONFIG;
         if (grid >= args.n_tiles) grid = grid / args.n_tiles * args.n_tiles;
     }
     args.status = e->status_word;
+    if (Cfg::kOneHot) {
+        args.tune = e->onehot_tune;
+        // one sixteenth of the time the MMAs of one unit take at full rate (8 MMAs of 65 ns per 64-deep chunk): the largest
+        // delay, 15 steps, stays below the unit of slack that the delayed CTAs have
+        args.stagger_ns = (args.k_chunks / args.splits) * 32U;
+    }
     umma_gemm_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, args);
     ++e->launches;
     return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
@@ -723,7 +638,6 @@ mgt_status_t GemmBackpropInput(mgt_engine* e, cudaStream_t st, const __half* dz,
     GemmArgs a = BaseArgs(M, N, K, p.bn, 1);
     a.out_f32 = epi.out_f32; a.ld_f32 = epi.ld_f32; a.out_f16 = epi.out_f16; a.ld_f16 = epi.ld_f16;
     a.add_f32 = epi.add_f32; a.ld_add = epi.ld_add; a.mask = epi.mask; a.ld_mask = epi.ld_mask;
-    a.mask_bits = epi.mask_bits; a.ld_bits = epi.ld_bits;
     a.colsum = colsum;
     CUtensorMap ta, tb;
     MGT_MAP(e->Map(&ta, dz, K, M, dz_pitch, 64, 128));
@@ -986,10 +900,8 @@ mgt_status_t mgt_engine_create(int32_t device_id, mgt_engine_t** out_engine) {
     }
     e->encode = reinterpret_cast<EncodeTiledFn>(fn);
     if (const char* path = std::getenv("MGT_RESIDUAL_PATH")) e->layered_tower = std::strcmp(path, "layered") == 0;
-    if (const char* units = std::getenv("MGT_ONEHOT_UNITS")) e->balanced_units = std::strcmp(units, "tiles") != 0;
-    if (cudaMalloc(&e->status_word, sizeof(int)) != cudaSuccess || cudaMemset(e->status_word, 0, sizeof(int)) != cudaSuccess ||
-        cudaMalloc(&e->work_dev, static_cast<size_t>(mgt_engine::kWorkSlots) * e->sm_count * kWorkStride * sizeof(uint4)) != cudaSuccess) {
-        if (e->status_word) cudaFree(e->status_word);
+    if (const char* tune = std::getenv("MGT_ONEHOT_TUNE")) e->onehot_tune = static_cast<uint32_t>(std::strtoul(tune, nullptr, 0));
+    if (cudaMalloc(&e->status_word, sizeof(int)) != cudaSuccess || cudaMemset(e->status_word, 0, sizeof(int)) != cudaSuccess) {
         delete e;
         return MGT_CUDA_FAILURE;
     }
@@ -1002,7 +914,6 @@ mgt_status_t mgt_engine_destroy(mgt_engine_t* e) {
     if (e->ev_last) cudaEventDestroy(e->ev_last);
     if (e->ev_now) cudaEventDestroy(e->ev_now);
     if (e->status_word) cudaFree(e->status_word);
-    if (e->work_dev) cudaFree(e->work_dev);
     delete e;
     return MGT_OK;
 }
@@ -1037,6 +948,7 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
                                       float* workspace, uint64_t workspace_floats, uint32_t chunks, uint32_t ppb, int32_t half_ig,
                                       int32_t half_lin, mgt_backward_profile_t* profile, mgt_gradient_ready_fn ready, void* ready_user,
                                       void* stream_v, uint32_t position_tile) {
+    (void)position_tile;
     if (e == nullptr || !ValidShape(shape) || w == nullptr || states == nullptr || labels == nullptr || loss == nullptr || grad == nullptr ||
         B == 0 || workspace == nullptr || chunks == 0 || ppb == 0) {
         return MGT_INVALID_CONFIG;
@@ -1068,7 +980,6 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     auto dz_tape = [&](uint32_t k) { return reinterpret_cast<__half*>(base + ws.off_dz2 + ws.dz_stride * k); };   // [0] hidden, [k+1] fc2 of block k
     auto dz1_tape = [&](uint32_t k) { return reinterpret_cast<__half*>(base + ws.off_dz1t + ws.dz_stride * k); };  // fc1 of block k
     __half* dz1_h = reinterpret_cast<__half*>(base + ws.off_dz1);
-    uint32_t* a1_bits = reinterpret_cast<uint32_t*>(base + ws.off_a1bits);
     float* partial = reinterpret_cast<float*>(base + ws.off_partial);
     float* head_partial = reinterpret_cast<float*>(base + ws.off_head);
     float* colsum = reinterpret_cast<float*>(base + ws.off_colsum);
@@ -1118,7 +1029,6 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     {
         GemmArgs a = BaseArgs(H1, B, IN + 1, CfgEmbFwd::NACC * CfgEmbFwd::BN, 1);
         a.out_f16 = a1_h; a.ld_f16 = ws.p_a1;
-        a.out_bits = a1_bits; a.ld_bits = ws.a1_words;  // [a1 > 0], one bit per element: the mask of the hidden layer's dX GEMM
         a.states = reinterpret_cast<const uint8_t*>(states); a.state_len = s.state_len; a.value_pad = s.state_value_pad; a.samples = B; a.in_rows = IN;
         CUtensorMap ta;
         MGT_MAP(e->Map(&ta, hw.in_table, H1, IN + 1, hw.p1, 64, 64));
@@ -1213,6 +1123,62 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
         MGT_TRY(GemmBackpropInput<Epi::kAddMaskF32F16>(e, st, dz1_tape(k), ws.p_dz, hw.w1[k], hw.p2, B, H2, H2, d1,
                                                         colsum + ws.colsum_slot_floats * (R + k), nullptr));
     }
+    if (!timer.Mark(profile ? &profile->residual_backward_ms : nullptr)) return MGT_CUDA_FAILURE;
+
+    // Order of what follows: the dX GEMMs run first, down to the embedding gradient; the weight-gradient GEMMs of the tower
+    // and of the hidden layer (which only read tapes) come last. The embedding table is 86 % of the parameters: this way
+    // its gradient is complete - and the early-range hook can hand it to the exchange - while a third of a millisecond
+    // of weight-gradient work is still to run. The gradient-ready notifications keep the reference's order.
+
+    // ---- hidden layer backward, dX part (mlp_backward.cu:1417-1438): dz_tape(0) = dcur * [x0 > 0]
+    dz_cur = dz_tape(0);
+    if (half_ig) {
+        GemmArgs d{};  // dz1 = (dzh * Wh^T) * [a1 > 0]
+        d.mask = a1_h; d.ld_mask = ws.p_a1; d.out_f16 = dz1_h; d.ld_f16 = ws.p_dz1;
+        if (cudaMemsetAsync(colsum_h1, 0, (uint64_t)PlanBackprop(e, B, H1, H2).rows * H1 * sizeof(float), st) != cudaSuccess) return MGT_CUDA_FAILURE;
+        MGT_TRY(GemmBackpropInput<Epi::kMaskF16>(e, st, dz_cur, ws.p_dz, hw.wh, hw.p2, B, H1, H2, d, colsum_h1, grad + InputBias(s)));
+    } else {
+        // --input-grad-fp16 0: the embedding gradient wants dz1 in fp32 (mlp_backward.cu:1433-1504, float one-hot GEMM).
+        // da1 from the same fp16 operands with fp32 accumulation, masked in fp32, then the table gradient on CUDA cores.
+        using namespace mgt::fp32path;
+        const uint64_t bh1 = (uint64_t)B * H1;
+        if (Sgemm<false, true>(st, B, H1, H2, dz_cur, ws.p_dz, hw.wh, hw.p2, da1_f32, H1) != cudaSuccess) return MGT_CUDA_FAILURE;
+        MaskKernel<__half><<<GridFor(bh1, 256, e->sm_count), 256, 0, st>>>(da1_f32, nullptr, a1_h, H1, ws.p_a1, bh1, false, dz1_f32);
+        ColumnSumKernel<<<(H1 + 7) / 8, 256, 0, st>>>(dz1_f32, B, H1, grad + InputBias(s));
+        e->launches += 3;
+        if (cudaGetLastError() != cudaSuccess) return MGT_CUDA_FAILURE;
+    }
+    if (!timer.Mark(profile ? &profile->hidden_backward_ms : nullptr)) return MGT_CUDA_FAILURE;
+
+    // ---- embedding gradient: grad W_in = onehot^T * dz1  (mlp_backward.cu:1440-1504); the input-bias
+    // gradient (mlp_backward.cu:1505) is the column sum written by the GEMM above
+    if (!half_ig) {
+        using namespace mgt::fp32path;
+        EmbeddingGradKernel<float><<<dim3(s.state_len, (H1 + 63) / 64), 128, 2ULL * s.state_value_pad * 64 * sizeof(float), st>>>(
+            reinterpret_cast<const uint8_t*>(states), dz1_f32, H1, B, s.state_value_pad, H1, grad);
+        ++e->launches;
+        if (cudaGetLastError() != cudaSuccess) return MGT_CUDA_FAILURE;
+    } else {
+        GemmArgs a = BaseArgs(H1, IN, B, CfgEmbGrad::NACC * CfgEmbGrad::BN, 1);
+        const uint64_t tiles = (uint64_t)a.m_tiles * a.n_tiles;
+        // Two splits keep fp32 atomics order-independent (0 + a + b == 0 + b + a); use them when one
+        // split would leave a large part of the last wave idle.
+        const uint64_t waves1 = (tiles + e->sm_count - 1) / e->sm_count;
+        const uint64_t waves2 = (2 * tiles + e->sm_count - 1) / e->sm_count;
+        const uint32_t splits = (a.k_chunks >= 2 && waves2 < 2 * waves1) ? 2U : 1U;
+        a = BaseArgs(H1, IN, B, CfgEmbGrad::NACC * CfgEmbGrad::BN, splits);
+        a.out_f32 = grad; a.ld_f32 = H1;
+        a.states = reinterpret_cast<const uint8_t*>(states); a.state_len = s.state_len; a.value_pad = s.state_value_pad; a.samples = B;
+        a.in_rows = 0xFFFFFFFFU;  // no all-ones row in this direction
+        if (a.splits > 1 && cudaMemsetAsync(grad, 0, (uint64_t)IN * H1 * sizeof(float), st) != cudaSuccess) return MGT_CUDA_FAILURE;
+        CUtensorMap ta;
+        MGT_MAP(e->Map(&ta, dz1_h, H1, B, ws.p_dz1, 64, 64));
+        MGT_TRY(LaunchGemm<CfgEmbGrad>(e, ta, ta, a, st));
+    }
+    // table and input bias are complete: tell a caller who asked to hear of it before the weight-gradient GEMMs are enqueued
+    if (e->early_fn != nullptr && e->early_fn(e->early_user, 2U * R + 2U, 0, InputBias(s) + H1, stream_v) != MGT_OK) return MGT_CUDA_FAILURE;
+    if (!timer.Mark(profile ? &profile->input_grad_ms : nullptr)) return MGT_CUDA_FAILURE;
+
     if (R > 0) {
         // weight gradients of all blocks: two grouped split-K GEMMs (fc2: r1_k^T dz2_k, fc1: x_k^T dz1_k)
         MGT_TRY(GemmGradWeightsGrouped(e, st, r1_h(0), ws.p_act, ws.r1_stride, dz_tape(1), ws.p_dz, ws.dz_stride, R, B, H2, H2, partial,
@@ -1235,85 +1201,12 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     }
     if (!timer.Mark(profile ? &profile->residual_backward_ms : nullptr)) return MGT_CUDA_FAILURE;
 
-    // ---- hidden layer backward (mlp_backward.cu:1417-1438): dz_tape(0) = dcur * [x0 > 0]
-    dz_cur = dz_tape(0);
+    // ---- hidden layer backward, dW part; every kernel that reads the hidden weights was enqueued long before, so a caller
+    // may update the range in place as soon as it is announced
     MGT_TRY(GemmGradWeights(e, st, a1_h, ws.p_a1, dz_cur, ws.p_dz, B, H1, H2, partial, ws.partial_floats, grad + HiddenWeight(s)));
-    if (half_ig) {
-        GemmArgs d{};  // dz1 = (dzh * Wh^T) * [a1 > 0], the mask from the 1-bit-per-element copy the embedding GEMM wrote (17 MB, not 272 MB)
-        d.mask = a1_h; d.ld_mask = ws.p_a1; d.mask_bits = a1_bits; d.ld_bits = ws.a1_words; d.out_f16 = dz1_h; d.ld_f16 = ws.p_dz1;
-        if (cudaMemsetAsync(colsum_h1, 0, (uint64_t)PlanBackprop(e, B, H1, H2).rows * H1 * sizeof(float), st) != cudaSuccess) return MGT_CUDA_FAILURE;
-        MGT_TRY(GemmBackpropInput<Epi::kMaskF16>(e, st, dz_cur, ws.p_dz, hw.wh, hw.p2, B, H1, H2, d, colsum_h1, grad + InputBias(s)));
-    } else {
-        // --input-grad-fp16 0: the embedding gradient wants dz1 in fp32 (mlp_backward.cu:1433-1504, float one-hot GEMM).
-        // da1 from the same fp16 operands with fp32 accumulation, masked in fp32, then the table gradient on CUDA cores.
-        using namespace mgt::fp32path;
-        const uint64_t bh1 = (uint64_t)B * H1;
-        if (Sgemm<false, true>(st, B, H1, H2, dz_cur, ws.p_dz, hw.wh, hw.p2, da1_f32, H1) != cudaSuccess) return MGT_CUDA_FAILURE;
-        MaskKernel<__half><<<GridFor(bh1, 256, e->sm_count), 256, 0, st>>>(da1_f32, nullptr, a1_h, H1, ws.p_a1, bh1, false, dz1_f32);
-        ColumnSumKernel<<<(H1 + 7) / 8, 256, 0, st>>>(dz1_f32, B, H1, grad + InputBias(s));
-        e->launches += 3;
-        if (cudaGetLastError() != cudaSuccess) return MGT_CUDA_FAILURE;
-    }
-    // announced only now, after the last kernel that reads the hidden weights: a caller may update a range in place as
-    // soon as it is announced
     MGT_TRY(notify(HiddenWeight(s), (uint64_t)H1 * H2 + H2));
     if (!timer.Mark(profile ? &profile->hidden_backward_ms : nullptr)) return MGT_CUDA_FAILURE;
-
-    // ---- embedding gradient: grad W_in = onehot^T * dz1  (mlp_backward.cu:1440-1504); the input-bias
-    // gradient (mlp_backward.cu:1505) is the column sum written by the GEMM above
-    if (!half_ig) {
-        using namespace mgt::fp32path;
-        EmbeddingGradKernel<float><<<dim3(s.state_len, (H1 + 63) / 64), 128, 2ULL * s.state_value_pad * 64 * sizeof(float), st>>>(
-            reinterpret_cast<const uint8_t*>(states), dz1_f32, H1, B, s.state_value_pad, H1, grad);
-        ++e->launches;
-        if (cudaGetLastError() != cudaSuccess) return MGT_CUDA_FAILURE;
-    } else {
-        constexpr uint32_t kCols = CfgEmbGrad::NACC * CfgEmbGrad::BN;
-        GemmArgs a = BaseArgs(H1, IN, B, kCols, 1);
-        const uint64_t tiles = (uint64_t)a.m_tiles * a.n_tiles;
-        // Two splits keep fp32 atomics order-independent (0 + a + b == 0 + b + a); use them when one
-        // split would leave a large part of the last wave idle.
-        const uint64_t waves1 = (tiles + e->sm_count - 1) / e->sm_count;
-        const uint64_t waves2 = (2 * tiles + e->sm_count - 1) / e->sm_count;
-        const uint32_t splits = (a.k_chunks >= 2 && waves2 < 2 * waves1) ? 2U : 1U;
-        a = BaseArgs(H1, IN, B, kCols, splits);
-        a.out_f32 = grad; a.ld_f32 = H1;
-        a.states = reinterpret_cast<const uint8_t*>(states); a.state_len = s.state_len; a.value_pad = s.state_value_pad; a.samples = B;
-        a.in_rows = 0xFFFFFFFFU;  // no all-ones row in this direction
-        if (a.splits > 1 && cudaMemsetAsync(grad, 0, (uint64_t)IN * H1 * sizeof(float), st) != cudaSuccess) return MGT_CUDA_FAILURE;
-        CUtensorMap ta;
-        MGT_MAP(e->Map(&ta, dz1_h, H1, B, ws.p_dz1, 64, 64));
-        // The table rows in blocks of `position_tile` positions, one launch each (the reference's own tiling unit,
-        // mlp_backward.cu:1440-1459): a finished block of rows is a finished range of the gradient, and the early-range
-        // hook hands it to the exchange while the next block is still being computed - that launch is tensor-bound and
-        // leaves HBM and NVLink idle. Needs the balanced work lists (a block is not a whole number of 512-row tiles).
-        const uint32_t tile_pos = (position_tile == 0U || position_tile >= s.state_len || !e->balanced_units || e->early_fn == nullptr) ? s.state_len : position_tile;
-        const uint32_t blocks = (s.state_len + tile_pos - 1U) / tile_pos;
-        for (uint32_t blk = 0; blk < blocks; ++blk) {
-            const uint32_t r0 = blk * tile_pos * s.state_value_pad;
-            const uint32_t r1 = blk + 1U == blocks ? IN : (blk + 1U) * tile_pos * s.state_value_pad;
-            GemmArgs ab = a;
-            if (blocks > 1U) {
-                ab.n_begin = r0; ab.n_end = r1;
-                ab.n_tiles = (r1 - r0 + kCols - 1U) / kCols;  // sizes the grid
-            }
-            MGT_TRY(LaunchGemm<CfgEmbGrad>(e, ta, ta, ab, st));
-            if (blk + 1U < blocks && e->early_fn(e->early_user, 2U * R + 2U, (uint64_t)r0 * H1, (uint64_t)(r1 - r0) * H1, stream_v) != MGT_OK) return MGT_CUDA_FAILURE;
-        }
-    }
-    if (!timer.Mark(profile ? &profile->input_grad_ms : nullptr)) return MGT_CUDA_FAILURE;
     MGT_TRY(notify(0, InputBias(s) + H1));
-    return MGT_OK;
-}
-
-mgt_status_t mgt_debug_work_list(uint32_t grid, uint32_t m_tiles, uint32_t splits, uint32_t n_begin, uint32_t n_end, uint32_t max_cols,
-                                 uint32_t* out_units, uint32_t out_capacity_units, uint32_t* out_stride) {
-    if (out_units == nullptr || out_stride == nullptr) return MGT_INVALID_CONFIG;
-    std::vector<WorkUnit> list;
-    if (!BuildWorkList(grid, m_tiles, splits, n_begin, n_end, max_cols, &list)) return MGT_INVALID_CONFIG;
-    if (list.size() > out_capacity_units) return MGT_CAPACITY_EXCEEDED;
-    std::memcpy(out_units, list.data(), list.size() * sizeof(WorkUnit));
-    *out_stride = kWorkStride;
     return MGT_OK;
 }
 
@@ -1323,16 +1216,6 @@ mgt_status_t mgt_engine_set_early_range_hook(mgt_engine_t* e, mgt_gradient_ready
     e->early_user = user;
     return MGT_OK;
 }
-
-#ifdef MGT_PROBE_TIMELINE
-// working-build hook: copies the per-CTA cycle counters of the one-hot kernels to the host and clears them
-__attribute__((visibility("default"))) mgt_status_t mgt_probe_read(unsigned long long* out) {
-    if (cudaDeviceSynchronize() != cudaSuccess) return MGT_CUDA_FAILURE;
-    if (cudaMemcpyFromSymbol(out, g_probe_cycles, sizeof(unsigned long long) * 2 * 148 * 8) != cudaSuccess) return MGT_CUDA_FAILURE;
-    static unsigned long long zeros[2 * 148 * 8] = {};
-    return cudaMemcpyToSymbol(g_probe_cycles, zeros, sizeof(zeros)) == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
-}
-#endif
 
 mgt_status_t mgt_debug_gemm(mgt_engine_t* e, const uint16_t* a, uint32_t lda, int32_t a_mn, const uint16_t* b, uint32_t ldb, int32_t b_mn,
                             float* d, uint32_t m, uint32_t n, uint32_t k, uint32_t splits, float* partial_scratch, void* stream) {

@@ -131,6 +131,11 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* map, int
         : "memory");
 }
 
+// Asks for the box at (x, y) to be brought into L2; nothing arrives in shared memory and nothing is signalled.
+__device__ __forceinline__ void tma_prefetch_2d(const void* map, int32_t x, int32_t y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y) : "memory");
+}
+
 // The same for a 3-D tensor (x innermost): used when one descriptor spans a stack of equally shaped matrices.
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* map, int32_t x, int32_t y, int32_t z, uint64_t* bar) {
     asm volatile(

@@ -39,6 +39,11 @@ struct ExchangeContext {
     uint16_t* w_half = nullptr;
     float* m = nullptr;
     float* v = nullptr;
+    float* grad = nullptr;
+    uint32_t world_size = 1, global_rank = 0;
+    bool early_update_after_backward = true;  // the early range: exchange under the weight-gradient GEMMs, AdamW once backward has ended
+    bool have_deferred = false;
+    uint64_t deferred_offset = 0, deferred_count = 0;
     uint32_t scheduled_ranges = 0, scheduled_chunks = 0, next_event = 0, expected_ranges = 0;
     bool have_pending = false;
     uint64_t pending_offset = 0, pending_count = 0;
@@ -46,13 +51,19 @@ struct ExchangeContext {
     bool have_early = false;  // the early-range hook already sent [early_begin, early_end)
     uint64_t early_begin = 0, early_end = 0;
 
-    // `whole`: no chunking - for the range(s) left when backward has ended and nothing remains to overlap with
-    bool LaunchRange(uint64_t offset, uint64_t count, cudaStream_t producer, bool whole) {
+    // `whole`: no chunking - for the range(s) left when backward has ended and nothing remains to overlap with.
+    // `exchange_only`: average the gradients now, leave the AdamW update of the range to the caller (UpdateDeferred).
+    bool LaunchRange(uint64_t offset, uint64_t count, cudaStream_t producer, bool whole, bool exchange_only = false) {
         cudaEvent_t ev = (*events)[next_event++ % events->size()];
         if (!CUDA_OK(cudaEventRecord(ev, producer)) || !CUDA_OK(cudaStreamWaitEvent(comm_stream, ev, 0))) return false;
         while (count > 0) {
             const uint64_t chunk = whole ? count : std::min<uint64_t>(count, bucket_params);
-            if (mgt_comm_allreduce_average_adamw(comm, offset, chunk, &adamw, w, w_half, m, v, comm_stream) != MGT_OK) return false;
+            if (exchange_only) {
+                const mgt_allreduce_config_t ar{world_size, global_rank, 0, chunk};
+                if (mgt_comm_allreduce_average(comm, &ar, grad + offset, comm_stream) != MGT_OK) return false;
+            } else if (mgt_comm_allreduce_average_adamw(comm, offset, chunk, &adamw, w, w_half, m, v, comm_stream) != MGT_OK) {
+                return false;
+            }
             offset += chunk;
             count -= chunk;
             ++scheduled_chunks;
@@ -63,6 +74,17 @@ struct ExchangeContext {
         if (!have_pending) return true;
         have_pending = false;
         return LaunchRange(pending_offset, pending_count, producer, whole);
+    }
+    // AdamW of the range whose exchange ran without it; `stream` has already waited for the exchange.
+    bool UpdateDeferred(cudaStream_t stream) {
+        if (!have_deferred) return true;
+        have_deferred = false;
+        mgt_adamw_config_t cfg = adamw;
+        cfg.param_count = deferred_count;
+        const uint64_t o = deferred_offset;
+        const mgt_status_t st = w_half != nullptr ? mgt_launch_adamw_with_half_mirror(&cfg, w + o, w_half + o, grad + o, m + o, v + o, stream)
+                                                  : mgt_launch_adamw(&cfg, w + o, grad + o, m + o, v + o, stream);
+        return st == MGT_OK;
     }
 };
 
@@ -100,9 +122,18 @@ mgt_status_t OnEarlyRange(void* user, uint32_t ready_id, uint64_t offset, uint64
     (void)ready_id;
     if (ctx->comm == nullptr || ctx->comm_stream == nullptr || ctx->events == nullptr || count == 0) return MGT_INVALID_CONFIG;
     if (ctx->have_early && offset != ctx->early_end) return MGT_INVALID_CONFIG;  // blocks come in order, end to end
-    if (!ctx->Flush(static_cast<cudaStream_t>(producer_stream)) || !ctx->LaunchRange(offset, count, static_cast<cudaStream_t>(producer_stream), true)) {
+    // The AdamW update moves 30 bytes per parameter through HBM and would fight the HBM-bound weight-gradient GEMMs that
+    // run now; the NVLink exchange alone hardly touches local memory. So the update of this range is left for later,
+    // unless an earlier early range is still waiting for its own (then this one takes the fused path).
+    const bool defer = ctx->early_update_after_backward && !ctx->have_deferred;
+    if (!ctx->Flush(static_cast<cudaStream_t>(producer_stream)) || !ctx->LaunchRange(offset, count, static_cast<cudaStream_t>(producer_stream), true, defer)) {
         ctx->failed = true;
         return MGT_NCCL_FAILURE;
+    }
+    if (defer) {
+        ctx->have_deferred = true;
+        ctx->deferred_offset = offset;
+        ctx->deferred_count = count;
     }
     if (!ctx->have_early) ctx->early_begin = offset;
     ctx->have_early = true;
@@ -209,14 +240,10 @@ int main(int argc, char** argv) {
     if (!CUDA_OK(cudaEventCreate(&ev_start)) || !CUDA_OK(cudaEventCreate(&ev_walk)) || !CUDA_OK(cudaEventCreate(&ev_backward)) ||
         !CUDA_OK(cudaEventCreate(&ev_allreduce)) || !CUDA_OK(cudaEventCreate(&ev_stop)) ||
         !CUDA_OK(cudaEventCreateWithFlags(&ev_comm_done, cudaEventDisableTiming))) return EXIT_FAILURE;
-    // `overlap` is what the reference calls overlap (tool:737) and what the files report. This trainer also takes the
-    // per-range path with a single rank: the "exchange" is then just the AdamW update of each range on the second stream,
-    // under the rest of backward, instead of one pass over all parameters after it.
     const bool overlap = comm_enabled && opt.overlap_allreduce && opt.world_size > 1;
-    const bool per_range = comm_enabled && opt.overlap_allreduce;
     const uint32_t expected_ranges = 2U * opt.nrd + 3U;
     std::vector<cudaEvent_t> ready_events;
-    if (per_range) {
+    if (overlap) {
         ready_events.resize(expected_ranges + 1U, nullptr);
         for (cudaEvent_t& ev : ready_events)
             if (!CUDA_OK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming))) return EXIT_FAILURE;
@@ -248,7 +275,7 @@ int main(int argc, char** argv) {
         // the resumed run restarts its step counter, as the reference does (tool:765,830)
         const mgt_adamw_config_t adamw{P, static_cast<uint64_t>(step) + 1ULL, opt.lr, 0.9f, 0.999f, 1.0e-8f, opt.weight_decay};
         ExchangeContext exchange;
-        if (per_range) {
+        if (overlap) {
             exchange.enabled = true;
             exchange.comm = comm;
             exchange.comm_stream = comm_stream;
@@ -256,14 +283,15 @@ int main(int argc, char** argv) {
             exchange.bucket_params = std::max<uint64_t>(1ULL, opt.allreduce_bucket_bytes / sizeof(float));
             exchange.adamw = adamw;
             exchange.expected_ranges = expected_ranges;
-            exchange.w = d_w; exchange.w_half = d_w_half; exchange.m = d_m; exchange.v = d_v;
+            exchange.w = d_w; exchange.w_half = d_w_half; exchange.m = d_m; exchange.v = d_v; exchange.grad = d_grad;
+            exchange.world_size = opt.world_size; exchange.global_rank = opt.global_rank;
         }
-        if (mgt_engine_set_early_range_hook(engine, per_range ? OnEarlyRange : nullptr, per_range ? &exchange : nullptr) != MGT_OK) return EXIT_FAILURE;
+        if (mgt_engine_set_early_range_hook(engine, overlap ? OnEarlyRange : nullptr, overlap ? &exchange : nullptr) != MGT_OK) return EXIT_FAILURE;
         mgt_backward_profile_t bw{};
         const mgt_status_t st = mgt_launch_mlp_loss_grad(engine, &shape, d_w, d_w_half, d_states, d_labels, B, d_loss, d_grad, d_ws, ws_floats,
                                                          opt.input_grad_partial_chunks, opt.input_grad_positions_per_block, opt.input_grad_fp16,
-                                                         opt.linear_fp16, opt.backward_profile ? &bw : nullptr, per_range ? OnGradientReady : nullptr,
-                                                         per_range ? &exchange : nullptr, compute, opt.input_grad_position_tile);
+                                                         opt.linear_fp16, opt.backward_profile ? &bw : nullptr, overlap ? OnGradientReady : nullptr,
+                                                         overlap ? &exchange : nullptr, compute, opt.input_grad_position_tile);
         if (st != MGT_OK) {
             log << "rank=" << opt.global_rank << " step=" << step << " phase=backward status=" << mgt_status_name(st) << " status_code=" << st << "\n";
             std::cerr << "backward failed: " << mgt_status_name(st) << " (" << st << ")\n";
@@ -272,11 +300,12 @@ int main(int argc, char** argv) {
         if (!CUDA_OK(cudaEventRecord(ev_backward, compute))) return EXIT_FAILURE;
         uint32_t overlap_ranges = 0, overlap_chunks = 0;
         bool weights_updated = false;
-        if (per_range) {
+        if (overlap) {
             if (exchange.failed || exchange.scheduled_ranges != expected_ranges || !exchange.Flush(compute, true)) return EXIT_FAILURE;
-            overlap_ranges = overlap ? exchange.scheduled_ranges : 0U;
-            overlap_chunks = overlap ? exchange.scheduled_chunks : 0U;
+            overlap_ranges = exchange.scheduled_ranges;
+            overlap_chunks = exchange.scheduled_chunks;
             if (!CUDA_OK(cudaEventRecord(ev_comm_done, comm_stream)) || !CUDA_OK(cudaStreamWaitEvent(compute, ev_comm_done, 0))) return EXIT_FAILURE;
+            if (!exchange.UpdateDeferred(compute)) return EXIT_FAILURE;
             weights_updated = true;  // AdamW ran inside the exchange kernels
         } else if (opt.world_size > 1) {
             const mgt_allreduce_config_t ar{opt.world_size, opt.global_rank, step, P};

@@ -50,12 +50,6 @@ struct GemmArgs {
     uint32_t ld_add;
     const __half* mask;
     uint32_t ld_mask;
-    // The same mask as one bit per element: word (row, c / 32) bit (c % 32) = [activation(row, c) > 0]. When given, the
-    // kMaskF16 / kAddMaskF32F16 epilogues read it instead of `mask` (4 bytes per row and chunk instead of 64).
-    const uint32_t* mask_bits;
-    uint32_t ld_bits;        // words per row
-    // kEmbFwd: where to write those bits for the activation it produces (rows = samples, may be null)
-    uint32_t* out_bits;
     float* partial;
     // Optional fp32 column sums of the values the kMaskF16 / kAddMaskF32F16 epilogues produce
     // (bias gradients): row (blockIdx.x * 8 + epilogue warp) of colsum[gridDim.x * 8][N] accumulates
@@ -67,15 +61,20 @@ struct GemmArgs {
     uint32_t value_pad;      // classes per position
     uint32_t samples;
     uint32_t in_rows;        // state_len * value_pad; row `in_rows` is the all-ones (bias) row
-    // Optional work list (one-hot kernels): CTA b runs units work[b * work_stride + 0, 1, ...] until one with n_count == 0.
-    // A unit is an M tile, a K split and n_count (<= NACC * BN) consecutive columns of N starting at n_base: the host cuts the
-    // N range so that every CTA gets the same amount of work (no partial last wave) and so that neighbouring CTAs reach
-    // their epilogues at different times. Null: units are whole tiles, dealt round-robin.
-    const uint4* work;       // {m tile, n_base, n_count, split}
-    uint32_t work_stride;
-    uint32_t n_begin, n_end; // host side only: the N range a work list is to cover (0, 0 = all of N)
+    // Tuning switches of the one-hot kernels (kTune* bits) and the start delay step of kTuneStagger in nanoseconds
+    uint32_t tune;
+    uint32_t stagger_ns;
     int* status;             // device status word, 0 = ok
 };
+
+// kTuneStagger: CTAs that have one unit less than the busiest ones (the last round of tiles is rarely full) start late, by
+//   (blockIdx % 16) * stagger_ns: the slack they have anyway is spent so that the CTAs stop reaching their epilogues - a
+//   burst of output traffic during which a CTA's tensor pipe idles - all at the same moment.
+// kTuneSpin: the two hand-overs of the synthesised operand (stage released -> synthesis, stage published -> MMA) poll
+//   with test_wait instead of the suspending try_wait.
+// kTunePrefetch: the TMA warp asks L2 for the A boxes kPrefetchChunks chunks ahead of the one it loads.
+constexpr uint32_t kTuneStagger = 1U, kTuneSpin = 2U, kTunePrefetch = 4U;
+constexpr uint32_t kPrefetchChunks = 8U;
 
 // BSTAT_: "B-stationary" - for short reductions (K <= 64*SB_) the whole B operand of the CTA's N tile is loaded
 // once and stays in shared memory while the CTA streams its M tiles (all units of a CTA then share the N tile).
@@ -124,11 +123,6 @@ struct GemmCfg {
     static_assert(!BSTAT_ || (!kOneHot && NACC_ == 1), "B-stationary applies to TMA-fed single-accumulator tiles");
     static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
-
-#ifdef MGT_PROBE_TIMELINE
-// [CTA][8]: MMA thread: total, wait acc_empty, wait full_a, wait full_b, issue; synth warp 0: wait empty_b, work; items
-__device__ unsigned long long g_probe_cycles[2 * 148 * 8];  // forward kernel first, gradient kernel second
-#endif
 
 namespace detail {
 
@@ -272,6 +266,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
+    if (Cfg::kOneHot && (args.tune & kTuneStagger) != 0U && blockIdx.x < total_units) {
+        const uint32_t my_units = (total_units - blockIdx.x + gridDim.x - 1U) / gridDim.x;
+        const uint32_t max_units = (total_units + gridDim.x - 1U) / gridDim.x;
+        if (my_units < max_units) {
+            if (threadIdx.x == 0) {
+                const uint64_t wait_ns = static_cast<uint64_t>(blockIdx.x % 16U) * args.stagger_ns;
+                const uint64_t t0 = global_timer_ns();
+                while (global_timer_ns() - t0 < wait_ns) __nanosleep(500);
+            }
+            __syncthreads();
+        }
+    }
 
     // unit -> (m tile, n tile, split): splits of one tile are neighbours for TMA-fed GEMMs; for the
     // embedding layers units that share the A stream (same m tile and split) are neighbours.
@@ -291,38 +297,29 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
     };
     auto chunk_begin = [&](uint32_t sp) { return static_cast<uint32_t>((static_cast<uint64_t>(sp) * args.k_chunks) / args.splits); };
-    // The ui-th unit of this CTA: from the work list when there is one, else tile (blockIdx.x + ui * gridDim.x).
-    struct Unit { uint32_t id, mt, nt, sp, n_base, n_count; };
-    auto get_unit = [&](uint32_t ui, Unit& u) -> bool {
-        if (Cfg::kOneHot && args.work != nullptr) {
-            if (ui + 1U >= args.work_stride) return false;
-            const uint4 w = __ldg(args.work + static_cast<uint64_t>(blockIdx.x) * args.work_stride + ui);
-            if (w.z == 0U) return false;
-            u.id = ui; u.mt = w.x; u.nt = 0U; u.n_base = w.y; u.n_count = w.z; u.sp = w.w;
-            return true;
-        }
-        const uint64_t unit = static_cast<uint64_t>(blockIdx.x) + static_cast<uint64_t>(ui) * gridDim.x;
-        if (unit >= total_units) return false;
-        u.id = static_cast<uint32_t>(unit);
-        decode(u.id, u.mt, u.nt, u.sp);
-        u.n_base = u.nt * (NACC * BN);
-        u.n_count = u.n_base < args.N ? min(static_cast<uint32_t>(NACC * BN), args.N - u.n_base) : 0U;
-        return true;
-    };
 
     if (warp == 0) {
         // ------------------------------- TMA producer -------------------------------------
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            Unit un;
-            for (uint32_t ui = 0; ok && get_unit(ui, un); ++ui) {
-                const uint32_t unit = un.id, mt = un.mt, nt = un.nt, sp = un.sp;
+            for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+                uint32_t mt, nt, sp;
+                decode(unit, mt, nt, sp);
                 const uint32_t c0 = chunk_begin(sp), c1 = chunk_begin(sp + 1);
                 for (uint32_t c = c0; c < c1; ++c, ++it) {
                     const uint32_t sa = it % SA, pa = (it / SA) & 1U;
                     if (!mbar_wait(&empty_a[sa], pa ^ 1U, cta_abort, kAbortProducerWait)) { ok = false; break; }
                     uint8_t* a_dst = a_ring + sa * Cfg::A_STAGE_BYTES;
+                    if (Cfg::kOneHot && (args.tune & kTunePrefetch) != 0U && c + kPrefetchChunks < c1) {
+                        const int32_t cp = static_cast<int32_t>((c + kPrefetchChunks) * 64U);
+                        if (Cfg::A_MN) {
+                            tma_prefetch_2d(&tma_a, static_cast<int32_t>(mt * BM), cp);
+                            tma_prefetch_2d(&tma_a, static_cast<int32_t>(mt * BM + 64), cp);
+                        } else {
+                            tma_prefetch_2d(&tma_a, cp, static_cast<int32_t>(mt * BM));
+                        }
+                    }
                     mbar_arrive_expect_tx(&full_a[sa], Cfg::A_STAGE_BYTES);
                     if (Cfg::GROUPED) {
                         const int32_t g = static_cast<int32_t>(group_of(unit));
@@ -334,7 +331,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     } else {
                         tma_load_2d(a_dst, &tma_a, static_cast<int32_t>(c * 64), static_cast<int32_t>(mt * BM), &full_a[sa]);
                     }
-                    if (!Cfg::kOneHot && (!Cfg::BSTAT || ui == 0U)) {
+                    if (!Cfg::kOneHot && (!Cfg::BSTAT || unit == blockIdx.x)) {
                         // B-stationary: chunk c of B lives in stage c for the whole kernel, loaded with the first unit
                         const uint32_t sb = Cfg::BSTAT ? (c - c0) : it % SB, pb = Cfg::BSTAT ? 0U : (it / SB) & 1U;
                         if (!Cfg::BSTAT && !mbar_wait(&empty_b[sb], pb ^ 1U, cta_abort, kAbortProducerWait)) { ok = false; break; }
@@ -366,47 +363,26 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     } else if (warp == 1) {
         // ------------------------------- UMMA issuer --------------------------------------
         if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_f16(BM, BN, Cfg::A_MN, Cfg::B_MN);
             uint32_t it = 0, unit_iter = 0;
             bool ok = true;
-#ifdef MGT_PROBE_TIMELINE
-            long long p_acc = 0, p_a = 0, p_b = 0, p_issue = 0;
-            const long long p_start = clock64();
-#define MGT_PROBE_T(var) const long long var = clock64()
-#define MGT_PROBE_ADD(dst, t0, t1) dst += (t1) - (t0)
-#else
-#define MGT_PROBE_T(var)
-#define MGT_PROBE_ADD(dst, t0, t1)
-#endif
-            Unit un;
-            for (uint32_t ui = 0; ok && get_unit(ui, un); ++ui, ++unit_iter) {
-                const uint32_t sp = un.sp;
+            for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++unit_iter) {
+                uint32_t mt, nt, sp;
+                decode(unit, mt, nt, sp);
                 const uint32_t c0 = chunk_begin(sp), c1 = chunk_begin(sp + 1);
                 const uint32_t ab = unit_iter % ACC_BUFS, aph = (unit_iter / ACC_BUFS) & 1U;
-                // one-hot kernels: accumulator `acc` holds columns [acc * BN, acc * BN + BN) of the unit; a narrow unit
-                // runs narrower MMAs (N a multiple of 16) and may leave the second accumulator out
-                uint32_t acc_idesc[NACC];
-#pragma unroll
-                for (int acc = 0; acc < NACC; ++acc) {
-                    const uint32_t lo = static_cast<uint32_t>(acc * BN);
-                    const uint32_t cols = !Cfg::kOneHot ? static_cast<uint32_t>(BN) : (un.n_count > lo ? min(static_cast<uint32_t>(BN), un.n_count - lo) : 0U);
-                    acc_idesc[acc] = cols == 0U ? 0U : make_idesc_f16(BM, (cols + 15U) & ~15U, Cfg::A_MN, Cfg::B_MN);
-                }
-                MGT_PROBE_T(q0);
                 if (!mbar_wait(&acc_empty[ab], aph ^ 1U, cta_abort, kAbortMmaWait)) { ok = false; break; }
-                MGT_PROBE_T(q1);
-                MGT_PROBE_ADD(p_acc, q0, q1);
                 tc_fence_after();
                 const uint32_t d_base = tmem_base + ab * (NACC * Cfg::ACC_COLS);
                 for (uint32_t c = c0; c < c1; ++c, ++it) {
                     const uint32_t sa = it % SA, pa = (it / SA) & 1U;
                     const uint32_t sb = Cfg::BSTAT ? (c - c0) : it % SB, pb = Cfg::BSTAT ? 0U : (it / SB) & 1U;
-                    MGT_PROBE_T(w0);
                     if (!mbar_wait(&full_a[sa], pa, cta_abort, kAbortMmaWait)) { ok = false; break; }
-                    MGT_PROBE_T(w1);
-                    if ((!Cfg::BSTAT || ui == 0U) && !mbar_wait(&full_b[sb], pb, cta_abort, kAbortMmaWait)) { ok = false; break; }
-                    MGT_PROBE_T(w2);
-                    MGT_PROBE_ADD(p_a, w0, w1);
-                    MGT_PROBE_ADD(p_b, w1, w2);
+                    if (!Cfg::BSTAT || unit == blockIdx.x) {
+                        const bool got = (Cfg::kOneHot && (args.tune & kTuneSpin) != 0U) ? mbar_wait_spin(&full_b[sb], pb, cta_abort, kAbortMmaWait)
+                                                                                       : mbar_wait(&full_b[sb], pb, cta_abort, kAbortMmaWait);
+                        if (!got) { ok = false; break; }
+                    }
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(a_ring + sa * Cfg::A_STAGE_BYTES);
                     const uint32_t b_addr = smem_u32(b_ring + sb * Cfg::B_STAGE_BYTES);
@@ -414,28 +390,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     const uint32_t ksteps = k_left >= 64U ? 4U : (k_left + 15U) / 16U;
 #pragma unroll
                     for (int acc = 0; acc < NACC; ++acc) {
-                        if (acc_idesc[acc] == 0U) continue;
                         for (uint32_t kk = 0; kk < ksteps; ++kk) {
                             const uint64_t a_desc = Cfg::A_MN ? make_smem_desc(a_addr + kk * 2048U, 8192U, 1024U)
                                                               : make_smem_desc(a_addr + kk * 32U, 16U, 1024U);
                             const uint64_t b_desc = Cfg::B_MN ? make_smem_desc(b_addr + acc * Cfg::B_ACC_BYTES + kk * 2048U, 8192U, 1024U)
                                                               : make_smem_desc(b_addr + acc * Cfg::B_ACC_BYTES + kk * 32U, 16U, 1024U);
-                            umma_f16(d_base + acc * Cfg::ACC_COLS, a_desc, b_desc, acc_idesc[acc], (c > c0 || kk > 0U) ? 1U : 0U);
+                            umma_f16(d_base + acc * Cfg::ACC_COLS, a_desc, b_desc, idesc, (c > c0 || kk > 0U) ? 1U : 0U);
                         }
                     }
                     umma_commit(&empty_a[sa]);
                     if (!Cfg::BSTAT) umma_commit(&empty_b[sb]);
-                    MGT_PROBE_T(w3);
-                    MGT_PROBE_ADD(p_issue, w2, w3);
                 }
                 if (ok) umma_commit(&acc_full[ab]);
             }
-#ifdef MGT_PROBE_TIMELINE
-            if (Cfg::kOneHot && blockIdx.x < 148) {
-                unsigned long long* o = g_probe_cycles + ((Cfg::BSRC == BSource::kOneHotGrad ? 148 : 0) + blockIdx.x) * 8;
-                o[0] = clock64() - p_start; o[1] = p_acc; o[2] = p_a; o[3] = p_b; o[4] = p_issue;
-            }
-#endif
         }
         __syncwarp();
     } else if (warp < 2U + Cfg::EPI_WARPS) {
@@ -450,9 +417,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         if constexpr (Cfg::kOneHot) {
             // Embedding layers: D is the transposed result, so a TMEM lane (row of D) is a column of the
             // row-major tensor and the 32 lanes of a warp already write consecutive addresses.
-            Unit un;
-            for (uint32_t ui = 0; ok && get_unit(ui, un); ++ui, ++unit_iter) {
-                const uint32_t mt = un.mt;
+            for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++unit_iter) {
+                uint32_t mt, nt, sp;
+                decode(unit, mt, nt, sp);
                 const uint32_t ab = unit_iter % ACC_BUFS, aph = (unit_iter / ACC_BUFS) & 1U;
                 if (!__all_sync(0xFFFFFFFFU, mbar_wait(&acc_full[ab], aph, cta_abort, kAbortEpilogueWait))) { ok = false; break; }
                 tc_fence_after();
@@ -462,27 +429,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 for (int acc = 0; acc < NACC; ++acc) {
 #pragma unroll 1
                     for (int cc = static_cast<int>(chunk_parity); cc < BN / 32; cc += Cfg::EPI_STRIDE) {
-                        const uint32_t local = static_cast<uint32_t>(acc * BN + cc * 32);  // column inside the unit
-                        if (local >= un.n_count) continue;
-                        const uint32_t n0 = un.n_base + local;
+                        const uint32_t n0 = (nt * NACC + acc) * BN + cc * 32;
+                        if (n0 >= args.N) continue;
                         uint32_t r[32];
                         tmem_ld_32x32(tmem_base + ((quad * 32U) << 16) + ab * (NACC * Cfg::ACC_COLS) + acc * Cfg::ACC_COLS + cc * 32, r);
                         tmem_ld_wait();
-                        const uint32_t valid = min(32U, un.n_count - local);
-                        if constexpr (Cfg::EPI == Epi::kEmbFwd) {
-                            if (args.out_bits != nullptr) {
-                                // this warp's 32 rows of D are 32 consecutive columns of the activation: one word of sign bits per
-                                // sample, taken from the value as it is stored (rounded to fp16: a tiny positive sum may round to 0)
-                                uint32_t word = 0;
-#pragma unroll
-                                for (int j = 0; j < 32; ++j) {
-                                    const __half h = __float2half_rn(fmaxf(__uint_as_float(r[j]), 0.0f));
-                                    const uint32_t b = __ballot_sync(0xFFFFFFFFU, m_ok && __half_as_ushort(h) != 0U);
-                                    if (lane == static_cast<uint32_t>(j)) word = b;
-                                }
-                                if (lane < valid && mt * BM + quad * 32U < args.M) args.out_bits[static_cast<uint64_t>(n0 + lane) * args.ld_bits + ((mt * BM + quad * 32U) >> 5)] = word;
-                            }
-                        }
+                        const uint32_t valid = min(32U, args.N - n0);
                         if (m_ok) {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) {
@@ -529,15 +481,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             }
             const uint32_t r4 = lane >> 3, c4 = (lane & 7U) * 4U;  // fp32 vectors: 4 rows x 8 lanes
             const uint32_t r8 = lane >> 2, c8 = (lane & 3U) * 8U;  // fp16 vectors: 8 rows x 4 lanes
-            const bool ld_vec = (!kHasAdd || (args.ld_add & 3U) == 0U) && (!kHasMask || args.mask_bits != nullptr || (args.ld_mask & 7U) == 0U) &&
+            const bool ld_vec = (!kHasAdd || (args.ld_add & 3U) == 0U) && (!kHasMask || (args.ld_mask & 7U) == 0U) &&
                                 (!kOutF32 || (args.ld_f32 & 3U) == 0U) && (kPartial ? (args.N & 3U) == 0U : (args.ld_f16 & 7U) == 0U);
             struct Operands {
                 float4 add[kHasAdd ? 8 : 1];
                 uint4 mask[kHasMask ? 4 : 1];
-                uint32_t bits;
                 float bias;
             };
-            const bool use_bits = kHasMask && args.mask_bits != nullptr;
             // requests the global operands of chunk n0 of the tile whose first row is m_base (vector form only)
             auto request = [&](Operands& o, uint32_t m_base, uint32_t rows_ok, uint32_t n0) {
                 if (n0 + 32U > args.N || !ld_vec) return;
@@ -551,21 +501,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     }
                 }
                 if constexpr (kHasMask) {
-                    if (use_bits) {
-                        o.bits = lane < rows_ok ? __ldg(args.mask_bits + static_cast<uint64_t>(m_base + lane) * args.ld_bits + (n0 >> 5)) : 0U;
-                    } else {
 #pragma unroll
-                        for (uint32_t i = 0; i < 4U; ++i) {
-                            const uint32_t rr = r8 + 8U * i;
-                            o.mask[i] = rr < rows_ok ? *reinterpret_cast<const uint4*>(args.mask + static_cast<uint64_t>(m_base + rr) * args.ld_mask + n0 + c8)
-                                                     : make_uint4(0, 0, 0, 0);
-                        }
+                    for (uint32_t i = 0; i < 4U; ++i) {
+                        const uint32_t rr = r8 + 8U * i;
+                        o.mask[i] = rr < rows_ok ? *reinterpret_cast<const uint4*>(args.mask + static_cast<uint64_t>(m_base + rr) * args.ld_mask + n0 + c8)
+                                                 : make_uint4(0, 0, 0, 0);
                     }
                 }
             };
-            Unit un;
-            for (uint32_t ui = 0; ok && get_unit(ui, un); ++ui, ++unit_iter) {
-                const uint32_t unit = un.id, mt = un.mt, nt = un.nt, sp = un.sp;
+            for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++unit_iter) {
+                uint32_t mt, nt, sp;
+                decode(unit, mt, nt, sp);
                 const uint32_t ab = unit_iter % ACC_BUFS, aph = (unit_iter / ACC_BUFS) & 1U;
                 const uint32_t m_base = mt * BM + quad * 32U;
                 const uint32_t rows_ok = m_base < args.M ? min(32U, args.M - m_base) : 0U;
@@ -615,10 +561,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     }
                     if constexpr (kHasMask) {
                         uint32_t bits = 0;
-                        if (use_bits) {
-                            // bits past the last column were written as 0, so a ragged chunk needs no extra care
-                            bits = vec ? cur.bits : (lane < rows_ok ? __ldg(args.mask_bits + static_cast<uint64_t>(m_base + lane) * args.ld_bits + (n0 >> 5)) : 0U);
-                        } else if (vec) {
+                        if (vec) {
                             uint8_t* mask_bytes = reinterpret_cast<uint8_t*>(mask_words);
 #pragma unroll
                             for (uint32_t i = 0; i < 4U; ++i) {
@@ -731,9 +674,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 uint8_t* row = buf + (n / BN) * Cfg::B_ACC_BYTES + (n % BN) * 128U;
                 return reinterpret_cast<uint16_t*>(row + ((((k >> 3) ^ (n & 7U)) << 4) | ((k & 7U) << 1)));
             };
-            // writes `value` (fp16 1.0 or 0) at the non-zero places of item (unit columns [n_base, n_base + n_count), chunk c)
-            // in stage buffer `buf`
-            auto apply = [&](uint8_t* buf, uint32_t n_base, uint32_t n_count, uint32_t c, uint16_t value) {
+            // writes `value` (fp16 1.0 or 0) at the non-zero places of item (nt, c) in stage buffer `buf`
+            auto apply = [&](uint8_t* buf, uint32_t nt, uint32_t c, uint16_t value) {
                 if constexpr (Cfg::BSRC == BSource::kOneHotFwd) {
                     // rows = samples (thread-owned), K = input rows [64c, 64c+64)
                     const uint32_t k0 = c * 64U;
@@ -743,8 +685,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll
                     for (uint32_t i = 0; i < (ROWS + NT - 1U) / NT; ++i) {
                         const uint32_t n = t + i * NT;
-                        const uint32_t sample = n_base + n;
-                        if (sample < args.samples && n < n_count) {
+                        const uint32_t sample = nt * ROWS + n;
+                        if (sample < args.samples && n < ROWS) {
                             const uint8_t* st = args.states + static_cast<uint64_t>(sample) * 80U;
                             for (uint32_t p = p_lo; p <= p_hi && p < L; ++p) {
                                 const uint32_t k = p * V + __ldg(st + p) - k0;
@@ -756,26 +698,29 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 } else {
                     // rows = input rows [r0, r0+ROWS), K = samples [64c, 64c+64); the four threads that
                     // share a sample sit in one warp and split its positions
-                    const uint32_t r0 = n_base;
+                    const uint32_t r0 = nt * ROWS;
                     const uint32_t k = t >> 2;
                     const uint32_t sample = c * 64U + k;
-                    if (sample < args.samples && n_count > 0U) {
+                    if (sample < args.samples) {
                         const uint8_t* st = args.states + static_cast<uint64_t>(sample) * 80U;
                         const uint32_t p_lo = r0 / V;
-                        const uint32_t p_hi = min((r0 + n_count - 1U) / V, L - 1U);
+                        const uint32_t p_hi = min((r0 + ROWS - 1U) / V, L - 1U);
                         for (uint32_t p = p_lo + (t & 3U); p <= p_hi && p < L; p += 4U) {
                             const uint32_t n = p * V + __ldg(st + p) - r0;
-                            if (n < n_count) *place(buf, n, k) = value;
+                            if (n < ROWS) *place(buf, n, k) = value;
                         }
                         const uint32_t nb = IN - r0;  // optional all-ones row (bias gradient)
-                        if ((t & 3U) == 0U && nb < n_count) *place(buf, nb, k) = value;
+                        if ((t & 3U) == 0U && nb < ROWS) *place(buf, nb, k) = value;
                     }
                 }
             };
             static_assert(Cfg::BSRC != BSource::kOneHotGrad || NT == 256U, "64 samples x 4 threads");
             // One stage hand-over: wait until the MMAs that read stage `sb` are done (warp-uniform).
+            const bool spin = (args.tune & kTuneSpin) != 0U;
             auto acquire = [&](uint32_t it) -> bool {
-                return __all_sync(0xFFFFFFFFU, mbar_wait(&empty_b[it % SB], ((it / SB) & 1U) ^ 1U, cta_abort, kAbortSynthWait));
+                const bool got = spin ? mbar_wait_spin(&empty_b[it % SB], ((it / SB) & 1U) ^ 1U, cta_abort, kAbortSynthWait)
+                                      : mbar_wait(&empty_b[it % SB], ((it / SB) & 1U) ^ 1U, cta_abort, kAbortSynthWait);
+                return __all_sync(0xFFFFFFFFU, got);
             };
             auto publish = [&](uint32_t it) {
                 fence_proxy_async_smem();
@@ -806,14 +751,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     auto offset_of = [&](uint32_t n, uint32_t k) -> uint32_t {
                         return (n / BN) * Cfg::B_ACC_BYTES + (n % BN) * 128U + ((((k >> 3) ^ (n & 7U)) << 4) | ((k & 7U) << 1));
                     };
-                    // places of item (unit, c) -> next[][]; advances the cursors (rewound at the first chunk of a unit)
-                    auto prepare = [&](const Unit& un, uint32_t c) {
+                    // places of item (nt, c) -> next[][]; advances the cursors (rewound at the first chunk of a unit)
+                    auto prepare = [&](uint32_t nt, uint32_t c) {
                         const uint32_t k0 = c * 64U;
                         const uint32_t kb = IN - k0;
 #pragma unroll
                         for (uint32_t i = 0; i < RPT; ++i) {
-                            const uint32_t n = t + i * NT, sample = un.n_base + n;
-                            const bool active = sample < args.samples && n < un.n_count;
+                            const uint32_t n = t + i * NT, sample = nt * ROWS + n;
+                            const bool active = sample < args.samples && n < ROWS;
                             const uint8_t* st = args.states + static_cast<uint64_t>(sample) * 80U;
                             Cursor& q = cur[i];
                             if (c == 0U) {
@@ -835,28 +780,27 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                             next[i][2] = (kb < 64U && active) ? offset_of(n, kb) : kNone;
                         }
                     };
-                    Unit un{}, un2{};
-                    uint32_t ui = 0;
-                    bool have = get_unit(0, un) && args.k_chunks > 0U;
+                    uint32_t unit = blockIdx.x, mt, nt, sp;
+                    bool have = unit < total_units && args.k_chunks > 0U;
                     uint32_t c = 0;
-                    if (have) prepare(un, 0);
+                    if (have) {
+                        decode(unit, mt, nt, sp);
+                        prepare(nt, 0);
+                    }
                     uint32_t it = 0;
                     while (have) {
-                        uint32_t ui2 = ui, c2 = c + 1U;
+                        uint32_t unit2 = unit, nt2 = nt, c2 = c + 1U;
                         bool have2 = true;
-                        un2 = un;
                         if (c2 >= args.k_chunks) {
-                            ui2 = ui + 1U;
+                            unit2 += gridDim.x;
                             c2 = 0;
-                            have2 = get_unit(ui2, un2);
+                            have2 = unit2 < total_units;
+                            if (have2) {
+                                uint32_t mt2, sp2;
+                                decode(unit2, mt2, nt2, sp2);
+                            }
                         }
-#ifdef MGT_PROBE_TIMELINE
-                        const long long s0 = clock64();
-#endif
                         if (!acquire(it)) break;
-#ifdef MGT_PROBE_TIMELINE
-                        const long long s1 = clock64();
-#endif
                         uint8_t* buf = b_ring + (it % SB) * Cfg::B_STAGE_BYTES;
 #pragma unroll
                         for (uint32_t i = 0; i < RPT; ++i)
@@ -876,15 +820,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                                 hist[SB - 1][i][j] = off;
                             }
                         publish(it);
-#ifdef MGT_PROBE_TIMELINE
-                        if (t == 0 && blockIdx.x < 148) {
-                            const long long s2 = clock64();
-                            unsigned long long* o = g_probe_cycles + blockIdx.x * 8;
-                            o[5] += s1 - s0; o[6] += s2 - s1; o[7] += 1;
-                        }
-#endif
-                        if (have2) prepare(un2, c2);
-                        ui = ui2; un = un2; c = c2; have = have2;
+                        if (have2) prepare(nt2, c2);
+                        unit = unit2; nt = nt2; c = c2; have = have2;
                         ++it;
                     }
                 }
@@ -903,9 +840,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     for (int q2 = 0; q2 < SB; ++q2)
 #pragma unroll
                         for (int j = 0; j < 4; ++j) hist[q2][j] = kNone;
-                    auto fetch = [&](const Unit& un, uint32_t c) {
-                        const uint32_t sample = c * 64U + k, r0 = un.n_base;
-                        const uint32_t p_lo = r0 / V, p_hi = min((r0 + max(un.n_count, 1U) - 1U) / V, L - 1U);
+                    auto fetch = [&](uint32_t nt, uint32_t c) {
+                        const uint32_t sample = c * 64U + k, r0 = nt * ROWS;
+                        const uint32_t p_lo = r0 / V, p_hi = min((r0 + ROWS - 1U) / V, L - 1U);
                         const uint8_t* st = args.states + static_cast<uint64_t>(sample) * 80U;
 #pragma unroll
                         for (uint32_t j = 0; j < 3U; ++j) {
@@ -916,29 +853,25 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     auto offset_of = [&](uint32_t n) -> uint32_t {
                         return (n / BN) * Cfg::B_ACC_BYTES + (n % BN) * 128U + ((((k >> 3) ^ (n & 7U)) << 4) | ((k & 7U) << 1));
                     };
-                    // the first unit of this CTA that has chunks at all (a split may be empty when K is short)
-                    Unit un{}, un2{};
-                    uint32_t ui = 0, c = 0, c_end = 0;
-                    bool have = false;
-                    while (get_unit(ui, un)) {
-                        c = chunk_begin(un.sp);
-                        c_end = chunk_begin(un.sp + 1);
-                        if (c < c_end) { have = true; break; }
-                        ++ui;
-                    }
-                    if (have) fetch(un, c);
+                    uint32_t unit = blockIdx.x, mt, nt, sp;
+                    decode(unit, mt, nt, sp);
+                    uint32_t c = chunk_begin(sp), c_end = chunk_begin(sp + 1);
+                    bool have = unit < total_units && c < c_end;
+                    if (have) fetch(nt, c);
                     uint32_t it = 0;
                     while (have) {
                         // coordinates of the item after this one
-                        uint32_t ui2 = ui, c2 = c + 1U, c_end2 = c_end;
+                        uint32_t unit2 = unit, nt2 = nt, c2 = c + 1U, c_end2 = c_end;
                         bool have2 = true;
-                        un2 = un;
                         if (c2 >= c_end2) {
-                            have2 = false;
-                            while (get_unit(++ui2, un2)) {
-                                c2 = chunk_begin(un2.sp);
-                                c_end2 = chunk_begin(un2.sp + 1);
-                                if (c2 < c_end2) { have2 = true; break; }
+                            unit2 += gridDim.x;
+                            have2 = unit2 < total_units;
+                            if (have2) {
+                                uint32_t mt2, sp2;
+                                decode(unit2, mt2, nt2, sp2);
+                                c2 = chunk_begin(sp2);
+                                c_end2 = chunk_begin(sp2 + 1);
+                                have2 = c2 < c_end2;
                             }
                         }
                         if (!acquire(it)) break;
@@ -949,15 +882,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                             if (off != kNone) *reinterpret_cast<uint16_t*>(buf + off) = 0;
                         }
                         __syncwarp();  // a place cleared by one lane may be set by another lane of this warp
-                        const uint32_t r0 = un.n_base, p_lo = r0 / V;
+                        const uint32_t r0 = nt * ROWS, p_lo = r0 / V;
                         uint32_t offs[4];
 #pragma unroll
                         for (uint32_t j = 0; j < 3U; ++j) {
                             const uint32_t n = (p_lo + q + 4U * j) * V + cur[j] - r0;
-                            offs[j] = (cur[j] != kNone && n < un.n_count) ? offset_of(n) : kNone;
+                            offs[j] = (cur[j] != kNone && n < ROWS) ? offset_of(n) : kNone;
                         }
                         const uint32_t nb = IN - r0;  // optional all-ones row
-                        offs[3] = (q == 0U && nb < un.n_count && c * 64U + k < args.samples) ? offset_of(nb) : kNone;
+                        offs[3] = (q == 0U && nb < ROWS && c * 64U + k < args.samples) ? offset_of(nb) : kNone;
 #pragma unroll
                         for (uint32_t j = 0; j < 4U; ++j) {
                             if (offs[j] != kNone) *reinterpret_cast<uint16_t*>(buf + offs[j]) = 0x3C00;
@@ -965,9 +898,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                             for (int q2 = 0; q2 + 1 < SB; ++q2) hist[q2][j] = hist[q2 + 1][j];
                             hist[SB - 1][j] = offs[j];
                         }
-                        if (have2) fetch(un2, c2);
+                        if (have2) fetch(nt2, c2);
                         publish(it);
-                        ui = ui2; un = un2; c = c2; c_end = c_end2; have = have2;
+                        unit = unit2; nt = nt2; c = c2; c_end = c_end2; have = have2;
                         ++it;
                     }
                 }
@@ -975,26 +908,28 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             if (!fast) {
                 // generic form (any class count, any split): recompute the places of an item from the states
                 uint32_t it = 0;
-                uint32_t h_base[SB] = {}, h_count[SB] = {}, h_c[SB] = {};  // the last SB items, oldest first: [0] is what the stage coming round now holds
+                uint32_t h_nt[SB] = {}, h_c[SB] = {};  // the last SB items, oldest first: [0] is what the stage coming round now holds
                 bool ok = true;
-                Unit un;
-                for (uint32_t ui = 0; ok && get_unit(ui, un); ++ui) {
-                    const uint32_t c0 = chunk_begin(un.sp), c1 = chunk_begin(un.sp + 1);
+                for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+                    uint32_t mt, nt, sp;
+                    decode(unit, mt, nt, sp);
+                    const uint32_t c0 = chunk_begin(sp), c1 = chunk_begin(sp + 1);
                     for (uint32_t c = c0; c < c1; ++c, ++it) {
                         if (!acquire(it)) { ok = false; break; }
                         uint8_t* buf = b_ring + (it % SB) * Cfg::B_STAGE_BYTES;
-                        if (it >= static_cast<uint32_t>(SB)) apply(buf, h_base[0], h_count[0], h_c[0], 0);
+                        if (it >= static_cast<uint32_t>(SB)) apply(buf, h_nt[0], h_c[0], 0);
                         __syncwarp();  // a place cleared by one lane may be set by another lane of this warp
-                        apply(buf, un.n_base, un.n_count, c, 0x3C00);
+                        apply(buf, nt, c, 0x3C00);
 #pragma unroll
-                        for (int q2 = 0; q2 + 1 < SB; ++q2) { h_base[q2] = h_base[q2 + 1]; h_count[q2] = h_count[q2 + 1]; h_c[q2] = h_c[q2 + 1]; }
-                        h_base[SB - 1] = un.n_base; h_count[SB - 1] = un.n_count; h_c[SB - 1] = c;
+                        for (int q2 = 0; q2 + 1 < SB; ++q2) { h_nt[q2] = h_nt[q2 + 1]; h_c[q2] = h_c[q2 + 1]; }
+                        h_nt[SB - 1] = nt; h_c[SB - 1] = c;
                         publish(it);
                     }
                 }
             }
         }
     }
+
     __syncwarp();
     tc_fence_before();
     __syncthreads();

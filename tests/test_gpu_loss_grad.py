@@ -43,7 +43,7 @@ def run_engine(engine, shape: MlpShape, w, states, labels, persistent_mirror=Tru
     return float(loss.item()), grad.cpu().numpy()
 
 
-def check_against_oracle(oracle, engine, shape, w, states, labels, tol=1e-3, **kw):
+def check_against_oracle(oracle, engine, shape, w, states, labels, tol=1e-3, section_tol=None, **kw):
     st, loss_o, grad_o = oracle.loss_grad_mixed(shape, w, states, labels)
     assert st == 0
     loss_g, grad_g = run_engine(engine, shape, w, states, labels, **kw)
@@ -58,7 +58,7 @@ def check_against_oracle(oracle, engine, shape, w, states, labels, tol=1e-3, **k
                 "tail": (in_w + shape.hd1 + shape.hd1 * shape.hd2 + shape.hd2, shape.param_count)}
     for name, (lo, hi) in sections.items():
         if np.abs(grad_o[lo:hi]).max() > 0:
-            assert rel_l2(grad_g[lo:hi], grad_o[lo:hi]) <= 3 * tol, (name, rel_l2(grad_g[lo:hi], grad_o[lo:hi]))
+            assert rel_l2(grad_g[lo:hi], grad_o[lo:hi]) <= (section_tol or 3 * tol), (name, rel_l2(grad_g[lo:hi], grad_o[lo:hi]))
     return loss_g, grad_g, loss_o, grad_o
 
 
@@ -183,23 +183,30 @@ def test_physical_p888_shape(oracle, engine, weights):
         lo += 2560 * 224 + 224
         w[lo:] = rng.standard_normal(shape.param_count - lo) * 0.04
     # With the trainer's 1e-4-scale initial weights the stated 1e-3 holds. With O(1) random weights 33 fp16-rounded layers
-    # amplify every last-bit difference in summation order: the rounding-point model itself sits 4.2e-3 (gradient rel-L2)
-    # from the true-fp32 reference on this case, so two correct fp16 realisations agree only to that order - 5e-3 here,
-    # and the GPU result must be as close to fp32 as the model is.
-    tol = 1e-3 if weights == "trainer_init" else 5e-3
-    loss_g, grad_g, loss_o, grad_o = check_against_oracle(oracle, engine, shape, w, states, labels.reshape(-1, 1), tol=tol)
-    assert abs(loss_g - loss_o) <= 1e-3 * abs(loss_o)
-    # every residual block on its own: weights and biases of fc1/fc2 of block k
+    # amplify every last-bit difference in summation order: the rounding-point model itself sits 4.2e-3 (gradient rel-L2;
+    # 2.2e-2 on the embedding table, whose gradient is a sum of fp16-rounded dz1 rows) from the true-fp32 reference on
+    # this case. Two correct fp16 realisations then agree only to that order, so the GPU result is held to the model
+    # within 5e-3 overall and, section by section, to 1.5 x the model's own distance from fp32.
     base = 72 * 72 * 2560 + 2560 + 2560 * 224 + 224
     blk = 2 * (224 * 224 + 224)
-    for k in range(16):
-        lo, hi = base + k * blk, base + (k + 1) * blk
-        if np.abs(grad_o[lo:hi]).max() > 0:
-            assert rel_l2(grad_g[lo:hi], grad_o[lo:hi]) <= 3 * tol, (k, rel_l2(grad_g[lo:hi], grad_o[lo:hi]))
-    if weights == "random":
-        _, loss_f, grad_f = oracle.loss_grad(shape, w, states, labels.reshape(-1, 1))
-        model_error = rel_l2(grad_o, grad_f)
-        assert rel_l2(grad_g, grad_f) <= 1.5 * model_error + 1e-4, (rel_l2(grad_g, grad_f), model_error)
+    lab = labels.reshape(-1, 1)
+    if weights == "trainer_init":
+        loss_g, grad_g, loss_o, grad_o = check_against_oracle(oracle, engine, shape, w, states, lab)
+        for k in range(16):  # every residual block on its own: weights and biases of fc1/fc2 of block k
+            lo, hi = base + k * blk, base + (k + 1) * blk
+            if np.abs(grad_o[lo:hi]).max() > 0:
+                assert rel_l2(grad_g[lo:hi], grad_o[lo:hi]) <= 3e-3, (k, rel_l2(grad_g[lo:hi], grad_o[lo:hi]))
+        return
+    loss_g, grad_g, loss_o, grad_o = check_against_oracle(oracle, engine, shape, w, states, lab, tol=5e-3, section_tol=1.0)
+    assert abs(loss_g - loss_o) <= 1e-3 * abs(loss_o)
+    _, loss_f, grad_f = oracle.loss_grad(shape, w, states, lab)
+    in_w = 72 * 72 * 2560
+    sections = [("embedding", 0, in_w), ("input_bias", in_w, in_w + 2560), ("hidden", in_w + 2560, base)]
+    sections += [(f"block{k}", base + k * blk, base + (k + 1) * blk) for k in range(16)] + [("output", base + 16 * blk, shape.param_count)]
+    for name, lo, hi in sections:
+        model_error = rel_l2(grad_o[lo:hi], grad_f[lo:hi])
+        assert rel_l2(grad_g[lo:hi], grad_o[lo:hi]) <= 1.5 * model_error + 1e-4, (name, rel_l2(grad_g[lo:hi], grad_o[lo:hi]), model_error)
+        assert rel_l2(grad_g[lo:hi], grad_f[lo:hi]) <= 1.5 * model_error + 1e-4, (name, rel_l2(grad_g[lo:hi], grad_f[lo:hi]), model_error)
 
 
 def test_argument_errors(engine):
