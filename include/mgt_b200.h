@@ -127,6 +127,25 @@ typedef struct {
 typedef mgt_status_t (*mgt_gradient_ready_fn)(void* user, uint32_t ready_id, uint64_t param_offset,
                                               uint64_t param_count, void* producer_stream);
 
+/* Options of the loss+gradient launch that the reference does not have (it computes with fp16 operands and an MSE loss
+ * only: native/include/mgt/config.hpp:37-40, native/cuda/mlp_backward.cu:932-943). The defaults are the reference's;
+ * nothing in the reference pins the others - they are checked against this repository's CPU restatement, which is
+ * pinned by finite differences.
+ *   operand_format  MGT_OPERAND_BF16: bfloat16 operands (weights, activations, dz tensors) with fp32 accumulation, the
+ *                   same rounding points as the fp16 flow. device_weights_half of the launch is then ignored (it is
+ *                   fp16 by contract): the bfloat16 copy is rebuilt from the fp32 weights inside the workspace.
+ *   loss_kind       MGT_LOSS_CROSS_ENTROPY (output_dim >= 2): the outputs are per-depth logits, class = depth - 1 where
+ *                   the labels carry the walk depth in every output slot (what mgt_launch_expand_scalar_labels writes),
+ *                   loss = mean over the batch of -log softmax(y)[class].
+ * Both need use_half_linear = 1; with use_half_linear = 0 a launch with options set returns MGT_INVALID_CONFIG. */
+enum { MGT_OPERAND_FP16 = 0, MGT_OPERAND_BF16 = 1 };
+enum { MGT_LOSS_MSE = 0, MGT_LOSS_CROSS_ENTROPY = 1 };
+typedef struct {
+    int32_t operand_format;
+    int32_t loss_kind;
+} mgt_train_options_t;
+mgt_status_t mgt_engine_set_train_options(mgt_engine_t* engine, const mgt_train_options_t* options);
+
 /* Early-range hook (optional; no counterpart in the reference). The embedding table and the input bias are 86 % of the
  * p888 parameters and the reference announces them last. This library computes their gradient BEFORE the weight-gradient
  * GEMMs of the residual blocks and of the hidden layer, and calls `hook` (same signature and rules as gradient_ready;

@@ -177,6 +177,14 @@ class Engine:
         st = int(self._lib.mgt_engine_check(self.handle, _stream(stream), C.byref(code)))
         return st, int(code.value)
 
+    def set_train_options(self, bf16: bool = False, cross_entropy: bool = False) -> int:
+        """mgt_engine_set_train_options: bfloat16 operands and/or cross-entropy on depth - 1 (defaults = the reference)."""
+        class Opt(C.Structure):
+            _fields_ = [("operand_format", C.c_int32), ("loss_kind", C.c_int32)]
+        opt = Opt(int(bf16), int(cross_entropy))
+        self._lib.mgt_engine_set_train_options.argtypes = [C.c_void_p, C.c_void_p]
+        return int(self._lib.mgt_engine_set_train_options(self.handle, C.byref(opt)))
+
     def set_early_range_hook(self, fn=None) -> int:
         """mgt_engine_set_early_range_hook: fn(user, ready_id, offset, count, stream) -> status, or None to remove it."""
         cb = GRADIENT_READY_FN(fn) if fn is not None else None

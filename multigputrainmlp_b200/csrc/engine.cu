@@ -182,9 +182,10 @@ struct mgt_engine {
     cudaEvent_t ev_last = nullptr, ev_now = nullptr;
     uint64_t launches = 0;  // kernels launched through this engine (host-side count)
     bool layered_tower = false;  // MGT_RESIDUAL_PATH=layered: per-layer GEMMs instead of the fused residual-tower kernels (both are tested)
-    uint32_t onehot_tune = 0;    // kTune* switches of the embedding-layer GEMMs (MGT_ONEHOT_TUNE overrides the default)
     mgt_gradient_ready_fn early_fn = nullptr;  // mgt_engine_set_early_range_hook
     void* early_user = nullptr;
+    mgt_train_options_t options{MGT_OPERAND_FP16, MGT_LOSS_MSE};  // mgt_engine_set_train_options
+    bool bf16_now = false;  // operand format of the launch being enqueued (set by mgt_launch_mlp_loss_grad, off otherwise)
 
     // fp16 3-D tensor map (a stack of `layers` equal matrices `layer_stride_bytes` apart), 128-byte swizzle, box depth 1
     bool Map3D(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t layers, uint64_t pitch_elems, uint64_t layer_stride_bytes,
@@ -259,12 +260,7 @@ mgt_status_t LaunchGemm(mgt_engine* e, const CUtensorMap& ta, const CUtensorMap&
         if (grid >= args.n_tiles) grid = grid / args.n_tiles * args.n_tiles;
     }
     args.status = e->status_word;
-    if (Cfg::kOneHot) {
-        args.tune = e->onehot_tune;
-        // one sixteenth of the time the MMAs of one unit take at full rate (8 MMAs of 65 ns per 64-deep chunk): the largest
-        // delay, 15 steps, stays below the unit of slack that the delayed CTAs have
-        args.stagger_ns = (args.k_chunks / args.splits) * 32U;
-    }
+    args.bf16 = e->bf16_now ? 1U : 0U;
     umma_gemm_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, args);
     ++e->launches;
     return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
@@ -304,13 +300,15 @@ GemmArgs BaseArgs(uint32_t M, uint32_t N, uint32_t K, uint32_t bn_total, uint32_
 
 // ---- small kernels ------------------------------------------------------------------------------
 
-// fp32 [rows][cols] (pitch src_pitch) -> fp16 [rows][dst_pitch], round-to-nearest-even.
-__global__ void RepackHalfKernel(const float* __restrict__ src, uint32_t rows, uint32_t cols, uint32_t src_pitch, __half* __restrict__ dst, uint32_t dst_pitch) {
+// fp32 [rows][cols] (pitch src_pitch) -> fp16 or bfloat16 [rows][dst_pitch], round-to-nearest-even.
+__global__ void RepackHalfKernel(const float* __restrict__ src, uint32_t rows, uint32_t cols, uint32_t src_pitch, __half* __restrict__ dst, uint32_t dst_pitch,
+                                 bool bf16) {
     const uint64_t total = (uint64_t)rows * cols;
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    uint16_t* out = reinterpret_cast<uint16_t*>(dst);
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         const uint32_t r = (uint32_t)(i / cols), c = (uint32_t)(i - (uint64_t)r * cols);
-        dst[(uint64_t)r * dst_pitch + c] = __float2half_rn(src[(uint64_t)r * src_pitch + c]);
+        out[(uint64_t)r * dst_pitch + c] = ptx::to_operand(src[(uint64_t)r * src_pitch + c], bf16);
     }
 }
 
@@ -416,7 +414,8 @@ ReduceRowsGroupedKernel(const float* __restrict__ src, uint32_t rows, uint32_t c
 constexpr int kHeadMaxPerLane = MGT_MAX_HD2 / 32;
 __global__ void __launch_bounds__(kHeadThreads)
 HeadOut1Kernel(const float* __restrict__ w_out, const float* __restrict__ b_out, const float* __restrict__ labels, const float* __restrict__ x,
-               uint32_t p_f32, uint32_t B, uint32_t H2, float* __restrict__ dzf, __half* __restrict__ dz_h, uint32_t p_dz, float* __restrict__ partials) {
+               uint32_t p_f32, uint32_t B, uint32_t H2, float* __restrict__ dzf, __half* __restrict__ dz_h, uint32_t p_dz, float* __restrict__ partials,
+               bool bf16) {
     __shared__ float s_acc[kHeadThreads / 32][2 * MGT_MAX_HD2 + 2];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31U;
     const uint32_t warps_total = gridDim.x * (kHeadThreads / 32);
@@ -454,7 +453,7 @@ HeadOut1Kernel(const float* __restrict__ w_out, const float* __restrict__ b_out,
                 const float d = xv[q] > 0.0f ? wreg[q] * dy : 0.0f;
                 dacc[q] += d;
                 dzf[(uint64_t)b * p_f32 + j] = d;
-                dz_h[(uint64_t)b * p_dz + j] = __float2half_rn(d);
+                reinterpret_cast<uint16_t*>(dz_h)[(uint64_t)b * p_dz + j] = ptx::to_operand(d, bf16);
             }
         }
     }
@@ -472,36 +471,67 @@ HeadOut1Kernel(const float* __restrict__ w_out, const float* __restrict__ b_out,
     }
 }
 
-// Output head for output_dim > 1 (native/cuda/mlp_backward.cu:1341-1363): fp16 operands, fp32
-// accumulate, MSE against the labels, dy rounded to fp16 for the two products that follow.
-// One warp per sample. Plain SIMT: this path carries little work (B x OUT x H2).
+// Output head for output_dim > 1 (native/cuda/mlp_backward.cu:1341-1363): 16-bit operands, fp32 accumulate, dy rounded to
+// the operand format for the two products that follow. kCrossEntropy = false: the reference's MSE against the labels.
+// kCrossEntropy = true (no counterpart in the reference): the outputs are per-depth logits, class = depth - 1 (the labels
+// carry the walk depth in every output slot), loss = mean over the batch of -log softmax(y)[class],
+// dy = (softmax(y) - onehot(class)) / B. One warp per sample. Plain SIMT: this path carries little work (B x OUT x H2).
+template <bool kCrossEntropy>
 __global__ void __launch_bounds__(kHeadThreads)
 HeadOutNKernel(const __half* __restrict__ w_out_h, uint32_t p_wout, const float* __restrict__ b_out, const float* __restrict__ labels,
                const __half* __restrict__ x_h, uint32_t p_act, const float* __restrict__ x_f32, uint32_t p_f32, uint32_t B, uint32_t H2, uint32_t OUT,
-               float* __restrict__ dy, __half* __restrict__ dy_h, float* __restrict__ dzf, __half* __restrict__ dz_h, uint32_t p_dz,
-               float* __restrict__ partials) {
-    extern __shared__ float s_dyn[];  // per warp: OUT floats of rounded dy
+               float* __restrict__ dy, __half* __restrict__ dy_h, uint32_t p_dy, float* __restrict__ dzf, __half* __restrict__ dz_h, uint32_t p_dz,
+               float* __restrict__ partials, bool bf16) {
+    extern __shared__ float s_dyn[];  // per warp: OUT floats (logits, then rounded dy)
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31U;
     const uint32_t warps_total = gridDim.x * (kHeadThreads / 32);
     float* s_dy = s_dyn + warp * OUT;
-    const float inv_n = 1.0f / static_cast<float>((uint64_t)B * OUT);
+    const uint16_t* wq = reinterpret_cast<const uint16_t*>(w_out_h);
+    const float inv_n = 1.0f / static_cast<float>(kCrossEntropy ? (uint64_t)B : (uint64_t)B * OUT);
     float loss = 0.0f;
     float dacc[kHeadMaxPerLane];
 #pragma unroll
     for (int q = 0; q < kHeadMaxPerLane; ++q) dacc[q] = 0.0f;
     for (uint32_t b = blockIdx.x * (kHeadThreads / 32) + warp; b < B; b += warps_total) {
-        const __half* row = x_h + (uint64_t)b * p_act;
+        const uint16_t* row = reinterpret_cast<const uint16_t*>(x_h) + (uint64_t)b * p_act;
+        float mx = -3.0e38f;
         for (uint32_t o = lane; o < OUT; o += 32) {
             float acc = 0.0f;
-            for (uint32_t j = 0; j < H2; ++j) acc += __half2float(row[j]) * __half2float(w_out_h[(uint64_t)j * p_wout + o]);
+            for (uint32_t j = 0; j < H2; ++j) acc += ptx::from_operand(row[j], bf16) * ptx::from_operand(wq[(uint64_t)j * p_wout + o], bf16);
             const float y = acc + b_out[o];
-            const float diff = y - labels[(uint64_t)b * OUT + o];
-            const float d = 2.0f * diff * inv_n;
-            loss += diff * diff * inv_n;
+            s_dy[o] = y;
+            mx = fmaxf(mx, y);
+        }
+        float log_sum = 0.0f;
+        uint32_t cls = 0;
+        if (kCrossEntropy) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFU, mx, o));
+            __syncwarp();
+            float sum = 0.0f;
+            for (uint32_t o = lane; o < OUT; o += 32) sum += expf(s_dy[o] - mx);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFU, sum, o);
+            log_sum = logf(sum) + mx;
+            // a depth outside 1..OUT cannot come from the walk generator with k_max <= OUT; clamp instead of reading out of bounds
+            const int c = __float2int_rn(labels[(uint64_t)b * OUT]) - 1;
+            cls = static_cast<uint32_t>(c < 0 ? 0 : (c >= static_cast<int>(OUT) ? static_cast<int>(OUT) - 1 : c));
+        }
+        for (uint32_t o = lane; o < OUT; o += 32) {
+            const float y = s_dy[o];
+            float d;
+            if (kCrossEntropy) {
+                d = (expf(y - log_sum) - (o == cls ? 1.0f : 0.0f)) * inv_n;
+                if (o == cls) loss += (log_sum - y) * inv_n;
+            } else {
+                const float diff = y - labels[(uint64_t)b * OUT + o];
+                d = 2.0f * diff * inv_n;
+                loss += diff * diff * inv_n;
+            }
             dy[(uint64_t)b * OUT + o] = d;
-            const __half dh = __float2half_rn(d);
-            dy_h[(uint64_t)b * p_wout + o] = dh;
-            s_dy[o] = __half2float(dh);
+            const uint16_t dh = ptx::to_operand(d, bf16);
+            reinterpret_cast<uint16_t*>(dy_h)[(uint64_t)b * p_dy + o] = dh;
+            s_dy[o] = ptx::from_operand(dh, bf16);
         }
         __syncwarp();
 #pragma unroll
@@ -509,11 +539,11 @@ HeadOutNKernel(const __half* __restrict__ w_out_h, uint32_t p_wout, const float*
             const uint32_t j = q * 32 + lane;
             if (j < H2) {
                 float acc = 0.0f;
-                for (uint32_t o = 0; o < OUT; ++o) acc += s_dy[o] * __half2float(w_out_h[(uint64_t)j * p_wout + o]);
+                for (uint32_t o = 0; o < OUT; ++o) acc += s_dy[o] * ptx::from_operand(wq[(uint64_t)j * p_wout + o], bf16);
                 const float d = x_f32[(uint64_t)b * p_f32 + j] > 0.0f ? acc : 0.0f;
                 dacc[q] += d;
                 dzf[(uint64_t)b * p_f32 + j] = d;
-                dz_h[(uint64_t)b * p_dz + j] = __float2half_rn(d);
+                reinterpret_cast<uint16_t*>(dz_h)[(uint64_t)b * p_dz + j] = ptx::to_operand(d, bf16);
             }
         }
         __syncwarp();
@@ -535,22 +565,20 @@ HeadOutNKernel(const __half* __restrict__ w_out_h, uint32_t p_wout, const float*
     }
 }
 
-// grad W_out[j][o] = sum_b x_h[b][j] * dy_h[b][o]; grad b_out[o] = sum_b dy[b][o].
-__global__ void HeadOutNGradKernel(const __half* __restrict__ x_h, uint32_t p_act, const __half* __restrict__ dy_h, uint32_t p_wout, const float* __restrict__ dy,
-                                   uint32_t B, uint32_t H2, uint32_t OUT, float* __restrict__ grad_w, float* __restrict__ grad_b) {
-    const uint32_t item = blockIdx.x * blockDim.x + threadIdx.x;
-    const uint32_t wcount = H2 * OUT;
-    if (item < wcount) {
-        const uint32_t j = item / OUT, o = item - j * OUT;
-        float sum = 0.0f;
-        for (uint32_t b = 0; b < B; ++b) sum += __half2float(x_h[(uint64_t)b * p_act + j]) * __half2float(dy_h[(uint64_t)b * p_wout + o]);
-        grad_w[item] = sum;
-    } else if (item < wcount + OUT) {
-        const uint32_t o = item - wcount;
-        float sum = 0.0f;
-        for (uint32_t b = 0; b < B; ++b) sum += dy[(uint64_t)b * OUT + o];
-        grad_b[o] = sum;
+// grad b_out[o] = sum_b dy[b][o]: one CTA per output, rows dealt to the threads and added in a fixed tree.
+__global__ void __launch_bounds__(256)
+HeadOutNBiasGradKernel(const float* __restrict__ dy, uint32_t B, uint32_t OUT, float* __restrict__ grad_b) {
+    __shared__ float s_sum[256];
+    const uint32_t o = blockIdx.x;
+    float sum = 0.0f;
+    for (uint32_t b = threadIdx.x; b < B; b += 256U) sum += dy[(uint64_t)b * OUT + o];
+    s_sum[threadIdx.x] = sum;
+    __syncthreads();
+    for (uint32_t w = 128U; w > 0U; w >>= 1) {
+        if (threadIdx.x < w) s_sum[threadIdx.x] += s_sum[threadIdx.x + w];
+        __syncthreads();
     }
+    if (threadIdx.x == 0) grad_b[o] = s_sum[0];
 }
 
 inline uint32_t GridFor(uint64_t items, uint32_t threads, int sm_count) {
@@ -728,6 +756,7 @@ mgt_status_t LaunchChain(mgt_engine* e, cudaStream_t st, const __half* w_first, 
     MGT_MAP(e->Map3D(&ts, a.tape_s, a.H, a.samples, tape_s_entries, a.ld_s, a.tape_s_stride * 2, 64, 128));
     MGT_MAP(e->Map3D(&tt, a.tape_t, a.H, a.samples, tape_t_entries, a.ld_t, a.tape_t_stride * 2, 64, 128));
     a.status = e->status_word;
+    a.bf16 = e->bf16_now ? 1U : 0U;
     const uint32_t grid = a.tiles < (uint32_t)e->sm_count ? a.tiles : (uint32_t)e->sm_count;
     tower_chain_kernel<BWD><<<grid, ChainCfg::THREADS, ChainCfg::SMEM_BYTES, st>>>(tw, ts, tt, a);
     ++e->launches;
@@ -900,7 +929,6 @@ mgt_status_t mgt_engine_create(int32_t device_id, mgt_engine_t** out_engine) {
     }
     e->encode = reinterpret_cast<EncodeTiledFn>(fn);
     if (const char* path = std::getenv("MGT_RESIDUAL_PATH")) e->layered_tower = std::strcmp(path, "layered") == 0;
-    if (const char* tune = std::getenv("MGT_ONEHOT_TUNE")) e->onehot_tune = static_cast<uint32_t>(std::strtoul(tune, nullptr, 0));
     if (cudaMalloc(&e->status_word, sizeof(int)) != cudaSuccess || cudaMemset(e->status_word, 0, sizeof(int)) != cudaSuccess) {
         delete e;
         return MGT_CUDA_FAILURE;
@@ -954,6 +982,14 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
         return MGT_INVALID_CONFIG;
     }
     const mgt_mlp_shape_t s = *shape;
+    const bool options_set = e->options.operand_format != MGT_OPERAND_FP16 || e->options.loss_kind != MGT_LOSS_MSE;
+    if (options_set && !half_lin) return MGT_INVALID_CONFIG;  // the options belong to the tensor-core data flow
+    if (e->options.loss_kind == MGT_LOSS_CROSS_ENTROPY && s.output_dim < 2U) return MGT_INVALID_CONFIG;
+    struct FormatScope {  // the operand format applies to the kernels enqueued by this call only
+        mgt_engine* e;
+        ~FormatScope() { e->bf16_now = false; }
+    } format_scope{e};
+    e->bf16_now = half_lin && e->options.operand_format == MGT_OPERAND_BF16;
     if (!half_lin) {
         // fp32 linear layers: the CUDA-core path (fp32_path.cuh); half_ig only selects the rounding of its embedding-gradient operand
         if (workspace_floats < Fp32WorkspaceFloats(s, B)) return MGT_CAPACITY_EXCEEDED;
@@ -998,7 +1034,8 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     // ---- fp16 weights: the caller's mirror as it lies when TMA can address it, else a padded copy
     HalfWeights hw{};
     const __half* w_half = reinterpret_cast<const __half*>(w_half_u16);
-    const bool direct = w_half != nullptr && (H1 % 8U) == 0 && (H2 % 8U) == 0 && (reinterpret_cast<uintptr_t>(w_half) & 15U) == 0;
+    // (the caller's mirror is fp16 by contract: with bfloat16 operands the copy is rebuilt from the fp32 weights each call)
+    const bool direct = w_half != nullptr && !e->bf16_now && (H1 % 8U) == 0 && (H2 % 8U) == 0 && (reinterpret_cast<uintptr_t>(w_half) & 15U) == 0;
     if (direct) {
         hw.in_table = w_half; hw.p1 = H1;
         hw.wh = w_half + HiddenWeight(s); hw.p2 = H2;
@@ -1010,7 +1047,7 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
             __half* dst = reinterpret_cast<__half*>(cur);
             cur += RoundUp((uint64_t)rows * pitch * 2, 1024);
             cudaMemsetAsync(dst, 0, (uint64_t)rows * pitch * 2, st);
-            RepackHalfKernel<<<GridFor((uint64_t)rows * cols, 256, e->sm_count), 256, 0, st>>>(src, rows, cols, cols, dst, pitch);
+            RepackHalfKernel<<<GridFor((uint64_t)rows * cols, 256, e->sm_count), 256, 0, st>>>(src, rows, cols, cols, dst, pitch, e->bf16_now);
             ++e->launches;
             return dst;
         };
@@ -1077,7 +1114,7 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     // the head also yields the fp32 column sums of dz: the bias gradient of the layer below it
     float* head_bias_dst = grad + (R > 0 ? Fc2B(s, R - 1) : HiddenBias(s));
     if (OUT == 1U) {
-        HeadOut1Kernel<<<kHeadBlocks, kHeadThreads, 0, st>>>(w + OutputWeight(s), w + OutputBias(s), labels, x_f32, ws.p_f32, B, H2, dzf, dz_cur, ws.p_dz, head_partial);
+        HeadOut1Kernel<<<kHeadBlocks, kHeadThreads, 0, st>>>(w + OutputWeight(s), w + OutputBias(s), labels, x_f32, ws.p_f32, B, H2, dzf, dz_cur, ws.p_dz, head_partial, e->bf16_now);
         const uint32_t items = 2 * H2 + 2;
         ReduceRowsKernel<<<(H2 + 1 + kReduceCols - 1) / kReduceCols, 256, 0, st>>>(head_partial, kHeadBlocks, items, 0, H2 + 1, grad + OutputWeight(s));
         ReduceRowsKernel<<<1, 256, 0, st>>>(head_partial, kHeadBlocks, items, H2 + 1, 1, loss);
@@ -1086,13 +1123,21 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     } else {
         float* dy = reinterpret_cast<float*>(base + ws.off_dy);
         __half* dy_h = reinterpret_cast<__half*>(base + ws.off_dyh);
-        HeadOutNKernel<<<kHeadBlocks, kHeadThreads, (kHeadThreads / 32) * OUT * sizeof(float), st>>>(
-            hw.wout, hw.pout, w + OutputBias(s), labels, x_h(R), ws.p_act, x_f32, ws.p_f32, B, H2, OUT, dy, dy_h, dzf, dz_cur, ws.p_dz, head_partial);
-        const uint32_t items = H2 * OUT + OUT;
-        HeadOutNGradKernel<<<(items + 127) / 128, 128, 0, st>>>(x_h(R), ws.p_act, dy_h, hw.pout, dy, B, H2, OUT, grad + OutputWeight(s), grad + OutputBias(s));
+        const size_t head_smem = (kHeadThreads / 32) * OUT * sizeof(float);
+        if (e->options.loss_kind == MGT_LOSS_CROSS_ENTROPY) {
+            HeadOutNKernel<true><<<kHeadBlocks, kHeadThreads, head_smem, st>>>(hw.wout, hw.pout, w + OutputBias(s), labels, x_h(R), ws.p_act, x_f32, ws.p_f32, B, H2, OUT,
+                                                                               dy, dy_h, ws.p_wout, dzf, dz_cur, ws.p_dz, head_partial, e->bf16_now);
+        } else {
+            HeadOutNKernel<false><<<kHeadBlocks, kHeadThreads, head_smem, st>>>(hw.wout, hw.pout, w + OutputBias(s), labels, x_h(R), ws.p_act, x_f32, ws.p_f32, B, H2, OUT,
+                                                                                dy, dy_h, ws.p_wout, dzf, dz_cur, ws.p_dz, head_partial, e->bf16_now);
+        }
         ReduceRowsKernel<<<1, 256, 0, st>>>(head_partial, kHeadBlocks, H2 + 1, 0, 1, loss);
         ReduceRowsKernel<<<(H2 + kReduceCols - 1) / kReduceCols, 256, 0, st>>>(head_partial, kHeadBlocks, H2 + 1, 1, H2, head_bias_dst);
+        HeadOutNBiasGradKernel<<<OUT, 256, 0, st>>>(dy, B, OUT, grad + OutputBias(s));
         e->launches += 4;
+        if (cudaGetLastError() != cudaSuccess) return MGT_CUDA_FAILURE;
+        // grad W_out = x_R^T * dy (16-bit operands, fp32 accumulate, mlp_backward.cu:1349-1354): the split-K weight-gradient GEMM
+        MGT_TRY(GemmGradWeights(e, st, x_h(R), ws.p_act, dy_h, ws.p_wout, B, H2, OUT, partial, ws.partial_floats, grad + OutputWeight(s)));
     }
     if (cudaGetLastError() != cudaSuccess) return MGT_CUDA_FAILURE;
     MGT_TRY(notify(OutputWeight(s), (uint64_t)H2 * OUT + OUT));
@@ -1207,6 +1252,14 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     MGT_TRY(notify(HiddenWeight(s), (uint64_t)H1 * H2 + H2));
     if (!timer.Mark(profile ? &profile->hidden_backward_ms : nullptr)) return MGT_CUDA_FAILURE;
     MGT_TRY(notify(0, InputBias(s) + H1));
+    return MGT_OK;
+}
+
+mgt_status_t mgt_engine_set_train_options(mgt_engine_t* e, const mgt_train_options_t* options) {
+    if (e == nullptr || options == nullptr) return MGT_INVALID_CONFIG;
+    if (options->operand_format != MGT_OPERAND_FP16 && options->operand_format != MGT_OPERAND_BF16) return MGT_INVALID_CONFIG;
+    if (options->loss_kind != MGT_LOSS_MSE && options->loss_kind != MGT_LOSS_CROSS_ENTROPY) return MGT_INVALID_CONFIG;
+    e->options = *options;
     return MGT_OK;
 }
 

@@ -2,6 +2,8 @@
 // tcgen05 (TMEM allocation, UMMA issue, commit, TMEM loads) and the descriptor encodings.
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -129,11 +131,6 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* map, int
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
-}
-
-// Asks for the box at (x, y) to be brought into L2; nothing arrives in shared memory and nothing is signalled.
-__device__ __forceinline__ void tma_prefetch_2d(const void* map, int32_t x, int32_t y) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y) : "memory");
 }
 
 // The same for a 3-D tensor (x innermost): used when one descriptor spans a stack of equally shaped matrices.
@@ -315,9 +312,31 @@ __host__ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, 
 // Instruction descriptor for kind::f16 with fp16 A/B and fp32 accumulator:
 // c_format(F32=1) bits [4,6), a_format/b_format (F16=0) bits [7,10)/[10,13), a_major bit 15,
 // b_major bit 16 (0 = K-major, 1 = MN-major), N>>3 in bits [17,23), M>>4 in bits [24,29).
-__host__ __device__ constexpr uint32_t make_idesc_f16(uint32_t m, uint32_t n, bool a_mn_major, bool b_mn_major) {
-    return (1U << 4) | ((a_mn_major ? 1U : 0U) << 15) | ((b_mn_major ? 1U : 0U) << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
+// bf16: both operands bfloat16 (format code 1) instead of fp16 (format code 0); the accumulator stays fp32.
+__host__ __device__ constexpr uint32_t make_idesc_f16(uint32_t m, uint32_t n, bool a_mn_major, bool b_mn_major, bool bf16 = false) {
+    return (1U << 4) | ((bf16 ? 1U : 0U) << 7) | ((bf16 ? 1U : 0U) << 10) | ((a_mn_major ? 1U : 0U) << 15) | ((b_mn_major ? 1U : 0U) << 16) |
+           ((n >> 3) << 17) | ((m >> 4) << 24);
 }
+
+// ---- 16-bit operand formats -------------------------------------------------------------------
+// The reference computes with fp16 operands; bfloat16 is this library's option. Both round to nearest even.
+__device__ __forceinline__ uint32_t pack_operand_pair(float lo, float hi, bool bf16) {
+    if (bf16) {
+        const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&p);
+    }
+    const __half2 p = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&p);
+}
+__device__ __forceinline__ uint16_t to_operand(float x, bool bf16) {
+    if (bf16) return __bfloat16_as_ushort(__float2bfloat16_rn(x));
+    return __half_as_ushort(__float2half_rn(x));
+}
+__device__ __forceinline__ float from_operand(uint16_t bits, bool bf16) {
+    if (bf16) return __uint_as_float(static_cast<uint32_t>(bits) << 16);
+    return __half2float(__ushort_as_half(bits));
+}
+__device__ __forceinline__ uint16_t operand_one(bool bf16) { return bf16 ? 0x3F80 : 0x3C00; }
 
 }  // namespace ptx
 }  // namespace mgt

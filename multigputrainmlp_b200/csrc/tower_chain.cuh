@@ -43,6 +43,7 @@ struct ChainArgs {
     uint64_t bits_stride;
     float* colsum;             // backward: slot j at colsum + j * colsum_stride, [tiles*4][H] partial column sums
     uint64_t colsum_stride;
+    uint32_t bf16;             // operands and tapes are bfloat16 instead of fp16
     int* status;
 };
 
@@ -74,22 +75,18 @@ __device__ __forceinline__ float warp_column_sums(float (&v)[32], uint32_t lane)
     return v[0];
 }
 
-// 32 floats -> 16 packed half2 words (round to nearest even) and the "half is positive" bit of each element
-__device__ __forceinline__ uint32_t pack_halfs(const float (&v)[32], uint32_t (&h)[16]) {
-    uint32_t acc_lo = 0, acc_hi = 0;
-    const __half2 zero = __floats2half2_rn(0.0f, 0.0f);
+// 32 floats -> 16 packed half2 words (round to nearest even) and the "value is positive" bit of each element. The bit
+// is taken from the fp32 value, as the reference takes its ReLU masks (mlp_backward.cu:944-1025 compare the fp32 copies):
+// a positive value too small for fp16 rounds to +0 in the operand but still lets its gradient through.
+__device__ __forceinline__ uint32_t pack_halfs(const float (&v)[32], uint32_t (&h)[16], bool bf16) {
+    uint32_t bits = 0;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-        const __half2 p = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
-        h[i] = *reinterpret_cast<const uint32_t*>(&p);
-        const uint32_t m = __hgt2_mask(p, zero);  // 0xFFFF per positive half
-        // element 2i -> bit 2i' of the low half-word, element 2i+1 -> bit 2i'+1 of the high half-word
-        const uint32_t sel = (1U << (2 * (i & 7))) | (1U << (16 + 2 * (i & 7) + 1));
-        if (i < 8) acc_lo |= m & sel; else acc_hi |= m & sel;
+        h[i] = ptx::pack_operand_pair(v[2 * i], v[2 * i + 1], bf16);
+        bits |= (v[2 * i] > 0.0f ? 1U : 0U) << (2 * i);
+        bits |= (v[2 * i + 1] > 0.0f ? 1U : 0U) << (2 * i + 1);
     }
-    const uint32_t lo16 = (acc_lo & 0x5555U) | ((acc_lo >> 16) & 0xAAAAU);
-    const uint32_t hi16 = (acc_hi & 0x5555U) | ((acc_hi >> 16) & 0xAAAAU);
-    return lo16 | (hi16 << 16);
+    return bits;
 }
 
 }  // namespace detail
@@ -182,7 +179,7 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     } else if (warp == 1) {
         // ------------------------------- UMMA issuer --------------------------------------
         if (lane == 0) {
-            const uint32_t idesc = make_idesc_f16(128, H, false, !BWD);
+            const uint32_t idesc = make_idesc_f16(128, H, false, !BWD, args.bf16 != 0U);
             uint32_t it = 0, uses = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < args.tiles && ok; tile += gridDim.x) {
@@ -343,7 +340,7 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
                     for (int j = 0; j < 32; ++j) raw[j] = __float_as_uint(v[j]);
                     tmem_st_32x32(tmem_base + lane_addr + kStateCol + cc * 32U, raw);
                     uint32_t h[16];
-                    words[ci] = detail::pack_halfs(v, h);
+                    words[ci] = detail::pack_halfs(v, h, args.bf16 != 0U);
                     store_operand(act_s, cc, h);
                     tmem_st_wait();
                     publish(&ready_s[cc >> 1]);
@@ -376,7 +373,7 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
                         if (BWD) apply_mask(v, mwords[ci]);
                         else add_bias_relu(v, ci);
                         uint32_t h[16];
-                        words[ci] = detail::pack_halfs(v, h);
+                        words[ci] = detail::pack_halfs(v, h, args.bf16 != 0U);
                         store_operand(act_t, cc, h);
                         publish(&ready_t[cc >> 1]);
                         if (BWD) {
@@ -410,7 +407,7 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
                         if (BWD) apply_mask(v, mwords[ci]);
                         else add_bias_relu(v, ci);
                         uint32_t h[16];
-                        words[ci] = detail::pack_halfs(v, h);
+                        words[ci] = detail::pack_halfs(v, h, args.bf16 != 0U);
                         if (!last) {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) raw[j] = __float_as_uint(v[j]);

@@ -61,20 +61,9 @@ struct GemmArgs {
     uint32_t value_pad;      // classes per position
     uint32_t samples;
     uint32_t in_rows;        // state_len * value_pad; row `in_rows` is the all-ones (bias) row
-    // Tuning switches of the one-hot kernels (kTune* bits) and the start delay step of kTuneStagger in nanoseconds
-    uint32_t tune;
-    uint32_t stagger_ns;
+    uint32_t bf16;           // operands and 16-bit outputs are bfloat16 instead of fp16
     int* status;             // device status word, 0 = ok
 };
-
-// kTuneStagger: CTAs that have one unit less than the busiest ones (the last round of tiles is rarely full) start late, by
-//   (blockIdx % 16) * stagger_ns: the slack they have anyway is spent so that the CTAs stop reaching their epilogues - a
-//   burst of output traffic during which a CTA's tensor pipe idles - all at the same moment.
-// kTuneSpin: the two hand-overs of the synthesised operand (stage released -> synthesis, stage published -> MMA) poll
-//   with test_wait instead of the suspending try_wait.
-// kTunePrefetch: the TMA warp asks L2 for the A boxes kPrefetchChunks chunks ahead of the one it loads.
-constexpr uint32_t kTuneStagger = 1U, kTuneSpin = 2U, kTunePrefetch = 4U;
-constexpr uint32_t kPrefetchChunks = 8U;
 
 // BSTAT_: "B-stationary" - for short reductions (K <= 64*SB_) the whole B operand of the CTA's N tile is loaded
 // once and stays in shared memory while the CTA streams its M tiles (all units of a CTA then share the N tile).
@@ -126,26 +115,22 @@ struct GemmCfg {
 
 namespace detail {
 
-__device__ __forceinline__ void store_f16x32(__half* dst, const float (&v)[32], uint32_t valid, bool vec_ok) {
+__device__ __forceinline__ void store_f16x32(__half* dst, const float (&v)[32], uint32_t valid, bool vec_ok, bool bf16) {
     if (valid == 32 && vec_ok) {
         uint4* p = reinterpret_cast<uint4*>(dst);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-            __half2 h0 = __floats2half2_rn(v[q * 8 + 0], v[q * 8 + 1]);
-            __half2 h1 = __floats2half2_rn(v[q * 8 + 2], v[q * 8 + 3]);
-            __half2 h2 = __floats2half2_rn(v[q * 8 + 4], v[q * 8 + 5]);
-            __half2 h3 = __floats2half2_rn(v[q * 8 + 6], v[q * 8 + 7]);
             uint4 u;
-            u.x = *reinterpret_cast<uint32_t*>(&h0);
-            u.y = *reinterpret_cast<uint32_t*>(&h1);
-            u.z = *reinterpret_cast<uint32_t*>(&h2);
-            u.w = *reinterpret_cast<uint32_t*>(&h3);
+            u.x = ptx::pack_operand_pair(v[q * 8 + 0], v[q * 8 + 1], bf16);
+            u.y = ptx::pack_operand_pair(v[q * 8 + 2], v[q * 8 + 3], bf16);
+            u.z = ptx::pack_operand_pair(v[q * 8 + 4], v[q * 8 + 5], bf16);
+            u.w = ptx::pack_operand_pair(v[q * 8 + 6], v[q * 8 + 7], bf16);
             p[q] = u;
         }
     } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j)
-            if (static_cast<uint32_t>(j) < valid) dst[j] = __float2half_rn(v[j]);
+            if (static_cast<uint32_t>(j) < valid) reinterpret_cast<uint16_t*>(dst)[j] = ptx::to_operand(v[j], bf16);
     }
 }
 
@@ -198,7 +183,11 @@ __device__ __forceinline__ uint32_t load_mask32(const __half* src, uint32_t vali
     } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j)
-            if (static_cast<uint32_t>(j) < valid && __half2float(src[j]) > 0.0f) bits |= 1U << j;
+            if (static_cast<uint32_t>(j) < valid) {
+                // positive in either 16-bit format: sign clear, magnitude non-zero
+                const uint16_t h = reinterpret_cast<const uint16_t*>(src)[j];
+                if (h != 0U && h < 0x8000U) bits |= 1U << j;
+            }
     }
     return bits;
 }
@@ -266,19 +255,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
-    if (Cfg::kOneHot && (args.tune & kTuneStagger) != 0U && blockIdx.x < total_units) {
-        const uint32_t my_units = (total_units - blockIdx.x + gridDim.x - 1U) / gridDim.x;
-        const uint32_t max_units = (total_units + gridDim.x - 1U) / gridDim.x;
-        if (my_units < max_units) {
-            if (threadIdx.x == 0) {
-                const uint64_t wait_ns = static_cast<uint64_t>(blockIdx.x % 16U) * args.stagger_ns;
-                const uint64_t t0 = global_timer_ns();
-                while (global_timer_ns() - t0 < wait_ns) __nanosleep(500);
-            }
-            __syncthreads();
-        }
-    }
-
     // unit -> (m tile, n tile, split): splits of one tile are neighbours for TMA-fed GEMMs; for the
     // embedding layers units that share the A stream (same m tile and split) are neighbours.
     auto group_of = [&](uint32_t unit) { return Cfg::GROUPED ? unit / units_per_group : 0U; };
@@ -311,15 +287,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     const uint32_t sa = it % SA, pa = (it / SA) & 1U;
                     if (!mbar_wait(&empty_a[sa], pa ^ 1U, cta_abort, kAbortProducerWait)) { ok = false; break; }
                     uint8_t* a_dst = a_ring + sa * Cfg::A_STAGE_BYTES;
-                    if (Cfg::kOneHot && (args.tune & kTunePrefetch) != 0U && c + kPrefetchChunks < c1) {
-                        const int32_t cp = static_cast<int32_t>((c + kPrefetchChunks) * 64U);
-                        if (Cfg::A_MN) {
-                            tma_prefetch_2d(&tma_a, static_cast<int32_t>(mt * BM), cp);
-                            tma_prefetch_2d(&tma_a, static_cast<int32_t>(mt * BM + 64), cp);
-                        } else {
-                            tma_prefetch_2d(&tma_a, cp, static_cast<int32_t>(mt * BM));
-                        }
-                    }
                     mbar_arrive_expect_tx(&full_a[sa], Cfg::A_STAGE_BYTES);
                     if (Cfg::GROUPED) {
                         const int32_t g = static_cast<int32_t>(group_of(unit));
@@ -363,7 +330,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     } else if (warp == 1) {
         // ------------------------------- UMMA issuer --------------------------------------
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_f16(BM, BN, Cfg::A_MN, Cfg::B_MN);
+            const uint32_t idesc = make_idesc_f16(BM, BN, Cfg::A_MN, Cfg::B_MN, args.bf16 != 0U);
             uint32_t it = 0, unit_iter = 0;
             bool ok = true;
             for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++unit_iter) {
@@ -379,8 +346,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     const uint32_t sb = Cfg::BSTAT ? (c - c0) : it % SB, pb = Cfg::BSTAT ? 0U : (it / SB) & 1U;
                     if (!mbar_wait(&full_a[sa], pa, cta_abort, kAbortMmaWait)) { ok = false; break; }
                     if (!Cfg::BSTAT || unit == blockIdx.x) {
-                        const bool got = (Cfg::kOneHot && (args.tune & kTuneSpin) != 0U) ? mbar_wait_spin(&full_b[sb], pb, cta_abort, kAbortMmaWait)
-                                                                                       : mbar_wait(&full_b[sb], pb, cta_abort, kAbortMmaWait);
+                        // the synthesised operand is handed over on a two-stage ring: poll (test_wait) rather than suspend (try_wait)
+                        const bool got = Cfg::kOneHot ? mbar_wait_spin(&full_b[sb], pb, cta_abort, kAbortMmaWait)
+                                                      : mbar_wait(&full_b[sb], pb, cta_abort, kAbortMmaWait);
                         if (!got) { ok = false; break; }
                     }
                     tc_fence_after();
@@ -441,7 +409,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                                 if (static_cast<uint32_t>(j) < valid) {
                                     const float x = __uint_as_float(r[j]);
                                     if constexpr (Cfg::EPI == Epi::kEmbFwd) {
-                                        args.out_f16[static_cast<uint64_t>(n0 + j) * args.ld_f16 + m] = __float2half_rn(fmaxf(x, 0.0f));
+                                        reinterpret_cast<uint16_t*>(args.out_f16)[static_cast<uint64_t>(n0 + j) * args.ld_f16 + m] = to_operand(fmaxf(x, 0.0f), args.bf16 != 0U);
                                     } else {
                                         float* dst = args.out_f32 + static_cast<uint64_t>(n0 + j) * args.ld_f32 + m;
                                         if (args.splits > 1U) atomicAdd(dst, x); else *dst = x;
@@ -581,7 +549,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                             __syncwarp();
                         } else {
                             for (uint32_t rr = 0; rr < 32U; ++rr) {
-                                const bool positive = (rr < rows_ok && col_ok) ? (__half2float(args.mask[static_cast<uint64_t>(m_base + rr) * args.ld_mask + n0 + lane]) > 0.0f) : false;
+                                const uint16_t mh = (rr < rows_ok && col_ok) ? reinterpret_cast<const uint16_t*>(args.mask)[static_cast<uint64_t>(m_base + rr) * args.ld_mask + n0 + lane] : 0U;
+                                const bool positive = mh != 0U && mh < 0x8000U;
                                 const uint32_t row_bits = __ballot_sync(0xFFFFFFFFU, positive);
                                 if (lane == rr) bits = row_bits;
                             }
@@ -619,19 +588,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                                 if (rr < rows_ok) {
                                     const float4 x0 = *reinterpret_cast<const float4*>(tile + rr * TP + c8);
                                     const float4 x1 = *reinterpret_cast<const float4*>(tile + rr * TP + c8 + 4U);
-                                    const __half2 h0 = __floats2half2_rn(x0.x, x0.y), h1 = __floats2half2_rn(x0.z, x0.w);
-                                    const __half2 h2 = __floats2half2_rn(x1.x, x1.y), h3 = __floats2half2_rn(x1.z, x1.w);
+                                    const bool bf = args.bf16 != 0U;
                                     uint4 u;
-                                    u.x = *reinterpret_cast<const uint32_t*>(&h0);
-                                    u.y = *reinterpret_cast<const uint32_t*>(&h1);
-                                    u.z = *reinterpret_cast<const uint32_t*>(&h2);
-                                    u.w = *reinterpret_cast<const uint32_t*>(&h3);
+                                    u.x = pack_operand_pair(x0.x, x0.y, bf);
+                                    u.y = pack_operand_pair(x0.z, x0.w, bf);
+                                    u.z = pack_operand_pair(x1.x, x1.y, bf);
+                                    u.w = pack_operand_pair(x1.z, x1.w, bf);
                                     *reinterpret_cast<uint4*>(args.out_f16 + static_cast<uint64_t>(m_base + rr) * args.ld_f16 + n0 + c8) = u;
                                 }
                             }
                         } else {
                             for (uint32_t rr = 0; rr < rows_ok; ++rr)
-                                if (col_ok) args.out_f16[static_cast<uint64_t>(m_base + rr) * args.ld_f16 + n0 + lane] = __float2half_rn(tile[rr * TP + lane]);
+                                if (col_ok) reinterpret_cast<uint16_t*>(args.out_f16)[static_cast<uint64_t>(m_base + rr) * args.ld_f16 + n0 + lane] = to_operand(tile[rr * TP + lane], args.bf16 != 0U);
                         }
                     }
                     if constexpr (kHasMask) {
@@ -670,6 +638,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             constexpr uint32_t NT = 32U * Cfg::SYNTH_WARPS;
             const uint32_t V = args.value_pad, L = args.state_len, IN = args.in_rows;
             constexpr uint32_t ROWS = NACC * BN;  // rows of the synthesised operand per stage
+            const uint16_t one = operand_one(args.bf16 != 0U);  // 1.0 in the operand format
             auto place = [&](uint8_t* buf, uint32_t n, uint32_t k) -> uint16_t* {
                 uint8_t* row = buf + (n / BN) * Cfg::B_ACC_BYTES + (n % BN) * 128U;
                 return reinterpret_cast<uint16_t*>(row + ((((k >> 3) ^ (n & 7U)) << 4) | ((k & 7U) << 1)));
@@ -716,11 +685,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             };
             static_assert(Cfg::BSRC != BSource::kOneHotGrad || NT == 256U, "64 samples x 4 threads");
             // One stage hand-over: wait until the MMAs that read stage `sb` are done (warp-uniform).
-            const bool spin = (args.tune & kTuneSpin) != 0U;
             auto acquire = [&](uint32_t it) -> bool {
-                const bool got = spin ? mbar_wait_spin(&empty_b[it % SB], ((it / SB) & 1U) ^ 1U, cta_abort, kAbortSynthWait)
-                                      : mbar_wait(&empty_b[it % SB], ((it / SB) & 1U) ^ 1U, cta_abort, kAbortSynthWait);
-                return __all_sync(0xFFFFFFFFU, got);
+                return __all_sync(0xFFFFFFFFU, mbar_wait_spin(&empty_b[it % SB], ((it / SB) & 1U) ^ 1U, cta_abort, kAbortSynthWait));
             };
             auto publish = [&](uint32_t it) {
                 fence_proxy_async_smem();
@@ -814,7 +780,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll
                             for (uint32_t j = 0; j < 3U; ++j) {
                                 const uint32_t off = next[i][j];
-                                if (off != kNone) *reinterpret_cast<uint16_t*>(buf + off) = 0x3C00;
+                                if (off != kNone) *reinterpret_cast<uint16_t*>(buf + off) = one;
 #pragma unroll
                                 for (int q = 0; q + 1 < SB; ++q) hist[q][i][j] = hist[q + 1][i][j];
                                 hist[SB - 1][i][j] = off;
@@ -893,7 +859,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                         offs[3] = (q == 0U && nb < ROWS && c * 64U + k < args.samples) ? offset_of(nb) : kNone;
 #pragma unroll
                         for (uint32_t j = 0; j < 4U; ++j) {
-                            if (offs[j] != kNone) *reinterpret_cast<uint16_t*>(buf + offs[j]) = 0x3C00;
+                            if (offs[j] != kNone) *reinterpret_cast<uint16_t*>(buf + offs[j]) = one;
 #pragma unroll
                             for (int q2 = 0; q2 + 1 < SB; ++q2) hist[q2][j] = hist[q2 + 1][j];
                             hist[SB - 1][j] = offs[j];
@@ -919,7 +885,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                         uint8_t* buf = b_ring + (it % SB) * Cfg::B_STAGE_BYTES;
                         if (it >= static_cast<uint32_t>(SB)) apply(buf, h_nt[0], h_c[0], 0);
                         __syncwarp();  // a place cleared by one lane may be set by another lane of this warp
-                        apply(buf, nt, c, 0x3C00);
+                        apply(buf, nt, c, one);
 #pragma unroll
                         for (int q2 = 0; q2 + 1 < SB; ++q2) { h_nt[q2] = h_nt[q2 + 1]; h_c[q2] = h_c[q2 + 1]; }
                         h_nt[SB - 1] = nt; h_c[SB - 1] = c;

@@ -109,6 +109,33 @@ class Oracle:
                                               C.byref(loss), _p(grad))
         return st, float(loss.value), grad
 
+    def bn_param_count(self, shape) -> int:
+        self.lib.orc_bn_param_count.restype = C.c_uint64
+        return int(self.lib.orc_bn_param_count(shape.as_array()))
+
+    def loss_grad_ex(self, shape, weights, states, labels, *, half_linear=True, half_input_grad=True, bf16=False,
+                     cross_entropy=False, batch_norm=False, bn_eps=1e-5):
+        """orc_mlp_loss_grad_ex: the options the reference does not have (bfloat16 operands, cross-entropy on depth - 1,
+        batch normalisation). With batch_norm the weights carry gamma/beta behind the reference's parameters.
+        Returns (status, loss, grad, stats) with stats[layer][0|1][hd2] = batch mean / variance (None without batch norm)."""
+        class Opt(C.Structure):
+            _fields_ = [("half_linear", C.c_int), ("half_input_grad", C.c_int), ("operand_format", C.c_int), ("loss_kind", C.c_int),
+                        ("batch_norm", C.c_int), ("bn_eps", C.c_float)]
+        opt = Opt(int(half_linear), int(half_input_grad), int(bf16), int(cross_entropy), int(batch_norm), float(bn_eps))
+        b = states.shape[0]
+        total = shape.param_count + (self.bn_param_count(shape) if batch_norm else 0)
+        assert weights.size == total, (weights.size, total)
+        loss = C.c_float(0)
+        grad = np.zeros(total, np.float32)
+        stats = np.zeros((shape.residual_blocks + 1, 2, shape.hd2), np.float32) if batch_norm else None
+        st = self.lib.orc_mlp_loss_grad_ex(shape.as_array(), _p(weights), _p(states), _p(np.ascontiguousarray(labels, np.float32)), C.c_uint32(b),
+                                           C.byref(opt), C.byref(loss), _p(grad), _p(stats) if stats is not None else None)
+        return st, float(loss.value), grad, stats
+
+    def float_to_bf16(self, a):
+        a = np.asarray(a, np.float32).ravel()
+        return np.array([self.lib.orc_float_to_bf16_rn(C.c_float(float(x))) for x in a], np.uint16)
+
     def adamw(self, w, g, m, v, *, step, lr, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.0, half_mirror=None):
         hp = _p(half_mirror) if half_mirror is not None else None
         return self.lib.orc_adamw_step(_p(w), _p(g), _p(m), _p(v), C.c_uint64(w.size), C.c_uint64(step),

@@ -317,8 +317,24 @@ uint16_t orc_export_float_to_fp16(float value) {
     return (uint16_t)(sign | ((uint32_t)exp << 10U) | ((mant + 0x1000U) >> 13U));
 }
 
+uint16_t orc_float_to_bf16_rn(float value) {
+    uint32_t x;
+    std::memcpy(&x, &value, 4);
+    if ((x & 0x7fffffffU) > 0x7f800000U) return (uint16_t)((x >> 16) | 0x40U);  // NaN stays NaN
+    const uint32_t lsb = (x >> 16) & 1U;
+    x += 0x7fffU + lsb;  // round to nearest, ties to even
+    return (uint16_t)(x >> 16);
+}
+
+float orc_bf16_to_float(uint16_t bits) {
+    const uint32_t x = (uint32_t)bits << 16;
+    float out;
+    std::memcpy(&out, &x, 4);
+    return out;
+}
+
 namespace {
-inline float Q(float x) { return orc_half_to_float(orc_float_to_half_rn(x)); }
+inline float Q(float x, int fmt) { return fmt == ORC_OPERAND_BF16 ? orc_bf16_to_float(orc_float_to_bf16_rn(x)) : orc_half_to_float(orc_float_to_half_rn(x)); }
 
 // c[m,n] = sum_k a[m,k]*b[k,n], row-major, fp32 accumulate in k order.
 void MatMulNN(const float* a, const float* b, float* c, uint32_t m, uint32_t n, uint32_t k) {
@@ -354,25 +370,92 @@ void ColSum(const float* dz, float* out, uint32_t samples, uint32_t cols) {
         out[j] = sum;
     }
 }
-std::vector<float> Quantized(const std::vector<float>& v, bool on) {
+std::vector<float> Quantized(const std::vector<float>& v, bool on, int fmt) {
     if (!on) return v;
     std::vector<float> q(v.size());
-    for (size_t i = 0; i < v.size(); ++i) q[i] = Q(v[i]);
+    for (size_t i = 0; i < v.size(); ++i) q[i] = Q(v[i], fmt);
     return q;
+}
+
+// Training-mode batch normalisation of z[B][H] over the batch, column by column:
+//   y = gamma * (z - mean) * rstd + beta,  mean/var (biased) of the column, rstd = 1 / sqrt(var + eps).
+// Keeps xhat = (z - mean) * rstd and rstd for the backward pass. Sums run over the samples in order, in fp32.
+struct BnTape {
+    std::vector<float> xhat, rstd, mean, var;
+};
+void BnForward(const std::vector<float>& z, uint32_t B, uint32_t H, const float* gamma, const float* beta, float eps, std::vector<float>* y, BnTape* t) {
+    t->xhat.resize((uint64_t)B * H);
+    t->rstd.resize(H);
+    t->mean.resize(H);
+    t->var.resize(H);
+    y->resize((uint64_t)B * H);
+    const float inv_b = 1.0f / (float)B;
+    for (uint32_t j = 0; j < H; ++j) {
+        float s1 = 0.0f, s2 = 0.0f;
+        for (uint32_t b = 0; b < B; ++b) {
+            const float v = z[(uint64_t)b * H + j];
+            s1 += v;
+            s2 += v * v;
+        }
+        const float mean = s1 * inv_b;
+        float var = s2 * inv_b - mean * mean;
+        if (var < 0.0f) var = 0.0f;
+        const float rstd = 1.0f / std::sqrt(var + eps);
+        t->mean[j] = mean;
+        t->var[j] = var;
+        t->rstd[j] = rstd;
+        for (uint32_t b = 0; b < B; ++b) {
+            const float xh = (z[(uint64_t)b * H + j] - mean) * rstd;
+            t->xhat[(uint64_t)b * H + j] = xh;
+            (*y)[(uint64_t)b * H + j] = gamma[j] * xh + beta[j];
+        }
+    }
+}
+// dy -> dz through the normalisation; dgamma = sum dy * xhat, dbeta = sum dy, dz = gamma * rstd * (dy - mean(dy) - xhat * mean(dy * xhat))
+void BnBackward(const std::vector<float>& dy, uint32_t B, uint32_t H, const float* gamma, const BnTape& t, float* dgamma, float* dbeta, std::vector<float>* dz) {
+    dz->resize((uint64_t)B * H);
+    const float inv_b = 1.0f / (float)B;
+    for (uint32_t j = 0; j < H; ++j) {
+        float s1 = 0.0f, s2 = 0.0f;
+        for (uint32_t b = 0; b < B; ++b) {
+            const float g = dy[(uint64_t)b * H + j];
+            s1 += g;
+            s2 += g * t.xhat[(uint64_t)b * H + j];
+        }
+        dbeta[j] = s1;
+        dgamma[j] = s2;
+        const float m1 = s1 * inv_b, m2 = s2 * inv_b, k = gamma[j] * t.rstd[j];
+        for (uint32_t b = 0; b < B; ++b) {
+            const uint64_t i = (uint64_t)b * H + j;
+            (*dz)[i] = k * (dy[i] - m1 - t.xhat[i] * m2);
+        }
+    }
 }
 }  // namespace
 
-int orc_mlp_loss_grad_mixed(const orc_mlp_shape_t* shape, const float* w, const uint8_t* states, const float* labels,
-                            uint32_t B, int half_linear, int half_input_grad, float* loss, float* grad) {
-    if (!shape || !ValidShape(*shape) || !w || !states || !labels || !loss || !grad || B == 0) return ORC_INVALID_CONFIG;
+uint64_t orc_bn_param_count(const orc_mlp_shape_t* shape) {
+    if (!shape || !ValidShape(*shape)) return 0;
+    return 2ULL * (shape->residual_blocks + 1ULL) * shape->hd2;
+}
+
+int orc_mlp_loss_grad_ex(const orc_mlp_shape_t* shape, const float* w, const uint8_t* states, const float* labels, uint32_t B,
+                         const orc_train_options_t* opt, float* loss, float* grad, float* bn_batch_stats) {
+    if (!shape || !ValidShape(*shape) || !w || !states || !labels || !loss || !grad || !opt || B == 0) return ORC_INVALID_CONFIG;
     const orc_mlp_shape_t& s = *shape;
     const Offsets o = BuildOffsets(s);
     const uint32_t H1 = s.hd1, H2 = s.hd2, R = s.residual_blocks, OUT = s.output_dim;
-    const bool hl = half_linear != 0, hi = half_input_grad != 0;
+    const bool hl = opt->half_linear != 0, hi = opt->half_input_grad != 0, bn = opt->batch_norm != 0, ce = opt->loss_kind == ORC_LOSS_CROSS_ENTROPY;
+    const int fmt = opt->operand_format;
+    if (ce && OUT < 2) return ORC_INVALID_CONFIG;
+    // batch-norm scale and shift follow the reference's parameters: layer 0 = hidden layer, layer k + 1 = block k; each gamma[H2], beta[H2]
+    const uint64_t bn_base = o.total;
+    const uint64_t total = o.total + (bn ? 2ULL * (R + 1ULL) * H2 : 0ULL);
+    auto gamma_of = [&](uint32_t layer) { return w + bn_base + 2ULL * layer * H2; };
+    auto beta_of = [&](uint32_t layer) { return w + bn_base + 2ULL * layer * H2 + H2; };
     // weights mirror: mlp_backward.cu:1267-1271 / adamw.cu:45
     std::vector<float> wq(o.total);
-    for (uint64_t i = 0; i < o.total; ++i) wq[i] = hl ? Q(w[i]) : w[i];
-    std::fill(grad, grad + o.total, 0.0f);
+    for (uint64_t i = 0; i < o.total; ++i) wq[i] = hl ? Q(w[i], fmt) : w[i];
+    std::fill(grad, grad + total, 0.0f);
 
     // embedding forward: mlp_backward.cu:696-832 (mirror table AND mirror bias on the fp16 path)
     std::vector<float> a1((uint64_t)B * H1);
@@ -387,32 +470,46 @@ int orc_mlp_loss_grad_mixed(const orc_mlp_shape_t* shape, const float* w, const 
             a1[(uint64_t)b * H1 + h] = Relu(acc);
         }
     }
-    const std::vector<float> a1q = Quantized(a1, hl);
-    // hidden: mlp_backward.cu:1281-1291 (fp32 master bias)
-    std::vector<float> x((uint64_t)B * H2);
+    const std::vector<float> a1q = Quantized(a1, hl, fmt);
+    // hidden: mlp_backward.cu:1281-1291 (fp32 master bias); with batch norm the pre-activation is normalised before the ReLU
+    std::vector<BnTape> tapes(bn ? R + 1U : 0U);
+    std::vector<float> x((uint64_t)B * H2), zh;
     MatMulNN(a1q.data(), wq.data() + o.hidden_weight, x.data(), B, H2, H1);
     for (uint32_t b = 0; b < B; ++b)
-        for (uint32_t j = 0; j < H2; ++j) x[(uint64_t)b * H2 + j] = Relu(x[(uint64_t)b * H2 + j] + w[o.hidden_bias + j]);
+        for (uint32_t j = 0; j < H2; ++j) x[(uint64_t)b * H2 + j] += w[o.hidden_bias + j];
+    if (bn) {
+        zh = x;
+        BnForward(zh, B, H2, gamma_of(0), beta_of(0), opt->bn_eps, &x, &tapes[0]);
+    }
+    for (uint64_t i = 0; i < (uint64_t)B * H2; ++i) x[i] = Relu(x[i]);
     std::vector<std::vector<float>> xin(R + 1U), xinq(R + 1U), r1(R), r1q(R), rz2(R);
     xin[0] = x;
-    xinq[0] = Quantized(x, hl);
-    // residual blocks: mlp_backward.cu:1294-1323
+    xinq[0] = Quantized(x, hl, fmt);
+    // residual blocks: mlp_backward.cu:1294-1323; with batch norm the fc2 output is normalised before it joins the skip path
     for (uint32_t k = 0; k < R; ++k) {
         r1[k].resize((uint64_t)B * H2);
         rz2[k].resize((uint64_t)B * H2);
         MatMulNN(xinq[k].data(), wq.data() + Fc1W(s, o, k), r1[k].data(), B, H2, H2);
         for (uint32_t b = 0; b < B; ++b)
             for (uint32_t j = 0; j < H2; ++j) r1[k][(uint64_t)b * H2 + j] = Relu(r1[k][(uint64_t)b * H2 + j] + w[Fc1B(s, o, k) + j]);
-        r1q[k] = Quantized(r1[k], hl);
+        r1q[k] = Quantized(r1[k], hl, fmt);
         MatMulNN(r1q[k].data(), wq.data() + Fc2W(s, o, k), rz2[k].data(), B, H2, H2);
-        xin[k + 1].resize((uint64_t)B * H2);
         for (uint32_t b = 0; b < B; ++b)
+            for (uint32_t j = 0; j < H2; ++j) rz2[k][(uint64_t)b * H2 + j] += w[Fc2B(s, o, k) + j];
+        if (bn) {
+            const std::vector<float> z = rz2[k];
+            BnForward(z, B, H2, gamma_of(k + 1U), beta_of(k + 1U), opt->bn_eps, &rz2[k], &tapes[k + 1U]);
+        }
+        xin[k + 1].resize((uint64_t)B * H2);
+        for (uint64_t i = 0; i < (uint64_t)B * H2; ++i) xin[k + 1][i] = Relu(xin[k][i] + rz2[k][i]);
+        xinq[k + 1] = Quantized(xin[k + 1], hl, fmt);
+    }
+    if (bn && bn_batch_stats != nullptr) {
+        for (uint32_t l = 0; l <= R; ++l)
             for (uint32_t j = 0; j < H2; ++j) {
-                const uint64_t i = (uint64_t)b * H2 + j;
-                rz2[k][i] += w[Fc2B(s, o, k) + j];
-                xin[k + 1][i] = Relu(xin[k][i] + rz2[k][i]);
+                bn_batch_stats[(2ULL * l) * H2 + j] = tapes[l].mean[j];
+                bn_batch_stats[(2ULL * l + 1ULL) * H2 + j] = tapes[l].var[j];
             }
-        xinq[k + 1] = Quantized(xin[k + 1], hl);
     }
     // output head + loss: mlp_backward.cu:1333-1363
     const std::vector<float>& fin = xin[R];
@@ -439,48 +536,81 @@ int orc_mlp_loss_grad_mixed(const orc_mlp_shape_t* shape, const float* w, const 
         grad[o.output_bias] = sum;
     } else {
         const uint64_t items = (uint64_t)B * OUT;
-        const float inv_n = 1.0f / (float)items;
         std::vector<float> outv(items), dy(items);
         MatMulNN(xinq[R].data(), wq.data() + o.output_weight, outv.data(), B, OUT, H2);
-        for (uint64_t i = 0; i < items; ++i) {
-            const float y = outv[i] + w[o.output_bias + (i % OUT)];
-            const float diff = y - labels[i];
-            dy[i] = 2.0f * diff * inv_n;
-            loss_acc += diff * diff * inv_n;
+        if (!ce) {
+            const float inv_n = 1.0f / (float)items;
+            for (uint64_t i = 0; i < items; ++i) {
+                const float y = outv[i] + w[o.output_bias + (i % OUT)];
+                const float diff = y - labels[i];
+                dy[i] = 2.0f * diff * inv_n;
+                loss_acc += diff * diff * inv_n;
+            }
+        } else {
+            // per-depth logits: class = depth - 1 (labels carry the walk depth K in every output slot), mean over the batch of
+            // -log softmax(y)[class]; dy = (softmax(y) - onehot(class)) / B
+            const float inv_b = 1.0f / (float)B;
+            for (uint32_t b = 0; b < B; ++b) {
+                const float depth = labels[(uint64_t)b * OUT];
+                const int32_t cls = (int32_t)std::lround(depth) - 1;
+                if (cls < 0 || cls >= (int32_t)OUT) return ORC_INVALID_CONFIG;
+                float mx = -3.0e38f;
+                for (uint32_t c = 0; c < OUT; ++c) {
+                    outv[(uint64_t)b * OUT + c] += w[o.output_bias + c];
+                    mx = std::max(mx, outv[(uint64_t)b * OUT + c]);
+                }
+                float sum = 0.0f;
+                for (uint32_t c = 0; c < OUT; ++c) sum += std::exp(outv[(uint64_t)b * OUT + c] - mx);
+                const float log_sum = std::log(sum) + mx;
+                loss_acc += (log_sum - outv[(uint64_t)b * OUT + (uint32_t)cls]) * inv_b;
+                for (uint32_t c = 0; c < OUT; ++c) {
+                    const float p = std::exp(outv[(uint64_t)b * OUT + c] - log_sum);
+                    dy[(uint64_t)b * OUT + c] = (p - (c == (uint32_t)cls ? 1.0f : 0.0f)) * inv_b;
+                }
+            }
         }
-        const std::vector<float> dyq = Quantized(dy, hl);
+        const std::vector<float> dyq = Quantized(dy, hl, fmt);
         MatMulTN(xinq[R].data(), dyq.data(), grad + o.output_weight, B, H2, OUT);
         MatMulNT(dyq.data(), wq.data() + o.output_weight, dcur.data(), B, H2, OUT);
         ColSum(dy.data(), grad + o.output_bias, B, OUT);
     }
     *loss = loss_acc;
     // residual backward: mlp_backward.cu:1367-1413
-    std::vector<float> dz2((uint64_t)B * H2), dra1((uint64_t)B * H2), dz1((uint64_t)B * H2), dprev((uint64_t)B * H2);
+    std::vector<float> dz2((uint64_t)B * H2), dra1((uint64_t)B * H2), dz1((uint64_t)B * H2), dprev((uint64_t)B * H2), dpre;
     for (uint32_t rb = R; rb > 0; --rb) {
         const uint32_t k = rb - 1U;
         for (uint64_t i = 0; i < (uint64_t)B * H2; ++i) dz2[i] = dcur[i] * ((xin[k][i] + rz2[k][i]) > 0.0f ? 1.0f : 0.0f);
-        const std::vector<float> dz2q = Quantized(dz2, hl);
+        dpre = dz2;  // gradient w.r.t. the sum entering the ReLU: goes down the skip path unchanged
+        if (bn) {
+            const std::vector<float> dy = dz2;
+            BnBackward(dy, B, H2, gamma_of(k + 1U), tapes[k + 1U], grad + bn_base + 2ULL * (k + 1U) * H2, grad + bn_base + 2ULL * (k + 1U) * H2 + H2, &dz2);
+        }
+        const std::vector<float> dz2q = Quantized(dz2, hl, fmt);
         MatMulTN(r1q[k].data(), dz2q.data(), grad + Fc2W(s, o, k), B, H2, H2);
         ColSum(dz2.data(), grad + Fc2B(s, o, k), B, H2);
         MatMulNT(dz2q.data(), wq.data() + Fc2W(s, o, k), dra1.data(), B, H2, H2);
         for (uint64_t i = 0; i < (uint64_t)B * H2; ++i) dz1[i] = dra1[i] * (r1[k][i] > 0.0f ? 1.0f : 0.0f);
-        const std::vector<float> dz1q = Quantized(dz1, hl);
+        const std::vector<float> dz1q = Quantized(dz1, hl, fmt);
         MatMulTN(xinq[k].data(), dz1q.data(), grad + Fc1W(s, o, k), B, H2, H2);
         ColSum(dz1.data(), grad + Fc1B(s, o, k), B, H2);
         MatMulNT(dz1q.data(), wq.data() + Fc1W(s, o, k), dprev.data(), B, H2, H2);
-        for (uint64_t i = 0; i < (uint64_t)B * H2; ++i) dprev[i] += dz2[i];
+        for (uint64_t i = 0; i < (uint64_t)B * H2; ++i) dprev[i] += dpre[i];
         dcur.swap(dprev);
     }
     // hidden backward: mlp_backward.cu:1417-1438
     std::vector<float> dzh((uint64_t)B * H2);
     for (uint64_t i = 0; i < (uint64_t)B * H2; ++i) dzh[i] = dcur[i] * (xin[0][i] > 0.0f ? 1.0f : 0.0f);
-    const std::vector<float> dzhq = Quantized(dzh, hl);
+    if (bn) {
+        const std::vector<float> dy = dzh;
+        BnBackward(dy, B, H2, gamma_of(0), tapes[0], grad + bn_base, grad + bn_base + H2, &dzh);
+    }
+    const std::vector<float> dzhq = Quantized(dzh, hl, fmt);
     MatMulTN(a1q.data(), dzhq.data(), grad + o.hidden_weight, B, H1, H2);
     ColSum(dzh.data(), grad + o.hidden_bias, B, H2);
     std::vector<float> da1((uint64_t)B * H1);
     MatMulNT(dzhq.data(), wq.data() + o.hidden_weight, da1.data(), B, H1, H2);
     for (uint64_t i = 0; i < (uint64_t)B * H1; ++i) da1[i] = da1[i] * (a1[i] > 0.0f ? 1.0f : 0.0f);
-    const std::vector<float> dzin = Quantized(da1, hi);
+    const std::vector<float> dzin = Quantized(da1, hi, fmt);
     // embedding gradient: mlp_backward.cu:1440-1505 (one-hot^T x dz1 is a scatter-add)
     for (uint32_t b = 0; b < B; ++b) {
         const uint8_t* st = states + (uint64_t)b * ORC_STATE_STORAGE_LEN;
@@ -491,6 +621,16 @@ int orc_mlp_loss_grad_mixed(const orc_mlp_shape_t* shape, const float* w, const 
     }
     ColSum(da1.data(), grad + o.input_bias, B, H1);
     return ORC_OK;
+}
+
+int orc_mlp_loss_grad_mixed(const orc_mlp_shape_t* shape, const float* w, const uint8_t* states, const float* labels,
+                            uint32_t B, int half_linear, int half_input_grad, float* loss, float* grad) {
+    orc_train_options_t opt{};
+    opt.half_linear = half_linear;
+    opt.half_input_grad = half_input_grad;
+    opt.operand_format = ORC_OPERAND_FP16;
+    opt.loss_kind = ORC_LOSS_MSE;
+    return orc_mlp_loss_grad_ex(shape, w, states, labels, B, &opt, loss, grad, nullptr);
 }
 
 int orc_adamw_step(float* weights, const float* grad, float* m, float* v, uint64_t n, uint64_t step, float lr,

@@ -75,6 +75,34 @@ int orc_mlp_loss_grad_mixed(const orc_mlp_shape_t* shape, const float* weights,
                             const uint8_t* states, const float* labels, uint32_t sample_count,
                             int half_linear, int half_input_grad, float* loss, float* grad);
 
+/* The same data flow with the options the reference does NOT have (so nothing in the reference pins them; they are
+ * pinned by finite differences in tests/test_oracle.py and are the checker for the library's opt-in extensions):
+ *   operand_format  ORC_OPERAND_BF16: operands rounded to bfloat16 (round to nearest even) instead of fp16
+ *   loss_kind       ORC_LOSS_CROSS_ENTROPY: per-depth logits (output_dim classes), class = depth - 1, mean over the
+ *                   batch of -log softmax; labels keep the trainer's layout (the depth in every output slot)
+ *   batch_norm      training-mode batch normalisation (batch statistics, biased variance, eps) of the hidden layer's
+ *                   pre-activation and of every block's fc2 output before it joins the skip path. Its scale and shift
+ *                   follow the reference's parameters in `weights`/`grad`: layer 0 = hidden, layer k + 1 = block k,
+ *                   each gamma[hd2] then beta[hd2] (orc_bn_param_count floats). bn_batch_stats (may be NULL) receives
+ *                   mean[hd2], var[hd2] per layer.
+ * With all options off this IS orc_mlp_loss_grad_mixed. */
+enum { ORC_OPERAND_FP16 = 0, ORC_OPERAND_BF16 = 1 };
+enum { ORC_LOSS_MSE = 0, ORC_LOSS_CROSS_ENTROPY = 1 };
+typedef struct {
+    int half_linear;
+    int half_input_grad;
+    int operand_format;
+    int loss_kind;
+    int batch_norm;
+    float bn_eps;
+} orc_train_options_t;
+uint64_t orc_bn_param_count(const orc_mlp_shape_t* shape);
+int orc_mlp_loss_grad_ex(const orc_mlp_shape_t* shape, const float* weights, const uint8_t* states,
+                         const float* labels, uint32_t sample_count, const orc_train_options_t* options,
+                         float* loss, float* grad, float* bn_batch_stats);
+uint16_t orc_float_to_bf16_rn(float value);
+float orc_bf16_to_float(uint16_t bits);
+
 /* native/src/mlp_cpu_ref.cpp:253-276; half_mirror (may be NULL) as adamw.cu:35-46. */
 int orc_adamw_step(float* weights, const float* grad, float* m, float* v, uint64_t param_count,
                    uint64_t step, float lr, float beta1, float beta2, float eps,

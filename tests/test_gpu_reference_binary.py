@@ -83,10 +83,11 @@ def test_side_by_side_with_reference_binary(tmp_path, flags):
 
 @pytest.mark.skipif(not os.path.exists(REF), reason="reference GPU trainer not built (make -C oracle ref_gpu)")
 def test_two_hundred_steps_track_the_reference(tmp_path):
-    """The README's p888 command for its full 200 steps, both binaries, same seeds. What is asserted is what was measured
-    and why: the two fp16 pipelines differ by rounding noise from the first step (state rel-L2 about 1e-3 per tensor,
-    no tensor stands out), and where the loss falls by a fifth per step (steps 35-45: 274 -> 84) that lag shows as up
-    to 1.4e-3 of the loss for a few steps; before and after, the losses agree to 1e-4 and better."""
+    """The README's p888 command for its full 200 steps, both binaries, same seeds: every per-step loss within the stated
+    1e-3. (The trainer's initial weights sit on a 1e-4 lattice and stay near it for the first dozens of Adam steps, so many
+    pre-activations cancel to zero up to rounding; which of those pass the ReLU in backward is decided by the sign of an
+    fp32 rounding residue. The masks are therefore taken from the fp32 values, as the reference takes them - with masks
+    from the fp16-rounded activations the two runs drifted apart by up to 1.4e-3 around step 40.)"""
     flags = ["--steps", 200, "--batch-size", 53248, "--k-min", 1, "--k-max", 29, "--hd1", 2556, "--hd2", 218, "--nrd", 16,
              "--input-grad-fp16", 1, "--input-grad-position-tile", 36, "--linear-fp16", 1, "--write-artifacts", 0]
     ref = np.array([r["loss"] for r in run(REF, tmp_path / "ref", flags)])
@@ -95,8 +96,5 @@ def test_two_hundred_steps_track_the_reference(tmp_path):
     rel = np.abs(ours - ref) / np.abs(ref)
     print(f"\n200 steps: worst {rel.max():.2e} at step {int(rel.argmax())}, steps over 1e-3: {int((rel > 1e-3).sum())}, "
           f"median {np.median(rel):.2e}, last 100 worst {rel[100:].max():.2e}")
-    assert rel.max() <= 3e-3                      # everywhere
-    assert (rel > TOL).sum() <= 6                 # the stated 1e-3 at all but a few steps of the steep descent
-    assert (rel > TOL).nonzero()[0].min(initial=199) >= 30 and (rel > TOL).nonzero()[0].max(initial=30) <= 60
-    assert rel[100:].max() <= 2e-4                # once the descent is over the runs coincide again
+    assert rel.max() <= TOL
     assert np.median(rel) <= 1e-4

@@ -197,3 +197,89 @@ def test_oracle_equals_reference_library(oracle, reference):
     la = oracle.loss_grad(shape, w, states, labels.reshape(-1, 1))
     lb = reference.loss_grad(shape, w, states, labels.reshape(-1, 1))
     assert la[0] == lb[0] == 0 and la[1] == lb[1] and np.array_equal(la[2], lb[2])
+
+
+# ---- options the reference does not have: pinned by finite differences and by reductions to pinned cases ----------------
+def _small_case(oracle, out_dim, samples=24, seed=5):
+    shape = MlpShape(6, 8, 12, 10, 2, out_dim)
+    rng = np.random.default_rng(seed)
+    states = np.zeros((samples, 80), np.uint8)
+    states[:, :6] = rng.integers(0, 8, (samples, 6))
+    depth = rng.integers(1, max(out_dim, 2) + 1, samples).astype(np.float32)
+    labels = np.repeat(depth.reshape(-1, 1), out_dim, axis=1)
+    w = (rng.standard_normal(shape.param_count) * 0.3).astype(np.float32)
+    return shape, w, states, labels
+
+
+def _finite_difference(f, w, index, h=1e-2):
+    wp, wm = w.copy(), w.copy()
+    wp[index] += h
+    wm[index] -= h
+    return (f(wp) - f(wm)) / (2 * h)
+
+
+def test_options_off_is_the_pinned_mixed_model(oracle):
+    shape, w, states, labels = _small_case(oracle, 3)
+    a = oracle.loss_grad_mixed(shape, w, states, labels)
+    b = oracle.loss_grad_ex(shape, w, states, labels)
+    assert a[0] == b[0] == 0 and a[1] == b[1] and np.array_equal(a[2], b[2])
+
+
+def test_cross_entropy_gradient_by_finite_differences(oracle):
+    shape, w, states, labels = _small_case(oracle, 5)
+    kw = dict(half_linear=False, half_input_grad=False, cross_entropy=True)
+    st, loss, grad, _ = oracle.loss_grad_ex(shape, w, states, labels, **kw)
+    assert st == 0 and 0.5 < loss < 5.0
+    # the loss is the mean negative log-likelihood of class depth - 1: uniform logits give log(5)
+    zero = np.zeros_like(w)
+    assert abs(oracle.loss_grad_ex(shape, zero, states, labels, **kw)[1] - np.log(5.0)) < 1e-6
+    f = lambda ww: oracle.loss_grad_ex(shape, ww, states, labels, **kw)[1]
+    rng = np.random.default_rng(0)
+    for index in list(rng.integers(0, shape.param_count, 12)) + [shape.param_count - 1, shape.param_count - 5]:
+        fd = _finite_difference(f, w, int(index))
+        assert abs(fd - grad[index]) <= 5e-3 + 2e-2 * abs(fd), (index, fd, grad[index])
+    # a depth outside 1..output_dim is refused
+    bad = labels.copy()
+    bad[0, :] = 6
+    assert oracle.loss_grad_ex(shape, w, states, bad, **kw)[0] == 1
+
+
+def test_batch_norm_gradient_by_finite_differences(oracle):
+    shape, w0, states, labels = _small_case(oracle, 1, samples=32)
+    nbn = oracle.bn_param_count(shape)
+    assert nbn == 2 * 3 * 10
+    rng = np.random.default_rng(3)
+    bn = np.concatenate([np.concatenate([1.0 + 0.2 * rng.standard_normal(10), 0.1 * rng.standard_normal(10)]) for _ in range(3)]).astype(np.float32)
+    w = np.concatenate([w0, bn])
+    kw = dict(half_linear=False, half_input_grad=False, batch_norm=True, bn_eps=1e-5)
+    st, loss, grad, stats = oracle.loss_grad_ex(shape, w, states, labels[:, :1], **kw)
+    assert st == 0 and np.isfinite(grad).all() and stats.shape == (3, 2, 10) and (stats[:, 1] >= 0).all()
+    f = lambda ww: oracle.loss_grad_ex(shape, ww, states, labels[:, :1], **kw)[1]
+    picks = list(rng.integers(0, shape.param_count, 10)) + list(range(shape.param_count, shape.param_count + nbn, 7))
+    for index in picks:
+        fd = _finite_difference(f, w, int(index), h=5e-3)
+        assert abs(fd - grad[index]) <= 2e-2 + 3e-2 * abs(fd), (index, fd, grad[index])
+    # a bias that is normalised away has (numerically) no gradient: hidden bias and every fc2 bias
+    in_w = 6 * 8 * 12
+    hidden_b = slice(in_w + 12 + 12 * 10, in_w + 12 + 12 * 10 + 10)
+    assert np.abs(grad[hidden_b]).max() <= 1e-4 * np.abs(grad).max()
+    # the batch is what is normalised: the outcome does not depend on the order of the samples
+    perm = rng.permutation(32)
+    st2, loss2, grad2, _ = oracle.loss_grad_ex(shape, w, states[perm], labels[perm][:, :1], **kw)
+    assert abs(loss2 - loss) <= 1e-5 * abs(loss) and np.abs(grad2 - grad).max() <= 1e-4 * np.abs(grad).max()
+
+
+def test_bfloat16_rounding_and_its_envelope(oracle):
+    # round to nearest even on the 16 upper bits
+    vals = np.array([1.0, 1.00390625, 1.005859375, -3.140625, 65536.0, 1e-40, 0.0], np.float32)
+    bits = oracle.float_to_bf16(vals)
+    back = (bits.astype(np.uint32) << 16).view(np.float32)
+    assert back[0] == 1.0 and back[1] == 1.0 and back[2] == 1.0078125 and back[4] == 65536.0 and back[6] == 0.0
+    assert np.all(np.abs(back[:5] - vals[:5]) <= np.abs(vals[:5]) * 2.0 ** -8)
+    shape, w, states, labels = _small_case(oracle, 1, samples=32)
+    _, loss_f, grad_f = oracle.loss_grad(shape, w, states, labels[:, :1])
+    _, loss_h, grad_h, _ = oracle.loss_grad_ex(shape, w, states, labels[:, :1])
+    _, loss_b, grad_b, _ = oracle.loss_grad_ex(shape, w, states, labels[:, :1], bf16=True)
+    rel = lambda a, b: float(np.sqrt(((a - b) ** 2).sum() / (b ** 2).sum()))
+    # bfloat16 keeps 8 bits of mantissa against fp16's 11: about 8 times the rounding error, same data flow
+    assert rel(grad_h, grad_f) < rel(grad_b, grad_f) < 3e-2 and abs(loss_b - loss_f) <= 2e-2 * abs(loss_f)
