@@ -31,6 +31,8 @@ struct TrainOptions {
     std::string puzzle_json, target_bin;  // a puzzle definition from files instead of the built-in cyclic shifts
     uint32_t checkpoint_period_steps = 0;
     bool resume_step = false;
+    // options of the loss+gradient launch that the reference does not have (mgt_train_options_t): "fp16" | "bf16", "mse" | "ce"
+    std::string operand_format = "fp16", loss = "mse";
 };
 
 // Every flag takes exactly one value; unknown flags, missing values and unparsable values fail

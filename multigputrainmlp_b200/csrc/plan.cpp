@@ -86,6 +86,7 @@ bool ParseTrainOptions(int argc, const char* const* argv, TrainOptions* o) {
         {"--resume-checkpoint", text(&o->resume_checkpoint)},
         {"--checkpoint-period-steps", u32(&o->checkpoint_period_steps)}, {"--resume-step", flag(&o->resume_step)},
         {"--puzzle-json", text(&o->puzzle_json)}, {"--target-bin", text(&o->target_bin)},
+        {"--operand-format", text(&o->operand_format)}, {"--loss", text(&o->loss)},
     };
     for (int i = 1; i < argc; i += 2) {
         if (i + 1 >= argc) return false;
@@ -105,6 +106,10 @@ bool ValidateTrainOptions(const TrainOptions& o) {
     if (o.world_size > 128) return false;  // kMaxRuntimeDevices, config.hpp:22
     if (o.gradient_carousel_slots == 0 || o.input_grad_partial_chunks == 0 || o.input_grad_positions_per_block == 0) return false;
     if (o.allreduce_bucket_bytes == 0 || o.allreduce_bucket_bytes % sizeof(float) != 0) return false;
+    if (o.operand_format != "fp16" && o.operand_format != "bf16") return false;
+    if (o.loss != "mse" && o.loss != "ce") return false;
+    if (o.loss == "ce" && (o.output_dim < 2 || o.k_max > o.output_dim)) return false;  // one logit per walk depth
+    if ((o.loss == "ce" || o.operand_format == "bf16") && !o.linear_fp16) return false;
     return true;
 }
 

@@ -146,7 +146,7 @@ const char kUsage[] =
     "[--batch-size N --k-min N --k-max N --hd1 N --hd2 N --nrd N --write-artifacts 0|1 --backward-profile 0|1 --overlap-allreduce 0|1 "
     "--input-grad-partial-chunks N --input-grad-positions-per-block N --input-grad-position-tile N --input-grad-fp16 0|1 --linear-fp16 0|1 "
     "--persistent-half-weights 0|1 --lt-workspace-bytes N --nccl-id-file PATH --resume-checkpoint DIR "
-    "--checkpoint-period-steps N --resume-step 0|1 --puzzle-json PATH --target-bin PATH]\n";
+    "--checkpoint-period-steps N --resume-step 0|1 --puzzle-json PATH --target-bin PATH --operand-format fp16|bf16 --loss mse|ce]\n";
 
 }  // namespace
 
@@ -204,6 +204,8 @@ int main(int argc, char** argv) {
 
     mgt_engine_t* engine = nullptr;
     if (mgt_engine_create(static_cast<int32_t>(opt.device_id), &engine) != MGT_OK) return EXIT_FAILURE;
+    const mgt_train_options_t train_options{opt.operand_format == "bf16" ? MGT_OPERAND_BF16 : MGT_OPERAND_FP16, opt.loss == "ce" ? MGT_LOSS_CROSS_ENTROPY : MGT_LOSS_MSE};
+    if (mgt_engine_set_train_options(engine, &train_options) != MGT_OK) return EXIT_FAILURE;
     // the communicator stands where the reference creates its NCCL context, also for one rank (tool:708-713)
     mgt_comm_t* comm = nullptr;
     if (mgt_comm_create(static_cast<int32_t>(opt.device_id), opt.world_size, opt.global_rank, opt.nccl_id_file.empty() ? nullptr : opt.nccl_id_file.c_str(), P, &comm) != MGT_OK) {

@@ -24,6 +24,7 @@ def engine():
 
 
 def run_engine(engine, shape: MlpShape, w, states, labels, persistent_mirror=True, callback=None, profile=None):
+    w = np.ascontiguousarray(w[:shape.param_count])
     cshape = mgt.CudaMlpShape(shape.state_len, shape.state_value_pad, shape.hd1, shape.hd2, shape.residual_blocks, shape.output_dim)
     b = states.shape[0]
     dw = torch.from_numpy(w).to(DEV)
@@ -207,6 +208,74 @@ def test_physical_p888_shape(oracle, engine, weights):
         model_error = rel_l2(grad_o[lo:hi], grad_f[lo:hi])
         assert rel_l2(grad_g[lo:hi], grad_o[lo:hi]) <= 1.5 * model_error + 1e-4, (name, rel_l2(grad_g[lo:hi], grad_o[lo:hi]), model_error)
         assert rel_l2(grad_g[lo:hi], grad_f[lo:hi]) <= 1.5 * model_error + 1e-4, (name, rel_l2(grad_g[lo:hi], grad_f[lo:hi]), model_error)
+
+
+# ---- options the reference does not have (pinned by the oracle's finite-difference tests, not by the reference) ----------
+def _options_case(oracle, dims, n, seed, scale=0.03):
+    moves, target = oracle.cyclic_puzzle(72, 18)
+    _, states, depth, _ = oracle.random_walks(moves, target, seed=seed, epoch=0, step=0, rank=0, k_min=1, k_max=29, samples=n)
+    shape = MlpShape(*dims)
+    rng = np.random.default_rng(seed)
+    w = (rng.standard_normal(shape.param_count) * scale).astype(np.float32)
+    labels = np.ascontiguousarray(np.repeat(depth.reshape(-1, 1), shape.output_dim, axis=1).astype(np.float32))  # what ExpandScalarLabels writes
+    return shape, w, states, labels
+
+
+def _check_option_case(oracle, shape, w, states, labels, *, bf16, cross_entropy, tol):
+    eng = mgt.Engine(0)
+    try:
+        assert eng.set_train_options(bf16=bf16, cross_entropy=cross_entropy) == 0
+        loss_g, grad_g = run_engine(eng, shape, w, states, labels)
+    finally:
+        eng.close()
+    st, loss_o, grad_o, _ = oracle.loss_grad_ex(shape, w, states, labels, bf16=bf16, cross_entropy=cross_entropy)
+    assert st == 0 and np.isfinite(grad_g).all()
+    assert abs(loss_g - loss_o) <= tol * max(abs(loss_o), 1e-6), (loss_g, loss_o)
+    assert rel_l2(grad_g, grad_o) <= tol, rel_l2(grad_g, grad_o)
+    # and against exact arithmetic: no further from it than the rounding model is
+    st, loss_f, grad_f, _ = oracle.loss_grad_ex(shape, w, states, labels, half_linear=False, half_input_grad=False, cross_entropy=cross_entropy)
+    model_error = rel_l2(grad_o, grad_f)
+    assert rel_l2(grad_g, grad_f) <= 1.5 * model_error + 1e-4, (rel_l2(grad_g, grad_f), model_error)
+    return loss_g, grad_g
+
+
+@pytest.mark.parametrize("dims,n", [((72, 72, 128, 224, 3, 29), 600), ((72, 72, 64, 64, 2, 5), 257), ((72, 72, 40, 24, 1, 29), 100)])
+def test_cross_entropy_on_depth(oracle, dims, n):
+    shape, w, states, labels = _options_case(oracle, dims, n, seed=21)
+    if shape.output_dim < 29:
+        labels = np.minimum(labels, shape.output_dim)
+    loss, _ = _check_option_case(oracle, shape, w, states, labels, bf16=False, cross_entropy=True, tol=2e-3)
+    assert 0.5 * np.log(shape.output_dim) < loss < 2.0 * np.log(shape.output_dim)  # near-uniform logits at these weight scales
+
+
+@pytest.mark.parametrize("dims,n", [((72, 72, 128, 224, 3, 1), 500), ((72, 72, 64, 96, 2, 3), 260), ((72, 72, 40, 24, 1, 1), 100)])
+def test_bfloat16_operands(oracle, dims, n):
+    # 8 bits of mantissa: a last-bit flip is 2^-9 of the value, so two correct realisations agree to a few 1e-3
+    shape, w, states, labels = _options_case(oracle, dims, n, seed=22)
+    _check_option_case(oracle, shape, w, states, labels, bf16=True, cross_entropy=False, tol=8e-3)
+
+
+def test_wide_deep_variant_bf16_cross_entropy(oracle):
+    # hd1 4096, hd2 512 (the reference's compile-time caps, per-layer residual path), 29 per-depth logits, bfloat16, cross-entropy
+    shape, w, states, labels = _options_case(oracle, (72, 72, 4096, 512, 2, 29), 96, seed=23, scale=0.01)
+    _check_option_case(oracle, shape, w, states, labels, bf16=True, cross_entropy=True, tol=8e-3)
+
+
+def test_option_errors(engine):
+    cshape = mgt.CudaMlpShape(8, 8, 16, 16, 2, 1)
+    t = torch.zeros(4096, device=DEV)
+    floats = mgt.mlp_loss_grad_workspace_floats(cshape, 32)
+    big = torch.zeros(floats, device=DEV)
+    st8 = torch.zeros(32, 80, dtype=torch.uint8, device=DEV)
+    eng = mgt.Engine(0)
+    try:
+        assert eng.set_train_options(cross_entropy=True) == 0
+        assert eng.launch_mlp_loss_grad(cshape, t, None, st8, t, 32, t, t, big, floats) == 1            # one output has no classes
+        assert eng.set_train_options(bf16=True) == 0
+        assert eng.launch_mlp_loss_grad(cshape, t, None, st8, t, 32, t, t, big, floats, use_half_linear=False) == 1  # options need the tensor-core flow
+        assert eng.set_train_options() == 0
+    finally:
+        eng.close()
 
 
 def test_argument_errors(engine):
