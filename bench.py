@@ -418,10 +418,19 @@ def main():
     loss_pinned = torch.zeros(1).pin_memory()
     other_launches = 0
 
-    def step(s: int, profile=None):
+    def step(s: int, profile=None, marks=None):
         nonlocal other_launches
+
+        def mark():
+            if marks is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append(ev)
+
+        mark()
         st = mgt.launch_random_walk_kernel(walk_cfg, SEED, 0, s, rank, moves_d, target_d, states, labels, meta)
         assert st == 0, st
+        mark()
         cfg = mgt.AdamWKernelConfig(params, s + 1, LR)
         if exchange is not None:
             exchange.begin_step(cfg, w, w_half, m, v)
@@ -430,12 +439,14 @@ def main():
                                          gradient_ready=exchange.callback if exchange is not None else None)
         assert st == 0, mgt.status_name(st)
         other_launches += 1
+        mark()
         if exchange is not None:
             exchange.finish_step()
         if exchange is None or not exchange.fused:
             st = mgt.launch_adamw_kernel_with_half_mirror(cfg, w, w_half, grad, m, v)
             assert st == 0, st
             other_launches += 1
+        mark()
 
     def barrier():
         torch.cuda.synchronize()
@@ -512,6 +523,21 @@ def main():
         emb_ms.append(prof.input_forward_ms)
         grad_ms.append(prof.input_grad_ms)
     stage_ms = {n: round(getattr(prof, n), 4) for n, _ in prof._fields_}
+    # where a step's time goes on the compute stream (outside the timed region; the stage timer is off here): the walk
+    # kernel, forward + backward (with the overlapped part of the exchange beside it), and what is left after backward
+    # has ended - the exchange's tail and the optimizer work that was not overlapped.
+    spans = np.zeros(3)
+    timeline_steps = 5
+    for s in range(timeline_steps):
+        marks = []
+        step(args.warmup + args.steps + e2e_steps + 3 + s, marks=marks)
+        torch.cuda.synchronize()
+        spans += np.array([marks[i].elapsed_time(marks[i + 1]) for i in range(3)])
+    spans_t = torch.tensor(spans / timeline_steps, device=dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(spans_t, op=dist.ReduceOp.MAX)
+    timeline_ms = dict(zip(("walk", "forward_backward", "after_backward"), (round(float(x), 4) for x in spans_t.tolist())))
     emb = float(np.median(emb_ms))
     algo_tflops = EMB_ALGO_FLOP_PER_CANDIDATE * batch / (emb * 1e-3) / 1e12
     exec_tflops = EMB_EXEC_FLOP_PER_CANDIDATE * batch / (emb * 1e-3) / 1e12
@@ -574,7 +600,7 @@ def main():
         "gpu_launches": int(launches), "roofline": roofline, "roofline_other": roofline_other if batch == BATCH else None, "comm": (args.comm if world > 1 else "none"),
         "step_tflops_algorithmic": FLOP_PER_CANDIDATE * value / world / 1e12,
         "step_frac_of_fp16_peak": FLOP_PER_CANDIDATE * value / world / 1e12 / peaks["tflops_sustained"],
-        "stage_ms": stage_ms, "final_loss": final_loss, "comm_check": comm_check, "reference_gpu": reference_gpu,
+        "stage_ms": stage_ms, "timeline_ms": timeline_ms, "final_loss": final_loss, "comm_check": comm_check, "reference_gpu": reference_gpu,
     }
     if batch != BATCH:
         line["config"]["batch_per_rank"] = batch

@@ -137,14 +137,42 @@ typedef mgt_status_t (*mgt_gradient_ready_fn)(void* user, uint32_t ready_id, uin
  *   loss_kind       MGT_LOSS_CROSS_ENTROPY (output_dim >= 2): the outputs are per-depth logits, class = depth - 1 where
  *                   the labels carry the walk depth in every output slot (what mgt_launch_expand_scalar_labels writes),
  *                   loss = mean over the batch of -log softmax(y)[class].
- * Both need use_half_linear = 1; with use_half_linear = 0 a launch with options set returns MGT_INVALID_CONFIG. */
+ *   batch_norm      1: training-mode batch normalisation (biased batch variance, bn_eps) of the hidden layer's
+ *                   pre-activation (before its ReLU) and of every residual block's fc2 output (before the skip add). The
+ *                   scale/shift vectors follow the reference's parameters in device_weights and device_grad: layer 0 =
+ *                   hidden layer, layer k + 1 = block k, each gamma[hd2] then beta[hd2] - mgt_bn_param_count() more
+ *                   floats in both arrays, announced to gradient_ready as ONE more range after the reference's last one
+ *                   (2*residual_blocks + 4 calls). The workspace is larger: ask
+ *                   mgt_mlp_loss_grad_workspace_floats_with_options. See mgt_engine_set_batch_norm_state for the
+ *                   statistics over all ranks and the running statistics.
+ * All need use_half_linear = 1; with use_half_linear = 0 a launch with options set returns MGT_INVALID_CONFIG. */
 enum { MGT_OPERAND_FP16 = 0, MGT_OPERAND_BF16 = 1 };
 enum { MGT_LOSS_MSE = 0, MGT_LOSS_CROSS_ENTROPY = 1 };
 typedef struct {
     int32_t operand_format;
     int32_t loss_kind;
+    int32_t batch_norm;
+    float bn_eps; /* > 0 when batch_norm is set (1e-5 is the usual value) */
 } mgt_train_options_t;
 mgt_status_t mgt_engine_set_train_options(mgt_engine_t* engine, const mgt_train_options_t* options);
+uint64_t mgt_mlp_loss_grad_workspace_floats_with_options(const mgt_mlp_shape_t* shape, uint32_t sample_count,
+                                                         uint32_t input_grad_partial_chunks, int32_t use_half_input_grad,
+                                                         int32_t use_half_linear, const mgt_train_options_t* options);
+uint64_t mgt_bn_param_count(const mgt_mlp_shape_t* shape); /* 2 * (residual_blocks + 1) * hd2; 0 = invalid shape */
+
+/* Batch statistics over all ranks ("sync" batch norm) and running statistics; both optional.
+ *   exchange(user, device_buffer, float_count, stream) is called on the launching thread, 2 * (residual_blocks + 1)
+ *   times per launch (once per layer in forward, once in backward), and must enqueue on `stream` an in-place AVERAGE of
+ *   device_buffer[0..float_count) over all ranks (float_count = 2 * hd2: forward mean and mean of squares, backward
+ *   mean(dy) and mean(dy * xhat) of this rank's samples; every rank holds the same number of samples).
+ *   device_exchange_buffer is where the engine puts those numbers - e.g. the buffer of a second, small mgt_comm (one
+ *   communicator is driven from one stream: the gradient exchange keeps its own). Both NULL: statistics of this rank only.
+ *   device_running_stats, if not NULL: (residual_blocks + 1) x {mean[hd2], var[hd2]}, updated every launch as
+ *   running = (1 - momentum) * running + momentum * batch (variance unbiased over world_size * sample_count samples). */
+typedef mgt_status_t (*mgt_stats_exchange_fn)(void* user, float* device_buffer, uint64_t float_count, void* stream);
+mgt_status_t mgt_engine_set_batch_norm_state(mgt_engine_t* engine, float* device_running_stats, float momentum,
+                                             uint32_t world_size, float* device_exchange_buffer,
+                                             mgt_stats_exchange_fn exchange, void* user);
 
 /* Early-range hook (optional; no counterpart in the reference). The embedding table and the input bias are 86 % of the
  * p888 parameters and the reference announces them last. This library computes their gradient BEFORE the weight-gradient
@@ -275,6 +303,14 @@ typedef struct {
 mgt_status_t mgt_format_step_record(int32_t argc, const char* const* argv, const mgt_step_record_t* record,
                                     int32_t overlap_allreduce, int32_t comm_enabled, int32_t resumed, char* start_line,
                                     char* log_line, char* profile_row, uint32_t capacity);
+/* Folds trained batch normalisation (mgt_train_options_t.batch_norm) into the layers it follows, with the RUNNING
+ * statistics: the hidden layer's and every fc2's weight columns are scaled by gamma / sqrt(var + eps) and the biases
+ * become (b - mean) * that + beta. Host arrays; weights (the reference's layout, mgt_mlp_param_count floats) are changed
+ * in place and then describe a network without normalisation - what the weights/ files hold ("normalization": "none",
+ * native/tools/mgt_native_train_smoke.cu:343). scale_shift and running_stats: mgt_bn_param_count floats each, layer 0 =
+ * hidden layer, layer k + 1 = block k; {gamma, beta} resp. {mean, var} of hd2 floats per layer. */
+mgt_status_t mgt_fold_batch_norm(const mgt_mlp_shape_t* shape, float* weights, const float* scale_shift,
+                                 const float* running_stats, float eps);
 /* The trainer's software float->fp16 converter used for weights/ files (tool:215-229). */
 uint16_t mgt_export_float_to_fp16(float value);
 /* weights/ (fp16 per-layer files + manifest + weights.f32.bin) and checkpoint/ (tool:241-390) from host arrays. */

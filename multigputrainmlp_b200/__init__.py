@@ -19,6 +19,7 @@ from .api import (  # noqa: F401
     launch_random_walk_kernel,
     load_puzzle_definition,
     mlp_loss_grad_workspace_floats,
+    bn_param_count,
     status_name,
     validate_adamw_kernel_config,
     validate_cuda_mlp_shape,

@@ -136,13 +136,35 @@ def validate_cuda_mlp_shape(shape: CudaMlpShape) -> int:
     return int(_lib.load().mgt_validate_mlp_shape(C.byref(s)))
 
 
+class _TrainOptions(C.Structure):
+    """mgt_train_options_t"""
+    _fields_ = [("operand_format", C.c_int32), ("loss_kind", C.c_int32), ("batch_norm", C.c_int32), ("bn_eps", C.c_float)]
+
+
 def mlp_loss_grad_workspace_floats(shape, sample_count, input_grad_partial_chunks=1, use_half_input_grad=True,
-                                   use_half_linear=True) -> int:
+                                   use_half_linear=True, batch_norm=False) -> int:
     s = shape.c()
-    return int(_lib.load().mgt_mlp_loss_grad_workspace_floats(C.byref(s), sample_count, input_grad_partial_chunks,
-                                                              int(use_half_input_grad), int(use_half_linear)))
+    lib = _lib.load()
+    if not batch_norm:
+        return int(lib.mgt_mlp_loss_grad_workspace_floats(C.byref(s), sample_count, input_grad_partial_chunks,
+                                                          int(use_half_input_grad), int(use_half_linear)))
+    opt = _TrainOptions(0, 0, 1, 1e-5)
+    lib.mgt_mlp_loss_grad_workspace_floats_with_options.restype = C.c_uint64
+    lib.mgt_mlp_loss_grad_workspace_floats_with_options.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_int32, C.c_int32, C.c_void_p]
+    return int(lib.mgt_mlp_loss_grad_workspace_floats_with_options(C.byref(s), sample_count, input_grad_partial_chunks,
+                                                                   int(use_half_input_grad), int(use_half_linear), C.byref(opt)))
 
 
+def bn_param_count(shape) -> int:
+    """mgt_bn_param_count: floats of batch-norm scale/shift that follow the reference's parameters (2 * (blocks + 1) * hd2)."""
+    s = shape.c()
+    lib = _lib.load()
+    lib.mgt_bn_param_count.restype = C.c_uint64
+    lib.mgt_bn_param_count.argtypes = [C.c_void_p]
+    return int(lib.mgt_bn_param_count(C.byref(s)))
+
+
+STATS_EXCHANGE_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p)
 GRADIENT_READY_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint64, C.c_void_p)
 
 
@@ -177,13 +199,21 @@ class Engine:
         st = int(self._lib.mgt_engine_check(self.handle, _stream(stream), C.byref(code)))
         return st, int(code.value)
 
-    def set_train_options(self, bf16: bool = False, cross_entropy: bool = False) -> int:
-        """mgt_engine_set_train_options: bfloat16 operands and/or cross-entropy on depth - 1 (defaults = the reference)."""
-        class Opt(C.Structure):
-            _fields_ = [("operand_format", C.c_int32), ("loss_kind", C.c_int32)]
-        opt = Opt(int(bf16), int(cross_entropy))
+    def set_train_options(self, bf16: bool = False, cross_entropy: bool = False, batch_norm: bool = False, bn_eps: float = 1e-5) -> int:
+        """mgt_engine_set_train_options: bfloat16 operands, cross-entropy on depth - 1, batch normalisation (defaults = the reference)."""
+        opt = _TrainOptions(int(bf16), int(cross_entropy), int(batch_norm), float(bn_eps))
         self._lib.mgt_engine_set_train_options.argtypes = [C.c_void_p, C.c_void_p]
         return int(self._lib.mgt_engine_set_train_options(self.handle, C.byref(opt)))
+
+    def set_batch_norm_state(self, running_stats=None, momentum: float = 0.1, world_size: int = 1, exchange_buffer=None, exchange=None) -> int:
+        """mgt_engine_set_batch_norm_state. `exchange(user, device_pointer, float_count, stream) -> status` must enqueue an
+        in-place average of the buffer over all ranks on `stream`; `exchange_buffer` is a device tensor or a raw pointer."""
+        cb = STATS_EXCHANGE_FN(exchange) if exchange is not None else None
+        self._stats_keepalive = (cb, running_stats, exchange_buffer)
+        buf = exchange_buffer if isinstance(exchange_buffer, int) or exchange_buffer is None else _ptr(exchange_buffer)
+        self._lib.mgt_engine_set_batch_norm_state.argtypes = [C.c_void_p, C.c_void_p, C.c_float, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p]
+        return int(self._lib.mgt_engine_set_batch_norm_state(self.handle, _ptr(running_stats), momentum, world_size, buf,
+                                                             C.cast(cb, C.c_void_p) if cb is not None else None, None))
 
     def set_early_range_hook(self, fn=None) -> int:
         """mgt_engine_set_early_range_hook: fn(user, ready_id, offset, count, stream) -> status, or None to remove it."""

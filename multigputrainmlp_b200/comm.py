@@ -42,6 +42,7 @@ class GradientRangeScheduler:
     lag: int = 0                                     # notifications a range is held back (1 = fused update behind an engine that announces a layer before its dX GEMM)
     whole_tail: bool = True                          # ranges left at finish() go out unchunked: nothing remains to overlap with
     launch_early: Optional[Callable[[int, int], None]] = None   # how a range from the early hook is sent (default: like any other)
+    coalesce: bool = False                           # join ranges that touch in memory into one launch of at most bucket_params
     scheduled_ranges: int = 0
     scheduled_chunks: int = 0
     log: List[ScheduledChunk] = field(default_factory=list)
@@ -96,11 +97,24 @@ class GradientRangeScheduler:
                 param_offset += cnt
         param_count = end - param_offset
         if param_count > 0:
-            self._pending.append((ready_id, param_offset, param_count))
+            self._append(ready_id, param_offset, param_count)
         # the range that closes backward waits for finish(), where it goes out whole
         last = self.whole_tail and self.expected_ranges is not None and self.scheduled_ranges == self.expected_ranges
-        self._flush(max(self.lag, 1 if last else 0))
+        # with coalescing the newest entry is held back as well: the next range may still join it
+        self._flush(max(self.lag, 1 if (last or self.coalesce) else 0))
         return 0
+
+    def _append(self, ready_id: int, offset: int, count: int) -> None:
+        """Backward announces the ranges of a layer group end to end (the residual blocks, last to first, then the hidden
+        layer below them). Every launch costs a handshake with all peers, so ranges that touch are joined while the sum
+        stays within one bucket; the joined range carries the id of its latest member."""
+        if self.coalesce and self._pending:
+            _, p_off, p_cnt = self._pending[-1]
+            touches = offset + count == p_off or p_off + p_cnt == offset
+            if touches and p_cnt + count <= max(1, self.bucket_params):
+                self._pending[-1] = (ready_id, min(offset, p_off), p_cnt + count)
+                return
+        self._pending.append((ready_id, offset, count))
 
     def finish(self) -> None:
         self._flush(0, whole=self.whole_tail)
@@ -182,7 +196,7 @@ class OverlappedGradientExchange:
     callback, the way the reference trainer's step loop does (tool:785-821)."""
 
     def __init__(self, backend: PeerBackend, device, bucket_bytes: int = 4 << 20, residual_blocks: int = 16, fused_adamw: bool = True,
-                 early_update_after_backward: bool = True):
+                 early_update_after_backward: bool = True, coalesce: bool = True):
         import torch
         self.torch = torch
         self.backend = backend
@@ -200,7 +214,8 @@ class OverlappedGradientExchange:
         self.early_update_after_backward = early_update_after_backward and fused_adamw
         self._deferred = []
         self.scheduler = GradientRangeScheduler(self._launch, self._wait_for_producer, bucket_params=max(1, bucket_bytes // 4),
-                                                expected_ranges=2 * residual_blocks + 3, lag=0, launch_early=self._launch_early)
+                                                expected_ranges=2 * residual_blocks + 3, lag=0, launch_early=self._launch_early,
+                                                coalesce=coalesce)
 
     def _wait_for_producer(self):
         ev = self.events[self._ev % len(self.events)]

@@ -11,6 +11,7 @@
 //     still reach the bias), reduced over CTAs in a fixed order;
 //   * activations are kept once (fp16 tape + one in-place fp32 residual stream).
 #include "../../include/mgt_b200.h"
+#include "batch_norm.cuh"
 #include "fp32_path.cuh"
 #include "tower_chain.cuh"
 #include "umma_gemm.cuh"
@@ -67,6 +68,9 @@ struct Workspace {
     uint64_t off_bits, bits_stride;  // ReLU sign bits of the residual tower: 2R+1 entries of bits_stride words
     uint64_t x_stride, r1_stride;  // bytes between consecutive blocks' tensors
     uint64_t partial_floats, head_blocks;
+    // batch normalisation (only planned when it is on): fp32 pre-activations of the R+1 normalised layers, their saved
+    // mean / rstd, partial sums of the reductions, the statistics vector when the caller gives no exchange buffer
+    uint64_t off_bn_z, bn_z_stride, off_bn_save, off_bn_partial, off_bn_stats;
     uint64_t total_bytes;
 };
 
@@ -85,7 +89,7 @@ inline uint32_t CurrentDeviceSmCount() {
     return PlanSmCount(sms);
 }
 
-Workspace PlanWorkspace(const mgt_mlp_shape_t& s, uint32_t B, uint32_t sm_count) {
+Workspace PlanWorkspace(const mgt_mlp_shape_t& s, uint32_t B, uint32_t sm_count, bool batch_norm = false) {
     Workspace w{};
     w.B = B; w.H1 = s.hd1; w.H2 = s.hd2; w.R = s.residual_blocks; w.OUT = s.output_dim;
     w.IN = s.state_len * s.state_value_pad;
@@ -141,6 +145,13 @@ Workspace PlanWorkspace(const mgt_mlp_shape_t& s, uint32_t B, uint32_t sm_count)
     w.off_wint = take(wint_halfs * 2 + 1024ULL * (2 * w.R + 4));
     w.off_dy = take((uint64_t)B * s.output_dim * 4);
     w.off_dyh = take((uint64_t)B * w.p_wout * 2);
+    if (batch_norm) {
+        w.bn_z_stride = RoundUp((uint64_t)B * w.p_f32 * 4, 1024);
+        w.off_bn_z = take(w.bn_z_stride * (w.R + 1));
+        w.off_bn_save = take((uint64_t)(w.R + 1) * 2 * s.hd2 * 4);
+        w.off_bn_partial = take((uint64_t)bn::kMaxBlocks * 2 * s.hd2 * 4);
+        w.off_bn_stats = take(2ULL * s.hd2 * 4);
+    }
     w.total_bytes = off + 1024;  // slack to align the caller's base
     return w;
 }
@@ -184,7 +195,14 @@ struct mgt_engine {
     bool layered_tower = false;  // MGT_RESIDUAL_PATH=layered: per-layer GEMMs instead of the fused residual-tower kernels (both are tested)
     mgt_gradient_ready_fn early_fn = nullptr;  // mgt_engine_set_early_range_hook
     void* early_user = nullptr;
-    mgt_train_options_t options{MGT_OPERAND_FP16, MGT_LOSS_MSE};  // mgt_engine_set_train_options
+    mgt_train_options_t options{MGT_OPERAND_FP16, MGT_LOSS_MSE, 0, 1.0e-5f};  // mgt_engine_set_train_options
+    // mgt_engine_set_batch_norm_state
+    float* bn_running = nullptr;
+    float bn_momentum = 0.1f;
+    uint32_t bn_world = 1;
+    float* bn_exchange_buffer = nullptr;
+    mgt_stats_exchange_fn bn_exchange = nullptr;
+    void* bn_exchange_user = nullptr;
     bool bf16_now = false;  // operand format of the launch being enqueued (set by mgt_launch_mlp_loss_grad, off otherwise)
 
     // fp16 3-D tensor map (a stack of `layers` equal matrices `layer_stride_bytes` apart), 128-byte swizzle, box depth 1
@@ -961,14 +979,39 @@ mgt_status_t mgt_engine_check(mgt_engine_t* e, void* stream, int32_t* out_device
     return MGT_OK;
 }
 
-uint64_t mgt_mlp_loss_grad_workspace_floats(const mgt_mlp_shape_t* shape, uint32_t sample_count, uint32_t chunks,
-                                            int32_t use_half_input_grad, int32_t use_half_linear) {
+static uint64_t WorkspaceFloats(const mgt_mlp_shape_t* shape, uint32_t sample_count, uint32_t chunks, int32_t use_half_input_grad, int32_t use_half_linear,
+                                bool batch_norm) {
     if (!ValidShape(shape) || sample_count == 0 || chunks == 0) return 0;
-    if (!use_half_linear) return Fp32WorkspaceFloats(*shape, sample_count);
-    const Workspace w = PlanWorkspace(*shape, sample_count, CurrentDeviceSmCount());
+    if (!use_half_linear) return batch_norm ? 0 : Fp32WorkspaceFloats(*shape, sample_count);
+    const Workspace w = PlanWorkspace(*shape, sample_count, CurrentDeviceSmCount(), batch_norm);
     // fp32 embedding-gradient operand: da1 and dz1 [samples][hd1] in fp32 behind the tensor-core workspace
     const uint64_t extra = use_half_input_grad ? 0 : 2ULL * sample_count * shape->hd1;
     return (w.total_bytes + 3) / 4 + extra + (extra ? 256 : 0);
+}
+
+uint64_t mgt_mlp_loss_grad_workspace_floats(const mgt_mlp_shape_t* shape, uint32_t sample_count, uint32_t chunks,
+                                            int32_t use_half_input_grad, int32_t use_half_linear) {
+    return WorkspaceFloats(shape, sample_count, chunks, use_half_input_grad, use_half_linear, false);
+}
+
+uint64_t mgt_mlp_loss_grad_workspace_floats_with_options(const mgt_mlp_shape_t* shape, uint32_t sample_count, uint32_t chunks, int32_t use_half_input_grad,
+                                                         int32_t use_half_linear, const mgt_train_options_t* options) {
+    return WorkspaceFloats(shape, sample_count, chunks, use_half_input_grad, use_half_linear, options != nullptr && options->batch_norm != 0);
+}
+
+uint64_t mgt_bn_param_count(const mgt_mlp_shape_t* shape) { return ValidShape(shape) ? 2ULL * (shape->residual_blocks + 1ULL) * shape->hd2 : 0; }
+
+mgt_status_t mgt_engine_set_batch_norm_state(mgt_engine_t* e, float* device_running_stats, float momentum, uint32_t world_size, float* device_exchange_buffer,
+                                             mgt_stats_exchange_fn exchange, void* user) {
+    if (e == nullptr || !(momentum >= 0.0f && momentum <= 1.0f) || world_size == 0) return MGT_INVALID_CONFIG;
+    if ((exchange != nullptr) != (device_exchange_buffer != nullptr)) return MGT_INVALID_CONFIG;
+    e->bn_running = device_running_stats;
+    e->bn_momentum = momentum;
+    e->bn_world = world_size;
+    e->bn_exchange_buffer = device_exchange_buffer;
+    e->bn_exchange = exchange;
+    e->bn_exchange_user = user;
+    return MGT_OK;
 }
 
 mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* shape, const float* w, const uint16_t* w_half_u16,
@@ -982,7 +1025,8 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
         return MGT_INVALID_CONFIG;
     }
     const mgt_mlp_shape_t s = *shape;
-    const bool options_set = e->options.operand_format != MGT_OPERAND_FP16 || e->options.loss_kind != MGT_LOSS_MSE;
+    const bool bnorm = e->options.batch_norm != 0;
+    const bool options_set = e->options.operand_format != MGT_OPERAND_FP16 || e->options.loss_kind != MGT_LOSS_MSE || bnorm;
     if (options_set && !half_lin) return MGT_INVALID_CONFIG;  // the options belong to the tensor-core data flow
     if (e->options.loss_kind == MGT_LOSS_CROSS_ENTROPY && s.output_dim < 2U) return MGT_INVALID_CONFIG;
     struct FormatScope {  // the operand format applies to the kernels enqueued by this call only
@@ -1001,7 +1045,7 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
         return LaunchFp32Path(e, s, w, reinterpret_cast<const uint8_t*>(states), labels, B, loss, grad, workspace, half_ig != 0, profile, tell,
                               static_cast<cudaStream_t>(stream_v));
     }
-    const Workspace ws = PlanWorkspace(s, B, PlanSmCount(e->sm_count));
+    const Workspace ws = PlanWorkspace(s, B, PlanSmCount(e->sm_count), bnorm);
     const uint64_t f32_extra = half_ig ? 0 : 2ULL * B * s.hd1;  // da1, dz1 in fp32 for the fp32 embedding gradient
     if (workspace_floats < (ws.total_bytes + 3) / 4 + f32_extra + (f32_extra ? 256 : 0)) return MGT_CAPACITY_EXCEEDED;
     cudaStream_t st = static_cast<cudaStream_t>(stream_v);
@@ -1029,6 +1073,56 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
         if (ready == nullptr) return MGT_OK;
         const mgt_status_t r = ready(ready_user, ready_id++, off, count, stream_v);
         return r == MGT_OK ? MGT_OK : MGT_CUDA_FAILURE;  // the reference maps a failing callback to kCudaFailure
+    };
+
+    // ---- batch normalisation (opt-in): fp32 pre-activations z of every normalised layer are kept, layer 0 = hidden
+    // layer, layer k + 1 = fc2 of block k; gamma/beta and their gradients follow the reference's parameters
+    const uint64_t bn_base = ParamCount(s);
+    auto z_tape = [&](uint32_t layer) { return reinterpret_cast<float*>(base + ws.off_bn_z + ws.bn_z_stride * layer); };
+    auto bn_mean = [&](uint32_t layer) { return reinterpret_cast<float*>(base + ws.off_bn_save) + 2ULL * layer * H2; };
+    auto bn_rstd = [&](uint32_t layer) { return bn_mean(layer) + H2; };
+    float* bn_partial = reinterpret_cast<float*>(base + ws.off_bn_partial);
+    float* bn_stats = bnorm && e->bn_exchange_buffer != nullptr ? e->bn_exchange_buffer : reinterpret_cast<float*>(base + ws.off_bn_stats);
+    const uint32_t bn_blocks = bn::BlocksFor(B, e->sm_count);
+    const uint32_t bn_reduce_grid = (H2 + bn::kReduceCols - 1U) / bn::kReduceCols, bn_reduce_threads = bn::kReduceCols * bn::kReduceParts;
+    auto bn_exchange = [&]() -> mgt_status_t {
+        if (e->bn_exchange == nullptr) return MGT_OK;
+        return e->bn_exchange(e->bn_exchange_user, bn_stats, 2ULL * H2, stream_v) == MGT_OK ? MGT_OK : MGT_CUDA_FAILURE;
+    };
+    // z_tape(layer) -> x_f32 / x_h(layer): x = relu(bn(z)) for the hidden layer, relu(x + bn(z)) for a block
+    auto bn_forward = [&](uint32_t layer) -> mgt_status_t {
+        bn::ColumnMomentsKernel<false><<<bn_blocks, bn::kThreads, 0, st>>>(z_tape(layer), ws.p_f32, nullptr, 0, nullptr, nullptr, B, H2, bn_partial);
+        bn::ReduceMomentsKernel<<<bn_reduce_grid, bn_reduce_threads, 0, st>>>(bn_partial, bn_blocks, H2, 1.0f / (float)B, bn_stats, nullptr, nullptr);
+        MGT_TRY(bn_exchange());
+        const float* gamma = w + bn_base + 2ULL * layer * H2;
+        float* running = e->bn_running != nullptr ? e->bn_running + 2ULL * layer * H2 : nullptr;
+        const double n = (double)B * e->bn_world;
+        const float unbias = n > 1.0 ? (float)(n / (n - 1.0)) : 1.0f;
+        uint16_t* xh = reinterpret_cast<uint16_t*>(x_h(layer));
+        if (layer == 0U) {
+            bn::ApplyForwardKernel<false><<<bn_blocks, bn::kThreads, 0, st>>>(z_tape(layer), ws.p_f32, bn_stats, gamma, gamma + H2, e->options.bn_eps, B, H2, x_f32,
+                                                                             ws.p_f32, xh, ws.p_act, e->bf16_now, bn_mean(layer), bn_rstd(layer), running,
+                                                                             e->bn_momentum, unbias);
+        } else {
+            bn::ApplyForwardKernel<true><<<bn_blocks, bn::kThreads, 0, st>>>(z_tape(layer), ws.p_f32, bn_stats, gamma, gamma + H2, e->options.bn_eps, B, H2, x_f32,
+                                                                            ws.p_f32, xh, ws.p_act, e->bf16_now, bn_mean(layer), bn_rstd(layer), running,
+                                                                            e->bn_momentum, unbias);
+        }
+        e->launches += 3;
+        return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
+    };
+    // dzf (gradient w.r.t. the sum entering the ReLU above the layer) -> dz_tape(layer) = gradient w.r.t. z, plus the
+    // gradients of gamma, beta and of the bias inside z
+    auto bn_backward = [&](uint32_t layer, float* bias_grad) -> mgt_status_t {
+        bn::ColumnMomentsKernel<true><<<bn_blocks, bn::kThreads, 0, st>>>(dzf, ws.p_f32, z_tape(layer), ws.p_f32, bn_mean(layer), bn_rstd(layer), B, H2, bn_partial);
+        float* dgamma = grad + bn_base + 2ULL * layer * H2;
+        bn::ReduceMomentsKernel<<<bn_reduce_grid, bn_reduce_threads, 0, st>>>(bn_partial, bn_blocks, H2, 1.0f / (float)B, bn_stats, dgamma + H2, dgamma);
+        MGT_TRY(bn_exchange());
+        bn::ApplyBackwardKernel<<<bn_blocks, bn::kThreads, 0, st>>>(dzf, ws.p_f32, z_tape(layer), ws.p_f32, bn_mean(layer), bn_rstd(layer), w + bn_base + 2ULL * layer * H2,
+                                                                    bn_stats, B, H2, reinterpret_cast<uint16_t*>(dz_tape(layer)), ws.p_dz, e->bf16_now, bn_partial);
+        bn::ReduceSumsKernel<<<bn_reduce_grid, bn_reduce_threads, 0, st>>>(bn_partial, bn_blocks, H2, bias_grad);
+        e->launches += 4;
+        return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
     };
 
     // ---- fp16 weights: the caller's mirror as it lies when TMA can address it, else a padded copy
@@ -1077,12 +1171,18 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     {
         GemmArgs epi{};
         epi.bias = w + HiddenBias(s); epi.out_f32 = x_f32; epi.ld_f32 = ws.p_f32; epi.out_f16 = x_h(0); epi.ld_f16 = ws.p_act;
-        MGT_TRY(GemmForward<Epi::kBiasReluF32F16>(e, st, a1_h, ws.p_a1, hw.wh, hw.p2, B, H2, H1, epi));
+        if (bnorm) {
+            epi.out_f32 = z_tape(0);
+            MGT_TRY(GemmForward<Epi::kBiasF32>(e, st, a1_h, ws.p_a1, hw.wh, hw.p2, B, H2, H1, epi));
+            MGT_TRY(bn_forward(0));
+        } else {
+            MGT_TRY(GemmForward<Epi::kBiasReluF32F16>(e, st, a1_h, ws.p_a1, hw.wh, hw.p2, B, H2, H1, epi));
+        }
     }
     if (!timer.Mark(profile ? &profile->hidden_forward_ms : nullptr)) return MGT_CUDA_FAILURE;
 
     // ---- residual blocks forward (mlp_backward.cu:1294-1323)
-    const bool chain = ChainEligible(e, s);
+    const bool chain = ChainEligible(e, s) && !bnorm;  // batch statistics need the whole batch between two layers: one kernel per layer
     const uint64_t w_layer_stride = R > 0 ? (uint64_t)(reinterpret_cast<const uint8_t*>(hw.w2[0]) - reinterpret_cast<const uint8_t*>(hw.w1[0])) : 16;
     ChainArgs ca{};
     ca.samples = B; ca.H = H2; ca.R = R; ca.tiles = (B + 127U) / 128U;
@@ -1105,6 +1205,12 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
         GemmArgs e2{};
         e2.bias = w + Fc2B(s, k); e2.add_f32 = x_f32; e2.ld_add = ws.p_f32; e2.out_f32 = x_f32; e2.ld_f32 = ws.p_f32;
         e2.out_f16 = x_h(k + 1); e2.ld_f16 = ws.p_act;
+        if (bnorm) {
+            e2.out_f32 = z_tape(k + 1U);
+            MGT_TRY(GemmForward<Epi::kBiasF32>(e, st, r1_h(k), ws.p_act, hw.w2[k], hw.p2, B, H2, H2, e2));
+            MGT_TRY(bn_forward(k + 1U));
+            continue;
+        }
         MGT_TRY(GemmForward<Epi::kBiasResReluF32F16>(e, st, r1_h(k), ws.p_act, hw.w2[k], hw.p2, B, H2, H2, e2));
     }
     if (!timer.Mark(profile ? &profile->residual_forward_ms : nullptr)) return MGT_CUDA_FAILURE;
@@ -1159,6 +1265,7 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     }
     for (uint32_t rb = R; rb > 0 && !chain; --rb) {
         const uint32_t k = rb - 1U;
+        if (bnorm) MGT_TRY(bn_backward(k + 1U, grad + Fc2B(s, k)));  // dz_tape(k + 1) = gradient w.r.t. the fc2 output; dzf goes down the skip path as it is
         GemmArgs d2{};  // dz1 = (dz2 * W2^T) * [r1 > 0]
         d2.mask = r1_h(k); d2.ld_mask = ws.p_act; d2.out_f16 = dz1_tape(k); d2.ld_f16 = ws.p_dz;
         MGT_TRY(GemmBackpropInput<Epi::kMaskF16>(e, st, dz_tape(k + 1), ws.p_dz, hw.w2[k], hw.p2, B, H2, H2, d2, colsum + ws.colsum_slot_floats * k, nullptr));
@@ -1177,6 +1284,7 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
 
     // ---- hidden layer backward, dX part (mlp_backward.cu:1417-1438): dz_tape(0) = dcur * [x0 > 0]
     dz_cur = dz_tape(0);
+    if (bnorm) MGT_TRY(bn_backward(0, grad + HiddenBias(s)));
     if (half_ig) {
         GemmArgs d{};  // dz1 = (dzh * Wh^T) * [a1 > 0]
         d.mask = a1_h; d.ld_mask = ws.p_a1; d.out_f16 = dz1_h; d.ld_f16 = ws.p_dz1;
@@ -1236,7 +1344,8 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
             dst.offset[k] = Fc1B(s, k);
             dst.offset[R + k] = k > 0 ? Fc2B(s, k - 1) : HiddenBias(s);
         }
-        ReduceRowsGroupedKernel<<<dim3((H2 + kReduceCols - 1) / kReduceCols, 2 * R), 256, 0, st>>>(colsum, colsum_rows, H2, ws.colsum_slot_floats, grad, dst);
+        // (with batch normalisation b2_k and the hidden bias got their gradients from the normalisation's backward pass)
+        ReduceRowsGroupedKernel<<<dim3((H2 + kReduceCols - 1) / kReduceCols, bnorm ? R : 2 * R), 256, 0, st>>>(colsum, colsum_rows, H2, ws.colsum_slot_floats, grad, dst);
         ++e->launches;
         if (cudaGetLastError() != cudaSuccess) return MGT_CUDA_FAILURE;
         for (uint32_t rb = R; rb > 0; --rb) {
@@ -1252,6 +1361,7 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     MGT_TRY(notify(HiddenWeight(s), (uint64_t)H1 * H2 + H2));
     if (!timer.Mark(profile ? &profile->hidden_backward_ms : nullptr)) return MGT_CUDA_FAILURE;
     MGT_TRY(notify(0, InputBias(s) + H1));
+    if (bnorm) MGT_TRY(notify(bn_base, 2ULL * (R + 1ULL) * H2));
     return MGT_OK;
 }
 
@@ -1259,6 +1369,7 @@ mgt_status_t mgt_engine_set_train_options(mgt_engine_t* e, const mgt_train_optio
     if (e == nullptr || options == nullptr) return MGT_INVALID_CONFIG;
     if (options->operand_format != MGT_OPERAND_FP16 && options->operand_format != MGT_OPERAND_BF16) return MGT_INVALID_CONFIG;
     if (options->loss_kind != MGT_LOSS_MSE && options->loss_kind != MGT_LOSS_CROSS_ENTROPY) return MGT_INVALID_CONFIG;
+    if (options->batch_norm != 0 && !(options->bn_eps > 0.0f)) return MGT_INVALID_CONFIG;
     e->options = *options;
     return MGT_OK;
 }

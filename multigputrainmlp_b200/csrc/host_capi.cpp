@@ -2,6 +2,7 @@
 #include "../../include/mgt_b200.h"
 #include "host_plan.hpp"
 
+#include <cmath>
 #include <algorithm>
 #include <filesystem>
 #include <string>
@@ -75,6 +76,31 @@ mgt_status_t mgt_format_step_record(int32_t argc, const char* const* argv, const
 }
 
 uint16_t mgt_export_float_to_fp16(float value) { return ExportFloatToFp16(value); }
+
+mgt_status_t mgt_fold_batch_norm(const mgt_mlp_shape_t* shape, float* weights, const float* scale_shift, const float* running_stats, float eps) {
+    if (shape == nullptr || weights == nullptr || scale_shift == nullptr || running_stats == nullptr || !(eps > 0.0f)) return MGT_INVALID_CONFIG;
+    if (mgt_validate_mlp_shape(shape) != MGT_OK) return MGT_INVALID_CONFIG;
+    const uint64_t H1 = shape->hd1, H2 = shape->hd2, R = shape->residual_blocks;
+    const uint64_t hidden_w = (uint64_t)shape->state_len * shape->state_value_pad * H1 + H1, hidden_b = hidden_w + H1 * H2, tower = hidden_b + H2;
+    // y = gamma * (z - mean) / sqrt(var + eps) + beta with z = x W + b  ==  x (W diag(s)) + ((b - mean) s + beta),  s = gamma / sqrt(var + eps)
+    auto fold = [&](uint64_t layer, float* w, uint64_t rows, float* b) {
+        const float* gamma = scale_shift + 2ULL * layer * H2;
+        const float* beta = gamma + H2;
+        const float* mean = running_stats + 2ULL * layer * H2;
+        const float* var = mean + H2;
+        for (uint64_t j = 0; j < H2; ++j) {
+            const float s = gamma[j] / std::sqrt(var[j] + eps);
+            for (uint64_t i = 0; i < rows; ++i) w[i * H2 + j] *= s;
+            b[j] = (b[j] - mean[j]) * s + beta[j];
+        }
+    };
+    fold(0, weights + hidden_w, H1, weights + hidden_b);
+    for (uint64_t k = 0; k < R; ++k) {
+        float* fc2_w = weights + tower + k * 2ULL * (H2 * H2 + H2) + H2 * H2 + H2;
+        fold(k + 1ULL, fc2_w, H2, fc2_w + H2 * H2);
+    }
+    return MGT_OK;
+}
 
 mgt_status_t mgt_load_puzzle_definition(const char* group_json, const char* target_bin, uint32_t group_id, uint32_t state_len, uint32_t move_count,
                                         mgt_train_state_t* moves, mgt_train_state_t* target) {

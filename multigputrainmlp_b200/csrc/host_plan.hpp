@@ -33,6 +33,10 @@ struct TrainOptions {
     bool resume_step = false;
     // options of the loss+gradient launch that the reference does not have (mgt_train_options_t): "fp16" | "bf16", "mse" | "ce"
     std::string operand_format = "fp16", loss = "mse";
+    // batch normalisation of the hidden layer and of every block's fc2 output (statistics over all ranks); the scale/shift
+    // vectors and the running statistics live beside the reference's files, and the exported weights have them folded in
+    bool batch_norm = false;
+    float bn_eps = 1.0e-5f, bn_momentum = 0.1f;
 };
 
 // Every flag takes exactly one value; unknown flags, missing values and unparsable values fail

@@ -87,6 +87,7 @@ bool ParseTrainOptions(int argc, const char* const* argv, TrainOptions* o) {
         {"--checkpoint-period-steps", u32(&o->checkpoint_period_steps)}, {"--resume-step", flag(&o->resume_step)},
         {"--puzzle-json", text(&o->puzzle_json)}, {"--target-bin", text(&o->target_bin)},
         {"--operand-format", text(&o->operand_format)}, {"--loss", text(&o->loss)},
+        {"--batch-norm", flag(&o->batch_norm)}, {"--bn-eps", f32(&o->bn_eps)}, {"--bn-momentum", f32(&o->bn_momentum)},
     };
     for (int i = 1; i < argc; i += 2) {
         if (i + 1 >= argc) return false;
@@ -109,7 +110,8 @@ bool ValidateTrainOptions(const TrainOptions& o) {
     if (o.operand_format != "fp16" && o.operand_format != "bf16") return false;
     if (o.loss != "mse" && o.loss != "ce") return false;
     if (o.loss == "ce" && (o.output_dim < 2 || o.k_max > o.output_dim)) return false;  // one logit per walk depth
-    if ((o.loss == "ce" || o.operand_format == "bf16") && !o.linear_fp16) return false;
+    if ((o.loss == "ce" || o.operand_format == "bf16" || o.batch_norm) && !o.linear_fp16) return false;
+    if (o.batch_norm && (!(o.bn_eps > 0.0f) || !(o.bn_momentum >= 0.0f && o.bn_momentum <= 1.0f))) return false;
     return true;
 }
 

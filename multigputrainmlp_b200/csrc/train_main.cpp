@@ -95,22 +95,28 @@ mgt_status_t OnGradientReady(void* user, uint32_t ready_id, uint64_t offset, uin
     (void)ready_id;
     ++ctx->scheduled_ranges;
     // The engine announces a range after the last kernel that reads its weights, so the fused exchange + update can go
-    // out at once. The range that closes backward (the embedding table) is kept for Flush(whole): nothing is left to
-    // overlap with, so it is not cut into buckets.
-    if (!ctx->Flush(static_cast<cudaStream_t>(producer_stream))) { ctx->failed = true; return MGT_NCCL_FAILURE; }
+    // out without holding it back for safety. It is held back for another reason: every launch costs a handshake with all
+    // peers, and backward announces the ranges of the residual blocks end to end (last block first, the hidden layer
+    // below them), so ranges that touch in memory are joined while the sum stays within one bucket. The range that closes
+    // backward (the embedding table) is kept for Flush(whole): nothing is left to overlap with, so it is not cut up.
     if (ctx->have_early && ctx->early_begin == offset && ctx->early_end <= offset + count) {
         // leading blocks of this range went out through the hook: only the rest is left
         count = offset + count - ctx->early_end;
         offset = ctx->early_end;
         if (count == 0) return MGT_OK;
     }
-    if (ctx->expected_ranges != 0 && ctx->scheduled_ranges == ctx->expected_ranges) {
-        ctx->have_pending = true;
-        ctx->pending_offset = offset;
-        ctx->pending_count = count;
-        return MGT_OK;
+    if (ctx->have_pending) {
+        const bool touches = offset + count == ctx->pending_offset || ctx->pending_offset + ctx->pending_count == offset;
+        if (touches && ctx->pending_count + count <= ctx->bucket_params) {
+            ctx->pending_offset = std::min(ctx->pending_offset, offset);
+            ctx->pending_count += count;
+            return MGT_OK;
+        }
+        if (!ctx->Flush(static_cast<cudaStream_t>(producer_stream))) { ctx->failed = true; return MGT_NCCL_FAILURE; }
     }
-    if (!ctx->LaunchRange(offset, count, static_cast<cudaStream_t>(producer_stream), false)) { ctx->failed = true; return MGT_NCCL_FAILURE; }
+    ctx->have_pending = true;
+    ctx->pending_offset = offset;
+    ctx->pending_count = count;
     return MGT_OK;
 }
 
@@ -141,12 +147,47 @@ mgt_status_t OnEarlyRange(void* user, uint32_t ready_id, uint64_t offset, uint64
     return MGT_OK;
 }
 
+// Batch-norm statistics over all ranks: a second, small communicator driven from the compute stream (one communicator
+// belongs to one stream; the gradient exchange keeps its own).
+struct StatsContext {
+    mgt_comm_t* comm = nullptr;
+    uint32_t world_size = 1, global_rank = 0;
+};
+mgt_status_t OnStatsExchange(void* user, float* device_buffer, uint64_t float_count, void* stream) {
+    auto* ctx = static_cast<StatsContext*>(user);
+    if (ctx == nullptr || ctx->comm == nullptr) return MGT_INVALID_CONFIG;
+    const mgt_allreduce_config_t ar{ctx->world_size, ctx->global_rank, 0, float_count};
+    return mgt_comm_allreduce_average(ctx->comm, &ar, device_buffer, stream);
+}
+
+// checkpoint/batch_norm.f32.bin: scale/shift, their AdamW moments, running statistics - four sections of `count` floats,
+// beside the reference's checkpoint files, which keep their format.
+bool WriteBatchNormState(const std::string& dir, const std::vector<float>& scale_shift, const std::vector<float>& m, const std::vector<float>& v,
+                         const std::vector<float>& running, uint32_t layers, uint32_t width, float eps, float momentum) {
+    std::ofstream data(dir + "/checkpoint/batch_norm.f32.bin", std::ios::binary | std::ios::trunc);
+    for (const std::vector<float>* section : {&scale_shift, &m, &v, &running})
+        data.write(reinterpret_cast<const char*>(section->data()), static_cast<std::streamsize>(section->size() * sizeof(float)));
+    std::ofstream man(dir + "/checkpoint/batch_norm.json", std::ios::trunc);
+    man << "{\n  \"format\": \"mgt_batch_norm_state_v1\",\n  \"layers\": " << layers << ",\n  \"width\": " << width << ",\n  \"eps\": " << eps
+        << ",\n  \"momentum\": " << momentum << ",\n  \"dtype\": \"f32\",\n  \"sections\": [\"scale_shift\", \"adam_m\", \"adam_v\", \"running_stats\"],\n"
+        << "  \"section_floats\": " << scale_shift.size() << ",\n  \"layer_layout\": \"layer 0 = hidden layer, layer k+1 = residual block k; scale_shift: gamma[width], "
+        << "beta[width]; running_stats: mean[width], var[width]\"\n}\n";
+    return static_cast<bool>(data) && static_cast<bool>(man);
+}
+bool ReadBatchNormState(const std::string& checkpoint_dir, std::vector<float>* scale_shift, std::vector<float>* m, std::vector<float>* v, std::vector<float>* running) {
+    std::ifstream data(checkpoint_dir + "/batch_norm.f32.bin", std::ios::binary);
+    if (!data) return false;
+    for (std::vector<float>* section : {scale_shift, m, v, running})
+        data.read(reinterpret_cast<char*>(section->data()), static_cast<std::streamsize>(section->size() * sizeof(float)));
+    return static_cast<bool>(data);
+}
+
 const char kUsage[] =
     "usage: mgt_native_train --output-dir DIR --steps N --device-id ID --world-size N --global-rank R --local-rank R "
     "[--batch-size N --k-min N --k-max N --hd1 N --hd2 N --nrd N --write-artifacts 0|1 --backward-profile 0|1 --overlap-allreduce 0|1 "
     "--input-grad-partial-chunks N --input-grad-positions-per-block N --input-grad-position-tile N --input-grad-fp16 0|1 --linear-fp16 0|1 "
     "--persistent-half-weights 0|1 --lt-workspace-bytes N --nccl-id-file PATH --resume-checkpoint DIR "
-    "--checkpoint-period-steps N --resume-step 0|1 --puzzle-json PATH --target-bin PATH --operand-format fp16|bf16 --loss mse|ce]\n";
+    "--checkpoint-period-steps N --resume-step 0|1 --puzzle-json PATH --target-bin PATH --operand-format fp16|bf16 --loss mse|ce --batch-norm 0|1 --bn-eps X --bn-momentum X]\n";
 
 }  // namespace
 
@@ -172,10 +213,23 @@ int main(int argc, char** argv) {
     const uint64_t P = plan.total_params;
     if (mgt_mlp_param_count(&shape) != P) return EXIT_FAILURE;
 
+    // trained floats on the device: the reference's parameters, then (with --batch-norm 1) the scale/shift vectors
+    const uint64_t NBN = opt.batch_norm ? mgt_bn_param_count(&shape) : 0;
+    const uint64_t T = P + NBN;
     std::vector<float> weights(P), adam_m(P, 0.0f), adam_v(P, 0.0f);
+    std::vector<float> bn_scale_shift(NBN, 0.0f), bn_m(NBN, 0.0f), bn_v(NBN, 0.0f), bn_running(NBN, 0.0f);
+    for (uint64_t i = 0; i < NBN; ++i) {
+        const bool first_half = (i / shape.hd2) % 2ULL == 0;
+        bn_scale_shift[i] = first_half ? 1.0f : 0.0f;  // gamma = 1, beta = 0
+        bn_running[i] = first_half ? 0.0f : 1.0f;      // mean = 0, var = 1
+    }
     InitialWeights(&weights);
     const bool resumed = !opt.resume_checkpoint.empty();
     if (resumed && !ReadCheckpoint(opt.resume_checkpoint, &weights, &adam_m, &adam_v)) return EXIT_FAILURE;
+    if (resumed && NBN != 0 && !ReadBatchNormState(opt.resume_checkpoint, &bn_scale_shift, &bn_m, &bn_v, &bn_running)) {
+        std::cerr << "--batch-norm 1: " << opt.resume_checkpoint << "/batch_norm.f32.bin not found or too short\n";
+        return EXIT_FAILURE;
+    }
     // Step numbering of a resumed run: the reference restarts at 0 (tool:765,830), which replays the first walk batches
     // and AdamW bias corrections. With --resume-step 1 the count written beside the checkpoint (checkpoint/step.txt; the
     // manifest itself stays byte-compatible) is continued, so that N + M steps in two runs equal N + M steps in one.
@@ -204,27 +258,39 @@ int main(int argc, char** argv) {
 
     mgt_engine_t* engine = nullptr;
     if (mgt_engine_create(static_cast<int32_t>(opt.device_id), &engine) != MGT_OK) return EXIT_FAILURE;
-    const mgt_train_options_t train_options{opt.operand_format == "bf16" ? MGT_OPERAND_BF16 : MGT_OPERAND_FP16, opt.loss == "ce" ? MGT_LOSS_CROSS_ENTROPY : MGT_LOSS_MSE};
+    const mgt_train_options_t train_options{opt.operand_format == "bf16" ? MGT_OPERAND_BF16 : MGT_OPERAND_FP16, opt.loss == "ce" ? MGT_LOSS_CROSS_ENTROPY : MGT_LOSS_MSE,
+                                            opt.batch_norm ? 1 : 0, opt.bn_eps};
     if (mgt_engine_set_train_options(engine, &train_options) != MGT_OK) return EXIT_FAILURE;
     // the communicator stands where the reference creates its NCCL context, also for one rank (tool:708-713)
     mgt_comm_t* comm = nullptr;
-    if (mgt_comm_create(static_cast<int32_t>(opt.device_id), opt.world_size, opt.global_rank, opt.nccl_id_file.empty() ? nullptr : opt.nccl_id_file.c_str(), P, &comm) != MGT_OK) {
+    if (mgt_comm_create(static_cast<int32_t>(opt.device_id), opt.world_size, opt.global_rank, opt.nccl_id_file.empty() ? nullptr : opt.nccl_id_file.c_str(), T, &comm) != MGT_OK) {
         return EXIT_FAILURE;
+    }
+    mgt_comm_t* stats_comm = nullptr;
+    StatsContext stats_ctx;
+    if (NBN != 0 && opt.world_size > 1) {
+        const std::string stats_id = opt.nccl_id_file + ".bn";
+        if (mgt_comm_create(static_cast<int32_t>(opt.device_id), opt.world_size, opt.global_rank, stats_id.c_str(), 2ULL * shape.hd2, &stats_comm) != MGT_OK) return EXIT_FAILURE;
+        stats_ctx.comm = stats_comm;
+        stats_ctx.world_size = opt.world_size;
+        stats_ctx.global_rank = opt.global_rank;
     }
     const bool comm_enabled = true;
 
+    float* d_bn_running = nullptr;
     float *d_w = nullptr, *d_labels = nullptr, *d_walk_labels = nullptr, *d_loss = nullptr, *d_ws = nullptr, *d_m = nullptr, *d_v = nullptr;
     uint16_t* d_w_half = nullptr;
     mgt_train_state_t *d_states = nullptr, *d_moves = nullptr, *d_target = nullptr;
     mgt_walk_meta_t* d_meta = nullptr;
     float* d_grad = mgt_comm_gradient_buffer(comm);  // peers map this buffer; with one rank it is plain device memory
-    const uint64_t ws_floats = mgt_mlp_loss_grad_workspace_floats(&shape, B, opt.input_grad_partial_chunks, opt.input_grad_fp16, opt.linear_fp16);
+    const uint64_t ws_floats = mgt_mlp_loss_grad_workspace_floats_with_options(&shape, B, opt.input_grad_partial_chunks, opt.input_grad_fp16, opt.linear_fp16, &train_options);
     if (ws_floats == 0 || d_grad == nullptr) return EXIT_FAILURE;
     cudaStream_t compute = nullptr, comm_stream = nullptr;
-    bool ok = CUDA_OK(cudaMalloc(&d_w, P * 4)) && (!(opt.linear_fp16 && opt.persistent_half_weights) || CUDA_OK(cudaMalloc(&d_w_half, P * 2))) &&
+    bool ok = CUDA_OK(cudaMalloc(&d_w, T * 4)) && (!(opt.linear_fp16 && opt.persistent_half_weights) || CUDA_OK(cudaMalloc(&d_w_half, T * 2))) &&
+              (NBN == 0 || CUDA_OK(cudaMalloc(&d_bn_running, NBN * 4))) &&
               CUDA_OK(cudaMalloc(&d_labels, static_cast<uint64_t>(B) * opt.output_dim * 4)) &&
               (opt.output_dim == 1 || CUDA_OK(cudaMalloc(&d_walk_labels, static_cast<uint64_t>(B) * 4))) && CUDA_OK(cudaMalloc(&d_loss, 4)) &&
-              CUDA_OK(cudaMalloc(&d_ws, ws_floats * 4)) && CUDA_OK(cudaMalloc(&d_m, P * 4)) && CUDA_OK(cudaMalloc(&d_v, P * 4)) &&
+              CUDA_OK(cudaMalloc(&d_ws, ws_floats * 4)) && CUDA_OK(cudaMalloc(&d_m, T * 4)) && CUDA_OK(cudaMalloc(&d_v, T * 4)) &&
               CUDA_OK(cudaMalloc(&d_states, static_cast<uint64_t>(B) * 80)) && CUDA_OK(cudaMalloc(&d_meta, static_cast<uint64_t>(B) * 16)) &&
               CUDA_OK(cudaMalloc(&d_moves, 18 * 80)) && CUDA_OK(cudaMalloc(&d_target, 80)) &&
               CUDA_OK(cudaStreamCreateWithFlags(&compute, cudaStreamNonBlocking)) && CUDA_OK(cudaStreamCreateWithFlags(&comm_stream, cudaStreamNonBlocking));
@@ -233,7 +299,14 @@ int main(int argc, char** argv) {
          CUDA_OK(cudaMemcpy(d_v, adam_v.data(), P * 4, cudaMemcpyHostToDevice)) && CUDA_OK(cudaMemcpy(d_moves, moves, sizeof(moves), cudaMemcpyHostToDevice)) &&
          CUDA_OK(cudaMemcpy(d_target, target, sizeof(target), cudaMemcpyHostToDevice));
     if (!ok) return EXIT_FAILURE;
-    if (d_w_half != nullptr && mgt_launch_float_to_half(d_w, P, d_w_half, compute) != MGT_OK) return EXIT_FAILURE;
+    if (NBN != 0) {
+        ok = CUDA_OK(cudaMemcpy(d_w + P, bn_scale_shift.data(), NBN * 4, cudaMemcpyHostToDevice)) && CUDA_OK(cudaMemcpy(d_m + P, bn_m.data(), NBN * 4, cudaMemcpyHostToDevice)) &&
+             CUDA_OK(cudaMemcpy(d_v + P, bn_v.data(), NBN * 4, cudaMemcpyHostToDevice)) && CUDA_OK(cudaMemcpy(d_bn_running, bn_running.data(), NBN * 4, cudaMemcpyHostToDevice));
+        if (!ok) return EXIT_FAILURE;
+        if (mgt_engine_set_batch_norm_state(engine, d_bn_running, opt.bn_momentum, opt.world_size, stats_comm != nullptr ? mgt_comm_gradient_buffer(stats_comm) : nullptr,
+                                            stats_comm != nullptr ? OnStatsExchange : nullptr, &stats_ctx) != MGT_OK) return EXIT_FAILURE;
+    }
+    if (d_w_half != nullptr && mgt_launch_float_to_half(d_w, T, d_w_half, compute) != MGT_OK) return EXIT_FAILURE;
 
     std::filesystem::create_directories(opt.output_dir);
     std::ofstream log(std::filesystem::path(opt.output_dir) / "train.log");
@@ -243,7 +316,7 @@ int main(int argc, char** argv) {
         !CUDA_OK(cudaEventCreate(&ev_allreduce)) || !CUDA_OK(cudaEventCreate(&ev_stop)) ||
         !CUDA_OK(cudaEventCreateWithFlags(&ev_comm_done, cudaEventDisableTiming))) return EXIT_FAILURE;
     const bool overlap = comm_enabled && opt.overlap_allreduce && opt.world_size > 1;
-    const uint32_t expected_ranges = 2U * opt.nrd + 3U;
+    const uint32_t expected_ranges = 2U * opt.nrd + 3U + (NBN != 0 ? 1U : 0U);  // batch norm: one more range, the scale/shift vectors
     std::vector<cudaEvent_t> ready_events;
     if (overlap) {
         ready_events.resize(expected_ranges + 1U, nullptr);
@@ -257,8 +330,17 @@ int main(int argc, char** argv) {
     auto write_checkpoint = [&](uint32_t steps_done, bool with_weights) -> bool {
         if (!CUDA_OK(cudaMemcpy(weights.data(), d_w, P * 4, cudaMemcpyDeviceToHost)) || !CUDA_OK(cudaMemcpy(adam_m.data(), d_m, P * 4, cudaMemcpyDeviceToHost)) ||
             !CUDA_OK(cudaMemcpy(adam_v.data(), d_v, P * 4, cudaMemcpyDeviceToHost))) return false;
-        if (with_weights && !WriteWeights(opt.output_dir, plan, weights)) return false;
+        if (NBN != 0 && (!CUDA_OK(cudaMemcpy(bn_scale_shift.data(), d_w + P, NBN * 4, cudaMemcpyDeviceToHost)) || !CUDA_OK(cudaMemcpy(bn_m.data(), d_m + P, NBN * 4, cudaMemcpyDeviceToHost)) ||
+                         !CUDA_OK(cudaMemcpy(bn_v.data(), d_v + P, NBN * 4, cudaMemcpyDeviceToHost)) ||
+                         !CUDA_OK(cudaMemcpy(bn_running.data(), d_bn_running, NBN * 4, cudaMemcpyDeviceToHost)))) return false;
+        if (with_weights) {
+            // the weights/ files describe a network without normalisation: fold it in with the running statistics
+            std::vector<float> exported = weights;
+            if (NBN != 0 && mgt_fold_batch_norm(&shape, exported.data(), bn_scale_shift.data(), bn_running.data(), opt.bn_eps) != MGT_OK) return false;
+            if (!WriteWeights(opt.output_dir, plan, exported)) return false;
+        }
         if (!WriteCheckpoint(opt.output_dir, plan, weights, adam_m, adam_v)) return false;
+        if (NBN != 0 && !WriteBatchNormState(opt.output_dir, bn_scale_shift, bn_m, bn_v, bn_running, opt.nrd + 1U, shape.hd2, opt.bn_eps, opt.bn_momentum)) return false;
         std::ofstream out(opt.output_dir + "/checkpoint/step.txt", std::ios::trunc);
         out << steps_done << "\n";
         return static_cast<bool>(out);
@@ -275,7 +357,7 @@ int main(int argc, char** argv) {
         if (!CUDA_OK(cudaEventRecord(ev_walk, compute))) return EXIT_FAILURE;
 
         // the resumed run restarts its step counter, as the reference does (tool:765,830)
-        const mgt_adamw_config_t adamw{P, static_cast<uint64_t>(step) + 1ULL, opt.lr, 0.9f, 0.999f, 1.0e-8f, opt.weight_decay};
+        const mgt_adamw_config_t adamw{T, static_cast<uint64_t>(step) + 1ULL, opt.lr, 0.9f, 0.999f, 1.0e-8f, opt.weight_decay};
         ExchangeContext exchange;
         if (overlap) {
             exchange.enabled = true;
@@ -310,7 +392,7 @@ int main(int argc, char** argv) {
             if (!exchange.UpdateDeferred(compute)) return EXIT_FAILURE;
             weights_updated = true;  // AdamW ran inside the exchange kernels
         } else if (opt.world_size > 1) {
-            const mgt_allreduce_config_t ar{opt.world_size, opt.global_rank, step, P};
+            const mgt_allreduce_config_t ar{opt.world_size, opt.global_rank, step, T};
             if (mgt_comm_allreduce_average(comm, &ar, d_grad, compute) != MGT_OK) return EXIT_FAILURE;
             overlap_chunks = 1;
         }
@@ -329,7 +411,8 @@ int main(int argc, char** argv) {
             !CUDA_OK(cudaEventElapsedTime(&rec.adam_ms, ev_allreduce, ev_stop))) return EXIT_FAILURE;
         if (!CUDA_OK(cudaMemcpy(&last_loss, d_loss, 4, cudaMemcpyDeviceToHost))) return EXIT_FAILURE;
         int32_t code = 0;
-        if (mgt_engine_check(engine, compute, &code) != MGT_OK || mgt_comm_check(comm, comm_stream, &code) != MGT_OK) {
+        if (mgt_engine_check(engine, compute, &code) != MGT_OK || mgt_comm_check(comm, comm_stream, &code) != MGT_OK ||
+            (stats_comm != nullptr && mgt_comm_check(stats_comm, compute, &code) != MGT_OK)) {
             std::cerr << "device wait timed out (code " << code << ")\n";
             return EXIT_FAILURE;
         }
@@ -355,13 +438,13 @@ int main(int argc, char** argv) {
     if (!WriteMetadataEnv(opt.output_dir, plan, overlap, comm_enabled, resumed) || !WriteLayersJson(opt.output_dir, plan) ||
         !WriteLinearOpsManifest(opt.output_dir, plan)) return EXIT_FAILURE;
 
-    if (mgt_comm_destroy(comm) != MGT_OK) return EXIT_FAILURE;
+    if (mgt_comm_destroy(comm) != MGT_OK || mgt_comm_destroy(stats_comm) != MGT_OK) return EXIT_FAILURE;
     mgt_engine_destroy(engine);
     for (cudaEvent_t ev : ready_events) cudaEventDestroy(ev);
     for (cudaEvent_t ev : {ev_start, ev_walk, ev_backward, ev_allreduce, ev_stop, ev_comm_done}) cudaEventDestroy(ev);
     for (void* p : {static_cast<void*>(d_target), static_cast<void*>(d_moves), static_cast<void*>(d_meta), static_cast<void*>(d_states), static_cast<void*>(d_v),
                     static_cast<void*>(d_m), static_cast<void*>(d_ws), static_cast<void*>(d_loss), static_cast<void*>(d_labels), static_cast<void*>(d_walk_labels),
-                    static_cast<void*>(d_w_half), static_cast<void*>(d_w)})
+                    static_cast<void*>(d_w_half), static_cast<void*>(d_w), static_cast<void*>(d_bn_running)})
         if (p != nullptr) cudaFree(p);
     cudaStreamDestroy(comm_stream);
     cudaStreamDestroy(compute);

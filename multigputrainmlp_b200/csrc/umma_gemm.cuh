@@ -35,6 +35,7 @@ enum class Epi : int {
     kPartialF32,           // partial[split][m][n] = acc
     kEmbFwd,               // out_f16[n][m] = relu(acc)            (D is the transposed activation)
     kEmbGrad,              // out_f32[n][m] (+)= acc               (D is the transposed gradient)
+    kBiasF32,              // out_f32 = acc + bias                 (a pre-activation kept in fp32: input of batch normalisation)
 };
 
 struct GemmArgs {
@@ -429,10 +430,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             // instruction. The global operands of a chunk (residual/skip values, ReLU mask source, bias) are
             // requested one chunk ahead - for the first chunk of a tile before the tile's MMAs have even finished -
             // so their latency is off the critical path. Ragged shapes take a scalar form without prefetch.
-            constexpr bool kHasBias = Cfg::EPI == Epi::kBiasReluF16 || Cfg::EPI == Epi::kBiasReluF32F16 || Cfg::EPI == Epi::kBiasResReluF32F16;
+            constexpr bool kPlainF32 = Cfg::EPI == Epi::kBiasF32;  // fp32 out only: no ReLU, no 16-bit copy
+            constexpr bool kHasBias = Cfg::EPI == Epi::kBiasReluF16 || Cfg::EPI == Epi::kBiasReluF32F16 || Cfg::EPI == Epi::kBiasResReluF32F16 || kPlainF32;
             constexpr bool kHasAdd = Cfg::EPI == Epi::kBiasResReluF32F16 || Cfg::EPI == Epi::kAddMaskF32F16;
             constexpr bool kHasMask = Cfg::EPI == Epi::kMaskF16 || Cfg::EPI == Epi::kAddMaskF32F16;
-            constexpr bool kOutF32 = Cfg::EPI == Epi::kBiasReluF32F16 || Cfg::EPI == Epi::kBiasResReluF32F16 || Cfg::EPI == Epi::kAddMaskF32F16;
+            constexpr bool kOutF32 = Cfg::EPI == Epi::kBiasReluF32F16 || Cfg::EPI == Epi::kBiasResReluF32F16 || Cfg::EPI == Epi::kAddMaskF32F16 || kPlainF32;
             constexpr bool kPartial = Cfg::EPI == Epi::kPartialF32;
             constexpr uint32_t TP = Cfg::EPI_TILE_PITCH;  // floats per staged row (16-byte aligned, bank-friendly)
             float* tile = epi_stage + ew * (Cfg::EPI_WARP_BYTES / 4);
@@ -450,7 +452,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             const uint32_t r4 = lane >> 3, c4 = (lane & 7U) * 4U;  // fp32 vectors: 4 rows x 8 lanes
             const uint32_t r8 = lane >> 2, c8 = (lane & 3U) * 8U;  // fp16 vectors: 8 rows x 4 lanes
             const bool ld_vec = (!kHasAdd || (args.ld_add & 3U) == 0U) && (!kHasMask || (args.ld_mask & 7U) == 0U) &&
-                                (!kOutF32 || (args.ld_f32 & 3U) == 0U) && (kPartial ? (args.N & 3U) == 0U : (args.ld_f16 & 7U) == 0U);
+                                (!kOutF32 || (args.ld_f32 & 3U) == 0U) && (kPartial ? (args.N & 3U) == 0U : (kPlainF32 || (args.ld_f16 & 7U) == 0U));
             struct Operands {
                 float4 add[kHasAdd ? 8 : 1];
                 uint4 mask[kHasMask ? 4 : 1];
@@ -557,7 +559,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                         }
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = ((bits >> j) & 1U) ? v[j] : 0.0f;
-                    } else if constexpr (!kPartial) {
+                    } else if constexpr (!kPartial && !kPlainF32) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
                     }
@@ -580,7 +582,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                                 if (col_ok) base[rr * ld + lane] = tile[rr * TP + lane];
                         }
                     }
-                    if constexpr (!kPartial) {
+                    if constexpr (!kPartial && !kPlainF32) {
                         if (vec) {
 #pragma unroll
                             for (uint32_t i = 0; i < 4U; ++i) {

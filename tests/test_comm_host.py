@@ -108,6 +108,38 @@ def test_early_blocks_go_out_whole_and_the_closing_call_sends_the_rest():
     assert len(launches) == n and sched.on_early(34, 0, 0) == 1
 
 
+def test_touching_ranges_are_joined_into_bucket_sized_launches():
+    # the engine's order: output layer, blocks 15..0 (fc2 then fc1), the embedding range through the early hook once its
+    # GEMM is enqueued (before the weight-gradient GEMMs in the engine, here after the ranges for simplicity), hidden layer
+    bucket = (4 << 20) // 4
+    launches = []
+    sched = GradientRangeScheduler(lambda off, cnt: launches.append((off, cnt)), lambda: None, bucket_params=bucket, expected_ranges=35,
+                                   coalesce=True)
+    ranges = p888_ranges()
+    for step in range(2):
+        launches.clear()
+        sched.begin_step()
+        assert sched.on_early(34, *ranges[34]) == 0
+        for i in range(35):
+            assert sched.on_ready(i, *ranges[i]) == 0
+        sched.finish()
+        assert launches[0] == ranges[34]
+        rest = launches[1:]
+        assert len(rest) == 3                               # 34 ranges (2.18 M floats) in three launches instead of 34
+        assert all(c <= bucket for _, c in rest)
+        assert sum(c for _, c in launches) == 15460289
+        covered = sorted(launches)
+        assert all(covered[i][0] + covered[i][1] == covered[i + 1][0] for i in range(len(covered) - 1))
+    # ranges that do not touch are never joined, and a joined launch never exceeds the bucket
+    launches.clear()
+    sched = GradientRangeScheduler(lambda off, cnt: launches.append((off, cnt)), lambda: None, bucket_params=100, coalesce=True)
+    sched.begin_step()
+    for off, cnt in [(900, 60), (860, 40), (800, 60), (100, 50), (150, 50), (300, 10)]:
+        assert sched.on_ready(0, off, cnt) == 0
+    sched.finish()
+    assert launches == [(860, 100), (800, 60), (100, 100), (300, 10)]
+
+
 def test_scheduler_rejects_unexpected_ranges():
     sched = GradientRangeScheduler(lambda o, c: None, lambda: None, expected_ranges=3)
     sched.begin_step()
