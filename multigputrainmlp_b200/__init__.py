@@ -20,6 +20,7 @@ from .api import (  # noqa: F401
     load_puzzle_definition,
     mlp_loss_grad_workspace_floats,
     bn_param_count,
+    fold_batch_norm,
     status_name,
     validate_adamw_kernel_config,
     validate_cuda_mlp_shape,

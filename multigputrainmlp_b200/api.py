@@ -164,6 +164,25 @@ def bn_param_count(shape) -> int:
     return int(lib.mgt_bn_param_count(C.byref(s)))
 
 
+def fold_batch_norm(shape, weights, scale_shift, running_stats, eps: float = 1e-5):
+    """mgt_fold_batch_norm on host arrays: a copy of `weights` (the reference's layout) with the normalisation folded into
+    the hidden layer and into every block's fc2, using the running statistics. Raises MgtError on a bad argument."""
+    import numpy as np
+    s = shape.c()
+    lib = _lib.load()
+    out = np.array(weights, dtype=np.float32, copy=True).ravel()
+    ss = np.ascontiguousarray(scale_shift, dtype=np.float32).ravel()
+    rs = np.ascontiguousarray(running_stats, dtype=np.float32).ravel()
+    n = bn_param_count(shape)
+    if out.size != shape.param_count or ss.size != n or rs.size != n:
+        raise MgtError(1, "fold_batch_norm: array sizes")
+    lib.mgt_fold_batch_norm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float]
+    st = int(lib.mgt_fold_batch_norm(C.byref(s), out.ctypes.data_as(C.c_void_p), ss.ctypes.data_as(C.c_void_p), rs.ctypes.data_as(C.c_void_p), eps))
+    if st != 0:
+        raise MgtError(st, "fold_batch_norm")
+    return out
+
+
 STATS_EXCHANGE_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p)
 GRADIENT_READY_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint64, C.c_void_p)
 

@@ -193,10 +193,11 @@ class PeerBackend:
 
 class OverlappedGradientExchange:
     """Wires a back-end, a second CUDA stream and the scheduler to the engine's gradient-ready
-    callback, the way the reference trainer's step loop does (tool:785-821)."""
+    callback, the way the reference trainer's step loop does (tool:785-821). `extra_ranges`: announcements beyond the
+    reference's 2 * blocks + 3 (1 with batch normalisation: the scale/shift vectors, announced last)."""
 
     def __init__(self, backend: PeerBackend, device, bucket_bytes: int = 4 << 20, residual_blocks: int = 16, fused_adamw: bool = True,
-                 early_update_after_backward: bool = True, coalesce: bool = True):
+                 early_update_after_backward: bool = True, coalesce: bool = True, extra_ranges: int = 0):
         import torch
         self.torch = torch
         self.backend = backend
@@ -206,6 +207,7 @@ class OverlappedGradientExchange:
         self.events = [torch.cuda.Event() for _ in range(2 * residual_blocks + 4)]
         self._ev = 0
         self.done_event = torch.cuda.Event()
+        self.early_done_event = torch.cuda.Event()
         self.adamw: Optional[AdamWKernelConfig] = None
         self.state = None
         # The range from the early hook is exchanged while HBM-bound weight-gradient GEMMs run. Its AdamW update (30 bytes of
@@ -214,7 +216,7 @@ class OverlappedGradientExchange:
         self.early_update_after_backward = early_update_after_backward and fused_adamw
         self._deferred = []
         self.scheduler = GradientRangeScheduler(self._launch, self._wait_for_producer, bucket_params=max(1, bucket_bytes // 4),
-                                                expected_ranges=2 * residual_blocks + 3, lag=0, launch_early=self._launch_early,
+                                                expected_ranges=2 * residual_blocks + 3 + extra_ranges, lag=0, launch_early=self._launch_early,
                                                 coalesce=coalesce)
 
     def _wait_for_producer(self):
@@ -239,6 +241,7 @@ class OverlappedGradientExchange:
         if st != 0:
             raise MgtError(st, "gradient exchange")
         self._deferred.append((offset, count))
+        self.early_done_event.record(self.comm_stream)
 
     def begin_step(self, adamw: AdamWKernelConfig, w, w_half, m, v):
         self.adamw = adamw
@@ -255,7 +258,9 @@ class OverlappedGradientExchange:
     def finish_step(self):
         self.scheduler.finish()
         self.done_event.record(self.comm_stream)
-        self.torch.cuda.current_stream(self.device).wait_event(self.done_event)  # tool:820-821
+        compute = self.torch.cuda.current_stream(self.device)
+        # the deferred update only needs the early range's own exchange: it runs beside the tail of the exchange
+        compute.wait_event(self.early_done_event if self._deferred else self.done_event)
         if self._deferred:
             from .api import launch_adamw_kernel_with_half_mirror
             w, w_half, m, v = self.state
@@ -267,6 +272,7 @@ class OverlappedGradientExchange:
                 st = launch_adamw_kernel_with_half_mirror(cfg, w[offset:hi], w_half[offset:hi], grad[offset:hi], m[offset:hi], v[offset:hi])
                 if st != 0:
                     raise MgtError(st, "AdamW")
+            compute.wait_event(self.done_event)  # tool:820-821
 
 
 class NcclBackend:

@@ -43,6 +43,7 @@ struct ExchangeContext {
     uint32_t world_size = 1, global_rank = 0;
     bool early_update_after_backward = true;  // the early range: exchange under the weight-gradient GEMMs, AdamW once backward has ended
     bool have_deferred = false;
+    cudaEvent_t early_done = nullptr;  // recorded behind the exchange of the deferred range
     uint64_t deferred_offset = 0, deferred_count = 0;
     uint32_t scheduled_ranges = 0, scheduled_chunks = 0, next_event = 0, expected_ranges = 0;
     bool have_pending = false;
@@ -137,6 +138,7 @@ mgt_status_t OnEarlyRange(void* user, uint32_t ready_id, uint64_t offset, uint64
         return MGT_NCCL_FAILURE;
     }
     if (defer) {
+        if (ctx->early_done != nullptr && !CUDA_OK(cudaEventRecord(ctx->early_done, ctx->comm_stream))) return MGT_CUDA_FAILURE;
         ctx->have_deferred = true;
         ctx->deferred_offset = offset;
         ctx->deferred_count = count;
@@ -311,10 +313,11 @@ int main(int argc, char** argv) {
     std::filesystem::create_directories(opt.output_dir);
     std::ofstream log(std::filesystem::path(opt.output_dir) / "train.log");
     std::ofstream profile(std::filesystem::path(opt.output_dir) / "profile.jsonl");
-    cudaEvent_t ev_start, ev_walk, ev_backward, ev_allreduce, ev_stop, ev_comm_done;
+    cudaEvent_t ev_start, ev_walk, ev_backward, ev_allreduce, ev_stop, ev_comm_done, ev_early_done;
     if (!CUDA_OK(cudaEventCreate(&ev_start)) || !CUDA_OK(cudaEventCreate(&ev_walk)) || !CUDA_OK(cudaEventCreate(&ev_backward)) ||
         !CUDA_OK(cudaEventCreate(&ev_allreduce)) || !CUDA_OK(cudaEventCreate(&ev_stop)) ||
-        !CUDA_OK(cudaEventCreateWithFlags(&ev_comm_done, cudaEventDisableTiming))) return EXIT_FAILURE;
+        !CUDA_OK(cudaEventCreateWithFlags(&ev_comm_done, cudaEventDisableTiming)) ||
+        !CUDA_OK(cudaEventCreateWithFlags(&ev_early_done, cudaEventDisableTiming))) return EXIT_FAILURE;
     const bool overlap = comm_enabled && opt.overlap_allreduce && opt.world_size > 1;
     const uint32_t expected_ranges = 2U * opt.nrd + 3U + (NBN != 0 ? 1U : 0U);  // batch norm: one more range, the scale/shift vectors
     std::vector<cudaEvent_t> ready_events;
@@ -369,6 +372,7 @@ int main(int argc, char** argv) {
             exchange.expected_ranges = expected_ranges;
             exchange.w = d_w; exchange.w_half = d_w_half; exchange.m = d_m; exchange.v = d_v; exchange.grad = d_grad;
             exchange.world_size = opt.world_size; exchange.global_rank = opt.global_rank;
+            exchange.early_done = ev_early_done;
         }
         if (mgt_engine_set_early_range_hook(engine, overlap ? OnEarlyRange : nullptr, overlap ? &exchange : nullptr) != MGT_OK) return EXIT_FAILURE;
         mgt_backward_profile_t bw{};
@@ -388,8 +392,10 @@ int main(int argc, char** argv) {
             if (exchange.failed || exchange.scheduled_ranges != expected_ranges || !exchange.Flush(compute, true)) return EXIT_FAILURE;
             overlap_ranges = exchange.scheduled_ranges;
             overlap_chunks = exchange.scheduled_chunks;
-            if (!CUDA_OK(cudaEventRecord(ev_comm_done, comm_stream)) || !CUDA_OK(cudaStreamWaitEvent(compute, ev_comm_done, 0))) return EXIT_FAILURE;
-            if (!exchange.UpdateDeferred(compute)) return EXIT_FAILURE;
+            if (!CUDA_OK(cudaEventRecord(ev_comm_done, comm_stream))) return EXIT_FAILURE;
+            // the deferred update needs only its own range's exchange: it runs beside the tail of the exchange
+            if (exchange.have_deferred && !CUDA_OK(cudaStreamWaitEvent(compute, ev_early_done, 0))) return EXIT_FAILURE;
+            if (!exchange.UpdateDeferred(compute) || !CUDA_OK(cudaStreamWaitEvent(compute, ev_comm_done, 0))) return EXIT_FAILURE;
             weights_updated = true;  // AdamW ran inside the exchange kernels
         } else if (opt.world_size > 1) {
             const mgt_allreduce_config_t ar{opt.world_size, opt.global_rank, step, T};
@@ -441,7 +447,7 @@ int main(int argc, char** argv) {
     if (mgt_comm_destroy(comm) != MGT_OK || mgt_comm_destroy(stats_comm) != MGT_OK) return EXIT_FAILURE;
     mgt_engine_destroy(engine);
     for (cudaEvent_t ev : ready_events) cudaEventDestroy(ev);
-    for (cudaEvent_t ev : {ev_start, ev_walk, ev_backward, ev_allreduce, ev_stop, ev_comm_done}) cudaEventDestroy(ev);
+    for (cudaEvent_t ev : {ev_start, ev_walk, ev_backward, ev_allreduce, ev_stop, ev_comm_done, ev_early_done}) cudaEventDestroy(ev);
     for (void* p : {static_cast<void*>(d_target), static_cast<void*>(d_moves), static_cast<void*>(d_meta), static_cast<void*>(d_states), static_cast<void*>(d_v),
                     static_cast<void*>(d_m), static_cast<void*>(d_ws), static_cast<void*>(d_loss), static_cast<void*>(d_labels), static_cast<void*>(d_walk_labels),
                     static_cast<void*>(d_w_half), static_cast<void*>(d_w), static_cast<void*>(d_bn_running)})

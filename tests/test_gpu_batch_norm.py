@@ -263,3 +263,128 @@ def test_batch_norm_option_errors():
         assert eng.set_batch_norm_state(None, 0.1, 0) == 1
     finally:
         eng.close()
+
+
+# ---- the trainer binary with --batch-norm 1 ------------------------------------------------------------------------------
+import json  # noqa: E402
+import os  # noqa: E402
+import subprocess  # noqa: E402
+
+from helpers import trainer_init_weights  # noqa: E402
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BIN = os.path.join(ROOT, "bin", "mgt_native_train")
+
+
+def run_trainer(out_dir, *flags, rank=0, world=1, check=True, wait=True):
+    cmd = [BIN, "--output-dir", str(out_dir), "--device-id", rank, "--world-size", world, "--global-rank", rank, "--local-rank", rank, *flags]
+    if not wait:
+        return subprocess.Popen([str(c) for c in cmd], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+    res = subprocess.run([str(c) for c in cmd], capture_output=True, text=True, timeout=300)
+    if check:
+        assert res.returncode == 0, res.stderr + res.stdout
+    return res
+
+
+def oracle_bn_training(oracle, shape, *, batch, steps, k_max, lr, momentum, eps=1e-5, world=1, seed=1234):
+    """The trainer's loop on the CPU oracle with batch normalisation over the joint batch of all ranks."""
+    moves, target = oracle.cyclic_puzzle(72, 18)
+    p, nbn = shape.param_count, oracle.bn_param_count(shape)
+    w = np.concatenate([trainer_init_weights(p), np.zeros(nbn, np.float32)])
+    w[p:].reshape(-1, 2, shape.hd2)[:, 0, :] = 1.0
+    m, v = np.zeros_like(w), np.zeros_like(w)
+    running = np.zeros((shape.residual_blocks + 1, 2, shape.hd2), np.float32)
+    running[:, 1, :] = 1.0
+    losses = []
+    n = batch * world
+    for step in range(steps):
+        parts = [oracle.random_walks(moves, target, seed=seed, epoch=0, step=step, rank=r, k_min=1, k_max=k_max, samples=batch) for r in range(world)]
+        states = np.concatenate([q[1] for q in parts])
+        labels = np.concatenate([q[2] for q in parts]).reshape(-1, 1)
+        st, loss, grad, stats = oracle.loss_grad_ex(shape, w, states, labels, batch_norm=True, bn_eps=eps)
+        assert st == 0
+        assert oracle.adamw(w, grad, m, v, step=step + 1, lr=lr) == 0
+        running[:, 0, :] = (1 - momentum) * running[:, 0, :] + momentum * stats[:, 0, :]
+        running[:, 1, :] = (1 - momentum) * running[:, 1, :] + momentum * stats[:, 1, :] * (n / (n - 1.0))
+        losses.append(loss)
+    return w, running, losses
+
+
+def read_bn_state(run_dir, nbn):
+    raw = np.fromfile(run_dir / "checkpoint" / "batch_norm.f32.bin", np.float32)
+    assert raw.size == 4 * nbn
+    return {name: raw[i * nbn:(i + 1) * nbn] for i, name in enumerate(("scale_shift", "adam_m", "adam_v", "running_stats"))}
+
+
+def test_trainer_with_batch_norm_tracks_the_oracle_and_exports_folded_weights(tmp_path, oracle):
+    shape = MlpShape(72, 72, 256, 64, 2, 1)
+    cshape = cshape_of(shape)
+    common = ["--batch-size", 512, "--k-min", 1, "--k-max", 29, "--hd1", 256, "--hd2", 64, "--nrd", 2, "--lr", 0.001, "--batch-norm", 1, "--bn-momentum", 0.2]
+    d = tmp_path / "bn"
+    run_trainer(d, "--steps", 3, *common)
+    w, running, losses = oracle_bn_training(oracle, shape, batch=512, steps=3, k_max=29, lr=1e-3, momentum=0.2)
+    rows = [json.loads(line) for line in open(d / "profile.jsonl")]
+    for row, want in zip(rows, losses):
+        assert abs(row["loss"] - want) <= 2e-3 * abs(want), (row["loss"], want)
+    p, nbn = shape.param_count, oracle.bn_param_count(shape)
+    state = np.fromfile(d / "checkpoint" / "state.f32.bin", np.float32)
+    assert state.size == 3 * p                                           # the reference's checkpoint keeps its format
+    bn = read_bn_state(d, nbn)
+    # AdamW's first steps move every parameter by about lr whatever the gradient's size, so a sign flip of a near-zero
+    # gradient shows as 2 * lr: compare against the distance travelled
+    travelled = np.abs(w[:p] - trainer_init_weights(p)).max()
+    # (the biases in front of a normalisation are left out: their true gradient is zero, what arrives is rounding noise
+    # of either sign, and AdamW turns it into steps of +-lr)
+    checked = np.ones(p, bool)
+    hidden_b = 72 * 72 * 256 + 256 + 256 * 64
+    checked[hidden_b:hidden_b + 64] = False
+    for k in range(2):
+        b2 = hidden_b + 64 + k * 2 * (64 * 64 + 64) + 64 * 64 + 64 + 64 * 64
+        checked[b2:b2 + 64] = False
+    diff = np.abs(state[:p] - w[:p])[checked]
+    # (and a gradient at the edge of fp16 underflow is zero in one realisation and tiny in the other: no step against
+    # a full one. Few elements are affected, each by at most the distance travelled.)
+    assert np.quantile(diff, 0.99) <= 0.35 * travelled and diff.max() <= 1.1 * travelled, (np.quantile(diff, 0.99), diff.max(), travelled)
+    assert rel_l2(state[:p][checked], w[:p][checked]) <= 0.2
+    assert np.abs(bn["scale_shift"] - w[p:]).max() <= 0.7 * travelled
+    np.testing.assert_allclose(bn["running_stats"].reshape(running.shape), running, rtol=2e-2, atol=2e-3)
+    meta = json.load(open(d / "checkpoint" / "batch_norm.json"))
+    assert meta["layers"] == 3 and meta["width"] == 64 and meta["section_floats"] == nbn
+    # weights/ holds the folded network (no normalisation left), from the very code the library exports
+    exported = np.fromfile(d / "weights" / "weights.f32.bin", np.float32)
+    folded = mgt.fold_batch_norm(cshape, state[:p], bn["scale_shift"], bn["running_stats"], 1e-5)
+    assert np.array_equal(exported, folded) and not np.array_equal(exported, state[:p])
+    # 2 + 1 steps through a checkpoint end in the state of 3 steps in one run, normalisation state included
+    run_trainer(tmp_path / "two", "--steps", 2, *common)
+    run_trainer(tmp_path / "third", "--steps", 1, "--resume-checkpoint", tmp_path / "two" / "checkpoint", "--resume-step", 1, *common)
+    assert np.array_equal(np.fromfile(tmp_path / "third" / "checkpoint" / "state.f32.bin", np.float32), state)
+    again = read_bn_state(tmp_path / "third", nbn)
+    assert all(np.array_equal(again[k], bn[k]) for k in bn)
+    # a checkpoint without the normalisation state cannot be resumed with --batch-norm 1; bad values are refused
+    run_trainer(tmp_path / "plain", "--steps", 1, *common[:-4])
+    res = run_trainer(tmp_path / "bad", "--steps", 1, "--resume-checkpoint", tmp_path / "plain" / "checkpoint", *common, check=False)
+    assert res.returncode != 0
+    assert run_trainer(tmp_path / "bad2", "--steps", 1, *common, "--bn-eps", 0, check=False).returncode != 0
+    assert run_trainer(tmp_path / "bad3", "--steps", 1, *common, "--linear-fp16", 0, check=False).returncode != 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_normalise_with_joint_statistics(tmp_path, oracle):
+    shape = MlpShape(72, 72, 128, 32, 2, 1)
+    id_file = tmp_path / "nccl.id"
+    flags = ["--steps", 3, "--batch-size", 256, "--k-min", 1, "--k-max", 29, "--hd1", 128, "--hd2", 32, "--nrd", 2, "--lr", 0.001, "--batch-norm", 1,
+             "--nccl-id-file", id_file]
+    procs = [run_trainer(tmp_path / f"rank{r}", *flags, rank=r, world=2, wait=False) for r in range(2)]
+    outs = [q.communicate(timeout=300) for q in procs]
+    assert all(q.returncode == 0 for q in procs), outs
+    nbn = oracle.bn_param_count(shape)
+    states = [np.fromfile(tmp_path / f"rank{r}" / "checkpoint" / "state.f32.bin", np.float32) for r in range(2)]
+    bns = [read_bn_state(tmp_path / f"rank{r}", nbn) for r in range(2)]
+    assert np.array_equal(states[0], states[1]) and all(np.array_equal(bns[0][k], bns[1][k]) for k in bns[0])   # replicas bit-identical
+    w, running, losses = oracle_bn_training(oracle, shape, batch=256, steps=3, k_max=29, lr=1e-3, momentum=0.1, world=2)
+    np.testing.assert_allclose(bns[0]["running_stats"].reshape(running.shape), running, rtol=2e-2, atol=2e-3)   # statistics of BOTH ranks' samples
+    rows = [[json.loads(line) for line in open(tmp_path / f"rank{r}" / "profile.jsonl")] for r in range(2)]
+    assert rows[0][0]["overlap_ranges"] == 8                                                                     # 2 * 2 + 3 and the scale/shift range
+    for i, want in enumerate(losses):
+        got = 0.5 * (rows[0][i]["loss"] + rows[1][i]["loss"])    # each rank reports the loss of its own samples
+        assert abs(got - want) <= 2e-3 * abs(want), (got, want)
