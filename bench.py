@@ -340,8 +340,13 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-reference-gpu", action="store_true", help="skip the side-by-side run of the reference's GPU trainer and bin/mgt_native_train")
     ap.add_argument("--reference-gpu-steps", type=int, default=30)
-    ap.add_argument("--workload", default="step", choices=["step", "collective"],
-                    help="step: the p888 training step (headline); collective: the gradient-exchange microbenchmark (bench_collective.py, needs >= 2 ranks)")
+    ap.add_argument("--workload", default="step", choices=["step", "collective", "variant"],
+                    help="step: the p888 training step (headline); collective: the gradient-exchange microbenchmark (bench_collective.py, needs >= 2 "
+                         "ranks); variant: a training step with the options the reference does not have (bench_variants.py, see --variant)")
+    ap.add_argument("--variant", default="p888_bn", choices=["p888_bn", "wide"],
+                    help="p888_bn: the p888 model with batch normalisation; wide: hd1 4096, hd2 512, 32 blocks, 29 logits, bfloat16, cross-entropy, batch 131072")
+    ap.add_argument("--batch-norm", action="store_true", help="--workload variant: batch normalisation also in a variant that has none by default")
+    ap.add_argument("--variant-batch", type=int, default=0, help=argparse.SUPPRESS)
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -353,9 +358,12 @@ def main():
             print(json.dumps(run_reference_cpu(args, args.steps, args.warmup)), flush=True)
         return
 
-    if args.workload == "collective":
-        import bench_collective
-        line = bench_collective.run(args)
+    if args.workload in ("collective", "variant"):
+        if args.workload == "collective":
+            import bench_collective as other
+        else:
+            import bench_variants as other
+        line = other.run(args)
         if line:
             print(json.dumps(line), flush=True)
         return

@@ -21,6 +21,7 @@ from .api import (  # noqa: F401
     mlp_loss_grad_workspace_floats,
     bn_param_count,
     fold_batch_norm,
+    launch_expand_scalar_labels,
     status_name,
     validate_adamw_kernel_config,
     validate_cuda_mlp_shape,

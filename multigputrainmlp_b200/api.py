@@ -106,6 +106,11 @@ class AdamWKernelConfig:
         return _Adam(self.param_count, self.step, self.learning_rate, self.beta1, self.beta2, self.eps, self.weight_decay)
 
 
+def launch_expand_scalar_labels(scalar_labels, sample_count: int, output_dim: int, expanded_labels, stream=None) -> int:
+    """ExpandScalarLabelsKernel (native/tools/mgt_native_train_smoke.cu:74-80): labels[b][o] = scalar[b] for every output."""
+    return int(_lib.load().mgt_launch_expand_scalar_labels(_ptr(scalar_labels), sample_count, output_dim, _ptr(expanded_labels), _stream(stream)))
+
+
 def validate_random_walk_kernel_config(config: RandomWalkKernelConfig) -> int:
     cfg = config.c()
     return int(_lib.load().mgt_validate_random_walk_config(C.byref(cfg)))

@@ -27,7 +27,7 @@ namespace bn {
 
 constexpr uint32_t kThreads = 256;
 constexpr uint32_t kMaxBlocks = 592;  // partial rows per reduction
-constexpr uint32_t kReduceParts = 32; // ReduceMomentsKernel: threads that share one column
+constexpr uint32_t kReduceParts = 128; // reduction kernels: threads that share one column (a power of two)
 constexpr uint32_t kReduceCols = 8;   // columns per CTA of the reduction kernels
 
 __host__ __device__ inline uint32_t BlocksFor(uint32_t rows, int sm_count) {
@@ -143,8 +143,9 @@ ColumnMomentsKernel(const float* __restrict__ a, uint32_t ld_a, const float* __r
     }
 }
 
-// Sum of `blocks` partial rows of `width` floats each, in a fixed order: kReduceParts threads share a column (each adds
-// every kReduceParts-th row), then one thread adds their results. Returns the total in the threads with part == 0.
+// Sum of `blocks` partial rows, in a fixed order: kReduceParts threads share a column (each adds every kReduceParts-th
+// row: at most five dependent loads for 592 rows), then a binary tree over their results in shared memory. Returns the
+// total in the threads with part == 0.
 __device__ __forceinline__ float AddPartialRows(const float* __restrict__ partial, uint32_t blocks, uint64_t row_stride, uint32_t col, bool in_range,
                                                 uint32_t part, uint32_t c, float* smem) {
     float s = 0.0f;
@@ -154,9 +155,12 @@ __device__ __forceinline__ float AddPartialRows(const float* __restrict__ partia
     }
     smem[part * kReduceCols + c] = s;
     __syncthreads();
-    float total = 0.0f;
-    if (part == 0U)
-        for (uint32_t p = 0; p < kReduceParts; ++p) total += smem[p * kReduceCols + c];
+#pragma unroll
+    for (uint32_t half = kReduceParts / 2U; half > 0U; half >>= 1) {
+        if (part < half) smem[part * kReduceCols + c] += smem[(part + half) * kReduceCols + c];
+        __syncthreads();
+    }
+    const float total = smem[c];
     __syncthreads();
     return total;
 }

@@ -433,6 +433,7 @@ ReduceRowsGroupedKernel(const float* __restrict__ src, uint32_t rows, uint32_t c
 // partials[CTA][2*H2+2] = { grad W_out[H2], grad b_out, loss, column sums of dz[H2] } and are added
 // in a fixed order by ReduceRowsKernel.
 constexpr int kHeadMaxPerLane = MGT_MAX_HD2 / 32;
+constexpr size_t kHeadStagedSmemLimit = 160U * 1024U;  // dynamic shared memory of HeadOutNKernel with staged weights (two CTAs per SM at up to 96 KB)
 __global__ void __launch_bounds__(kHeadThreads)
 HeadOut1Kernel(const float* __restrict__ w_out, const float* __restrict__ b_out, const float* __restrict__ labels, const float* __restrict__ x,
                uint32_t p_f32, uint32_t B, uint32_t H2, float* __restrict__ dzf, __half* __restrict__ dz_h, uint32_t p_dz, float* __restrict__ partials,
@@ -496,18 +497,32 @@ HeadOut1Kernel(const float* __restrict__ w_out, const float* __restrict__ b_out,
 // the operand format for the two products that follow. kCrossEntropy = false: the reference's MSE against the labels.
 // kCrossEntropy = true (no counterpart in the reference): the outputs are per-depth logits, class = depth - 1 (the labels
 // carry the walk depth in every output slot), loss = mean over the batch of -log softmax(y)[class],
-// dy = (softmax(y) - onehot(class)) / B. One warp per sample. Plain SIMT: this path carries little work (B x OUT x H2).
-template <bool kCrossEntropy>
+// dy = (softmax(y) - onehot(class)) / B. One warp per sample, plain SIMT (B x OUT x H2 multiply-adds twice). kStageW: the
+// output weights are converted once per CTA into shared memory ([H2][OUT | 1] floats: rows for the forward product, a
+// lane per row without bank conflicts for the backward one); read from global memory instead, the lane-per-row access of
+// the backward product touches 32 sectors per instruction and the kernel is bound by L2 (5.4 ms instead of 0.5 ms at
+// batch 131072, hd2 512, 29 outputs).
+template <bool kCrossEntropy, bool kStageW>
 __global__ void __launch_bounds__(kHeadThreads)
 HeadOutNKernel(const __half* __restrict__ w_out_h, uint32_t p_wout, const float* __restrict__ b_out, const float* __restrict__ labels,
                const __half* __restrict__ x_h, uint32_t p_act, const float* __restrict__ x_f32, uint32_t p_f32, uint32_t B, uint32_t H2, uint32_t OUT,
                float* __restrict__ dy, __half* __restrict__ dy_h, uint32_t p_dy, float* __restrict__ dzf, __half* __restrict__ dz_h, uint32_t p_dz,
                float* __restrict__ partials, bool bf16) {
-    extern __shared__ float s_dyn[];  // per warp: OUT floats (logits, then rounded dy)
+    extern __shared__ float s_dyn[];  // per warp: OUT floats (logits, then rounded dy); then the staged weights
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31U;
     const uint32_t warps_total = gridDim.x * (kHeadThreads / 32);
     float* s_dy = s_dyn + warp * OUT;
     const uint16_t* wq = reinterpret_cast<const uint16_t*>(w_out_h);
+    const uint32_t outp = OUT | 1U;
+    float* w_s = s_dyn + (kHeadThreads / 32) * OUT;
+    if (kStageW) {
+        for (uint32_t i = threadIdx.x; i < H2 * OUT; i += kHeadThreads) {
+            const uint32_t j = i / OUT, o = i % OUT;
+            w_s[j * outp + o] = ptx::from_operand(wq[(uint64_t)j * p_wout + o], bf16);
+        }
+        __syncthreads();
+    }
+    auto weight = [&](uint32_t j, uint32_t o) -> float { return kStageW ? w_s[j * outp + o] : ptx::from_operand(wq[(uint64_t)j * p_wout + o], bf16); };
     const float inv_n = 1.0f / static_cast<float>(kCrossEntropy ? (uint64_t)B : (uint64_t)B * OUT);
     float loss = 0.0f;
     float dacc[kHeadMaxPerLane];
@@ -518,7 +533,7 @@ HeadOutNKernel(const __half* __restrict__ w_out_h, uint32_t p_wout, const float*
         float mx = -3.0e38f;
         for (uint32_t o = lane; o < OUT; o += 32) {
             float acc = 0.0f;
-            for (uint32_t j = 0; j < H2; ++j) acc += ptx::from_operand(row[j], bf16) * ptx::from_operand(wq[(uint64_t)j * p_wout + o], bf16);
+            for (uint32_t j = 0; j < H2; ++j) acc += ptx::from_operand(row[j], bf16) * weight(j, o);
             const float y = acc + b_out[o];
             s_dy[o] = y;
             mx = fmaxf(mx, y);
@@ -560,7 +575,7 @@ HeadOutNKernel(const __half* __restrict__ w_out_h, uint32_t p_wout, const float*
             const uint32_t j = q * 32 + lane;
             if (j < H2) {
                 float acc = 0.0f;
-                for (uint32_t o = 0; o < OUT; ++o) acc += s_dy[o] * ptx::from_operand(wq[(uint64_t)j * p_wout + o], bf16);
+                for (uint32_t o = 0; o < OUT; ++o) acc += s_dy[o] * weight(j, o);
                 const float d = x_f32[(uint64_t)b * p_f32 + j] > 0.0f ? acc : 0.0f;
                 dacc[q] += d;
                 dzf[(uint64_t)b * p_f32 + j] = d;
@@ -1232,14 +1247,19 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     } else {
         float* dy = reinterpret_cast<float*>(base + ws.off_dy);
         __half* dy_h = reinterpret_cast<__half*>(base + ws.off_dyh);
-        const size_t head_smem = (kHeadThreads / 32) * OUT * sizeof(float);
-        if (e->options.loss_kind == MGT_LOSS_CROSS_ENTROPY) {
-            HeadOutNKernel<true><<<kHeadBlocks, kHeadThreads, head_smem, st>>>(hw.wout, hw.pout, w + OutputBias(s), labels, x_h(R), ws.p_act, x_f32, ws.p_f32, B, H2, OUT,
-                                                                               dy, dy_h, ws.p_wout, dzf, dz_cur, ws.p_dz, head_partial, e->bf16_now);
-        } else {
-            HeadOutNKernel<false><<<kHeadBlocks, kHeadThreads, head_smem, st>>>(hw.wout, hw.pout, w + OutputBias(s), labels, x_h(R), ws.p_act, x_f32, ws.p_f32, B, H2, OUT,
-                                                                                dy, dy_h, ws.p_wout, dzf, dz_cur, ws.p_dz, head_partial, e->bf16_now);
-        }
+        const size_t warp_smem = (kHeadThreads / 32) * OUT * sizeof(float);
+        const size_t staged_smem = warp_smem + (size_t)H2 * (OUT | 1U) * sizeof(float);
+        const bool stage_w = staged_smem <= kHeadStagedSmemLimit;
+        const bool ce = e->options.loss_kind == MGT_LOSS_CROSS_ENTROPY;
+        auto launch_head = [&](auto kernel, size_t smem) -> bool {
+            if (smem > 48U * 1024U && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kHeadStagedSmemLimit) != cudaSuccess) return false;
+            kernel<<<kHeadBlocks, kHeadThreads, smem, st>>>(hw.wout, hw.pout, w + OutputBias(s), labels, x_h(R), ws.p_act, x_f32, ws.p_f32, B, H2, OUT, dy, dy_h, ws.p_wout,
+                                                           dzf, dz_cur, ws.p_dz, head_partial, e->bf16_now);
+            return true;
+        };
+        const bool launched = stage_w ? (ce ? launch_head(HeadOutNKernel<true, true>, staged_smem) : launch_head(HeadOutNKernel<false, true>, staged_smem))
+                                      : (ce ? launch_head(HeadOutNKernel<true, false>, warp_smem) : launch_head(HeadOutNKernel<false, false>, warp_smem));
+        if (!launched) return MGT_CUDA_FAILURE;
         ReduceRowsKernel<<<1, 256, 0, st>>>(head_partial, kHeadBlocks, H2 + 1, 0, 1, loss);
         ReduceRowsKernel<<<(H2 + kReduceCols - 1) / kReduceCols, 256, 0, st>>>(head_partial, kHeadBlocks, H2 + 1, 1, H2, head_bias_dst);
         HeadOutNBiasGradKernel<<<OUT, 256, 0, st>>>(dy, B, OUT, grad + OutputBias(s));

@@ -219,7 +219,9 @@ def test_exported_weight_files_rebuild_the_model(tmp_path, oracle):
     assert np.max(np.abs(y_files - y_f32)) <= 5e-3 * max(1.0, np.max(np.abs(y_f32)))
 
 
-REF_SCRIPTS = "/root/reference/native/tests/scripts"
+# the reference checkout: MGT_REFERENCE_DIR if set, else a directory `reference` beside this repository
+REF_SCRIPTS = os.path.join(os.environ.get("MGT_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "..", "reference"),
+                           "native", "tests", "scripts")
 
 
 @pytest.mark.skipif(not os.path.exists(os.path.join(REF_SCRIPTS, "check_native_train_artifacts.sh")),
