@@ -207,91 +207,6 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// ---- CTA pairs (cta_group::2): two CTAs of a cluster issue ONE MMA over both SMs ---------------
-// CTA rank inside its cluster; the even CTA of a pair is the one that issues the MMAs.
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-// Barrier over all threads of all CTAs of the cluster (release/acquire at cluster scope).
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// Address of the same shared-memory location in CTA `rank` of the cluster (shared::cluster window).
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-    return r;
-}
-// Arrive on an mbarrier of another CTA of the cluster; releases this thread's earlier writes at cluster scope.
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// try_wait that acquires at cluster scope: pairs with mbar_arrive_cluster from the peer CTA.
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* cta_abort, int code) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    const uint64_t start = global_timer_ns();
-    uint32_t spins = 0;
-    while (!mbar_try_wait_cluster(bar, parity)) {
-        if ((++spins & 63U) == 0U) {
-            if (*cta_abort != 0) return false;
-            if (global_timer_ns() - start > kWaitLimitNs) {
-                *cta_abort = code;
-                return false;
-            }
-        }
-    }
-    return true;
-}
-// Generic-proxy writes of this thread become visible to the async proxy (TMA, tcgen05) in every state space.
-__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
-
-// TMEM allocation for a CTA pair: warp 1 of BOTH CTAs executes each of these, with the same arguments.
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_holder, uint32_t columns) {
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_holder)), "r"(columns) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish_pair() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t columns) {
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns) : "memory");
-}
-// D (+)= A * B over the pair: M = 256 (each CTA holds its 128 rows of A in its own shared memory and its 128 rows of D in
-// its own TMEM), N columns of B split in halves between the two CTAs. Issued by ONE thread of the even CTA; descriptors
-// and the TMEM address are CTA-relative and apply to both CTAs.
-__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// Arrives on the mbarrier at this shared-memory offset in every CTA named by cta_mask once all MMAs issued so far by
-// this thread have completed (a signal to both CTAs of the pair; it carries no data).
-__device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-                 ::"r"(smem_u32(bar)), "h"(cta_mask) : "memory");
-}
-// 2-D tiled TMA load into THIS CTA's shared memory whose completion is counted on an mbarrier that may live in the
-// peer CTA (bar_cluster_addr is a shared::cluster address). A plain load by one CTA for itself.
-__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* map, int32_t x, int32_t y, uint32_t bar_cluster_addr) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
-        : "memory");
-}
-
 // ---- descriptors ----------------------------------------------------------------------------
 // Shared-memory matrix descriptor (64-bit): start address >> 4 in bits [0,14), leading byte
 // offset >> 4 in [16,30), stride byte offset >> 4 in [32,46), descriptor version 1 in [46,48),
