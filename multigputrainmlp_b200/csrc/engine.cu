@@ -297,14 +297,8 @@ template <int BN> using CfgDwG = GemmCfg<BN, 1, true, BSource::kTmaMN, Epi::kPar
 // Two 256-column accumulators per unit (all of TMEM) and a two-stage one-hot ring. Measured alternatives at p888: 2 x 192
 // columns with a three-stage ring 1.44 ms, one double-buffered 256-column accumulator (epilogue under the next unit's
 // MMAs, but the table tile re-read twice as often) 1.37 ms, this form 1.14 ms: the K loop already issues MMAs back to back.
-// The one-hot GEMMs: a unit is 128 rows x two accumulators of BN columns. Two widths are built so that the units can fill
-// the last wave: at p888 (batch 53 248, 148 SMs) 2 x 256 columns give 2 080 forward units = 14.05 waves, 2 x 240 columns
-// give 2 220 units = exactly 15 waves of narrower units (6 % less time); the 5 184 table rows of the gradient are
-// 10.1 units of 512 rows but 10.8 units of 480.
-template <int BN> using CfgEmbFwdT = GemmCfg<BN, 2, true, BSource::kOneHotFwd, Epi::kEmbFwd, 4, 2>;
-template <int BN> using CfgEmbGradT = GemmCfg<BN, 2, true, BSource::kOneHotGrad, Epi::kEmbGrad, 4, 2>;
-using CfgEmbFwd = CfgEmbFwdT<256>;
-using CfgEmbGrad = CfgEmbGradT<256>;
+using CfgEmbFwd = GemmCfg<256, 2, true, BSource::kOneHotFwd, Epi::kEmbFwd, 4, 2>;
+using CfgEmbGrad = GemmCfg<256, 2, true, BSource::kOneHotGrad, Epi::kEmbGrad, 4, 2>;
 // (One accumulator per unit with two units in flight - the epilogue of one draining under the MMAs of the next, operand
 // ring four deep - was measured at p888: forward 1.40 ms against 1.22 ms, gradient 1.56 ms against 1.13 ms. A K chunk
 // costs about a thousand cycles in hand-overs whatever it feeds, so it should feed eight MMAs, not four.)
@@ -1182,15 +1176,12 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
 
     // ---- embedding forward: a1 = relu([onehot | 1] * [W_in ; b_in])  (mlp_backward.cu:755-832)
     {
-        // time of the launch ~ waves x unit width
-        auto waves_width = [&](uint32_t bn) { return (((uint64_t)((H1 + 127U) / 128U) * ((B + 2U * bn - 1U) / (2U * bn)) + e->sm_count - 1) / e->sm_count) * bn; };
-        const bool narrow = waves_width(240) < waves_width(256);
-        GemmArgs a = BaseArgs(H1, B, IN + 1, 2U * (narrow ? 240U : 256U), 1);
+        GemmArgs a = BaseArgs(H1, B, IN + 1, CfgEmbFwd::NACC * CfgEmbFwd::BN, 1);
         a.out_f16 = a1_h; a.ld_f16 = ws.p_a1;
         a.states = reinterpret_cast<const uint8_t*>(states); a.state_len = s.state_len; a.value_pad = s.state_value_pad; a.samples = B; a.in_rows = IN;
         CUtensorMap ta;
         MGT_MAP(e->Map(&ta, hw.in_table, H1, IN + 1, hw.p1, 64, 64));
-        MGT_TRY(narrow ? LaunchGemm<CfgEmbFwdT<240>>(e, ta, ta, a, st) : LaunchGemm<CfgEmbFwd>(e, ta, ta, a, st));
+        MGT_TRY(LaunchGemm<CfgEmbFwd>(e, ta, ta, a, st));
     }
     if (!timer.Mark(profile ? &profile->input_forward_ms : nullptr)) return MGT_CUDA_FAILURE;
 
@@ -1344,29 +1335,22 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
         ++e->launches;
         if (cudaGetLastError() != cudaSuccess) return MGT_CUDA_FAILURE;
     } else {
-        // Two splits keep fp32 atomics order-independent (0 + a + b == 0 + b + a); use them when one split would leave a
-        // large part of the last wave idle. Time of the launch ~ waves x unit width / splits: take the cheaper width.
-        auto plan = [&](uint32_t bn, uint32_t* splits_out) -> uint64_t {
-            const GemmArgs t = BaseArgs(H1, IN, B, 2U * bn, 1);
-            const uint64_t tiles = (uint64_t)t.m_tiles * t.n_tiles;
-            const uint64_t waves1 = (tiles + e->sm_count - 1) / e->sm_count;
-            const uint64_t waves2 = (2 * tiles + e->sm_count - 1) / e->sm_count;
-            const uint32_t splits = (t.k_chunks >= 2 && waves2 < 2 * waves1) ? 2U : 1U;
-            *splits_out = splits;
-            return (splits == 2U ? waves2 : 2U * waves1) * bn;  // in half units
-        };
-        uint32_t splits256 = 1, splits240 = 1;
-        const uint64_t cost256 = plan(256, &splits256), cost240 = plan(240, &splits240);
-        const bool narrow = cost240 < cost256;
-        const uint32_t splits = narrow ? splits240 : splits256;
-        GemmArgs a = BaseArgs(H1, IN, B, 2U * (narrow ? 240U : 256U), splits);
+        const uint32_t unit_rows = CfgEmbGrad::NACC * CfgEmbGrad::BN;
+        GemmArgs a = BaseArgs(H1, IN, B, unit_rows, 1);
+        const uint64_t tiles = (uint64_t)a.m_tiles * a.n_tiles;
+        // Two splits keep fp32 atomics order-independent (0 + a + b == 0 + b + a); use them when one
+        // split would leave a large part of the last wave idle.
+        const uint64_t waves1 = (tiles + e->sm_count - 1) / e->sm_count;
+        const uint64_t waves2 = (2 * tiles + e->sm_count - 1) / e->sm_count;
+        const uint32_t splits = (a.k_chunks >= 2 && waves2 < 2 * waves1) ? 2U : 1U;
+        a = BaseArgs(H1, IN, B, unit_rows, splits);
         a.out_f32 = grad; a.ld_f32 = H1;
         a.states = reinterpret_cast<const uint8_t*>(states); a.state_len = s.state_len; a.value_pad = s.state_value_pad; a.samples = B;
         a.in_rows = 0xFFFFFFFFU;  // no all-ones row in this direction
         if (a.splits > 1 && cudaMemsetAsync(grad, 0, (uint64_t)IN * H1 * sizeof(float), st) != cudaSuccess) return MGT_CUDA_FAILURE;
         CUtensorMap ta;
         MGT_MAP(e->Map(&ta, dz1_h, H1, B, ws.p_dz1, 64, 64));
-        MGT_TRY(narrow ? LaunchGemm<CfgEmbGradT<240>>(e, ta, ta, a, st) : LaunchGemm<CfgEmbGrad>(e, ta, ta, a, st));
+        MGT_TRY(LaunchGemm<CfgEmbGrad>(e, ta, ta, a, st));
     }
     // table and input bias are complete: tell a caller who asked to hear of it before the weight-gradient GEMMs are enqueued
     if (e->early_fn != nullptr && e->early_fn(e->early_user, 2U * R + 2U, 0, InputBias(s) + H1, stream_v) != MGT_OK) return MGT_CUDA_FAILURE;

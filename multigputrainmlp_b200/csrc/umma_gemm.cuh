@@ -103,7 +103,7 @@ struct GemmCfg {
     static constexpr int EPI_STAGE_BYTES = EPI_WARPS * EPI_WARP_BYTES;
     static constexpr int SMEM_BYTES = 1024 + SA_ * A_STAGE_BYTES + SB_ * B_STAGE_BYTES + 256 + EPI_STAGE_BYTES;
     static_assert(BN_ % 16 == 0 && BN_ >= 16 && BN_ <= 256, "UMMA N");
-    static_assert(BN_ % 32 == 0 || (kOneHot && BN_ % 16 == 0), "epilogue drains 32 columns at a time (the embedding epilogues also take a last half chunk)");
+    static_assert(BN_ % 32 == 0, "epilogue drains 32 columns at a time");
     static_assert(NACC_ == 1 || NACC_ == 2, "one or two accumulators");
     static_assert(EPI_WARPS_ == 8 || EPI_WARPS_ == 16, "epilogue warps");
     static_assert(!kOneHot || EPI_WARPS_ == 8, "the synthesis warps follow eight epilogue warps");
@@ -397,14 +397,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll 1
                 for (int acc = 0; acc < NACC; ++acc) {
 #pragma unroll 1
-                    for (int cc = static_cast<int>(chunk_parity); cc < (BN + 31) / 32; cc += Cfg::EPI_STRIDE) {
+                    for (int cc = static_cast<int>(chunk_parity); cc < BN / 32; cc += Cfg::EPI_STRIDE) {
                         const uint32_t n0 = (nt * NACC + acc) * BN + cc * 32;
                         if (n0 >= args.N) continue;
                         uint32_t r[32];
                         tmem_ld_32x32(tmem_base + ((quad * 32U) << 16) + ab * (NACC * Cfg::ACC_COLS) + acc * Cfg::ACC_COLS + cc * 32, r);
                         tmem_ld_wait();
-                        // (a tile width that is no multiple of 32 ends in a half chunk: the columns behind it belong to nobody)
-                        const uint32_t valid = min(min(32U, static_cast<uint32_t>(BN - cc * 32)), args.N - n0);
+                        const uint32_t valid = min(32U, args.N - n0);
                         if (m_ok) {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) {
