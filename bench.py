@@ -322,6 +322,16 @@ def run_gpu_trainers_side_by_side(world: int, steps: int) -> dict:
     return out
 
 
+def claim_stdout():
+    """stdout carries ONE JSON line and nothing else: libraries write banners there (NCCL prints its version at the first
+    collective), so file descriptor 1 is pointed at stderr for the rest of the process and the line goes to the returned
+    file, which is the original stdout."""
+    sys.stdout.flush()
+    original = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    return original
+
+
 # ------------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -348,6 +358,7 @@ def main():
     ap.add_argument("--batch-norm", action="store_true", help="--workload variant: batch normalisation also in a variant that has none by default")
     ap.add_argument("--variant-batch", type=int, default=0, help=argparse.SUPPRESS)
     args = ap.parse_args()
+    out = claim_stdout()
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -355,7 +366,7 @@ def main():
 
     if args.impl == "reference":
         if rank == 0:
-            print(json.dumps(run_reference_cpu(args, args.steps, args.warmup)), flush=True)
+            print(json.dumps(run_reference_cpu(args, args.steps, args.warmup)), file=out, flush=True)
         return
 
     if args.workload in ("collective", "variant"):
@@ -365,7 +376,7 @@ def main():
             import bench_variants as other
         line = other.run(args)
         if line:
-            print(json.dumps(line), flush=True)
+            print(json.dumps(line), file=out, flush=True)
         return
 
     import torch
@@ -616,7 +627,7 @@ def main():
     if not args.no_cpu_baseline and world == 1:
         cpu = run_reference_cpu(args, args.steps_cpu, args.warmup_cpu)
         line["cpu_baseline"] = cpu["cpu_baseline"]
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=out, flush=True)
     if world > 1:
         import torch.distributed as dist
         dist.barrier()
