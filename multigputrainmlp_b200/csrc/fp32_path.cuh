@@ -98,13 +98,14 @@ __global__ void BiasReluKernel(const float* __restrict__ z, const float* __restr
 // out = (d (+ add)) * [act > 0]; optionally also rounded through fp16 (the operand form of the fp16 embedding gradient)
 template <class Act>
 __global__ void MaskKernel(const float* __restrict__ d, const float* __restrict__ add, const Act* __restrict__ act, uint32_t cols, uint32_t act_pitch,
-                           uint64_t total, bool round_half, float* __restrict__ out) {
+                           uint64_t total, bool round_half, float* __restrict__ out, bool act_by_columns = false) {
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         const uint64_t r = i / cols, c = i - r * cols;
         float v = d[i];
         if (add != nullptr) v += add[i];
-        v = ToFloat(act[r * act_pitch + c]) > 0.0f ? v : 0.0f;
+        // act_by_columns: the activation is stored with one row per column of d (act[c][r])
+        v = ToFloat(act[act_by_columns ? c * act_pitch + r : r * act_pitch + c]) > 0.0f ? v : 0.0f;
         out[i] = round_half ? __half2float(__float2half_rn(v)) : v;
     }
 }

@@ -36,6 +36,9 @@ enum class Epi : int {
     kEmbFwd,               // out_f16[n][m] = relu(acc)            (D is the transposed activation)
     kEmbGrad,              // out_f32[n][m] (+)= acc               (D is the transposed gradient)
     kBiasF32,              // out_f32 = acc + bias                 (a pre-activation kept in fp32: input of batch normalisation)
+    kEmbFwdRows,           // out_f16[m][n] = relu(acc), bits[m][n / 32] bit (n % 32) = [acc > 0]   (the activation kept as D lies: one row
+                           // per output column of the layer; the sign words are the ReLU mask the backward pass needs)
+    kMaskRowsumF16,        // out_f16[m][n] = acc * [bit n of bits[m]]; rowsum[(n tile, warp of the quadrant)][m] = sum over the warp's columns
 };
 
 struct GemmArgs {
@@ -56,6 +59,12 @@ struct GemmArgs {
     // (bias gradients): row (blockIdx.x * 8 + epilogue warp) of colsum[gridDim.x * 8][N] accumulates
     // what that warp handled. The buffer must be zero before the launch.
     float* colsum;
+    // kMaskRowsumF16: fp32 row sums of the masked values, one partial row of M floats per (N tile, warp of a lane quadrant):
+    // rowsum[(n_tile * EPI_WARPS / 4 + w)][m]; every slot of a launch is written (no zeroing needed)
+    float* rowsum;
+    // kEmbFwdRows writes, kMaskRowsumF16 reads: one 32-bit word per row and 32 columns, ld_bits words per row
+    uint32_t* bits;
+    uint32_t ld_bits;
     // one-hot operand synthesis
     const uint8_t* states;   // [samples][80]
     uint32_t state_len;      // positions per state
@@ -99,7 +108,7 @@ struct GemmCfg {
     static constexpr int EPI_TILE_PITCH = 36;
     // per epilogue warp: a padded 32x32 fp32 tile, 32 words of ReLU-mask bits and four rows of column-sum accumulators
     // (the embedding epilogues write transposed and need no staging)
-    static constexpr int EPI_WARP_BYTES = kOneHot ? 0 : (32 * EPI_TILE_PITCH * 4 + 128 + 4 * 32 * 4);
+    static constexpr int EPI_WARP_BYTES = (kOneHot || EPI_ == Epi::kMaskRowsumF16) ? 0 : (32 * EPI_TILE_PITCH * 4 + 128 + 4 * 32 * 4);
     static constexpr int EPI_STAGE_BYTES = EPI_WARPS * EPI_WARP_BYTES;
     static constexpr int SMEM_BYTES = 1024 + SA_ * A_STAGE_BYTES + SB_ * B_STAGE_BYTES + 256 + EPI_STAGE_BYTES;
     static_assert(BN_ % 16 == 0 && BN_ >= 16 && BN_ <= 256, "UMMA N");
@@ -404,7 +413,33 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                         tmem_ld_32x32(tmem_base + ((quad * 32U) << 16) + ab * (NACC * Cfg::ACC_COLS) + acc * Cfg::ACC_COLS + cc * 32, r);
                         tmem_ld_wait();
                         const uint32_t valid = min(32U, args.N - n0);
-                        if (m_ok) {
+                        if constexpr (Cfg::EPI == Epi::kEmbFwdRows) {
+                            // a lane owns 32 consecutive columns of its row: 64 bytes, four 16-byte stores
+                            if (m_ok) {
+                                uint16_t* dst = reinterpret_cast<uint16_t*>(args.out_f16) + static_cast<uint64_t>(m) * args.ld_f16 + n0;
+                                if (args.bits != nullptr) {
+                                    uint32_t word = 0;
+#pragma unroll
+                                    for (int j = 0; j < 32; ++j) word |= (static_cast<uint32_t>(j) < valid && __uint_as_float(r[j]) > 0.0f) ? (1U << j) : 0U;
+                                    args.bits[static_cast<uint64_t>(m) * args.ld_bits + (n0 >> 5)] = word;
+                                }
+                                if (valid == 32U && (args.ld_f16 & 7U) == 0U) {
+#pragma unroll
+                                    for (int q = 0; q < 4; ++q) {
+                                        uint4 u;
+                                        u.x = pack_operand_pair(fmaxf(__uint_as_float(r[8 * q + 0]), 0.0f), fmaxf(__uint_as_float(r[8 * q + 1]), 0.0f), args.bf16 != 0U);
+                                        u.y = pack_operand_pair(fmaxf(__uint_as_float(r[8 * q + 2]), 0.0f), fmaxf(__uint_as_float(r[8 * q + 3]), 0.0f), args.bf16 != 0U);
+                                        u.z = pack_operand_pair(fmaxf(__uint_as_float(r[8 * q + 4]), 0.0f), fmaxf(__uint_as_float(r[8 * q + 5]), 0.0f), args.bf16 != 0U);
+                                        u.w = pack_operand_pair(fmaxf(__uint_as_float(r[8 * q + 6]), 0.0f), fmaxf(__uint_as_float(r[8 * q + 7]), 0.0f), args.bf16 != 0U);
+                                        reinterpret_cast<uint4*>(dst)[q] = u;
+                                    }
+                                } else {
+#pragma unroll
+                                    for (int j = 0; j < 32; ++j)
+                                        if (static_cast<uint32_t>(j) < valid) dst[j] = to_operand(fmaxf(__uint_as_float(r[j]), 0.0f), args.bf16 != 0U);
+                                }
+                            }
+                        } else if (m_ok) {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) {
                                 if (static_cast<uint32_t>(j) < valid) {
@@ -420,6 +455,76 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                         }
                     }
                 }
+                tc_fence_before();
+                mbar_arrive(&acc_empty[ab]);
+            }
+        } else if constexpr (Cfg::EPI == Epi::kMaskRowsumF16) {
+            // D and the output have a row per TMEM lane and the warp's 32 columns side by side in that row: 64 bytes per lane,
+            // written as four 16-byte vectors straight from registers; the mask of a chunk is one word per lane; the row
+            // sum is a sum over the lane's own registers. (Full 32-byte sectors; whole rows per warp are not needed.)
+            const bool vec_ok = (args.ld_f16 & 7U) == 0U;
+            constexpr int CPW = (BN / 32 + Cfg::EPI_STRIDE - 1) / Cfg::EPI_STRIDE;  // chunks of a unit per warp
+            // the mask words of a unit do not depend on its MMAs: those of the NEXT unit are requested while this one is drained
+            auto request = [&](uint32_t unit, uint32_t (&words)[CPW]) {
+                uint32_t mt, nt, sp;
+                decode(unit, mt, nt, sp);
+                const uint32_t m = mt * BM + quad * 32U + lane;
+#pragma unroll
+                for (int ci = 0; ci < CPW; ++ci) {
+                    const uint32_t n0 = nt * BN + (chunk_parity + ci * Cfg::EPI_STRIDE) * 32U;
+                    words[ci] = (unit < total_units && m < args.M && n0 < args.N) ? __ldg(args.bits + static_cast<uint64_t>(m) * args.ld_bits + (n0 >> 5)) : 0U;
+                }
+            };
+            uint32_t mw_next[CPW];
+            request(blockIdx.x, mw_next);
+            for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++unit_iter) {
+                uint32_t mt, nt, sp;
+                decode(unit, mt, nt, sp);
+                const uint32_t ab = unit_iter % ACC_BUFS, aph = (unit_iter / ACC_BUFS) & 1U;
+                const uint32_t m = mt * BM + quad * 32U + lane;
+                const bool m_ok = m < args.M;
+                uint32_t mw[CPW];
+#pragma unroll
+                for (int ci = 0; ci < CPW; ++ci) mw[ci] = mw_next[ci];
+                request(unit + gridDim.x, mw_next);
+                if (!__all_sync(0xFFFFFFFFU, mbar_wait(&acc_full[ab], aph, cta_abort, kAbortEpilogueWait))) { ok = false; break; }
+                tc_fence_after();
+                float row_sum = 0.0f;
+#pragma unroll
+                for (int ci = 0; ci < CPW; ++ci) {
+                    const uint32_t cc = chunk_parity + ci * Cfg::EPI_STRIDE;
+                    const uint32_t n0 = nt * BN + cc * 32U;
+                    if (cc >= static_cast<uint32_t>(BN / 32) || n0 >= args.N) continue;  // (warp-uniform)
+                    const uint32_t valid = min(32U, args.N - n0);
+                    const bool vec = valid == 32U && vec_ok;
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((quad * 32U) << 16) + ab * Cfg::ACC_COLS + cc * 32, r);
+                    tmem_ld_wait();
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = ((mw[ci] >> j) & 1U) ? __uint_as_float(r[j]) : 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) row_sum += v[j];  // (columns past N were masked with zeros above)
+                    if (m_ok) {
+                        uint16_t* dst = reinterpret_cast<uint16_t*>(args.out_f16) + static_cast<uint64_t>(m) * args.ld_f16 + n0;
+                        if (vec) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                uint4 u;
+                                u.x = pack_operand_pair(v[8 * q + 0], v[8 * q + 1], args.bf16 != 0U);
+                                u.y = pack_operand_pair(v[8 * q + 2], v[8 * q + 3], args.bf16 != 0U);
+                                u.z = pack_operand_pair(v[8 * q + 4], v[8 * q + 5], args.bf16 != 0U);
+                                u.w = pack_operand_pair(v[8 * q + 6], v[8 * q + 7], args.bf16 != 0U);
+                                reinterpret_cast<uint4*>(dst)[q] = u;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (static_cast<uint32_t>(j) < valid) dst[j] = to_operand(v[j], args.bf16 != 0U);
+                        }
+                    }
+                }
+                if (args.rowsum != nullptr && m_ok) args.rowsum[(static_cast<uint64_t>(nt) * Cfg::EPI_STRIDE + chunk_parity) * args.M + m] = row_sum;
                 tc_fence_before();
                 mbar_arrive(&acc_empty[ab]);
             }
