@@ -57,18 +57,16 @@ bool ValidShape(const mgt_mlp_shape_t* s) {
 // All offsets are in bytes from a 1024-byte aligned base inside the caller's float arena.
 struct Workspace {
     uint32_t B, H1, H2, R, OUT, IN;
-    uint32_t p_a1;    // pitch (halfs) of a1_h, rounded to 8
     uint32_t p_bt;    // pitch (halfs) of the tensors kept with one row per hd1 column (a1, dz1): samples rounded to 8
     uint64_t off_rowsum, rowsum_rows;  // partial row sums of the hidden layer's dX GEMM (input-bias gradient)
     uint64_t off_bits_h1;              // sign words of the embedding layer's pre-activation: [hd1][ld_bits_h1]
     uint32_t ld_bits_h1;
     uint32_t p_act;   // pitch (halfs) of x_h / r1_h, rounded to 8
     uint32_t p_dz;    // pitch (halfs) of dz tensors over H2
-    uint32_t p_dz1;   // pitch (halfs) of dz1 over H1
     uint32_t p_f32;   // pitch (floats) of the fp32 residual / gradient streams
     uint32_t p_w1, p_w2, p_wout;  // pitches of the internal fp16 weight copy
     uint64_t off_a1, off_x, off_r1, off_xf, off_dzf, off_dz2, off_dz1t, off_dz1, off_partial, off_head, off_wint, off_dy, off_dyh, off_colsum;
-    uint64_t colsum_floats, colsum_slot_floats, off_colsum_h1, dz_stride;
+    uint64_t colsum_floats, colsum_slot_floats, dz_stride;
     uint64_t off_bits, bits_stride;  // ReLU sign bits of the residual tower: 2R+1 entries of bits_stride words
     uint64_t x_stride, r1_stride;  // bytes between consecutive blocks' tensors
     uint64_t partial_floats, head_blocks;
@@ -97,10 +95,8 @@ Workspace PlanWorkspace(const mgt_mlp_shape_t& s, uint32_t B, uint32_t sm_count,
     Workspace w{};
     w.B = B; w.H1 = s.hd1; w.H2 = s.hd2; w.R = s.residual_blocks; w.OUT = s.output_dim;
     w.IN = s.state_len * s.state_value_pad;
-    w.p_a1 = (uint32_t)RoundUp(s.hd1, 8);
     w.p_act = (uint32_t)RoundUp(s.hd2, 8);
     w.p_dz = (uint32_t)RoundUp(s.hd2, 8);
-    w.p_dz1 = (uint32_t)RoundUp(s.hd1, 8);
     w.p_bt = (uint32_t)RoundUp(B, 8);
     w.p_f32 = (uint32_t)RoundUp(s.hd2, 4);
     w.p_w1 = (uint32_t)RoundUp(s.hd1, 8);
@@ -108,8 +104,8 @@ Workspace PlanWorkspace(const mgt_mlp_shape_t& s, uint32_t B, uint32_t sm_count,
     w.p_wout = (uint32_t)RoundUp(s.output_dim, 8);
     uint64_t off = 0;
     auto take = [&](uint64_t bytes) { const uint64_t o = off; off = RoundUp(off + bytes, 1024); return o; };
-    // a1 and dz1 lie either as [samples][hd1] or as [hd1][samples] (see mgt_engine::rows_layout): room for both
-    const uint64_t hidden_act_bytes = std::max((uint64_t)B * w.p_a1, (uint64_t)s.hd1 * w.p_bt) * 2;
+    // a1 and dz1 lie as [hd1][samples]: the way the two embedding GEMMs produce and consume them
+    const uint64_t hidden_act_bytes = (uint64_t)s.hd1 * w.p_bt * 2;
     w.off_a1 = take(hidden_act_bytes);
     w.x_stride = RoundUp((uint64_t)B * w.p_act * 2, 1024);
     w.off_x = take(w.x_stride * (w.R + 1));
@@ -138,13 +134,12 @@ Workspace PlanWorkspace(const mgt_mlp_shape_t& s, uint32_t B, uint32_t sm_count,
     w.off_partial = take(w.partial_floats * 4);
     w.head_blocks = kHeadBlocks;
     w.off_head = take((uint64_t)kHeadBlocks * (2ULL * s.hd2 + 2) * 4);
-    // per-warp column sums: one slot per residual dX GEMM (2R of them), one wider slot for the hidden dX GEMM
+    // per-warp column sums: one slot per residual dX GEMM (2R of them)
     const uint64_t chain_tiles = (B + 127) / 128;
     const uint64_t slot_rows = (uint64_t)sm_count * 16 > chain_tiles * 4 ? (uint64_t)sm_count * 16 : chain_tiles * 4;  // up to 16 epilogue warps per CTA
     w.colsum_slot_floats = slot_rows * s.hd2;
     w.colsum_floats = w.colsum_slot_floats * 2 * (w.R > 0 ? w.R : 1);
     w.off_colsum = take(w.colsum_floats * 4);
-    w.off_colsum_h1 = take((uint64_t)sm_count * 16 * s.hd1 * 4);
     w.rowsum_rows = 2ULL * ((B + 255) / 256);  // two epilogue warps per lane quadrant, one N tile per 256 samples
     w.off_rowsum = take(w.rowsum_rows * s.hd1 * 4);
     w.ld_bits_h1 = (uint32_t)RoundUp((B + 31) / 32, 8);  // (32-byte rows)
@@ -203,7 +198,6 @@ struct mgt_engine {
     std::mutex mu;
     cudaEvent_t ev_last = nullptr, ev_now = nullptr;
     uint64_t launches = 0;  // kernels launched through this engine (host-side count)
-    bool rows_layout = true;     // a1/dz1 as [hd1][samples] (MGT_HIDDEN_LAYOUT=samples: as [samples][hd1], the earlier form; both are tested)
     bool layered_tower = false;  // MGT_RESIDUAL_PATH=layered: per-layer GEMMs instead of the fused residual-tower kernels (both are tested)
     mgt_gradient_ready_fn early_fn = nullptr;  // mgt_engine_set_early_range_hook
     void* early_user = nullptr;
@@ -302,8 +296,6 @@ template <int BN, Epi EPI> using CfgDx = GemmCfg<BN, 1, false, BSource::kTmaK, E
 // B-stationary forms for reductions of at most 256 (the residual width): weights stay in shared memory
 template <int BN, Epi EPI> using CfgFwdS = GemmCfg<BN, 1, false, BSource::kTmaMN, EPI, 3, 4, true>;
 template <int BN, Epi EPI> using CfgDxS = GemmCfg<BN, 1, false, BSource::kTmaK, EPI, 3, 4, true>;
-// wide outputs (the hidden layer's dX): 128-column tiles drained by sixteen epilogue warps, one 32-column chunk each
-template <Epi EPI> using CfgDxW = GemmCfg<128, 1, false, BSource::kTmaK, EPI, 4, 4, true, false, 16>;
 template <int BN> using CfgDw = GemmCfg<BN, 1, true, BSource::kTmaMN, Epi::kPartialF32, 3, 3>; // act^T x dz
 // The hidden layer with its wide side (hd1) as rows: a1 and dz1 are kept as [hd1][samples], the way the two embedding GEMMs
 // produce and consume them, so that their epilogues and the hidden dX epilogue move 64 contiguous bytes per lane
@@ -314,10 +306,8 @@ template <int BN> using CfgDwG = GemmCfg<BN, 1, true, BSource::kTmaMN, Epi::kPar
 // Two 256-column accumulators per unit (all of TMEM) and a two-stage one-hot ring. Measured alternatives at p888: 2 x 192
 // columns with a three-stage ring 1.44 ms, one double-buffered 256-column accumulator (epilogue under the next unit's
 // MMAs, but the table tile re-read twice as often) 1.37 ms, this form 1.14 ms: the K loop already issues MMAs back to back.
-using CfgEmbFwd = GemmCfg<256, 2, true, BSource::kOneHotFwd, Epi::kEmbFwd, 4, 2>;
-using CfgEmbGrad = GemmCfg<256, 2, true, BSource::kOneHotGrad, Epi::kEmbGrad, 4, 2>;
-using CfgEmbFwdRows = GemmCfg<256, 2, true, BSource::kOneHotFwd, Epi::kEmbFwdRows, 4, 2>;
-using CfgEmbGradRows = GemmCfg<256, 2, false, BSource::kOneHotGrad, Epi::kEmbGrad, 4, 2>;
+using CfgEmbFwd = GemmCfg<256, 2, true, BSource::kOneHotFwd, Epi::kEmbFwdRows, 4, 2>;   // table[K][M] x onehot -> a1T[M][N]
+using CfgEmbGrad = GemmCfg<256, 2, false, BSource::kOneHotGrad, Epi::kEmbGrad, 4, 2>;    // dz1T[M][K] x onehot -> grad[N][M]
 // (One accumulator per unit with two units in flight - the epilogue of one draining under the MMAs of the next, operand
 // ring four deep - was measured at p888: forward 1.40 ms against 1.22 ms, gradient 1.56 ms against 1.13 ms. A K chunk
 // costs about a thousand cycles in hand-overs whatever it feeds, so it should feed eight MMAs, not four.)
@@ -708,20 +698,19 @@ mgt_status_t GemmForwardRows(mgt_engine* e, cudaStream_t st, const __half* act_t
 // How a dX GEMM is run: tile width, form, grid, and the rows of its column-sum scratch (one per epilogue warp of every CTA).
 struct BackpropPlan {
     uint32_t bn;
-    bool stationary, wide;
+    bool stationary;
     uint32_t grid, rows;
 };
 BackpropPlan PlanBackprop(const mgt_engine* e, uint32_t M, uint32_t N, uint32_t K) {
     BackpropPlan p{};
     const uint32_t sm = (uint32_t)e->sm_count;
-    p.wide = (K + 63) / 64 <= 4 && N % 128U == 0 && N >= 512U && N / 128U <= sm;
-    p.bn = p.wide ? 128U : PickBN(N);
+    p.bn = PickBN(N);
     const GemmArgs a = BaseArgs(M, N, K, p.bn, 1);
-    p.stationary = p.wide || (a.k_chunks <= 4 && a.n_tiles <= sm);
+    p.stationary = a.k_chunks <= 4 && a.n_tiles <= sm;
     const uint64_t units = (uint64_t)a.m_tiles * a.n_tiles;
     p.grid = (uint32_t)(units < (uint64_t)sm ? units : (uint64_t)sm);
     if (p.stationary && p.grid >= a.n_tiles) p.grid = p.grid / a.n_tiles * a.n_tiles;  // as LaunchGemm picks it
-    p.rows = p.grid * (p.wide ? 16U : 8U);
+    p.rows = p.grid * 8U;
     return p;
 }
 
@@ -739,9 +728,7 @@ mgt_status_t GemmBackpropInput(mgt_engine* e, cudaStream_t st, const __half* dz,
     CUtensorMap ta, tb;
     MGT_MAP(e->Map(&ta, dz, K, M, dz_pitch, 64, 128));
     MGT_MAP(e->Map(&tb, w, K, N, w_pitch, 64, p.bn));
-    if (p.wide) {
-        MGT_TRY(LaunchGemm<CfgDxW<EPI>>(e, ta, tb, a, st));
-    } else if (p.stationary) {
+    if (p.stationary) {
         MGT_TRY(p.bn == 224 ? LaunchGemm<CfgDxS<224, EPI>>(e, ta, tb, a, st) : LaunchGemm<CfgDxS<256, EPI>>(e, ta, tb, a, st));
     } else {
         MGT_TRY(p.bn == 224 ? LaunchGemm<CfgDx<224, EPI>>(e, ta, tb, a, st) : LaunchGemm<CfgDx<256, EPI>>(e, ta, tb, a, st));
@@ -1038,7 +1025,6 @@ mgt_status_t mgt_engine_create(int32_t device_id, mgt_engine_t** out_engine) {
         return MGT_CUDA_FAILURE;
     }
     e->encode = reinterpret_cast<EncodeTiledFn>(fn);
-    if (const char* layout = std::getenv("MGT_HIDDEN_LAYOUT")) e->rows_layout = std::strcmp(layout, "samples") != 0;
     if (const char* path = std::getenv("MGT_RESIDUAL_PATH")) e->layered_tower = std::strcmp(path, "layered") == 0;
     if (cudaMalloc(&e->status_word, sizeof(int)) != cudaSuccess || cudaMemset(e->status_word, 0, sizeof(int)) != cudaSuccess) {
         delete e;
@@ -1156,10 +1142,8 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     float* partial = reinterpret_cast<float*>(base + ws.off_partial);
     float* head_partial = reinterpret_cast<float*>(base + ws.off_head);
     float* colsum = reinterpret_cast<float*>(base + ws.off_colsum);
-    float* colsum_h1 = reinterpret_cast<float*>(base + ws.off_colsum_h1);
     const uint32_t H1 = s.hd1, H2 = s.hd2, R = s.residual_blocks, OUT = s.output_dim, IN = ws.IN;
 
-    const bool rows_layout = e->rows_layout;
     StageTimer timer{e, st, profile};
     if (!timer.Start()) return MGT_CUDA_FAILURE;
     uint32_t ready_id = 0;
@@ -1253,12 +1237,12 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     // ---- embedding forward: a1 = relu([onehot | 1] * [W_in ; b_in])  (mlp_backward.cu:755-832)
     {
         GemmArgs a = BaseArgs(H1, B, IN + 1, CfgEmbFwd::NACC * CfgEmbFwd::BN, 1);
-        a.out_f16 = a1_h; a.ld_f16 = rows_layout ? ws.p_bt : ws.p_a1;
-        a.bits = rows_layout ? reinterpret_cast<uint32_t*>(base + ws.off_bits_h1) : nullptr; a.ld_bits = ws.ld_bits_h1;
+        a.out_f16 = a1_h; a.ld_f16 = ws.p_bt;
+        a.bits = reinterpret_cast<uint32_t*>(base + ws.off_bits_h1); a.ld_bits = ws.ld_bits_h1;
         a.states = reinterpret_cast<const uint8_t*>(states); a.state_len = s.state_len; a.value_pad = s.state_value_pad; a.samples = B; a.in_rows = IN;
         CUtensorMap ta;
         MGT_MAP(e->Map(&ta, hw.in_table, H1, IN + 1, hw.p1, 64, 64));
-        MGT_TRY(rows_layout ? LaunchGemm<CfgEmbFwdRows>(e, ta, ta, a, st) : LaunchGemm<CfgEmbFwd>(e, ta, ta, a, st));
+        MGT_TRY(LaunchGemm<CfgEmbFwd>(e, ta, ta, a, st));
     }
     if (!timer.Mark(profile ? &profile->input_forward_ms : nullptr)) return MGT_CUDA_FAILURE;
 
@@ -1268,12 +1252,10 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
         epi.bias = w + HiddenBias(s); epi.out_f32 = x_f32; epi.ld_f32 = ws.p_f32; epi.out_f16 = x_h(0); epi.ld_f16 = ws.p_act;
         if (bnorm) {
             epi.out_f32 = z_tape(0);
-            MGT_TRY(rows_layout ? GemmForwardRows<Epi::kBiasF32>(e, st, a1_h, ws.p_bt, hw.wh, hw.p2, B, H2, H1, epi)
-                                : GemmForward<Epi::kBiasF32>(e, st, a1_h, ws.p_a1, hw.wh, hw.p2, B, H2, H1, epi));
+            MGT_TRY(GemmForwardRows<Epi::kBiasF32>(e, st, a1_h, ws.p_bt, hw.wh, hw.p2, B, H2, H1, epi));
             MGT_TRY(bn_forward(0));
         } else {
-            MGT_TRY(rows_layout ? GemmForwardRows<Epi::kBiasReluF32F16>(e, st, a1_h, ws.p_bt, hw.wh, hw.p2, B, H2, H1, epi)
-                                : GemmForward<Epi::kBiasReluF32F16>(e, st, a1_h, ws.p_a1, hw.wh, hw.p2, B, H2, H1, epi));
+            MGT_TRY(GemmForwardRows<Epi::kBiasReluF32F16>(e, st, a1_h, ws.p_bt, hw.wh, hw.p2, B, H2, H1, epi));
         }
     }
     if (!timer.Mark(profile ? &profile->hidden_forward_ms : nullptr)) return MGT_CUDA_FAILURE;
@@ -1387,22 +1369,17 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     // ---- hidden layer backward, dX part (mlp_backward.cu:1417-1438): dz_tape(0) = dcur * [x0 > 0]
     dz_cur = dz_tape(0);
     if (bnorm) MGT_TRY(bn_backward(0, grad + HiddenBias(s)));
-    if (half_ig && rows_layout) {
+    if (half_ig) {
         // dz1T = (Wh * dzh^T) * [pre-activation of a1 > 0], the input-bias gradient from its row sums
         MGT_TRY(GemmBackpropInputRows(e, st, hw.wh, hw.p2, dz_cur, ws.p_dz, B, H1, H2, reinterpret_cast<uint32_t*>(base + ws.off_bits_h1), ws.ld_bits_h1, dz1_h,
                                       ws.p_bt, reinterpret_cast<float*>(base + ws.off_rowsum), ws.rowsum_rows, grad + InputBias(s)));
-    } else if (half_ig) {
-        GemmArgs d{};  // dz1 = (dzh * Wh^T) * [a1 > 0]
-        d.mask = a1_h; d.ld_mask = ws.p_a1; d.out_f16 = dz1_h; d.ld_f16 = ws.p_dz1;
-        if (cudaMemsetAsync(colsum_h1, 0, (uint64_t)PlanBackprop(e, B, H1, H2).rows * H1 * sizeof(float), st) != cudaSuccess) return MGT_CUDA_FAILURE;
-        MGT_TRY(GemmBackpropInput<Epi::kMaskF16>(e, st, dz_cur, ws.p_dz, hw.wh, hw.p2, B, H1, H2, d, colsum_h1, grad + InputBias(s)));
     } else {
         // --input-grad-fp16 0: the embedding gradient wants dz1 in fp32 (mlp_backward.cu:1433-1504, float one-hot GEMM).
         // da1 from the same fp16 operands with fp32 accumulation, masked in fp32, then the table gradient on CUDA cores.
         using namespace mgt::fp32path;
         const uint64_t bh1 = (uint64_t)B * H1;
         if (Sgemm<false, true>(st, B, H1, H2, dz_cur, ws.p_dz, hw.wh, hw.p2, da1_f32, H1) != cudaSuccess) return MGT_CUDA_FAILURE;
-        MaskKernel<__half><<<GridFor(bh1, 256, e->sm_count), 256, 0, st>>>(da1_f32, nullptr, a1_h, H1, rows_layout ? ws.p_bt : ws.p_a1, bh1, false, dz1_f32, rows_layout);
+        MaskKernel<__half><<<GridFor(bh1, 256, e->sm_count), 256, 0, st>>>(da1_f32, nullptr, a1_h, H1, ws.p_bt, bh1, false, dz1_f32, true);
         ColumnSumKernel<<<(H1 + 7) / 8, 256, 0, st>>>(dz1_f32, B, H1, grad + InputBias(s));
         e->launches += 3;
         if (cudaGetLastError() != cudaSuccess) return MGT_CUDA_FAILURE;
@@ -1432,13 +1409,8 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
         a.in_rows = 0xFFFFFFFFU;  // no all-ones row in this direction
         if (a.splits > 1 && cudaMemsetAsync(grad, 0, (uint64_t)IN * H1 * sizeof(float), st) != cudaSuccess) return MGT_CUDA_FAILURE;
         CUtensorMap ta;
-        if (rows_layout) {
-            MGT_MAP(e->Map(&ta, dz1_h, B, H1, ws.p_bt, 64, 128));
-            MGT_TRY(LaunchGemm<CfgEmbGradRows>(e, ta, ta, a, st));
-        } else {
-            MGT_MAP(e->Map(&ta, dz1_h, H1, B, ws.p_dz1, 64, 64));
-            MGT_TRY(LaunchGemm<CfgEmbGrad>(e, ta, ta, a, st));
-        }
+        MGT_MAP(e->Map(&ta, dz1_h, B, H1, ws.p_bt, 64, 128));
+        MGT_TRY(LaunchGemm<CfgEmbGrad>(e, ta, ta, a, st));
     }
     // table and input bias are complete: tell a caller who asked to hear of it before the weight-gradient GEMMs are enqueued
     if (e->early_fn != nullptr && e->early_fn(e->early_user, 2U * R + 2U, 0, InputBias(s) + H1, stream_v) != MGT_OK) return MGT_CUDA_FAILURE;
@@ -1469,8 +1441,7 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
 
     // ---- hidden layer backward, dW part; every kernel that reads the hidden weights was enqueued long before, so a caller
     // may update the range in place as soon as it is announced
-    MGT_TRY(rows_layout ? GemmGradWeightsRows(e, st, a1_h, ws.p_bt, dz_cur, ws.p_dz, B, H1, H2, partial, ws.partial_floats, grad + HiddenWeight(s))
-                        : GemmGradWeights(e, st, a1_h, ws.p_a1, dz_cur, ws.p_dz, B, H1, H2, partial, ws.partial_floats, grad + HiddenWeight(s)));
+    MGT_TRY(GemmGradWeightsRows(e, st, a1_h, ws.p_bt, dz_cur, ws.p_dz, B, H1, H2, partial, ws.partial_floats, grad + HiddenWeight(s)));
     MGT_TRY(notify(HiddenWeight(s), (uint64_t)H1 * H2 + H2));
     if (!timer.Mark(profile ? &profile->hidden_backward_ms : nullptr)) return MGT_CUDA_FAILURE;
     MGT_TRY(notify(0, InputBias(s) + H1));

@@ -33,7 +33,6 @@ enum class Epi : int {
     kMaskF16,              // out_f16 = acc * [mask > 0]
     kAddMaskF32F16,        // v = (acc + add) * [mask > 0]; out_f32 = v (may alias add); out_f16 = v
     kPartialF32,           // partial[split][m][n] = acc
-    kEmbFwd,               // out_f16[n][m] = relu(acc)            (D is the transposed activation)
     kEmbGrad,              // out_f32[n][m] (+)= acc               (D is the transposed gradient)
     kBiasF32,              // out_f32 = acc + bias                 (a pre-activation kept in fp32: input of batch normalisation)
     kEmbFwdRows,           // out_f16[m][n] = relu(acc), bits[m][n / 32] bit (n % 32) = [acc > 0]   (the activation kept as D lies: one row
@@ -393,8 +392,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         uint32_t unit_iter = 0;
         bool ok = true;
         if constexpr (Cfg::kOneHot) {
-            // Embedding layers: D is the transposed result, so a TMEM lane (row of D) is a column of the
-            // row-major tensor and the 32 lanes of a warp already write consecutive addresses.
+            // Embedding layers. Forward: the activation is kept the way D lies ([hd1][samples]), a lane writes the 32
+            // columns of its row. Gradient: D is the transposed table gradient, a TMEM lane (row of D) is a column of the
+            // row-major table and the 32 lanes of a warp write consecutive addresses.
             for (uint32_t unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x, ++unit_iter) {
                 uint32_t mt, nt, sp;
                 decode(unit, mt, nt, sp);
@@ -444,12 +444,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                             for (int j = 0; j < 32; ++j) {
                                 if (static_cast<uint32_t>(j) < valid) {
                                     const float x = __uint_as_float(r[j]);
-                                    if constexpr (Cfg::EPI == Epi::kEmbFwd) {
-                                        reinterpret_cast<uint16_t*>(args.out_f16)[static_cast<uint64_t>(n0 + j) * args.ld_f16 + m] = to_operand(fmaxf(x, 0.0f), args.bf16 != 0U);
-                                    } else {
-                                        float* dst = args.out_f32 + static_cast<uint64_t>(n0 + j) * args.ld_f32 + m;
-                                        if (args.splits > 1U) atomicAdd(dst, x); else *dst = x;
-                                    }
+                                    float* dst = args.out_f32 + static_cast<uint64_t>(n0 + j) * args.ld_f32 + m;
+                                    if (args.splits > 1U) atomicAdd(dst, x); else *dst = x;
                                 }
                             }
                         }
