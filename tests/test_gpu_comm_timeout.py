@@ -26,7 +26,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, lonely_count):
     import torch.distributed as dist
     from multigputrainmlp_b200.comm import PeerBackend
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -61,7 +61,7 @@ def _worker(rank, world, port, out_dir):
         t0 = torch.cuda.Event(enable_timing=True)
         t1 = torch.cuda.Event(enable_timing=True)
         t0.record()
-        assert backend.allreduce_average(0, 1000) == 0       # the launch itself succeeds; the peer never joins
+        assert backend.allreduce_average(0, lonely_count) == 0   # the launch itself succeeds; the peer never joins
         t1.record()
         st, code = backend.check()
         result["status"], result["code"] = st, code
@@ -69,7 +69,7 @@ def _worker(rank, world, port, out_dir):
         # the context is alive: plain work on the same device still runs
         result["alive"] = float((torch.ones(8, device=dev) * 2).sum().item())
         # ... but this communicator is finished: no launch, same status, also from check()
-        result["next_launch"] = backend.allreduce_average(0, 1000)
+        result["next_launch"] = backend.allreduce_average(0, lonely_count)
         result["next_check"] = backend.check()[0]
     dist.barrier()  # rank 1 stays (idle, nothing in flight) until rank 0 has seen its status
     np.save(os.path.join(out_dir, f"rank{rank}.npy"), result, allow_pickle=True)
@@ -77,11 +77,14 @@ def _worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-def test_absent_peer_times_out_into_a_status(tmp_path):
+# 5000 floats: the handshaken kernels, which give up in their ready wait (code 1); 1000 floats: the push protocol of tiny
+# vectors, whose only wait is the one for the peers' vectors (code 3)
+@pytest.mark.parametrize("lonely_count,code", [(5000, 1), (1000, 3)])
+def test_absent_peer_times_out_into_a_status(tmp_path, lonely_count, code):
     import torch.multiprocessing as mp
-    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), lonely_count), nprocs=2, join=True)
     r0 = np.load(tmp_path / "rank0.npy", allow_pickle=True).item()
-    assert r0["status"] == 7 and r0["code"] == 1          # MGT_DEVICE_TIMEOUT, gave up in the ready wait
+    assert r0["status"] == 7 and r0["code"] == code       # MGT_DEVICE_TIMEOUT and the wait that gave up
     assert 150.0 <= r0["wait_ms"] <= 2000.0               # the 200 ms limit, not the 1 s default and not forever
     assert r0["alive"] == 16.0
     assert r0["next_launch"] == 7 and r0["next_check"] == 7

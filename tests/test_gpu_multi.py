@@ -40,8 +40,9 @@ def _worker(rank, world, port, n, out_dir):
     m = torch.zeros(n, device=dev)
     v = torch.zeros(n, device=dev)
     results = {}
-    # (offset, count): unaligned small range (one-shot), large range (two-shot), everything
-    cases = [(3, 225), (1000, 50400), (70001, 300007), (0, n)]
+    # (offset, count): three tiny vectors in a row (push protocol, both inbox slots, the first unaligned), a small range
+    # (handshaken one-shot), a large range (two-shot), everything
+    cases = [(3, 225), (7, 1024), (4096, 448), (1000, 50400), (70001, 300007), (0, n)]
     for idx, (off, cnt) in enumerate(cases):
         g = (rng.standard_normal(n) * 1e-3).astype(np.float32)
         grad.copy_(torch.from_numpy(g))
@@ -80,7 +81,7 @@ def test_two_rank_peer_allreduce_and_fused_adamw(tmp_path, oracle):
     n = 1_000_003
     mp.spawn(_worker, args=(2, _free_port(), n, str(tmp_path)), nprocs=2, join=True)
     r = [np.load(tmp_path / f"rank{i}.npz") for i in range(2)]
-    cases = [(3, 225), (1000, 50400), (70001, 300007), (0, n)]
+    cases = [(3, 225), (7, 1024), (4096, 448), (1000, 50400), (70001, 300007), (0, n)]
     for idx, (off, cnt) in enumerate(cases):
         want = oracle.allreduce_average([r[0][f"raw_{idx}"], r[1][f"raw_{idx}"]])
         for rank in range(2):
