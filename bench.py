@@ -41,8 +41,9 @@ EMB_ALGO_FLOP_PER_CANDIDATE = 72 * 2560   # the embedding forward counted as the
 EMB_EXEC_FLOP_PER_CANDIDATE = 2 * (72 * 72 + 1) * 2560  # what the one-hot GEMM executes on the tensor cores
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from an ncu capture (not measured by
 # this run: the source is named in the output next to the figure)
-EMB_FWD_DRAM_BYTES_PER_LAUNCH = 249_800_000
-EMB_FWD_DRAM_SOURCE = "ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch at batch 53248 (31.1 MB read + 218.7 MB written), captured 2026-11-25"
+EMB_FWD_DRAM_BYTES_PER_LAUNCH = 268_568_064
+EMB_FWD_DRAM_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch at batch 53248 (32.9 MB read + 235.7 MB written: "
+                       "the [hd1][B] activation and its sign words), single-pass capture of 2026-11-25, profiles/training_step_p888_launch_list.md")
 README_P888_FLAGS = ["--batch-size", "53248", "--k-min", "1", "--k-max", "29", "--hd1", "2556", "--hd2", "218", "--nrd", "16",
                      "--input-grad-fp16", "1", "--input-grad-position-tile", "36", "--linear-fp16", "1", "--write-artifacts", "0",
                      "--allreduce-bucket-bytes", "4194304"]  # the reference README's p888 command (README.md:48-64)
