@@ -87,7 +87,7 @@ def test_mlp_known_answer(oracle, golden):
     assert st == 0 and np.array_equal(out, g["kat_outputs"])
     st, loss, grad = oracle.loss_grad(shape, weights, states, labels)
     assert st == 0 and np.float32(loss) == g["kat_loss"] and np.array_equal(grad, g["kat_grad"])
-    # the survey's printed KAT
+    # known answers printed by the reference's CPU code for this case (recorded when the golden vectors were made)
     assert abs(out[0, 0] + 0.0405305214) < 1e-9 and abs(loss - 5.16307878) < 1e-6
     assert abs(grad[7] - 0.00150364335) < 1e-10 and abs(grad[-1] + 4.08083534) < 1e-6
 
