@@ -365,14 +365,28 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     const uint32_t b_addr = smem_u32(b_ring + sb * Cfg::B_STAGE_BYTES);
                     const uint32_t k_left = args.K - c * 64U;
                     const uint32_t ksteps = k_left >= 64U ? 4U : (k_left + 15U) / 16U;
+                    // Descriptors of the chunk's first K step; a later step only moves the start address (bits [0,14) in
+                    // units of 16 bytes, no carry: shared-memory addresses are below 2^18). One thread issues everything,
+                    // so the fewer dependent instructions stand between two MMAs the better: the full chunk is unrolled.
+                    constexpr uint64_t kStepA = Cfg::A_MN ? 2048U / 16U : 32U / 16U, kStepB = Cfg::B_MN ? 2048U / 16U : 32U / 16U;
+                    const uint64_t a_desc0 = Cfg::A_MN ? make_smem_desc(a_addr, 8192U, 1024U) : make_smem_desc(a_addr, 16U, 1024U);
+                    const uint32_t first = c > c0 ? 1U : 0U;
+                    if (ksteps == 4U) {
 #pragma unroll
-                    for (int acc = 0; acc < NACC; ++acc) {
-                        for (uint32_t kk = 0; kk < ksteps; ++kk) {
-                            const uint64_t a_desc = Cfg::A_MN ? make_smem_desc(a_addr + kk * 2048U, 8192U, 1024U)
-                                                              : make_smem_desc(a_addr + kk * 32U, 16U, 1024U);
-                            const uint64_t b_desc = Cfg::B_MN ? make_smem_desc(b_addr + acc * Cfg::B_ACC_BYTES + kk * 2048U, 8192U, 1024U)
-                                                              : make_smem_desc(b_addr + acc * Cfg::B_ACC_BYTES + kk * 32U, 16U, 1024U);
-                            umma_f16(d_base + acc * Cfg::ACC_COLS, a_desc, b_desc, idesc, (c > c0 || kk > 0U) ? 1U : 0U);
+                        for (int acc = 0; acc < NACC; ++acc) {
+                            const uint64_t b_desc0 = Cfg::B_MN ? make_smem_desc(b_addr + acc * Cfg::B_ACC_BYTES, 8192U, 1024U)
+                                                               : make_smem_desc(b_addr + acc * Cfg::B_ACC_BYTES, 16U, 1024U);
+#pragma unroll
+                            for (uint32_t kk = 0; kk < 4U; ++kk)
+                                umma_f16(d_base + acc * Cfg::ACC_COLS, a_desc0 + kk * kStepA, b_desc0 + kk * kStepB, idesc, kk == 0U ? first : 1U);
+                        }
+                    } else {
+#pragma unroll
+                        for (int acc = 0; acc < NACC; ++acc) {
+                            const uint64_t b_desc0 = Cfg::B_MN ? make_smem_desc(b_addr + acc * Cfg::B_ACC_BYTES, 8192U, 1024U)
+                                                               : make_smem_desc(b_addr + acc * Cfg::B_ACC_BYTES, 16U, 1024U);
+                            for (uint32_t kk = 0; kk < ksteps; ++kk)
+                                umma_f16(d_base + acc * Cfg::ACC_COLS, a_desc0 + kk * kStepA, b_desc0 + kk * kStepB, idesc, kk == 0U ? first : 1U);
                         }
                     }
                     umma_commit(&empty_a[sa]);
