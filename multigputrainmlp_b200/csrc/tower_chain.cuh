@@ -160,7 +160,7 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
                     const int32_t z = static_cast<int32_t>(BWD ? (2U * (R - 1U - (l >> 1)) + ((l & 1U) ^ 1U)) : l);
                     for (uint32_t c = 0; c < KC; ++c, ++it) {
                         const uint32_t s = it % SW, ph = (it / SW) & 1U;
-                        if (!mbar_wait(&w_empty[s], ph ^ 1U, cta_abort, kAbortChainWait)) { ok = false; break; }
+                        if (!mbar_wait_spin(&w_empty[s], ph ^ 1U, cta_abort, kAbortChainWait)) { ok = false; break; }
                         uint8_t* dst = w_ring + s * ChainCfg::W_STAGE_BYTES;
                         mbar_arrive_expect_tx(&w_full[s], stage_bytes);
                         if (BWD) {
@@ -190,18 +190,26 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
                         const uint32_t d_addr = tmem_base + (half ? kStateCol : 0U);
                         for (uint32_t c = 0; c < KC; ++c, ++it) {
                             const uint32_t s = it % SW, ph = (it / SW) & 1U;
-                            if (!mbar_wait(&ready[c], uses & 1U, cta_abort, kAbortChainWait)) { ok = false; break; }
-                            if (!mbar_wait(&w_full[s], ph, cta_abort, kAbortChainWait)) { ok = false; break; }
+                            // (the issuing thread polls its barriers: waking from a suspended wait costs more than the hand-over itself)
+                            if (!mbar_wait_spin(&ready[c], uses & 1U, cta_abort, kAbortChainWait)) { ok = false; break; }
+                            if (!mbar_wait_spin(&w_full[s], ph, cta_abort, kAbortChainWait)) { ok = false; break; }
                             tc_fence_after();
                             const uint32_t a_addr = a_base + c * 16384U;
                             const uint32_t b_addr = smem_u32(w_ring + s * ChainCfg::W_STAGE_BYTES);
                             const uint32_t k_left = H - c * 64U;
                             const uint32_t ksteps = k_left >= 64U ? 4U : (k_left + 15U) / 16U;
-                            for (uint32_t kk = 0; kk < ksteps; ++kk) {
-                                const uint64_t a_desc = make_smem_desc(a_addr + kk * 32U, 16U, 1024U);
-                                const uint64_t b_desc = BWD ? make_smem_desc(b_addr + kk * 32U, 16U, 1024U) : make_smem_desc(b_addr + kk * 2048U, 8192U, 1024U);
-                                // the second product of a block adds onto the state that already sits in TMEM
-                                umma_f16(d_addr, a_desc, b_desc, idesc, (half != 0U || c > 0U || kk > 0U) ? 1U : 0U);
+                            // descriptors of the chunk's first K step; a later step only moves the start address (units of 16
+                            // bytes, no carry out of the field). One thread issues everything: the full chunk is unrolled.
+                            const uint64_t a_desc0 = make_smem_desc(a_addr, 16U, 1024U);
+                            const uint64_t b_desc0 = BWD ? make_smem_desc(b_addr, 16U, 1024U) : make_smem_desc(b_addr, 8192U, 1024U);
+                            constexpr uint64_t kStepA = 32U / 16U, kStepB = BWD ? 32U / 16U : 2048U / 16U;
+                            // the second product of a block adds onto the state that already sits in TMEM
+                            const uint32_t first = (half != 0U || c > 0U) ? 1U : 0U;
+                            if (ksteps == 4U) {
+#pragma unroll
+                                for (uint32_t kk = 0; kk < 4U; ++kk) umma_f16(d_addr, a_desc0 + kk * kStepA, b_desc0 + kk * kStepB, idesc, kk == 0U ? first : 1U);
+                            } else {
+                                for (uint32_t kk = 0; kk < ksteps; ++kk) umma_f16(d_addr, a_desc0 + kk * kStepA, b_desc0 + kk * kStepB, idesc, kk == 0U ? first : 1U);
                             }
                             umma_commit(&w_empty[s]);
                         }
@@ -250,7 +258,7 @@ tower_chain_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         // lane 0 polls, the warp follows: the result is warp-uniform
         auto warp_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
             uint32_t done = 0;
-            if (lane == 0) done = mbar_wait(bar, parity, cta_abort, kAbortChainWait) ? 1U : 0U;
+            if (lane == 0) done = mbar_wait_spin(bar, parity, cta_abort, kAbortChainWait) ? 1U : 0U;
             return __shfl_sync(0xFFFFFFFFU, done, 0) != 0U;
         };
         auto publish = [&](uint64_t* bar) {

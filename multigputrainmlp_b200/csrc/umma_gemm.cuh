@@ -294,7 +294,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 const uint32_t c0 = chunk_begin(sp), c1 = chunk_begin(sp + 1);
                 for (uint32_t c = c0; c < c1; ++c, ++it) {
                     const uint32_t sa = it % SA, pa = (it / SA) & 1U;
-                    if (!mbar_wait(&empty_a[sa], pa ^ 1U, cta_abort, kAbortProducerWait)) { ok = false; break; }
+                    if (!mbar_wait_spin(&empty_a[sa], pa ^ 1U, cta_abort, kAbortProducerWait)) { ok = false; break; }
                     uint8_t* a_dst = a_ring + sa * Cfg::A_STAGE_BYTES;
                     mbar_arrive_expect_tx(&full_a[sa], Cfg::A_STAGE_BYTES);
                     if (Cfg::GROUPED) {
@@ -310,7 +310,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                     if (!Cfg::kOneHot && (!Cfg::BSTAT || unit == blockIdx.x)) {
                         // B-stationary: chunk c of B lives in stage c for the whole kernel, loaded with the first unit
                         const uint32_t sb = Cfg::BSTAT ? (c - c0) : it % SB, pb = Cfg::BSTAT ? 0U : (it / SB) & 1U;
-                        if (!Cfg::BSTAT && !mbar_wait(&empty_b[sb], pb ^ 1U, cta_abort, kAbortProducerWait)) { ok = false; break; }
+                        if (!Cfg::BSTAT && !mbar_wait_spin(&empty_b[sb], pb ^ 1U, cta_abort, kAbortProducerWait)) { ok = false; break; }
                         uint8_t* b_dst = b_ring + sb * Cfg::B_STAGE_BYTES;
                         mbar_arrive_expect_tx(&full_b[sb], Cfg::B_STAGE_BYTES);
 #pragma unroll
@@ -347,18 +347,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 decode(unit, mt, nt, sp);
                 const uint32_t c0 = chunk_begin(sp), c1 = chunk_begin(sp + 1);
                 const uint32_t ab = unit_iter % ACC_BUFS, aph = (unit_iter / ACC_BUFS) & 1U;
-                if (!mbar_wait(&acc_empty[ab], aph ^ 1U, cta_abort, kAbortMmaWait)) { ok = false; break; }
+                if (!mbar_wait_spin(&acc_empty[ab], aph ^ 1U, cta_abort, kAbortMmaWait)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_base = tmem_base + ab * (NACC * Cfg::ACC_COLS);
                 for (uint32_t c = c0; c < c1; ++c, ++it) {
                     const uint32_t sa = it % SA, pa = (it / SA) & 1U;
                     const uint32_t sb = Cfg::BSTAT ? (c - c0) : it % SB, pb = Cfg::BSTAT ? 0U : (it / SB) & 1U;
-                    if (!mbar_wait(&full_a[sa], pa, cta_abort, kAbortMmaWait)) { ok = false; break; }
+                    // (the issuing thread polls its barriers: waking from a suspended wait costs more than the hand-over itself)
+                    if (!mbar_wait_spin(&full_a[sa], pa, cta_abort, kAbortMmaWait)) { ok = false; break; }
                     if (!Cfg::BSTAT || unit == blockIdx.x) {
-                        // the synthesised operand is handed over on a two-stage ring: poll (test_wait) rather than suspend (try_wait)
-                        const bool got = Cfg::kOneHot ? mbar_wait_spin(&full_b[sb], pb, cta_abort, kAbortMmaWait)
-                                                      : mbar_wait(&full_b[sb], pb, cta_abort, kAbortMmaWait);
-                        if (!got) { ok = false; break; }
+                        if (!mbar_wait_spin(&full_b[sb], pb, cta_abort, kAbortMmaWait)) { ok = false; break; }
                     }
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(a_ring + sa * Cfg::A_STAGE_BYTES);
