@@ -393,6 +393,41 @@ ReduceRowsKernel(const float* __restrict__ src, uint32_t rows, uint64_t row_stri
     }
 }
 
+// The three reductions behind HeadOut1Kernel in one launch: items [0, H2] -> grad W_out and grad b_out (contiguous in the
+// parameter layout), item H2 + 1 -> the loss, items [H2 + 2, 2 H2 + 2) -> the bias gradient of the layer below the head.
+// Same thread-to-row assignment and order of additions as ReduceRowsKernel.
+__global__ void __launch_bounds__(256)
+ReduceHeadKernel(const float* __restrict__ src, uint32_t rows, uint32_t H2, float* __restrict__ grad_out_layer, float* __restrict__ loss,
+                 float* __restrict__ bias_below) {
+    __shared__ float s_part[32][kReduceCols + 1];
+    const uint32_t items = 2U * H2 + 2U;
+    const uint32_t cl = threadIdx.x & (kReduceCols - 1U), g = threadIdx.x / kReduceCols;
+    const uint32_t c = blockIdx.x * kReduceCols + cl;
+    float sum = 0.0f;
+    if (c < items) {
+        const float* p = src + c;
+        uint32_t r = g;
+        for (; r + 96U < rows; r += 128U) {
+            const float a0 = p[(uint64_t)r * items];
+            const float a1 = p[(uint64_t)(r + 32U) * items];
+            const float a2 = p[(uint64_t)(r + 64U) * items];
+            const float a3 = p[(uint64_t)(r + 96U) * items];
+            sum += a0; sum += a1; sum += a2; sum += a3;
+        }
+        for (; r < rows; r += 32U) sum += p[(uint64_t)r * items];
+    }
+    s_part[g][cl] = sum;
+    __syncthreads();
+    if (g == 0 && c < items) {
+        float total = s_part[0][cl];
+#pragma unroll
+        for (int q = 1; q < 32; ++q) total += s_part[q][cl];
+        if (c <= H2) grad_out_layer[c] = total;
+        else if (c == H2 + 1U) *loss = total;
+        else bias_below[c - H2 - 2U] = total;
+    }
+}
+
 // The two reducers above for a stack of problems: blockIdx.y selects the problem.
 __global__ void __launch_bounds__(256)
 ReducePartialsGroupedKernel(const float* __restrict__ partial, uint32_t splits, uint64_t count, float* __restrict__ out, uint64_t out_group_stride) {
@@ -1300,11 +1335,8 @@ mgt_status_t mgt_launch_mlp_loss_grad(mgt_engine_t* e, const mgt_mlp_shape_t* sh
     float* head_bias_dst = grad + (R > 0 ? Fc2B(s, R - 1) : HiddenBias(s));
     if (OUT == 1U) {
         HeadOut1Kernel<<<kHeadBlocks, kHeadThreads, 0, st>>>(w + OutputWeight(s), w + OutputBias(s), labels, x_f32, ws.p_f32, B, H2, dzf, dz_cur, ws.p_dz, head_partial, e->bf16_now);
-        const uint32_t items = 2 * H2 + 2;
-        ReduceRowsKernel<<<(H2 + 1 + kReduceCols - 1) / kReduceCols, 256, 0, st>>>(head_partial, kHeadBlocks, items, 0, H2 + 1, grad + OutputWeight(s));
-        ReduceRowsKernel<<<1, 256, 0, st>>>(head_partial, kHeadBlocks, items, H2 + 1, 1, loss);
-        ReduceRowsKernel<<<(H2 + kReduceCols - 1) / kReduceCols, 256, 0, st>>>(head_partial, kHeadBlocks, items, H2 + 2, H2, head_bias_dst);
-        e->launches += 4;
+        ReduceHeadKernel<<<(2 * H2 + 2 + kReduceCols - 1) / kReduceCols, 256, 0, st>>>(head_partial, kHeadBlocks, H2, grad + OutputWeight(s), loss, head_bias_dst);
+        e->launches += 2;
     } else {
         float* dy = reinterpret_cast<float*>(base + ws.off_dy);
         __half* dy_h = reinterpret_cast<__half*>(base + ws.off_dyh);
