@@ -40,6 +40,7 @@ constexpr uint32_t kFlagWords = 64;
 constexpr uint64_t kPushMaxFloats = 1024;  // vectors up to 4 KB go by the push protocol (PushAllreduceKernel)
 constexpr uint64_t kDefaultWaitLimitNs = 1000ULL * 1000ULL * 1000ULL;
 constexpr uint32_t kCommThreads = 256;
+constexpr uint32_t kPollSleepNs = 200;  // pause between two polls of a peer's flag (after the first few)
 constexpr uint64_t kOneShotMaxFloats = 65536;  // 256 KB: below this a single pass over all copies is cheaper than two handshaken phases
 
 struct CommDev {
@@ -49,6 +50,7 @@ struct CommDev {
     uint32_t world;
     uint32_t rank;
     uint64_t wait_limit_ns;  // how long a kernel waits for a peer before it gives up
+    uint32_t poll_sleep_ns;  // pause between two polls of a flag
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
@@ -84,6 +86,9 @@ __device__ bool WaitPeers(const CommDev& c, uint32_t base, uint32_t seq, int cod
         uint32_t spins = 0;
         // sequence numbers only grow, so a later value also releases the wait
         while (static_cast<int32_t>(ld_acquire_sys(slot) - seq) < 0) {
+            // back off between polls: hundreds of CTAs wait here at once, and their system-scope loads would otherwise
+            // compete with the GEMM kernels this exchange runs beside
+            if (spins >= 8U && c.poll_sleep_ns != 0U) __nanosleep(c.poll_sleep_ns);
             if ((++spins & 255U) == 0U && timer_ns() - start > c.wait_limit_ns) {
                 s_fail = 1;
                 atomicCAS(reinterpret_cast<int*>(c.flags[c.rank] + kFlagStatus), 0, code);
@@ -407,6 +412,7 @@ mgt_status_t mgt_comm_create(int32_t device_id, uint32_t world_size, uint32_t gl
     c->dev.world = world_size;
     c->dev.rank = global_rank;
     c->dev.wait_limit_ns = kDefaultWaitLimitNs;
+    c->dev.poll_sleep_ns = kPollSleepNs;
     c->peer_base[global_rank] = c->local;
     if (world_size > 1) {
         c->id_file = id_file;
