@@ -1,6 +1,5 @@
 // Element-wise AdamW with optional fp16 weight mirror: native/cuda/adamw.cu:8-46.
-// HBM-bound: 28 bytes (30 with the mirror) per parameter; 16-byte accesses, grid sized in
-// multiples of the SM count.
+// HBM-bound: 28 bytes (30 with the mirror) per parameter; 16-byte accesses, one per thread and array.
 #include "../../include/mgt_b200.h"
 #include "adamw_math.cuh"
 
@@ -9,8 +8,10 @@
 
 namespace {
 
+constexpr uint32_t kAdamWThreads = 128;
+
 template <bool kMirror>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kAdamWThreads)
 AdamWKernel(mgt_adamw_config_t config, float* __restrict__ w, __half* __restrict__ w_half, const float* __restrict__ g,
             float* __restrict__ m, float* __restrict__ v) {
     const mgt::AdamWScalars sc = mgt::MakeAdamWScalars(config.step, config.learning_rate, config.beta1, config.beta2, config.eps, config.weight_decay);
@@ -85,15 +86,17 @@ static mgt_status_t LaunchAdamW(const mgt_adamw_config_t* config, float* w, uint
     if (!Aligned16(w) || !Aligned16(g) || !Aligned16(m) || !Aligned16(v) || (mirror && (reinterpret_cast<uintptr_t>(w_half) & 7U))) {
         return MGT_INVALID_CONFIG;
     }
+    // One 16-byte item per thread in CTAs of 128 threads: 0.076 ms for the 15.46 M parameters of p888 against 0.080 ms as a
+    // grid-stride loop over 16 CTAs per SM. The loop in the kernel only serves counts beyond the grid limit.
     const uint64_t n4 = config->param_count >> 2;
-    const uint64_t want = (n4 + 255ULL) / 256ULL;
-    const uint64_t cap = static_cast<uint64_t>(SmCount()) * 16ULL;
+    const uint64_t want = (n4 + kAdamWThreads - 1ULL) / kAdamWThreads;
+    const uint64_t cap = 1ULL << 30;
     const uint32_t blocks = static_cast<uint32_t>(want < 1 ? 1 : (want < cap ? want : cap));
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (mirror) {
-        AdamWKernel<true><<<blocks, 256, 0, s>>>(*config, w, reinterpret_cast<__half*>(w_half), g, m, v);
+        AdamWKernel<true><<<blocks, kAdamWThreads, 0, s>>>(*config, w, reinterpret_cast<__half*>(w_half), g, m, v);
     } else {
-        AdamWKernel<false><<<blocks, 256, 0, s>>>(*config, w, nullptr, g, m, v);
+        AdamWKernel<false><<<blocks, kAdamWThreads, 0, s>>>(*config, w, nullptr, g, m, v);
     }
     return cudaGetLastError() == cudaSuccess ? MGT_OK : MGT_CUDA_FAILURE;
 }

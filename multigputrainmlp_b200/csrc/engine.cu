@@ -496,19 +496,32 @@ HeadOut1Kernel(const float* __restrict__ w_out, const float* __restrict__ b_out,
         dacc[q] = 0.0f;
     }
     float gb = 0.0f, loss = 0.0f;
-    for (uint32_t b = blockIdx.x * (kHeadThreads / 32) + warp; b < B; b += warps_total) {
+    // The row and the label of the warp's next sample are fetched before the current one is worked on: one sample is a
+    // chain of load -> five shuffles -> stores, and a warp that waits for each load in turn leaves HBM idle.
+    float xn[kHeadMaxPerLane], label_next = 0.0f;
+    auto fetch = [&](uint32_t b) {
         const float* row = x + (uint64_t)b * p_f32;
-        float xv[kHeadMaxPerLane];
-        float dot = 0.0f;
 #pragma unroll
         for (int q = 0; q < kHeadMaxPerLane; ++q) {
             const uint32_t j = q * 32 + lane;
-            xv[q] = j < H2 ? row[j] : 0.0f;
+            xn[q] = (b < B && j < H2) ? row[j] : 0.0f;
+        }
+        label_next = b < B ? labels[b] : 0.0f;
+    };
+    fetch(blockIdx.x * (kHeadThreads / 32) + warp);
+    for (uint32_t b = blockIdx.x * (kHeadThreads / 32) + warp; b < B; b += warps_total) {
+        float xv[kHeadMaxPerLane];
+        const float label = label_next;
+        float dot = 0.0f;
+#pragma unroll
+        for (int q = 0; q < kHeadMaxPerLane; ++q) {
+            xv[q] = xn[q];
             dot += xv[q] * wreg[q];
         }
+        fetch(b + warps_total);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xFFFFFFFFU, dot, o);
-        const float diff = (bias + dot) - labels[b];
+        const float diff = (bias + dot) - label;
         const float dy = 2.0f * diff * inv_n;
         if (lane == 0) { gb += dy; loss += diff * diff * inv_n; }
 #pragma unroll
