@@ -145,3 +145,35 @@ def test_adamw_against_oracle(oracle):
     assert mgt.validate_adamw_kernel_config(mgt.AdamWKernelConfig(8, 0, 1e-3)) == 1
     assert mgt.validate_adamw_kernel_config(mgt.AdamWKernelConfig(8, 1, 0.0)) == 1
     assert mgt.validate_adamw_kernel_config(mgt.AdamWKernelConfig(8, 1, 1e-3, beta1=1.0)) == 1
+
+
+
+def test_adamw_zero_and_denormal_gradients(oracle):
+    """Exact zeros (dead units, padding columns) are the common case in a real gradient and the kernel treats them apart
+    from the correctly rounded division and square root: a parameter whose gradient and moments are zero must not move,
+    signed zeros and denormals must come out as the plain operations give them (the oracle's CpuAdamWStep restatement)."""
+    rng = np.random.default_rng(11)
+    n = 100003
+    kinds = rng.integers(0, 6, n)
+    g0 = (rng.standard_normal(n) * 1e-3).astype(np.float32)
+    special = np.array([0.0, -0.0, 1e-41, -3e-39, 1e-20], np.float32)
+    g = np.where(kinds < 5, special[np.minimum(kinds, 4)], g0).astype(np.float32)
+    w = (rng.standard_normal(n) * 0.1).astype(np.float32)
+    w0 = w.copy()
+    m = np.zeros(n, np.float32)
+    v = np.zeros(n, np.float32)
+    dw, dm, dv, dg = (torch.from_numpy(x.copy()).to(DEV) for x in (w, m, v, g))
+    dh = torch.zeros(n, dtype=torch.half, device=DEV)
+    for step in (1, 2, 3):
+        assert oracle.adamw(w, g, m, v, step=step, lr=1e-3, wd=0.0) == 0
+        assert mgt.launch_adamw_kernel_with_half_mirror(mgt.AdamWKernelConfig(n, step, 1e-3), dw, dh, dg, dm, dv) == 0
+        torch.cuda.synchronize()
+        gw, gm, gv = dw.cpu().numpy(), dm.cpu().numpy(), dv.cpu().numpy()
+        assert np.isfinite(gw).all() and np.isfinite(gm).all() and np.isfinite(gv).all()
+        assert np.abs(gw - w).max() <= 2e-6
+        assert np.abs(gm - m).max() <= 2e-8
+        assert np.abs(gv - v).max() <= 2e-10
+        zero = kinds < 2
+        assert np.array_equal(gw[zero].view(np.uint32), w0[zero].view(np.uint32))
+        assert not gm[zero].any() and not gv[zero].any()
+        assert torch.equal(dh, dw.half())
