@@ -351,9 +351,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-reference-gpu", action="store_true", help="skip the side-by-side run of the reference's GPU trainer and bin/mgt_native_train")
     ap.add_argument("--reference-gpu-steps", type=int, default=30)
-    ap.add_argument("--workload", default="step", choices=["step", "collective", "variant"],
+    ap.add_argument("--workload", default="step", choices=["step", "collective", "variant", "optimizer"],
                     help="step: the p888 training step (headline); collective: the gradient-exchange microbenchmark (bench_collective.py, needs >= 2 "
-                         "ranks); variant: a training step with the options the reference does not have (bench_variants.py, see --variant)")
+                         "ranks); variant: a training step with the options the reference does not have (bench_variants.py, see --variant); "
+                         "optimizer: the AdamW kernel alone on gradients with and without exact zeros (bench_optimizer.py)")
     ap.add_argument("--variant", default="p888_bn", choices=["p888_bn", "wide"],
                     help="p888_bn: the p888 model with batch normalisation; wide: hd1 4096, hd2 512, 32 blocks, 29 logits, bfloat16, cross-entropy, batch 131072")
     ap.add_argument("--batch-norm", action="store_true", help="--workload variant: batch normalisation also in a variant that has none by default")
@@ -370,9 +371,11 @@ def main():
             print(json.dumps(run_reference_cpu(args, args.steps, args.warmup)), file=out, flush=True)
         return
 
-    if args.workload in ("collective", "variant"):
+    if args.workload in ("collective", "variant", "optimizer"):
         if args.workload == "collective":
             import bench_collective as other
+        elif args.workload == "optimizer":
+            import bench_optimizer as other
         else:
             import bench_variants as other
         line = other.run(args)

@@ -1,9 +1,11 @@
 """Host-side pieces of the benchmarks (no GPU): the puzzle bench.py builds itself, and the exchange schedules the
 collective benchmark times."""
 import numpy as np
+import pytest
 
 import bench
 import bench_collective
+import bench_optimizer
 import bench_variants
 
 
@@ -34,3 +36,23 @@ def test_variant_table_is_consistent():
         s = v["shape"]
         assert s["state_len"] == 72 and s["hd1"] <= 4096 and s["hd2"] <= 512 and s["residual_blocks"] <= 32, name
         assert not v["cross_entropy"] or s["output_dim"] >= 29          # one logit per walk depth 1..29
+
+
+def test_optimizer_bench_gradient_kinds():
+    n = 100000
+    g = bench_optimizer.gradient("normal", n)
+    assert g.dtype == np.float32 and np.isfinite(g).all() and np.abs(g).max() <= 1e-4
+    z = bench_optimizer.gradient("half_of_columns_zero", n)
+    frac = float((z == 0).mean())
+    assert 0.4 < frac < 0.6
+    rows = n // 2560
+    zero_cols = (z[:rows * 2560].reshape(rows, 2560) == 0).all(axis=0)  # whole columns, not scattered elements
+    assert 0.4 < float(zero_cols.mean()) < 0.6
+    live = np.tile(~zero_cols, rows)
+    assert np.array_equal(z[:rows * 2560][live], g[:rows * 2560][live])
+    assert not bench_optimizer.gradient("all_zero", n).any()
+    d = bench_optimizer.gradient("zeros_and_denormals", n)
+    tiny = np.float32(1.1754944e-38)
+    assert (np.signbit(d) & (d == 0)).any() and ((np.abs(d) > 0) & (np.abs(d) < tiny)).any()
+    with pytest.raises(ValueError):
+        bench_optimizer.gradient("other", 8)
