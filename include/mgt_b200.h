@@ -56,7 +56,8 @@ typedef struct { uint32_t depth; uint32_t last_move; uint64_t rng_counter; } mgt
  * Replaces mgt_cuda::RandomWalkKernelConfig / ValidateRandomWalkKernelConfig /
  * LaunchRandomWalkKernel (native/cuda/mgt_cuda/random_walk_kernel.cuh:10-29,
  * native/cuda/random_walk_kernel.cu:66-99). Bit-exact with the reference for the same
- * (seed, epoch, step, rank, sample). */
+ * (seed, epoch, step, rank, sample). Alignment of the device arrays (checked, MGT_INVALID_CONFIG otherwise): moves, target and
+ * labels 4 bytes, meta 8 bytes, states 16 bytes - what any device allocation satisfies. */
 typedef struct {
     uint32_t sample_count;
     uint32_t k_min;

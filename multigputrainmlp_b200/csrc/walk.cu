@@ -5,6 +5,10 @@
 // One thread walks one sample. The 18 move permutations live in shared memory; each thread keeps its two 72-byte
 // state buffers in shared memory as words of four positions, words of neighbouring threads next to each other:
 // byte gathers of a warp then fall into 32 different banks and a move writes 18 words per thread instead of 72 bytes.
+// The kernel is one warp's chain of instructions, as deep as the longest walk (about 775 instructions per move, three
+// quarters of them the 72 byte gathers), so moves are applied two at a time: every CTA first composes the 18 x 18 pairs
+// of permutations in shared memory (26 KB), the walk draws its moves one by one as the generator prescribes and gathers
+// once per pair.
 // The generator's `rng % bound` on the full 64-bit state is computed exactly with 32-bit multiplies
 // (x mod b = ((hi mod b) * (2^32 mod b) + lo mod b) mod b, each step by a multiply-high with ceil(2^32 / b) and one
 // correction), which is several times cheaper than a 64-bit remainder.
@@ -14,7 +18,7 @@
 
 namespace {
 
-constexpr int kWalkThreads = 64;
+constexpr int kWalkThreads = 128;
 constexpr int kStateWords = MGT_STATE_STORAGE_LEN / 4;  // 20 words hold the 72 positions (and the 8 pad bytes)
 
 __host__ __device__ inline uint64_t Mix64(uint64_t x) {
@@ -55,20 +59,47 @@ RandomWalkKernel(mgt_random_walk_config_t config, uint64_t base_seed, uint64_t e
                  const mgt_train_state_t* __restrict__ moves, const mgt_train_state_t* __restrict__ target,
                  mgt_train_state_t* __restrict__ states, float* __restrict__ labels, mgt_walk_meta_t* __restrict__ meta) {
     __shared__ __align__(4) uint8_t s_moves[MGT_MOVE_COUNT * MGT_STATE_STORAGE_LEN];  // pad positions map to themselves
+    // s_pairs[a][b][i] = moves[a][moves[b][i]]: "move a, then move b" as one gather (new[i] = old[move[i]] twice)
+    __shared__ __align__(4) uint8_t s_pairs[MGT_MOVE_COUNT * MGT_MOVE_COUNT * MGT_STATE_STORAGE_LEN];
     __shared__ uint32_t s_state[2][kStateWords][kWalkThreads];
 
     const uint32_t tid = threadIdx.x;
-    for (uint32_t i = tid; i < MGT_MOVE_COUNT * MGT_STATE_STORAGE_LEN; i += kWalkThreads) {
-        const uint32_t mv = i / MGT_STATE_STORAGE_LEN, pos = i - mv * MGT_STATE_STORAGE_LEN;
-        s_moves[i] = (mv < config.move_count && pos < config.state_len) ? moves[mv].v[pos] : static_cast<uint8_t>(pos);
-    }
-    for (uint32_t wd = 0; wd < kStateWords; ++wd) {
-        uint32_t packed = 0;
+    // identity bytes of word wd where the position is at or beyond state_len, the given bytes elsewhere
+    auto keep_valid = [&](uint32_t given, uint32_t wd, bool identity) -> uint32_t {
+        uint32_t out = 0;
+#pragma unroll
         for (uint32_t k = 0; k < 4U; ++k) {
             const uint32_t pos = wd * 4U + k;
-            packed |= static_cast<uint32_t>(pos < config.state_len ? target->v[pos] : 0U) << (8U * k);
+            const uint32_t byte = pos < config.state_len ? (given >> (8U * k)) & 0xFFU : (identity ? pos : 0U);
+            out |= byte << (8U * k);
         }
-        s_state[0][wd][tid] = packed;
+        return out;
+    };
+    // the records are 80 bytes long and the arrays come from the device allocator: whole words can be read
+    constexpr uint32_t kMoveWords = MGT_MOVE_COUNT * kStateWords;
+    for (uint32_t i = tid; i < kMoveWords; i += kWalkThreads) {
+        const uint32_t mv = i / kStateWords, wd = i - mv * kStateWords;
+        const uint32_t given = mv < config.move_count ? reinterpret_cast<const uint32_t*>(moves[mv].v)[wd] : 0U;
+        const uint32_t identity = 0x03020100U + wd * 0x04040404U;  // moves the puzzle does not have: never drawn, kept well-formed
+        reinterpret_cast<uint32_t*>(s_moves)[i] = mv < config.move_count ? keep_valid(given, wd, true) : identity;
+    }
+    {
+        const uint32_t* tw = reinterpret_cast<const uint32_t*>(target->v);
+#pragma unroll
+        for (uint32_t wd = 0; wd < kStateWords; ++wd) s_state[0][wd][tid] = keep_valid(__ldg(tw + wd), wd, false);
+    }
+    __syncthreads();
+    // compose the pairs: one word (four positions) per item; pairs with a move the puzzle does not have are never read
+    for (uint32_t i = tid; i < MGT_MOVE_COUNT * kMoveWords; i += kWalkThreads) {
+        const uint32_t wd = i % kStateWords, ab = i / kStateWords;
+        const uint32_t a = ab / MGT_MOVE_COUNT, b = ab - a * MGT_MOVE_COUNT;
+        if (a >= config.move_count || b >= config.move_count) continue;
+        const uint32_t inner = reinterpret_cast<const uint32_t*>(s_moves + b * MGT_STATE_STORAGE_LEN)[wd];
+        const uint8_t* outer = s_moves + a * MGT_STATE_STORAGE_LEN;
+        uint32_t packed = 0;
+#pragma unroll
+        for (uint32_t k = 0; k < 4U; ++k) packed |= static_cast<uint32_t>(outer[(inner >> (8U * k)) & 0xFFU]) << (8U * k);
+        reinterpret_cast<uint32_t*>(s_pairs)[i] = packed;
     }
     __syncthreads();
 
@@ -86,12 +117,18 @@ RandomWalkKernel(mgt_random_walk_config_t config, uint64_t base_seed, uint64_t e
     const uint32_t words = (config.state_len + 3U) / 4U;
     uint32_t last_move = config.move_count;
     uint32_t cur = 0;
-    for (uint32_t d = 0; d < depth; ++d) {
+    // the generator's next move (native/cuda/random_walk_kernel.cu:40-47: never the previous move again)
+    auto draw = [&]() -> uint32_t {
         uint32_t move = NextBounded(&rng, all_moves);
         if (last_move != config.move_count && move == last_move) {
             move = Mod32(move + 1U + NextBounded(&rng, other_moves), all_moves);
         }
-        const uint32_t* def = reinterpret_cast<const uint32_t*>(s_moves + move * MGT_STATE_STORAGE_LEN);
+        last_move = move;
+        return move;
+    };
+    // new[i] = old[def[i]] for the whole state
+    auto apply = [&](const uint8_t* def_bytes) {
+        const uint32_t* def = reinterpret_cast<const uint32_t*>(def_bytes);
         const uint8_t* src = reinterpret_cast<const uint8_t*>(&s_state[cur][0][0]);
         for (uint32_t wd = 0; wd < words; ++wd) {
             const uint32_t from = def[wd];  // four source positions
@@ -104,8 +141,13 @@ RandomWalkKernel(mgt_random_walk_config_t config, uint64_t base_seed, uint64_t e
             s_state[cur ^ 1U][wd][tid] = packed;
         }
         cur ^= 1U;
-        last_move = move;
+    };
+    uint32_t d = 0;
+    for (; d + 2U <= depth; d += 2U) {
+        const uint32_t first = draw(), second = draw();
+        apply(s_pairs + (first * MGT_MOVE_COUNT + second) * MGT_STATE_STORAGE_LEN);
     }
+    if (d < depth) apply(s_moves + draw() * MGT_STATE_STORAGE_LEN);
     if (active) {
         // the 80-byte record (pad bytes zero) as five 16-byte stores
         uint4* dst = reinterpret_cast<uint4*>(states + sample);
@@ -158,6 +200,12 @@ mgt_status_t mgt_launch_random_walk(const mgt_random_walk_config_t* config, uint
                                     float* device_labels, mgt_walk_meta_t* device_meta, void* stream) {
     if (mgt_validate_random_walk_config(config) != MGT_OK || device_moves == nullptr || device_target == nullptr ||
         device_states == nullptr || device_labels == nullptr || device_meta == nullptr) {
+        return MGT_INVALID_CONFIG;
+    }
+    // the kernel reads moves and target as words and writes a state record as five 16-byte vectors
+    if ((reinterpret_cast<uintptr_t>(device_moves) & 3U) != 0 || (reinterpret_cast<uintptr_t>(device_target) & 3U) != 0 ||
+        (reinterpret_cast<uintptr_t>(device_states) & 15U) != 0 || (reinterpret_cast<uintptr_t>(device_labels) & 3U) != 0 ||
+        (reinterpret_cast<uintptr_t>(device_meta) & 7U) != 0) {
         return MGT_INVALID_CONFIG;
     }
     const uint32_t blocks = (config->sample_count + kWalkThreads - 1U) / kWalkThreads;

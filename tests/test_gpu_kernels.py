@@ -116,6 +116,17 @@ def test_walk_config_errors():
                 mgt.RandomWalkKernelConfig(8, 1, 9, 18, 72, 81)):
         assert mgt.validate_random_walk_kernel_config(bad) == 1
     assert mgt.launch_random_walk_kernel(ok, 1, 0, 0, 0, None, None, None, None, None) == 1
+    # the kernel reads the puzzle as words and writes states as 16-byte vectors: arrays that are not aligned for that are
+    # refused before anything is launched
+    raw = torch.zeros(18 * 80 + 80 + 16, dtype=torch.uint8, device=DEV)
+    states = torch.zeros(8 * 80 + 16, dtype=torch.uint8, device=DEV)
+    labels = torch.zeros(8, device=DEV)
+    meta = torch.zeros(8 * 16, dtype=torch.uint8, device=DEV)
+    assert mgt.launch_random_walk_kernel(ok, 1, 0, 0, 0, raw[:1440], raw[1440:1520], states[:640], labels, meta) == 0
+    assert mgt.launch_random_walk_kernel(ok, 1, 0, 0, 0, raw[1:1441], raw[1444:1524], states[:640], labels, meta) == 1
+    assert mgt.launch_random_walk_kernel(ok, 1, 0, 0, 0, raw[:1440], raw[1442:1522], states[:640], labels, meta) == 1
+    assert mgt.launch_random_walk_kernel(ok, 1, 0, 0, 0, raw[:1440], raw[1440:1520], states[8:648], labels, meta) == 1
+    torch.cuda.synchronize()
 
 
 def test_adamw_against_oracle(oracle):
