@@ -49,6 +49,18 @@ def test_host_side_validation_without_gpu():
     assert mgt.validate_adamw_kernel_config(mgt.AdamWKernelConfig(8, 1, 1e-3, weight_decay=-1.0)) == 1
 
 
+def test_walk_launch_refuses_misaligned_arrays_before_any_launch():
+    # host-side argument checks only: nothing reaches the device (there is none here)
+    import multigputrainmlp_b200 as mgt
+    cfg = mgt.RandomWalkKernelConfig(8, 1, 9)
+    good = dict(moves=0x10000, target=0x20000, states=0x30000, labels=0x40000, meta=0x50000)
+    for name, bad in (("moves", 0x10001), ("target", 0x20002), ("states", 0x30008), ("labels", 0x40002), ("meta", 0x50004)):
+        a = dict(good)
+        a[name] = bad
+        assert mgt.launch_random_walk_kernel(cfg, 1, 0, 0, 0, a["moves"], a["target"], a["states"], a["labels"], a["meta"], stream=0) == 1, name
+    assert mgt.launch_random_walk_kernel(mgt.RandomWalkKernelConfig(0, 1, 9), 1, 0, 0, 0, *good.values(), stream=0) == 1
+
+
 def test_product_does_not_import_the_oracle():
     pkg = os.path.join(ROOT, "multigputrainmlp_b200")
     for dirpath, _, files in os.walk(pkg):
