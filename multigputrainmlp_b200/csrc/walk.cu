@@ -64,13 +64,17 @@ RandomWalkKernel(mgt_random_walk_config_t config, uint64_t base_seed, uint64_t e
     __shared__ uint32_t s_state[2][kStateWords][kWalkThreads];
 
     const uint32_t tid = threadIdx.x;
-    // identity bytes of word wd where the position is at or beyond state_len, the given bytes elsewhere
-    auto keep_valid = [&](uint32_t given, uint32_t wd, bool identity) -> uint32_t {
+    // Word wd of a record: the given bytes for positions below state_len. For a move (`as_move`) a pad position maps to
+    // itself, and so does a source position outside the record - a malformed table must not make the gathers below index
+    // outside the shared arrays; for a state the pad bytes are zero.
+    auto keep_valid = [&](uint32_t given, uint32_t wd, bool as_move) -> uint32_t {
         uint32_t out = 0;
 #pragma unroll
         for (uint32_t k = 0; k < 4U; ++k) {
             const uint32_t pos = wd * 4U + k;
-            const uint32_t byte = pos < config.state_len ? (given >> (8U * k)) & 0xFFU : (identity ? pos : 0U);
+            uint32_t byte = (given >> (8U * k)) & 0xFFU;
+            if (as_move && byte >= static_cast<uint32_t>(MGT_STATE_STORAGE_LEN)) byte = pos;
+            if (pos >= config.state_len) byte = as_move ? pos : 0U;
             out |= byte << (8U * k);
         }
         return out;
